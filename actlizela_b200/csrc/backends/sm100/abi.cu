@@ -1,0 +1,192 @@
+// extern "C" boundary of the cuda_sm100 backend (declared in include/actlize_la_sm100.h).
+// Argument checking mirrors the reference's C launchers (csrc/backends/ppu10/launch.cu:57-65,
+// csrc/backends/ppu15/bindings.cpp:28-31): reject null/ill-shaped input with an error code,
+// guard the grid-size products, never throw, never allocate, never synchronise.
+#include "actlize_la_sm100.h"
+#include "gdn_common.cuh"
+
+#include <climits>
+
+namespace gdn_sm100 {
+namespace {
+
+#include "sm100_policy_table.inc"   // generated from sm100_policy.json by the builder
+
+bool geometry_ok(int b, int t, int hk, int hv) {
+  if (b <= 0 || t <= 0 || hk <= 0 || hv <= 0 || hv % hk) return false;
+  if (hk > INT_MAX / kDim || hv > INT_MAX / kDim) return false;
+  const long long chunks = (t + kChunk - 1) / kChunk;
+  const long long heads = (long long)b * hv;
+  if (heads > INT_MAX / 4 || heads * chunks > INT_MAX / kChunk) return false;   // flattened grids, 32-bit TMA rows
+  if ((long long)b * t * hv * kDim > (1LL << 40)) return false;
+  return true;
+}
+
+bool config_ok(int config) { return config >= 0 && config <= 3; }
+// bit 0: prepare stage uses tcgen05 (1) or CUDA cores (0); configuration ids:
+// 0 = simt/simt, 1 = umma/umma, 2 = simt prepare + umma walk, 3 = umma prepare + simt walk
+bool prepare_is_umma(int config) { return config == 1 || config == 3; }
+bool walk_is_umma(int config) { return config == 1 || config == 2; }
+
+__global__ void apply_transition_kernel(const float* __restrict__ m, const float* __restrict__ off,
+                                        const float* __restrict__ s_in, float* __restrict__ s_out) {
+  // one CTA per 128x128 block: out = M @ S + b, 256 threads, each 64 outputs
+  __shared__ float tile_m[32][129];
+  __shared__ float tile_s[32][128];
+  const long long base = (long long)blockIdx.x * kDim * kDim;
+  const int col = threadIdx.x % kDim, rhalf = threadIdx.x / kDim;
+  float acc[64];
+#pragma unroll
+  for (int r = 0; r < 64; ++r) acc[r] = off[base + (rhalf * 64 + r) * kDim + col];
+  for (int k0 = 0; k0 < kDim; k0 += 32) {
+    __syncthreads();
+    for (int e = threadIdx.x; e < 32 * kDim; e += blockDim.x) {
+      tile_m[e % 32][e / 32] = m[base + (e / 32) * kDim + k0 + e % 32];   // M[row][k0+kk]
+      tile_s[e / kDim][e % kDim] = s_in[base + (k0 + e / kDim) * kDim + e % kDim];
+    }
+    __syncthreads();
+    for (int kk = 0; kk < 32; ++kk) {
+      const float sv = tile_s[kk][col];
+#pragma unroll
+      for (int r = 0; r < 64; ++r) acc[r] = fmaf(tile_m[kk][rhalf * 64 + r], sv, acc[r]);
+    }
+  }
+#pragma unroll
+  for (int r = 0; r < 64; ++r) s_out[base + (rhalf * 64 + r) * kDim + col] = acc[r];
+}
+
+}  // namespace
+}  // namespace gdn_sm100
+
+using namespace gdn_sm100;
+
+extern "C" int actlize_la_sm100_abi_version(void) { return ACTLIZE_LA_SM100_ABI_VERSION; }
+extern "C" int actlize_la_sm100_target_arch(void) { return 100; }
+extern "C" const char* actlize_la_sm100_numerical_contract(void) {
+  return "wy-splitbf16-state-bf16-out-sm100-v1";
+}
+
+extern "C" int actlize_la_sm100_configure(void) {
+  if (int rc = configure_simt()) return rc;
+  return configure_umma();
+}
+
+extern "C" int actlize_la_sm100_select(int b, int t, int hk, int hv, int gate_fp32) {
+  (void)gate_fp32;
+  if (!geometry_ok(b, t, hk, hv)) return -1;
+  for (const PolicyRow& row : kPolicyRows)
+    if (row.b == b && row.t == t && row.hk == hk && row.hv == hv) return row.config;
+  return kPolicyDefault;
+}
+
+extern "C" long long actlize_la_sm100_workspace_bytes(int b, int t, int hk, int hv, int config) {
+  if (!geometry_ok(b, t, hk, hv) || !config_ok(config)) return -1;
+  return workspace_bytes(Geometry{b, t, hk, hv});
+}
+
+extern "C" int actlize_la_sm100_launches_per_forward(int config) { return config_ok(config) ? 2 : -1; }
+
+extern "C" int actlize_la_sm100_device_status(int* status4, int reset) {
+  if (!status4) return int(cudaErrorInvalidValue);
+  return read_device_status(status4, reset);
+}
+
+extern "C" int actlize_la_sm100_forward_prepared(
+    const void* q, const void* k, const void* v, const void* g, const void* beta,
+    const float* initial, void* output, float* final_state,
+    void* workspace, long long workspace_bytes_given,
+    int b, int t, int hk, int hv, int gate_fp32, int config, void* opaque_stream) {
+  if (!q || !k || !v || !g || !beta || !output || !workspace) return int(cudaErrorInvalidValue);
+  if (!geometry_ok(b, t, hk, hv) || !config_ok(config)) return int(cudaErrorInvalidValue);
+  const Geometry geo{b, t, hk, hv};
+  if (workspace_bytes_given < workspace_bytes(geo)) return int(cudaErrorInvalidValue);
+  if ((reinterpret_cast<uintptr_t>(workspace) & 255) || (reinterpret_cast<uintptr_t>(q) & 15) ||
+      (reinterpret_cast<uintptr_t>(k) & 15) || (reinterpret_cast<uintptr_t>(v) & 15) ||
+      (reinterpret_cast<uintptr_t>(output) & 15))
+    return int(cudaErrorInvalidValue);
+  if (output == workspace || (void*)final_state == workspace || (void*)final_state == output)
+    return int(cudaErrorInvalidValue);
+  const Inputs in{static_cast<const __nv_bfloat16*>(q), static_cast<const __nv_bfloat16*>(k),
+                  static_cast<const __nv_bfloat16*>(v), g, static_cast<const __nv_bfloat16*>(beta),
+                  initial, static_cast<__nv_bfloat16*>(output), final_state, gate_fp32 ? 1 : 0};
+  const Workspace ws = carve_workspace(workspace, geo);
+  cudaStream_t stream = static_cast<cudaStream_t>(opaque_stream);
+  if (int rc = prepare_is_umma(config) ? launch_prepare_umma(in, geo, ws, stream)
+                                       : launch_prepare_simt(in, geo, ws, stream))
+    return rc;
+  return walk_is_umma(config) ? launch_walk_umma(in, geo, ws, stream)
+                              : launch_walk_simt(in, geo, ws, stream);
+}
+
+namespace {
+struct Arena {
+  long long q, k, v, g, beta, initial, output, final_state, workspace, total;
+};
+long long align256(long long x) { return (x + 255) & ~255LL; }
+Arena arena_layout(int b, int t, int hk, int hv, int gate_fp32, int has_initial, int has_final) {
+  Arena a{};
+  long long off = 0;
+  auto take = [&](long long bytes) { long long at = off; off = align256(off + bytes); return at; };
+  const long long qk = (long long)b * t * hk * kDim * 2, vv = (long long)b * t * hv * kDim * 2;
+  const long long sc = (long long)b * t * hv, st = (long long)b * hv * kDim * kDim * 4;
+  a.q = take(qk); a.k = take(qk); a.v = take(vv);
+  a.g = take(sc * (gate_fp32 ? 4 : 2)); a.beta = take(sc * 2);
+  a.initial = has_initial ? take(st) : -1;
+  a.output = take(vv);
+  a.final_state = has_final ? take(st) : -1;
+  a.workspace = take(workspace_bytes(Geometry{b, t, hk, hv}));
+  a.total = off;
+  return a;
+}
+}  // namespace
+
+extern "C" long long actlize_la_sm100_host_arena_bytes(int b, int t, int hk, int hv, int gate_fp32,
+                                                       int has_initial, int has_final, int config) {
+  if (!geometry_ok(b, t, hk, hv) || !config_ok(config)) return -1;
+  return arena_layout(b, t, hk, hv, gate_fp32, has_initial, has_final).total;
+}
+
+extern "C" int actlize_la_sm100_forward_host(
+    const void* q, const void* k, const void* v, const void* g, const void* beta,
+    const float* initial, void* output, float* final_state,
+    void* device_arena, long long device_arena_bytes,
+    int b, int t, int hk, int hv, int gate_fp32, int config, void* opaque_stream) {
+  if (!q || !k || !v || !g || !beta || !output || !device_arena) return int(cudaErrorInvalidValue);
+  if (!geometry_ok(b, t, hk, hv) || !config_ok(config)) return int(cudaErrorInvalidValue);
+  if (reinterpret_cast<uintptr_t>(device_arena) & 255) return int(cudaErrorInvalidValue);
+  const Arena a = arena_layout(b, t, hk, hv, gate_fp32, initial != nullptr, final_state != nullptr);
+  if (device_arena_bytes < a.total) return int(cudaErrorInvalidValue);
+  char* base = static_cast<char*>(device_arena);
+  cudaStream_t stream = static_cast<cudaStream_t>(opaque_stream);
+  const long long qk = (long long)b * t * hk * kDim * 2, vv = (long long)b * t * hv * kDim * 2;
+  const long long sc = (long long)b * t * hv, st = (long long)b * hv * kDim * kDim * 4;
+  cudaError_t e;
+#define GDN_COPY(dst, src, bytes, kind) \
+  if ((e = cudaMemcpyAsync(dst, src, bytes, kind, stream)) != cudaSuccess) return int(e)
+  GDN_COPY(base + a.q, q, qk, cudaMemcpyHostToDevice);
+  GDN_COPY(base + a.k, k, qk, cudaMemcpyHostToDevice);
+  GDN_COPY(base + a.v, v, vv, cudaMemcpyHostToDevice);
+  GDN_COPY(base + a.g, g, sc * (gate_fp32 ? 4 : 2), cudaMemcpyHostToDevice);
+  GDN_COPY(base + a.beta, beta, sc * 2, cudaMemcpyHostToDevice);
+  if (initial) GDN_COPY(base + a.initial, initial, st, cudaMemcpyHostToDevice);
+  const int rc = actlize_la_sm100_forward_prepared(
+      base + a.q, base + a.k, base + a.v, base + a.g, base + a.beta,
+      initial ? reinterpret_cast<const float*>(base + a.initial) : nullptr, base + a.output,
+      final_state ? reinterpret_cast<float*>(base + a.final_state) : nullptr,
+      base + a.workspace, a.total - a.workspace, b, t, hk, hv, gate_fp32, config, opaque_stream);
+  if (rc) return rc;
+  GDN_COPY(output, base + a.output, vv, cudaMemcpyDeviceToHost);
+  if (final_state) GDN_COPY(final_state, base + a.final_state, st, cudaMemcpyDeviceToHost);
+#undef GDN_COPY
+  return int(cudaStreamSynchronize(stream));
+}
+
+extern "C" int actlize_la_sm100_apply_transition(const float* transition, const float* offset,
+                                                 const float* state_in, float* state_out,
+                                                 int blocks, void* opaque_stream) {
+  if (!transition || !offset || !state_in || !state_out || blocks <= 0 || state_in == state_out)
+    return int(cudaErrorInvalidValue);
+  apply_transition_kernel<<<blocks, 256, 0, static_cast<cudaStream_t>(opaque_stream)>>>(
+      transition, offset, state_in, state_out);
+  return int(cudaGetLastError());
+}

@@ -1,0 +1,115 @@
+// Shared definitions of the sm_100a gated-delta-rule backend: geometry, the workspace
+// layout handed from the prepare kernel to the chunk walk, and small device helpers.
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <cstdint>
+
+#if defined(__CUDA_ARCH__) && (__CUDA_ARCH__ != 1000)
+#error "the cuda_sm100 backend is built for sm_100a only (nvcc -gencode arch=compute_100a,code=sm_100a)"
+#endif
+
+namespace gdn_sm100 {
+
+constexpr int kChunk = 64;    // tokens per chunk
+constexpr int kDim = 128;     // key and value head dimension
+constexpr float kScale = 0.08838834764831845f;  // 1/sqrt(128), applied exactly once
+
+struct Geometry {
+  int batch, sequence, key_heads, value_heads;
+  __host__ __device__ int chunks() const { return (sequence + kChunk - 1) / kChunk; }
+  __host__ __device__ int group() const { return value_heads / key_heads; }
+  __host__ __device__ long long blocks() const {
+    return (long long)batch * value_heads * chunks();
+  }
+};
+
+// Workspace: structure-of-arrays planes, one entry per (batch, value head, chunk) block,
+// block index = (b * Hv + hv) * chunks + c.  Per block:
+//   w_hi, w_lo  BF16 [64][128]  W = T (beta K Gamma), split W ~= hi + lo          (token, key dim)
+//   u           FP32 [64][128]  U = T (beta V)                                    (token, value dim)
+//   qs          BF16 [64][128]  Q * exp(prefix) / sqrt(128)                       (token, key dim)
+//   p           BF16 [64][64]   tril(Q K^T * exp(prefix_i - prefix_j)) / sqrt(128)
+//   gates       FP32 [128]      [0,64): exp(prefix_last - prefix_i), 0 for padding rows;
+//                               [64]: exp(prefix_last); rest unused
+struct Workspace {
+  __nv_bfloat16* w_hi;
+  __nv_bfloat16* w_lo;
+  float* u;
+  __nv_bfloat16* qs;
+  __nv_bfloat16* p;
+  float* gates;
+};
+
+constexpr long long kBlockBytes =
+    2LL * kChunk * kDim * 2 + kChunk * kDim * 4 + kChunk * kDim * 2 + kChunk * kChunk * 2 + 128 * 4;
+
+inline __host__ long long workspace_bytes(const Geometry& g) { return g.blocks() * kBlockBytes; }
+
+// Carve the planes out of one caller-owned allocation (256-byte aligned base required).
+inline __host__ Workspace carve_workspace(void* base, const Geometry& g) {
+  char* p = static_cast<char*>(base);
+  const long long n = g.blocks();
+  Workspace w;
+  w.w_hi = reinterpret_cast<__nv_bfloat16*>(p);  p += n * kChunk * kDim * 2;
+  w.w_lo = reinterpret_cast<__nv_bfloat16*>(p);  p += n * kChunk * kDim * 2;
+  w.u = reinterpret_cast<float*>(p);             p += n * kChunk * kDim * 4;
+  w.qs = reinterpret_cast<__nv_bfloat16*>(p);    p += n * kChunk * kDim * 2;
+  w.p = reinterpret_cast<__nv_bfloat16*>(p);     p += n * kChunk * kChunk * 2;
+  w.gates = reinterpret_cast<float*>(p);
+  return w;
+}
+
+struct Inputs {
+  const __nv_bfloat16* q;
+  const __nv_bfloat16* k;
+  const __nv_bfloat16* v;
+  const void* g;
+  const __nv_bfloat16* beta;
+  const float* initial;   // nullable
+  __nv_bfloat16* output;
+  float* final_state;     // nullable
+  int gate_fp32;
+};
+
+__device__ __forceinline__ float load_gate(const void* g, long long index, int gate_fp32) {
+  return gate_fp32 ? static_cast<const float*>(g)[index]
+                   : __bfloat162float(static_cast<const __nv_bfloat16*>(g)[index]);
+}
+
+// x ~= hi + lo with both parts BF16 (16 significant bits in total).
+__device__ __forceinline__ void split_bf16(float x, __nv_bfloat16& hi, __nv_bfloat16& lo) {
+  hi = __float2bfloat16_rn(x);
+  lo = __float2bfloat16_rn(x - __bfloat162float(hi));
+}
+
+__device__ __forceinline__ uint32_t pack_bf16(float lo_elem, float hi_elem) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo_elem, hi_elem);   // .x = first (low half)
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+
+// Inclusive prefix sum of 64 gate values held one per thread by two warps (threads 0..63).
+// `carry` is a shared float used to pass the first warp's total to the second.
+__device__ __forceinline__ float chunk_prefix64(float x, int tid, float* carry) {
+  const int lane = tid & 31;
+#pragma unroll
+  for (int d = 1; d < 32; d <<= 1) {
+    float y = __shfl_up_sync(0xffffffffu, x, d);
+    if (lane >= d) x += y;
+  }
+  if (tid == 31) *carry = x;
+  __syncthreads();
+  if (tid >= 32 && tid < 64) x += *carry;
+  return x;
+}
+
+// Launchers implemented by the kernel translation units; each returns a cudaError_t value.
+int launch_prepare_simt(const Inputs&, const Geometry&, const Workspace&, cudaStream_t);
+int launch_walk_simt(const Inputs&, const Geometry&, const Workspace&, cudaStream_t);
+int configure_simt();
+int launch_prepare_umma(const Inputs&, const Geometry&, const Workspace&, cudaStream_t);
+int launch_walk_umma(const Inputs&, const Geometry&, const Workspace&, cudaStream_t);
+int configure_umma();
+int read_device_status(int* host_out4, int reset);
+
+}  // namespace gdn_sm100

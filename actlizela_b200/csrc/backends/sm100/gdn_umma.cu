@@ -1,0 +1,684 @@
+// Tensor-core implementation (configuration "umma") of the two stages of the chunked
+// gated-delta-rule forward for sm_100a: tcgen05.mma with accumulators and A operands in tensor
+// memory, B operands in 128-byte-swizzled shared memory staged by TMA, mbarrier hand-offs.
+//
+// Orientation.  Every product is arranged so that its M dimension is 128 (one TMEM lane per row):
+// the state is held TRANSPOSED, St[v][k] (value index on lanes, key index on columns), so that
+//   (W S)^T = St W^T     (Q S)^T = St Q^T     (P N)^T = N^T P^T     St += (N*rel)^T K
+// all have M = 128 value rows, and St / N^T are consumed as A operands straight from tensor memory.
+//
+// Precision.  All MMAs are kind::f16 with BF16 operands and FP32 accumulation.  Quantities on the
+// path to the final state are carried as BF16 pairs x ~= hi + lo (16 significant bits):
+// the triangular inverse T (scaled by beta, exp(prefix)), W, the state operand of W S and N*rel.
+// K, V, Q are exact BF16 inputs.  U is never rounded (FP32 from accumulator to register).
+// Output-side operands (P, scaled Q, N for P N, the state operand of Q S) are single BF16.
+//
+// Math reference: the WY chunk form of the reference project (tests/wy_cpu.py:44-88;
+// prepare/state/output kernels csrc/gdn_chunk/gdn_wy_ppu.cu:7-292), re-derived in transposed form.
+#include "gdn_common.cuh"
+#include "umma.cuh"
+
+namespace gdn_sm100 {
+using namespace ptx;
+
+// =============================================================================== host: tensor maps
+int TensorMapEncoder::init() {
+  if (encode) return 0;
+  void* fn = nullptr;
+  cudaDriverEntryPointQueryResult query;
+  cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &query);
+  if (e != cudaSuccess) return int(e);
+  if (query != cudaDriverEntryPointSuccess || !fn) return int(cudaErrorNotSupported);
+  encode = reinterpret_cast<Fn>(fn);
+  return 0;
+}
+
+int TensorMapEncoder::bf16_2d(CUtensorMap* map, const void* base, uint64_t cols, uint64_t rows,
+                              uint32_t box_rows) const {
+  const cuuint64_t dims[2] = {cols, rows};
+  const cuuint64_t strides[1] = {cols * 2};
+  const cuuint32_t box[2] = {64, box_rows};
+  const cuuint32_t elem[2] = {1, 1};
+  CUresult r = encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box,
+                      elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                      CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : int(cudaErrorInvalidValue);
+}
+
+int TensorMapEncoder::bf16_4d(CUtensorMap* map, const void* base, uint64_t d0, uint64_t d1, uint64_t d2,
+                              uint64_t d3, uint32_t box_rows_d2) const {
+  const cuuint64_t dims[4] = {d0, d1, d2, d3};
+  const cuuint64_t strides[3] = {d0 * 2, d0 * d1 * 2, d0 * d1 * d2 * 2};
+  const cuuint32_t box[4] = {64, 1, box_rows_d2, 1};
+  const cuuint32_t elem[4] = {1, 1, 1, 1};
+  CUresult r = encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(base), dims, strides, box,
+                      elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                      CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : int(cudaErrorInvalidValue);
+}
+
+TensorMapEncoder& tensor_map_encoder() {
+  static TensorMapEncoder encoder;
+  return encoder;
+}
+
+namespace {
+
+constexpr float kLog2e = 1.4426950408889634f;
+constexpr int kBox = 8192;            // one TMA box: 64 rows x 128 bytes
+constexpr uint32_t kIdescN64 = idesc_bf16(128, 64, false, false);      // A K-major (smem or TMEM), B K-major
+constexpr uint32_t kIdescN64AT = idesc_bf16(128, 64, true, false);     // A MN-major (transposed smem tile)
+constexpr uint32_t kIdescN128BT = idesc_bf16(128, 128, false, true);   // B MN-major
+
+__device__ __forceinline__ uint8_t* align1024(uint8_t* p) {
+  return reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(p) + 1023) & ~uintptr_t(1023));
+}
+
+__device__ __forceinline__ float bf16_lo(uint32_t packed) { return __uint_as_float(packed << 16); }
+__device__ __forceinline__ float bf16_hi(uint32_t packed) { return __uint_as_float(packed & 0xffff0000u); }
+
+// byte offset of element (row, col) in a [64 rows][64 BF16] tile with 128-byte swizzle
+__device__ __forceinline__ int swizzled_offset(int row, int col) {
+  return row * 128 + ((((col >> 3) ^ (row & 7)) << 4) | ((col & 7) << 1));
+}
+
+// ================================================================================= prepare kernel
+// One CTA per (batch, value head, chunk) block, 128 threads, two CTAs per SM.
+//   phase 1  TMA: Q, K chunk tiles (key head of the group) and V tile; gate prefix by two warps
+//   phase 2  D1[128x64] = [Q;K] K^T                                  (one tcgen05 product, 8 instructions)
+//   phase 3  rows 0..63  -> P = tril(QK^T * decay)/sqrt(128) -> BF16 -> workspace
+//            rows 64..127-> A = tril(beta_i KK^T * decay, -1) -> shared (transposed, FP32)
+//   phase 4  T = (I+A)^-1: one column per thread, right-looking substitution in registers
+//            (warps 0,1); scaled query rows -> workspace (warps 2,3)
+//            T diag(beta exp(p)) and T diag(beta) -> BF16 hi/lo K-major tiles in shared memory
+//   phase 5  W^T = K^T (T diag(beta exp p))^T,  U^T = V^T (T diag(beta))^T   (A = transposed K / V tiles)
+//   phase 6  accumulators -> W hi/lo BF16, U FP32, gate vector -> workspace
+struct PrepLayout {
+  static constexpr int kQ0 = 0, kK0 = kBox, kQ1 = 2 * kBox, kK1 = 3 * kBox;   // [Q;K] stacked, two K atoms
+  static constexpr int kV0 = 4 * kBox, kV1 = 5 * kBox;
+  static constexpr int kTwH = 6 * kBox, kTwL = 7 * kBox, kTuH = 8 * kBox, kTuL = 9 * kBox;
+  static constexpr int kAt = 10 * kBox;                   // float [64][68]: At[j][i] = A[i][j]
+  static constexpr int kAtStride = 68;
+  static constexpr int kVec = kAt + 64 * kAtStride * 4;   // float [4][64]: pl2, beta, beta*exp(p), exp(p)/sqrt(128)
+  static constexpr int kBars = kVec + 4 * 64 * 4;         // 2 mbarriers, tmem slot, abort flag, carry
+  static constexpr int kTotal = kBars + 64;
+};
+constexpr int kPrepThreads = 128;
+constexpr int kPrepSmem = PrepLayout::kTotal + 1024;
+constexpr int kPrepTmemCols = 256;   // D1 [0,64)  DW [64,128)  DU [128,192)
+
+__global__ void __launch_bounds__(kPrepThreads)
+prepare_umma_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
+                    const __grid_constant__ CUtensorMap tm_v, Inputs in, Geometry geo, Workspace ws) {
+  extern __shared__ uint8_t raw_smem[];
+  uint8_t* sm = align1024(raw_smem);
+  using L = PrepLayout;
+  float* sAt = reinterpret_cast<float*>(sm + L::kAt);
+  float* s_pl2 = reinterpret_cast<float*>(sm + L::kVec);
+  float* s_beta = s_pl2 + 64;
+  float* s_coefw = s_beta + 64;
+  float* s_qscale = s_coefw + 64;
+  uint64_t* bar_tma = reinterpret_cast<uint64_t*>(sm + L::kBars);
+  uint64_t* bar_mma = bar_tma + 1;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_tma + 2);
+  volatile int* abort_word = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  float* carry = reinterpret_cast<float*>(tmem_slot + 2);
+  const AbortFlag abort{abort_word};
+
+  const int tid = threadIdx.x, warp = tid >> 5;
+  const int chunks = geo.chunks();
+  const int chunk = blockIdx.x % chunks;
+  const int bh = blockIdx.x / chunks;
+  const int b = bh / geo.value_heads, hv = bh % geo.value_heads;
+  const int hk = hv / geo.group();
+  const int t0 = chunk * kChunk;
+  const int valid = min(kChunk, geo.sequence - t0);
+  const long long block = blockIdx.x;
+
+  if (tid == 0) {
+    mbar_init(bar_tma, 1);
+    mbar_init(bar_mma, 1);
+    *abort_word = 0;
+    fence_barrier_init();
+    prefetch_tensormap(&tm_q);
+    prefetch_tensormap(&tm_k);
+    prefetch_tensormap(&tm_v);
+  }
+  if (warp == 0) {
+    tmem_alloc(tmem_slot, kPrepTmemCols);
+    tmem_relinquish();
+  }
+  float gate = 0.f, beta = 0.f;
+  if (tid < valid) {
+    const long long gi = ((long long)b * geo.sequence + t0 + tid) * geo.value_heads + hv;
+    gate = load_gate(in.g, gi, in.gate_fp32);
+    beta = __bfloat162float(in.beta[gi]);
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *tmem_slot;
+
+  if (tid == 0) {
+    mbar_arrive_expect_tx(bar_tma, 6 * kBox);
+    tma_load_4d(sm + L::kQ0, &tm_q, bar_tma, 0, hk, t0, b);
+    tma_load_4d(sm + L::kQ1, &tm_q, bar_tma, 64, hk, t0, b);
+    tma_load_4d(sm + L::kK0, &tm_k, bar_tma, 0, hk, t0, b);
+    tma_load_4d(sm + L::kK1, &tm_k, bar_tma, 64, hk, t0, b);
+    tma_load_4d(sm + L::kV0, &tm_v, bar_tma, 0, hv, t0, b);
+    tma_load_4d(sm + L::kV1, &tm_v, bar_tma, 64, hv, t0, b);
+  }
+  const float prefix = chunk_prefix64(gate, tid, carry);   // contains a __syncthreads
+  if (tid < kChunk) {
+    const float e = exp2f(prefix * kLog2e);
+    s_pl2[tid] = prefix * kLog2e;
+    s_beta[tid] = beta;
+    s_coefw[tid] = beta * e;
+    s_qscale[tid] = e * kScale;
+  }
+  __syncthreads();
+
+  // ---- phase 2: D1 = [Q;K] K^T
+  bool ok = mbar_wait(bar_tma, 0, abort, 1, chunk);
+  if (tid == 0 && ok) {
+    tc_fence_after();
+    const uint32_t base = smem_u32(sm);
+#pragma unroll
+    for (int ks = 0; ks < 8; ++ks) {
+      const uint32_t a = base + (ks < 4 ? L::kQ0 : L::kQ1) + (ks & 3) * 32;
+      const uint32_t bb = base + (ks < 4 ? L::kK0 : L::kK1) + (ks & 3) * 32;
+      mma_ss(tmem + 0, smem_desc(a, 16, 1024), smem_desc(bb, 16, 1024), kIdescN64, ks > 0);
+    }
+    mma_commit(bar_mma);
+  }
+  ok = ok && mbar_wait(bar_mma, 0, abort, 2, chunk);
+  tc_fence_after();
+
+  // ---- phase 3: masks and decays on D1
+  if (ok) {
+    const uint32_t taddr = tmem + (uint32_t(warp * 32) << 16);
+    const int i = tid & 63;
+    const float pi = s_pl2[i];
+    if (tid < 64) {
+      __nv_bfloat16* prow = ws.p + (block * kChunk + i) * kChunk;
+#pragma unroll
+      for (int cg = 0; cg < 4; ++cg) {
+        uint32_t d[16];
+        tmem_ld16(taddr + cg * 16, d);
+        tmem_wait_ld();
+        uint32_t packed[8];
+#pragma unroll
+        for (int jj = 0; jj < 16; jj += 2) {
+          const int j = cg * 16 + jj;
+          const float a0 = (j <= i) ? __uint_as_float(d[jj]) * exp2f(pi - s_pl2[j]) * kScale : 0.f;
+          const float a1 = (j + 1 <= i) ? __uint_as_float(d[jj + 1]) * exp2f(pi - s_pl2[j + 1]) * kScale : 0.f;
+          packed[jj >> 1] = pack_bf16(a0, a1);
+        }
+        uint4* dst = reinterpret_cast<uint4*>(prow + cg * 16);
+        dst[0] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+        dst[1] = make_uint4(packed[4], packed[5], packed[6], packed[7]);
+      }
+    } else {
+      const float bi = s_beta[i];
+#pragma unroll
+      for (int cg = 0; cg < 4; ++cg) {
+        uint32_t d[16];
+        tmem_ld16(taddr + cg * 16, d);
+        tmem_wait_ld();
+#pragma unroll
+        for (int jj = 0; jj < 16; ++jj) {
+          const int j = cg * 16 + jj;
+          sAt[j * L::kAtStride + i] = (j < i) ? bi * __uint_as_float(d[jj]) * exp2f(pi - s_pl2[j]) : 0.f;
+        }
+      }
+    }
+  }
+  __syncthreads();
+
+  // ---- phase 4: inverse (warps 0,1) and scaled query (warps 2,3)
+  if (ok && tid < 64) {
+    const int c = tid;
+    float x[64];
+#pragma unroll
+    for (int i = 0; i < 64; ++i) x[i] = (i == c) ? 1.f : 0.f;
+#pragma unroll
+    for (int j = 0; j < 63; ++j) {
+      const float xj = x[j];
+      const float* col = sAt + j * L::kAtStride;          // A[.][j], contiguous in the row index
+#pragma unroll
+      for (int i4 = ((j + 1) & ~3); i4 < 64; i4 += 4) {
+        const float4 a = *reinterpret_cast<const float4*>(col + i4);
+        if (i4 + 0 > j) x[i4 + 0] = fmaf(-a.x, xj, x[i4 + 0]);
+        if (i4 + 1 > j) x[i4 + 1] = fmaf(-a.y, xj, x[i4 + 1]);
+        if (i4 + 2 > j) x[i4 + 2] = fmaf(-a.z, xj, x[i4 + 2]);
+        if (i4 + 3 > j) x[i4 + 3] = fmaf(-a.w, xj, x[i4 + 3]);
+      }
+    }
+    const float cw = s_coefw[c], cu = s_beta[c];
+#pragma unroll
+    for (int i = 0; i < 64; ++i) {
+      __nv_bfloat16 hi, lo;
+      const int off = swizzled_offset(i, c);
+      split_bf16(x[i] * cw, hi, lo);
+      *reinterpret_cast<__nv_bfloat16*>(sm + L::kTwH + off) = hi;
+      *reinterpret_cast<__nv_bfloat16*>(sm + L::kTwL + off) = lo;
+      split_bf16(x[i] * cu, hi, lo);
+      *reinterpret_cast<__nv_bfloat16*>(sm + L::kTuH + off) = hi;
+      *reinterpret_cast<__nv_bfloat16*>(sm + L::kTuL + off) = lo;
+    }
+    fence_proxy_async_smem();
+  } else if (ok) {
+    const int row = tid - 64;
+    const float qs = s_qscale[row];
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+      const uint8_t* src = sm + (half ? L::kQ1 : L::kQ0) + row * 128;
+      __nv_bfloat16* dst = ws.qs + (block * kChunk + row) * kDim + half * 64;
+#pragma unroll
+      for (int cc = 0; cc < 8; ++cc) {
+        const uint4 v = *reinterpret_cast<const uint4*>(src + ((cc ^ (row & 7)) << 4));
+        uint4 o;
+        o.x = pack_bf16(bf16_lo(v.x) * qs, bf16_hi(v.x) * qs);
+        o.y = pack_bf16(bf16_lo(v.y) * qs, bf16_hi(v.y) * qs);
+        o.z = pack_bf16(bf16_lo(v.z) * qs, bf16_hi(v.z) * qs);
+        o.w = pack_bf16(bf16_lo(v.w) * qs, bf16_hi(v.w) * qs);
+        *reinterpret_cast<uint4*>(dst + cc * 8) = o;
+      }
+    }
+  }
+  __syncthreads();
+
+  // ---- phase 5: W^T and U^T
+  if (tid == 0 && ok) {
+    tc_fence_after();
+    const uint32_t base = smem_u32(sm);
+#pragma unroll
+    for (int part = 0; part < 2; ++part) {
+#pragma unroll
+      for (int ks = 0; ks < 4; ++ks) {
+        const uint64_t a = smem_desc(base + L::kK0 + ks * 2048, L::kK1 - L::kK0, 1024);
+        const uint64_t bb = smem_desc(base + (part ? L::kTwL : L::kTwH) + ks * 32, 16, 1024);
+        mma_ss(tmem + 64, a, bb, kIdescN64AT, (part | ks) != 0);
+      }
+    }
+#pragma unroll
+    for (int part = 0; part < 2; ++part) {
+#pragma unroll
+      for (int ks = 0; ks < 4; ++ks) {
+        const uint64_t a = smem_desc(base + L::kV0 + ks * 2048, L::kV1 - L::kV0, 1024);
+        const uint64_t bb = smem_desc(base + (part ? L::kTuL : L::kTuH) + ks * 32, 16, 1024);
+        mma_ss(tmem + 128, a, bb, kIdescN64AT, (part | ks) != 0);
+      }
+    }
+    mma_commit(bar_mma);
+  }
+  ok = ok && mbar_wait(bar_mma, 1, abort, 3, chunk);
+  tc_fence_after();
+
+  // ---- phase 6: write W (hi/lo), U, gate vector
+  if (ok) {
+    const uint32_t taddr = tmem + (uint32_t(warp * 32) << 16);
+    __nv_bfloat16* whi = ws.w_hi + block * kChunk * kDim + tid;
+    __nv_bfloat16* wlo = ws.w_lo + block * kChunk * kDim + tid;
+    float* up = ws.u + block * kChunk * kDim + tid;
+#pragma unroll
+    for (int cg = 0; cg < 4; ++cg) {
+      uint32_t d[16];
+      tmem_ld16(taddr + 64 + cg * 16, d);
+      tmem_wait_ld();
+#pragma unroll
+      for (int jj = 0; jj < 16; ++jj) {
+        __nv_bfloat16 hi, lo;
+        split_bf16(__uint_as_float(d[jj]), hi, lo);
+        whi[(cg * 16 + jj) * kDim] = hi;
+        wlo[(cg * 16 + jj) * kDim] = lo;
+      }
+    }
+#pragma unroll
+    for (int cg = 0; cg < 4; ++cg) {
+      uint32_t d[16];
+      tmem_ld16(taddr + 128 + cg * 16, d);
+      tmem_wait_ld();
+#pragma unroll
+      for (int jj = 0; jj < 16; ++jj) up[(cg * 16 + jj) * kDim] = __uint_as_float(d[jj]);
+    }
+    const float last = s_pl2[valid - 1];
+    if (tid < kChunk) ws.gates[block * 128 + tid] = (tid < valid) ? exp2f(last - s_pl2[tid]) : 0.f;
+    if (tid == kChunk) ws.gates[block * 128 + kChunk] = exp2f(last);
+  }
+  if (!ok) {
+    for (int i = 0; i < 20; ++i) __nanosleep(100000);   // let copies in flight land before the CTA leaves
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) tmem_dealloc(tmem, kPrepTmemCols);
+}
+
+// ==================================================================================== walk kernel
+// One CTA per (batch, value head), 320 threads, one CTA per SM.  Tensor memory (512 columns):
+//   ACC_S  [  0,128)  St FP32 accumulator (pre-scaled by the chunk decay before the update MMA)
+//   OP_SH  [128,192)  St BF16 hi, packed pairs (A operand of W S and Q S)
+//   OP_SL  [192,256)  St BF16 lo
+//   ACC_WS [256,320)  (W S)^T FP32
+//   OP_NH  [320,352)  (N*rel)^T BF16 hi      OP_NL [352,384) lo      OP_N16 [384,416) N^T BF16
+//   ACC_O  [416,480)  O^T FP32
+// Roles: warps 0-3 state chain (decay/split of St, N = U - W S); warps 4-7 output epilogue;
+//        warp 8 TMA producer; warp 9 MMA issuer.
+struct WalkLayout {
+  static constexpr int kWH = 0, kWL = 2 * kBox, kQS = 4 * kBox, kK = 6 * kBox, kP = 8 * kBox;
+  static constexpr int kGates = 9 * kBox;
+  static constexpr int kStage = 9 * kBox + 1024;
+  static constexpr int kStages = 3;
+  static constexpr int kTxBytes = 9 * kBox + 512;
+  static constexpr int kBars = kStages * kStage;
+  static constexpr int kTotal = kBars + 256;
+};
+constexpr int kWalkThreads = 320;
+constexpr int kWalkSmem = WalkLayout::kTotal + 1024;
+constexpr uint32_t kAccS = 0, kOpSH = 128, kOpSL = 192, kAccWS = 256, kOpNH = 320, kOpNL = 352, kOpN16 = 384,
+                   kAccO = 416;
+
+__global__ void __launch_bounds__(kWalkThreads, 1)
+walk_umma_kernel(const __grid_constant__ CUtensorMap tm_wh, const __grid_constant__ CUtensorMap tm_wl,
+                 const __grid_constant__ CUtensorMap tm_qs, const __grid_constant__ CUtensorMap tm_k,
+                 const __grid_constant__ CUtensorMap tm_p, Inputs in, Geometry geo, Workspace ws) {
+  extern __shared__ uint8_t raw_smem[];
+  uint8_t* sm = align1024(raw_smem);
+  using L = WalkLayout;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sm + L::kBars);
+  uint64_t* full = bars;                       // [kStages]
+  uint64_t* empty = bars + L::kStages;         // [kStages]
+  uint64_t* bar_ops = bars + 2 * L::kStages;   // state operands written (128 arrivals)
+  uint64_t* bar_ws = bar_ops + 1;              // W S product complete
+  uint64_t* bar_opn = bar_ops + 2;             // N operands written (128 arrivals)
+  uint64_t* bar_s = bar_ops + 3;               // state update complete
+  uint64_t* bar_o = bar_ops + 4;               // output accumulator complete
+  uint64_t* bar_ofree = bar_ops + 5;           // output accumulator drained (128 arrivals)
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_ops + 6);
+  volatile int* abort_word = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  const AbortFlag abort{abort_word};
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int bh = blockIdx.x;
+  const int b = bh / geo.value_heads, hv = bh % geo.value_heads;
+  const int hk = hv / geo.group();
+  const int chunks = geo.chunks();
+  const long long block0 = (long long)bh * chunks;
+
+  if (tid == 0) {
+    for (int s = 0; s < L::kStages; ++s) {
+      mbar_init(full + s, 1);
+      mbar_init(empty + s, 1);
+    }
+    mbar_init(bar_ops, 128);
+    mbar_init(bar_ws, 1);
+    mbar_init(bar_opn, 128);
+    mbar_init(bar_s, 1);
+    mbar_init(bar_o, 1);
+    mbar_init(bar_ofree, 128);
+    *abort_word = 0;
+    fence_barrier_init();
+  }
+  if (warp == 9) {
+    tmem_alloc(tmem_slot, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *tmem_slot;
+
+  if (warp < 4) {
+    // ------------------------------------------------------------------ state chain
+    const int v = tid;                                     // value row = TMEM lane
+    const uint32_t taddr = tmem + (uint32_t(warp * 32) << 16);
+    {
+      const float* init = in.initial ? in.initial + (long long)bh * kDim * kDim + v : nullptr;
+#pragma unroll
+      for (int cg = 0; cg < 8; ++cg) {
+        uint32_t vals[16];
+#pragma unroll
+        for (int j = 0; j < 16; ++j) vals[j] = init ? __float_as_uint(init[(cg * 16 + j) * kDim]) : 0u;
+        tmem_st16(taddr + kAccS + cg * 16, vals);
+      }
+      tmem_wait_st();
+    }
+    bool ok = true;
+    for (int c = 0; c < chunks && ok; ++c) {
+      const int s = c % L::kStages;
+      const float* gates = reinterpret_cast<const float*>(sm + s * L::kStage + L::kGates);
+      const float* urow = ws.u + (block0 + c) * kChunk * kDim + v;
+      float u[64];
+#pragma unroll
+      for (int i = 0; i < 64; ++i) u[i] = __ldg(urow + i * kDim);
+
+      if (c > 0) ok = mbar_wait(bar_s, (c - 1) & 1, abort, 10, c);
+      ok = ok && mbar_wait(full + s, (c / L::kStages) & 1, abort, 11, c);
+      if (!ok) break;
+      tc_fence_after();
+      const float gamma = gates[kChunk];
+#pragma unroll
+      for (int cg = 0; cg < 8; ++cg) {
+        uint32_t d[16], hi[8], lo[8];
+        tmem_ld16(taddr + kAccS + cg * 16, d);
+        tmem_wait_ld();
+#pragma unroll
+        for (int j = 0; j < 16; j += 2) {
+          const float s0 = __uint_as_float(d[j]), s1 = __uint_as_float(d[j + 1]);
+          const uint32_t h = pack_bf16(s0, s1);
+          hi[j >> 1] = h;
+          lo[j >> 1] = pack_bf16(s0 - bf16_lo(h), s1 - bf16_hi(h));
+          d[j] = __float_as_uint(s0 * gamma);
+          d[j + 1] = __float_as_uint(s1 * gamma);
+        }
+        tmem_st16(taddr + kAccS + cg * 16, d);
+        tmem_st8(taddr + kOpSH + cg * 8, hi);
+        tmem_st8(taddr + kOpSL + cg * 8, lo);
+      }
+      tmem_wait_st();
+      tc_fence_before();
+      mbar_arrive(bar_ops);
+
+      ok = mbar_wait(bar_ws, c & 1, abort, 12, c);
+      if (!ok) break;
+      tc_fence_after();
+#pragma unroll
+      for (int cg = 0; cg < 4; ++cg) {
+        uint32_t d[16], nh[8], nl[8], n16[8];
+        tmem_ld16(taddr + kAccWS + cg * 16, d);
+        tmem_wait_ld();
+#pragma unroll
+        for (int j = 0; j < 16; j += 2) {
+          const int i = cg * 16 + j;
+          const float n0 = u[i] - __uint_as_float(d[j]);
+          const float n1 = u[i + 1] - __uint_as_float(d[j + 1]);
+          const float r0 = n0 * gates[i], r1 = n1 * gates[i + 1];
+          const uint32_t h = pack_bf16(r0, r1);
+          nh[j >> 1] = h;
+          nl[j >> 1] = pack_bf16(r0 - bf16_lo(h), r1 - bf16_hi(h));
+          n16[j >> 1] = pack_bf16(n0, n1);
+        }
+        tmem_st8(taddr + kOpNH + cg * 8, nh);
+        tmem_st8(taddr + kOpNL + cg * 8, nl);
+        tmem_st8(taddr + kOpN16 + cg * 8, n16);
+      }
+      tmem_wait_st();
+      tc_fence_before();
+      mbar_arrive(bar_opn);
+    }
+    if (ok) ok = mbar_wait(bar_s, (chunks - 1) & 1, abort, 13, chunks);
+    if (ok && in.final_state) {
+      tc_fence_after();
+      float* fin = in.final_state + (long long)bh * kDim * kDim + v;
+#pragma unroll
+      for (int cg = 0; cg < 8; ++cg) {
+        uint32_t d[16];
+        tmem_ld16(taddr + kAccS + cg * 16, d);
+        tmem_wait_ld();
+#pragma unroll
+        for (int j = 0; j < 16; ++j) fin[(cg * 16 + j) * kDim] = __uint_as_float(d[j]);
+      }
+    }
+  } else if (warp < 8) {
+    // ------------------------------------------------------------------ output epilogue
+    const int v = tid - 128;
+    const uint32_t taddr = tmem + (uint32_t((warp - 4) * 32) << 16) + kAccO;
+    bool ok = true;
+    for (int c = 0; c < chunks && ok; ++c) {
+      ok = mbar_wait(bar_o, c & 1, abort, 20, c);
+      if (!ok) break;
+      tc_fence_after();
+      uint32_t o[64];
+#pragma unroll
+      for (int cg = 0; cg < 4; ++cg) {
+        uint32_t d[16];
+        tmem_ld16(taddr + cg * 16, d);
+        tmem_wait_ld();
+#pragma unroll
+        for (int j = 0; j < 16; ++j) o[cg * 16 + j] = d[j];
+      }
+      tc_fence_before();
+      mbar_arrive(bar_ofree);
+      const int t0 = c * kChunk;
+      const int valid = min(kChunk, geo.sequence - t0);
+      __nv_bfloat16* out = in.output + (((long long)b * geo.sequence + t0) * geo.value_heads + hv) * kDim + v;
+      const long long row = (long long)geo.value_heads * kDim;
+#pragma unroll
+      for (int i = 0; i < 64; ++i)
+        if (i < valid) out[i * row] = __float2bfloat16_rn(__uint_as_float(o[i]));
+    }
+  } else if (warp == 8) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      prefetch_tensormap(&tm_wh);
+      prefetch_tensormap(&tm_wl);
+      prefetch_tensormap(&tm_qs);
+      prefetch_tensormap(&tm_k);
+      prefetch_tensormap(&tm_p);
+      for (int c = 0; c < chunks; ++c) {
+        const int s = c % L::kStages;
+        if (c >= L::kStages && !mbar_wait(empty + s, ((c / L::kStages) - 1) & 1, abort, 30, c)) break;
+        uint8_t* st = sm + s * L::kStage;
+        const int row = int((block0 + c) * kChunk);
+        mbar_arrive_expect_tx(full + s, L::kTxBytes);
+        tma_load_2d(st + L::kWH, &tm_wh, full + s, 0, row);
+        tma_load_2d(st + L::kWH + kBox, &tm_wh, full + s, 64, row);
+        tma_load_2d(st + L::kWL, &tm_wl, full + s, 0, row);
+        tma_load_2d(st + L::kWL + kBox, &tm_wl, full + s, 64, row);
+        tma_load_2d(st + L::kQS, &tm_qs, full + s, 0, row);
+        tma_load_2d(st + L::kQS + kBox, &tm_qs, full + s, 64, row);
+        tma_load_4d(st + L::kK, &tm_k, full + s, 0, hk, c * kChunk, b);
+        tma_load_4d(st + L::kK + kBox, &tm_k, full + s, 64, hk, c * kChunk, b);
+        tma_load_2d(st + L::kP, &tm_p, full + s, 0, row);
+        bulk_load(st + L::kGates, ws.gates + (block0 + c) * 128, 512, full + s);
+      }
+    }
+    __syncwarp();
+  } else {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      bool ok = true;
+      for (int c = 0; c < chunks && ok; ++c) {
+        const int s = c % L::kStages;
+        const uint32_t st = smem_u32(sm + s * L::kStage);
+        ok = mbar_wait(full + s, (c / L::kStages) & 1, abort, 40, c) &&
+             mbar_wait(bar_ops, c & 1, abort, 41, c);
+        if (ok && c > 0) ok = mbar_wait(bar_ofree, (c - 1) & 1, abort, 42, c);
+        if (!ok) break;
+        tc_fence_after();
+        // (W S)^T = St W^T with St ~ SH + SL and W ~ WH + WL (the lo*lo term is dropped)
+#pragma unroll
+        for (int term = 0; term < 3; ++term) {
+          const uint32_t a = tmem + (term == 1 ? kOpSL : kOpSH);
+          const uint32_t wb = st + (term == 2 ? L::kWL : L::kWH);
+#pragma unroll
+          for (int ks = 0; ks < 8; ++ks)
+            mma_ts(tmem + kAccWS, a + ks * 8, smem_desc(wb + (ks >> 2) * kBox + (ks & 3) * 32, 16, 1024),
+                   kIdescN64, (term | ks) != 0);
+        }
+        mma_commit(bar_ws);
+        // O^T = St Qs^T (old state, BF16 hi part)
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks)
+          mma_ts(tmem + kAccO, tmem + kOpSH + ks * 8,
+                 smem_desc(st + L::kQS + (ks >> 2) * kBox + (ks & 3) * 32, 16, 1024), kIdescN64, ks != 0);
+
+        ok = mbar_wait(bar_opn, c & 1, abort, 43, c);
+        if (!ok) break;
+        tc_fence_after();
+        // St += (N*rel)^T K   (accumulator already holds gamma * St)
+#pragma unroll
+        for (int term = 0; term < 2; ++term) {
+#pragma unroll
+          for (int ks = 0; ks < 4; ++ks)
+            mma_ts(tmem + kAccS, tmem + (term ? kOpNL : kOpNH) + ks * 8,
+                   smem_desc(st + L::kK + ks * 2048, kBox, 1024), kIdescN128BT, 1);
+        }
+        mma_commit(bar_s);
+        // O^T += N^T P^T
+#pragma unroll
+        for (int ks = 0; ks < 4; ++ks)
+          mma_ts(tmem + kAccO, tmem + kOpN16 + ks * 8, smem_desc(st + L::kP + ks * 32, 16, 1024), kIdescN64, 1);
+        mma_commit(bar_o);
+        mma_commit(empty + s);
+      }
+    }
+    __syncwarp();
+  }
+  if (abort.raised()) {
+    for (int i = 0; i < 20; ++i) __nanosleep(100000);   // let copies in flight land before the CTA leaves
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 9) tmem_dealloc(tmem, 512);
+}
+
+}  // namespace
+
+// ======================================================================================= launchers
+int configure_umma() {
+  if (int rc = tensor_map_encoder().init()) return rc;
+  cudaError_t e = cudaFuncSetAttribute(prepare_umma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       kPrepSmem);
+  if (e != cudaSuccess) return int(e);
+  e = cudaFuncSetAttribute(walk_umma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kWalkSmem);
+  return int(e);
+}
+
+int launch_prepare_umma(const Inputs& in, const Geometry& geo, const Workspace& ws, cudaStream_t stream) {
+  TensorMapEncoder& enc = tensor_map_encoder();
+  if (int rc = enc.init()) return rc;
+  CUtensorMap tm_q, tm_k, tm_v;
+  if (int rc = enc.bf16_4d(&tm_q, in.q, kDim, geo.key_heads, geo.sequence, geo.batch, kChunk)) return rc;
+  if (int rc = enc.bf16_4d(&tm_k, in.k, kDim, geo.key_heads, geo.sequence, geo.batch, kChunk)) return rc;
+  if (int rc = enc.bf16_4d(&tm_v, in.v, kDim, geo.value_heads, geo.sequence, geo.batch, kChunk)) return rc;
+  prepare_umma_kernel<<<(unsigned)geo.blocks(), kPrepThreads, kPrepSmem, stream>>>(tm_q, tm_k, tm_v, in, geo, ws);
+  return int(cudaGetLastError());
+}
+
+int launch_walk_umma(const Inputs& in, const Geometry& geo, const Workspace& ws, cudaStream_t stream) {
+  TensorMapEncoder& enc = tensor_map_encoder();
+  if (int rc = enc.init()) return rc;
+  const uint64_t rows = uint64_t(geo.blocks()) * kChunk;
+  CUtensorMap tm_wh, tm_wl, tm_qs, tm_k, tm_p;
+  if (int rc = enc.bf16_2d(&tm_wh, ws.w_hi, kDim, rows, kChunk)) return rc;
+  if (int rc = enc.bf16_2d(&tm_wl, ws.w_lo, kDim, rows, kChunk)) return rc;
+  if (int rc = enc.bf16_2d(&tm_qs, ws.qs, kDim, rows, kChunk)) return rc;
+  if (int rc = enc.bf16_4d(&tm_k, in.k, kDim, geo.key_heads, geo.sequence, geo.batch, kChunk)) return rc;
+  if (int rc = enc.bf16_2d(&tm_p, ws.p, kChunk, rows, kChunk)) return rc;
+  walk_umma_kernel<<<geo.batch * geo.value_heads, kWalkThreads, kWalkSmem, stream>>>(tm_wh, tm_wl, tm_qs, tm_k,
+                                                                                    tm_p, in, geo, ws);
+  return int(cudaGetLastError());
+}
+
+int read_device_status(int* host_out4, int reset) {
+  cudaError_t e = cudaMemcpyFromSymbol(host_out4, g_device_status, 4 * sizeof(int));
+  if (e != cudaSuccess) return int(e);
+  if (reset) {
+    const int zero[4] = {0, 0, 0, 0};
+    e = cudaMemcpyToSymbol(g_device_status, zero, sizeof(zero));
+  }
+  return int(e);
+}
+
+}  // namespace gdn_sm100

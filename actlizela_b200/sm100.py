@@ -1,0 +1,133 @@
+"""cuda_sm100 forward: tensor validation, buffer ownership and the C-ABI call.
+
+The Python side plays the role of the reference's binding layer
+(csrc/backends/sm90/bindings.cpp:12-59 validation and allocation of out/final;
+actlize_la/_gdn_ppu10.py:37-56 / actlize_la/serving/gdn_core.py:86-125 workspace
+ownership and the ctypes launch): it checks shapes, dtypes, contiguity, alignment and
+device, allocates output, optional final state and the workspace, and issues one
+``actlize_la_sm100_forward_prepared`` call on the caller's current stream.  Inputs are
+never modified; nothing is normalised, activated or rescaled here.
+"""
+from __future__ import annotations
+
+from ._library import load_library
+from .sm100_policy import policy, selection_for
+
+MATH_CONTRACT = "wy-splitbf16-state-bf16-out-sm100-v1"
+_DIAGNOSTIC_IDS = {"simt": 0, "umma": 1, "simt-prepare+umma-walk": 2, "umma-prepare+simt-walk": 3}
+
+
+def configuration_id(name):
+    try:
+        return _DIAGNOSTIC_IDS[name]
+    except KeyError:
+        raise ValueError(f"unknown SM100 configuration: {name!r}; choose {tuple(_DIAGNOSTIC_IDS)}") from None
+
+
+def _validate(q, k, v, g, beta, initial_state):
+    import torch
+    if q.ndim != 4 or v.ndim != 4 or k.shape != q.shape:
+        raise ValueError("q/k must be [B,T,Hk,128] and v [B,T,Hv,128]")
+    b, t, hk, d = q.shape
+    hv = v.shape[2]
+    if d != 128 or v.shape[3] != 128 or tuple(v.shape[:2]) != (b, t):
+        raise ValueError("SM100 requires K=V=128 and matching batch/sequence")
+    if min(b, t, hk, hv) < 1 or hv % hk:
+        raise ValueError("SM100 requires positive sizes and Hv % Hk == 0")
+    if tuple(g.shape) != (b, t, hv) or tuple(beta.shape) != (b, t, hv):
+        raise ValueError("g and beta must be [B,T,Hv]")
+    bf16, fp32 = torch.bfloat16, torch.float32
+    if q.dtype != bf16 or k.dtype != bf16 or v.dtype != bf16 or beta.dtype != bf16:
+        raise ValueError("q, k, v and beta must be BF16")
+    if g.dtype not in (bf16, fp32):
+        raise ValueError("g must be BF16/FP32 natural-log decay, not raw logits")
+    tensors = [q, k, v, g, beta]
+    if initial_state is not None:
+        if tuple(initial_state.shape) != (b, hv, 128, 128) or initial_state.dtype != fp32:
+            raise ValueError("initial_state must be FP32 [B,Hv,128,128] in K-by-V order")
+        tensors.append(initial_state)
+    for x in tensors:
+        if x.device.type != "cuda" or x.device != q.device:
+            raise ValueError("all tensors must be on the same CUDA device")
+        if not x.is_contiguous():
+            raise ValueError("all tensors must be contiguous")
+        if x.requires_grad:
+            raise ValueError("forward-only operator: inputs must not require grad")
+    for x in (q, k, v):
+        if x.data_ptr() % 16:
+            raise ValueError("q, k and v must be 16-byte aligned")
+    return b, t, hk, hv
+
+
+class Sm100Forward:
+    """A verified native library bound to the forward contract; identity checked once."""
+
+    def __init__(self, library):
+        self.library = library
+        self._workspaces = {}
+
+    def workspace_bytes(self, b, t, hk, hv, config):
+        n = self.library.lib.actlize_la_sm100_workspace_bytes(b, t, hk, hv, config)
+        if n < 0:
+            raise ValueError("geometry exceeds the native grid limits")
+        return n
+
+    def _workspace(self, device, nbytes):
+        import torch
+        key = str(device)
+        held = self._workspaces.get(key)
+        if held is None or held.numel() < nbytes:
+            held = torch.empty(nbytes, dtype=torch.uint8, device=device)
+            self._workspaces[key] = held
+        return held
+
+    def __call__(self, q, k, v, g, beta, initial_state=None, output_final_state=True, *,
+                 configuration=None, mode="device", sm_count=None):
+        import torch
+        b, t, hk, hv = _validate(q, k, v, g, beta, initial_state)
+        if configuration is None:
+            config = selection_for(q, v, mode=mode, sm_count=sm_count).configuration_id
+        else:
+            config = configuration_id(configuration)
+        self.library.configure(q.device)
+        out = torch.empty_like(v)
+        final = (torch.empty((b, hv, 128, 128), dtype=torch.float32, device=q.device)
+                 if output_final_state else None)
+        nbytes = self.workspace_bytes(b, t, hk, hv, config)
+        workspace = self._workspace(q.device, nbytes)
+        with torch.cuda.device(q.device):
+            stream = torch.cuda.current_stream().cuda_stream
+            self.library.check(self.library.lib.actlize_la_sm100_forward_prepared(
+                q.data_ptr(), k.data_ptr(), v.data_ptr(), g.data_ptr(), beta.data_ptr(),
+                initial_state.data_ptr() if initial_state is not None else None,
+                out.data_ptr(), final.data_ptr() if final is not None else None,
+                workspace.data_ptr(), nbytes, b, t, hk, hv,
+                int(g.dtype == torch.float32), config, stream))
+        return out, final
+
+
+_FORWARD = {}
+
+
+def load_sm100():
+    """The forward bound to the verified native library; no kernel is launched by loading."""
+    library = load_library()
+    forward = _FORWARD.get(id(library))
+    if forward is None:
+        forward = _FORWARD[id(library)] = Sm100Forward(library)
+    return forward
+
+
+def gdn_chunk_sm100(q, k, v, g, beta, initial_state=None, output_final_state=True, *,
+                    backend="cuda_sm100", configuration=None, mode="device", sm_count=None):
+    """Explicit complete cuda_sm100 algorithm (the `wy_sm100` catalog entry)."""
+    if backend != "cuda_sm100":
+        raise ValueError(f"wy_sm100 cannot execute on {backend}")
+    if configuration is not None and configuration not in _DIAGNOSTIC_IDS:
+        raise ValueError(f"unknown SM100 configuration: {configuration}")
+    return load_sm100()(q, k, v, g, beta, initial_state, output_final_state,
+                        configuration=configuration, mode=mode, sm_count=sm_count)
+
+
+def registered_configurations():
+    return tuple(policy()["configurations"])

@@ -1,0 +1,91 @@
+"""Metadata-only configuration selection for the B200 backend.
+
+Static table in the style of the reference's actlize_la/sm90_policy.py:13-81 and
+sm90_policy.json: exact (B,T,Hk,Hv) rows, a labelled default for everything else, duplicate
+or unknown rows rejected at load.  Selection reads shapes and the device profile only:
+no gate values, no tensor copies, no launches, no runtime compilation, no autotuning.
+The same table is compiled into the native library (actlize_la_sm100_select).
+"""
+from dataclasses import dataclass
+from functools import lru_cache
+import hashlib
+import json
+from pathlib import Path
+
+from .device import device_profile, get_device_profile, validate_profile_options
+
+POLICY_FILE = Path(__file__).with_suffix(".json")
+
+
+@lru_cache(maxsize=1)
+def policy():
+    data = json.loads(POLICY_FILE.read_text())
+    if data.get("schema") != 1 or data.get("default") not in data.get("configurations", ()):
+        raise ValueError("invalid SM100 policy")
+    if set(data.get("configuration_ids", ())) != set(data["configurations"]):
+        raise ValueError("SM100 policy configuration ids do not cover the configurations")
+    rows = data["rows"]
+    keys = [tuple(r["shape"]) for r in rows]
+    if len(set(keys)) != len(keys) or any(r["configuration"] not in data["configurations"] for r in rows):
+        raise ValueError("duplicate or unknown SM100 policy row")
+    return data
+
+
+def policy_digest():
+    return hashlib.sha256(POLICY_FILE.read_bytes()).hexdigest()
+
+
+@dataclass(frozen=True)
+class Selection:
+    configuration: str
+    basis: str
+    policy_id: str
+
+    @property
+    def configuration_id(self):
+        return policy()["configuration_ids"][self.configuration]
+
+
+def tensor_backend(q):
+    """Device tensor -> backend name; only capability (10,0) is admitted, nothing is guessed."""
+    device = getattr(q, "device", None)
+    if device is None or device.type != "cuda":
+        raise ValueError("automatic GDN requires a CUDA device tensor")
+    profile = device_profile(device.index)
+    if profile.capability == (10, 0):
+        return "cuda_sm100"
+    raise ValueError("automatic GDN target unsupported; this build admits sm_100 devices only")
+
+
+def select(shape, profile):
+    """shape=(B,T,Hk,Hv,K,V); metadata only."""
+    data = policy()
+    if len(shape) != 6 or any(not isinstance(x, int) or x <= 0 for x in shape):
+        raise ValueError("SM100 selector requires positive B,T,Hk,Hv,K,V")
+    if shape[3] % shape[2] or tuple(shape[4:]) != tuple(data["head_dimensions"]):
+        raise ValueError("SM100 requires integral grouped value heads and K=V=128")
+    expected = data["device"]
+    if profile.capability != tuple(expected["capability"]):
+        raise ValueError("SM100 shape policy cannot be applied to another execution target")
+    if profile.source == "configured":
+        return Selection(data["default"], "perfmodel-unmeasured-default", data["id"])
+    if profile.source != "measured":
+        raise ValueError("unknown device profile source")
+    if expected["name_contains"] not in profile.name or profile.sm_count != expected["sm_count"]:
+        return Selection(data["default"], "unmeasured-device-default", data["id"])
+    for row in data["rows"]:
+        if tuple(row["shape"]) == tuple(shape[:4]):
+            return Selection(row["configuration"], "b200-measured-shape", data["id"])
+    return Selection(data["default"], "unmeasured-shape-default", data["id"])
+
+
+def selection_for(q, v, *, mode="device", sm_count=None):
+    validate_profile_options(mode, "cuda_sm100", sm_count)
+    if q.ndim != 4 or v.ndim != 4 or tuple(q.shape[:2]) != tuple(v.shape[:2]):
+        raise ValueError("SM100 requires q/v [B,T,H,D] with matching batch and sequence")
+    if q.device.type != "cuda" or q.device != v.device:
+        raise ValueError("SM100 q/v must be on the same CUDA device")
+    shape = tuple(int(x) for x in (*q.shape[:3], v.shape[2], q.shape[3], v.shape[3]))
+    profile = (get_device_profile(mode=mode, backend="cuda_sm100", sm_count=sm_count)
+               if mode == "perfmodel" else device_profile(q.device.index))
+    return select(shape, profile)

@@ -1,0 +1,116 @@
+/* C ABI of the B200 (sm_100a) chunked gated-delta-rule forward.
+ *
+ * This is the native boundary of the `cuda_sm100` backend.  It has the shape of the
+ * reference project's plain-C launch interfaces for its WY/residual kernel families
+ *   csrc/backends/ppu15/launch.h:6-17   (forward / target_arch / configure / forward_prepared)
+ *   csrc/backends/ppu10/launch.h:5-14   (configure / core_route_v2 / forward_prepared)
+ * and follows their conventions (csrc/backends/ppu10/launch.cu:51-84):
+ *   - every function returns 0 on success and a non-zero cudaError_t value otherwise
+ *     (cudaErrorInvalidValue for rejected arguments); nothing throws across the boundary;
+ *   - `stream` is the caller's CUDA stream as an opaque pointer (for PyTorch callers,
+ *     torch.cuda.current_stream().cuda_stream); the library never synchronises it;
+ *   - all buffers are caller-owned device memory; inputs are read-only; output, final
+ *     state and workspace are disjoint; strides are implied by contiguity;
+ *   - forward_prepared allocates nothing and queries no device property, so it can be
+ *     replayed inside a captured graph once `configure` has run on that device.
+ *
+ * Tensor contract (unchanged from the reference's gdn_forward, README.md:33-46):
+ *   q, k      [B, T, Hk, 128] BF16          v, output [B, T, Hv, 128] BF16
+ *   g         [B, T, Hv] natural-log decay, FP32 if gate_fp32 else BF16
+ *   beta      [B, T, Hv] BF16               Hv % Hk == 0, chunk 64, query scale 1/sqrt(128) built in
+ *   initial   [B, Hv, 128, 128] FP32, K-by-V order, may be NULL (zero state)
+ *   final     [B, Hv, 128, 128] FP32, may be NULL (no export)
+ */
+#ifndef ACTLIZE_LA_SM100_H_
+#define ACTLIZE_LA_SM100_H_
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define ACTLIZE_LA_SM100_ABI_VERSION 1
+
+/* Kernel configurations of the static shape table (see sm100_policy.json). */
+#define ACTLIZE_LA_SM100_CONFIG_SIMT 0      /* FP32 CUDA-core kernels: diagnostic / cross-check */
+#define ACTLIZE_LA_SM100_CONFIG_UMMA 1      /* tcgen05 + TMEM + TMA kernels */
+
+/* ABI version of this library; the loader refuses a mismatch.
+ * Counterpart: ala_abi_version in csrc/serving/abi.h:67-82. */
+int actlize_la_sm100_abi_version(void);
+
+/* Architecture the device code was built for: always 100.
+ * Replaces actlize_la_ppu15_target_arch (csrc/backends/ppu15/launch.h:11). */
+int actlize_la_sm100_target_arch(void);
+
+/* Identity string of the numerical contract, e.g. "wy-tf32-state-bf16-out-sm100-v1".
+ * Counterpart of the pybind attribute math_contract checked by
+ * actlize_la/gdn_sm90_interface.py:19-20. */
+const char* actlize_la_sm100_numerical_contract(void);
+
+/* One-time per-device set-up (shared-memory opt-in attributes).  Call once per device,
+ * with that device current, outside stream capture.
+ * Replaces actlize_la_ppu15_configure / actlize_la_ppu10_configure
+ * (csrc/backends/ppu15/launch.cu:7-12, csrc/backends/ppu10/launch.h:5). */
+int actlize_la_sm100_configure(void);
+
+/* Static shape policy: kernel configuration id for a geometry; host metadata only, no
+ * device access, no gate values.  Returns a negative value for an unsupported geometry.
+ * Replaces actlize_la_ppu10_core_route_v2 (csrc/backends/ppu10/launch.h:9-10). */
+int actlize_la_sm100_select(int batch, int sequence, int key_heads, int value_heads, int gate_fp32);
+
+/* Bytes of caller-owned scratch that forward_prepared needs for this geometry and
+ * configuration (the WY factors of every chunk); negative for an unsupported geometry.
+ * Replaces the Python-side workspace table gdn_core_workspace_specs
+ * (actlize_la/serving/gdn_core.py:14-22). */
+long long actlize_la_sm100_workspace_bytes(int batch, int sequence, int key_heads, int value_heads,
+                                           int config);
+
+/* Complete forward on caller-owned buffers: prepare kernel (per-chunk gate prefix, decay-masked
+ * K.K^T, unit-lower-triangular inverse, WY factors) followed by the sequential chunk walk.
+ * Replaces actlize_la_ppu15_forward_prepared / actlize_la_ppu10_forward_prepared
+ * (csrc/backends/ppu15/launch.h:12-17, csrc/backends/ppu10/launch.h:11-14). */
+int actlize_la_sm100_forward_prepared(
+    const void* q, const void* k, const void* v, const void* g, const void* beta,
+    const float* initial, void* output, float* final_state,
+    void* workspace, long long workspace_bytes,
+    int batch, int sequence, int key_heads, int value_heads, int gate_fp32, int config,
+    void* stream);
+
+/* Host-buffer convenience used for end-to-end measurement and by callers without device
+ * memory management: copies the host tensors to the device, runs forward_prepared and copies
+ * output / final state back, all on `stream`, then synchronises that stream.
+ * `device_arena` is caller-owned device memory of at least
+ * actlize_la_sm100_host_arena_bytes(...) bytes.  Follows the pack -> forward_prepared ->
+ * scatter shape of the reference's prefill adapter (csrc/serving/prefill.cu:196-255). */
+long long actlize_la_sm100_host_arena_bytes(int batch, int sequence, int key_heads, int value_heads,
+                                            int gate_fp32, int has_initial, int has_final,
+                                            int config);
+int actlize_la_sm100_forward_host(
+    const void* q, const void* k, const void* v, const void* g, const void* beta,
+    const float* initial, void* output, float* final_state,
+    void* device_arena, long long device_arena_bytes,
+    int batch, int sequence, int key_heads, int value_heads, int gate_fp32, int config,
+    void* stream);
+
+/* Sequence-parallel helpers (no counterpart in the reference, which has no multi-device
+ * path; the affine composition rule is that of csrc/gdn_chunk/gdn_scan_stage2.cu:4-8).
+ * state_out[b,h] = transition[b,h] @ state_in[b,h] + offset[b,h] for [B*Hv] FP32 128x128
+ * blocks: carries a segment's incoming state across its affine map. */
+int actlize_la_sm100_apply_transition(const float* transition, const float* offset,
+                                      const float* state_in, float* state_out,
+                                      int blocks, void* stream);
+
+/* Diagnostic word written by a kernel whose bounded wait ran out (all waits on barriers are
+ * bounded; a kernel that gives up drains, frees its tensor memory and returns): status4[0] = 0
+ * when healthy else a failure code, [1] block index, [2] wait site, [3] chunk.  Synchronises the
+ * device; `reset` != 0 clears the word.  Counterpart of the per-request `errors[]` status of the
+ * reference's serving ABI (csrc/serving/abi.h:8-17). */
+int actlize_la_sm100_device_status(int* status4, int reset);
+
+/* Number of kernel launches one forward_prepared call issues for this configuration. */
+int actlize_la_sm100_launches_per_forward(int config);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* ACTLIZE_LA_SM100_H_ */
