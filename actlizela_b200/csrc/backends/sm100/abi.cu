@@ -22,11 +22,17 @@ bool geometry_ok(int b, int t, int hk, int hv) {
   return true;
 }
 
-bool config_ok(int config) { return config >= 0 && config <= 3; }
+// Bits 4 and 5 of `config` restrict a call to one stage (per-kernel timing and diagnosis):
+// 0x10 = prepare stage only, 0x20 = walk stage only (the workspace must already hold the
+// factors of the same inputs).
+constexpr int kStageMask = 0x30, kPrepareOnly = 0x10, kWalkOnly = 0x20;
+bool config_ok(int config) {
+  return config >= 0 && (config & ~kStageMask) <= 3 && (config & kStageMask) != kStageMask;
+}
 // bit 0: prepare stage uses tcgen05 (1) or CUDA cores (0); configuration ids:
 // 0 = simt/simt, 1 = umma/umma, 2 = simt prepare + umma walk, 3 = umma prepare + simt walk
-bool prepare_is_umma(int config) { return config == 1 || config == 3; }
-bool walk_is_umma(int config) { return config == 1 || config == 2; }
+bool prepare_is_umma(int config) { return (config & 3) == 1 || (config & 3) == 3; }
+bool walk_is_umma(int config) { return (config & 3) == 1 || (config & 3) == 2; }
 
 __global__ void apply_transition_kernel(const float* __restrict__ m, const float* __restrict__ off,
                                         const float* __restrict__ s_in, float* __restrict__ s_out) {
@@ -84,7 +90,9 @@ extern "C" long long actlize_la_sm100_workspace_bytes(int b, int t, int hk, int 
   return workspace_bytes(Geometry{b, t, hk, hv});
 }
 
-extern "C" int actlize_la_sm100_launches_per_forward(int config) { return config_ok(config) ? 2 : -1; }
+extern "C" int actlize_la_sm100_launches_per_forward(int config) {
+  return !config_ok(config) ? -1 : (config & kStageMask) ? 1 : 2;
+}
 
 extern "C" int actlize_la_sm100_device_status(int* status4, int reset) {
   if (!status4) return int(cudaErrorInvalidValue);
@@ -111,9 +119,12 @@ extern "C" int actlize_la_sm100_forward_prepared(
                   initial, static_cast<__nv_bfloat16*>(output), final_state, gate_fp32 ? 1 : 0};
   const Workspace ws = carve_workspace(workspace, geo);
   cudaStream_t stream = static_cast<cudaStream_t>(opaque_stream);
-  if (int rc = prepare_is_umma(config) ? launch_prepare_umma(in, geo, ws, stream)
-                                       : launch_prepare_simt(in, geo, ws, stream))
-    return rc;
+  if (!(config & kWalkOnly)) {
+    if (int rc = prepare_is_umma(config) ? launch_prepare_umma(in, geo, ws, stream)
+                                         : launch_prepare_simt(in, geo, ws, stream))
+      return rc;
+  }
+  if (config & kPrepareOnly) return 0;
   return walk_is_umma(config) ? launch_walk_umma(in, geo, ws, stream)
                               : launch_walk_simt(in, geo, ws, stream);
 }

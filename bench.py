@@ -1,0 +1,285 @@
+#!/usr/bin/env python3
+"""Throughput of gdn_forward on synthetic data of the named shapes.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload NAME] [--impl reference]
+
+A step is one complete forward (prepare kernel + chunk walk) over one batch of synthetic input.
+At N GPUs every rank runs the same per-GPU workload on its own (batch, head) shard, with no
+data-path collective (weak scaling); the value is the tokens all ranks processed divided by
+the slowest rank's device time.  One JSON line is printed by rank 0.
+
+Timing: CUDA events on the stream the kernels are launched on, after >= 3 warm-up steps,
+bracketed by a barrier and a device synchronise; the working set (inputs, outputs and the
+workspace of WY factors) is several times the 126 MB L2, so no L2 flush is needed between
+steps.  `e2e` measures the same forward through the host-buffer entry of the C ABI with the
+host->device and device->host copies inside the timed region.  `--impl reference` times the CPU
+restatement of the reference's own FP32 path (oracle/) on the host cores instead.
+"""
+from __future__ import annotations
+
+import argparse
+import ctypes
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+METRIC = "gdn_forward tokens/s"
+UNIT = "tokens/s"
+
+
+def measured_peaks():
+    path = ROOT / "MEASURED_PEAKS.json"
+    if path.is_file():
+        data = json.loads(path.read_text())
+        return float(data["hbm_gbs"]), float(data.get("bf16_tflops", 1590.0)), "measured"
+    return 6650.0, 1590.0, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    QUERY = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+             "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+             "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index, self.rows, self.process = index, [], None
+
+    def start(self):
+        try:
+            self.process = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.QUERY}",
+                 "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except OSError:
+            self.process = None
+
+    def _read(self):
+        for line in self.process.stdout:
+            self.rows.append([x.strip() for x in line.split(",")])
+
+    def stop(self):
+        if self.process is not None:
+            self.process.terminate()
+            try:
+                self.process.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self.process.kill()
+        sm, top, reasons = [], [], set()
+        for row in self.rows:
+            if len(row) < 7:
+                continue
+            try:
+                sm.append(float(row[0]))
+                top.append(float(row[1]))
+            except ValueError:
+                continue
+            for name, cell in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"),
+                                  row[3:7]):
+                if cell.lower().startswith("active"):
+                    reasons.add(name)
+        return dict(sm_mhz=statistics.median(sm) if sm else None, sm_max_mhz=max(top) if top else None,
+                    reasons=sorted(reasons), samples=len(sm))
+
+
+def cpu_reference_run(workload, steps, warmup, sample_note):
+    """Times the CPU restatement of the reference's FP32 path on the host cores."""
+    import torch
+    from actlizela_b200.workloads import make_inputs
+    from oracle import gdn_oracle as oracle
+    inputs = make_inputs(workload)
+    for _ in range(warmup):
+        oracle.chunk_forward_fp32(*inputs, output_final_state=True)
+    start = time.perf_counter()
+    for _ in range(steps):
+        oracle.chunk_forward_fp32(*inputs, output_final_state=True)
+    elapsed = time.perf_counter() - start
+    value = workload.tokens * steps / elapsed
+    return dict(value=value, unit=UNIT, cores=torch.get_num_threads(), kind="port",
+                sample=sample_note, host_cpus=os.cpu_count(), ms_per_step=1e3 * elapsed / steps)
+
+
+def config_dict(workload, n_gpus, configuration):
+    return dict(workload=f"{workload.name} B{workload.batch} T{workload.length} Hk{workload.key_heads} "
+                         f"Hv{workload.value_heads} D128 chunk64 gate={workload.gate_dtype}"
+                         f"{' +initial' if workload.initial is not None else ''} per GPU",
+                configuration=configuration, sharding=f"batch x{n_gpus}, no collective",
+                l2="working set (inputs, outputs, WY workspace) exceeds the 126 MB L2; no flush between steps")
+
+
+def reference_arm(args, workload):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    sample = "full per-GPU workload each step, all host threads"
+    base = cpu_reference_run(workload, args.steps, min(args.warmup, 1), sample)
+    line = dict(metric=METRIC, value=base["value"], unit=UNIT, n_gpus=args.gpus, steps=args.steps,
+                warmup=min(args.warmup, 1), ms_per_step=base["ms_per_step"], higher_is_better=True,
+                scaling="weak", vs_baseline=None, dtype="f32", data="synthetic", impl="reference",
+                config=config_dict(workload, args.gpus, "cpu-oracle"),
+                cpu_baseline=dict(value=base["value"], unit=UNIT, cores=base["cores"], kind="port",
+                                  sample=sample),
+                e2e=dict(value=base["value"], unit=UNIT, h2d_bytes_per_step=0, d2h_bytes_per_step=0))
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser(description=__doc__)
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--workload", default="headline")
+    ap.add_argument("--configuration", default=None, help="diagnostic override of the policy table")
+    ap.add_argument("--impl", default="native", choices=("native", "reference"))
+    ap.add_argument("--skip-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+
+    from actlizela_b200.workloads import WORKLOADS, algorithmic_bytes, algorithmic_flops, make_inputs
+    workload = WORKLOADS[args.workload]
+    if args.impl == "reference":
+        return reference_arm(args, workload)
+
+    import torch
+    import torch.distributed as dist
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the product path has no CPU fallback")
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}; launch with torch.distributed.run")
+    torch.cuda.set_device(local)
+    device = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+    args.warmup = max(args.warmup, 3)
+
+    from actlizela_b200 import _library
+    from actlizela_b200.sm100 import configuration_id
+    from actlizela_b200.sm100_policy import selection_for
+    library = _library.load_library()
+    library.configure(device)
+    lib = library.lib
+
+    # every rank owns one per-GPU workload (its batch shard), generated from its own seed
+    shard = workload.sliced(seed=workload.seed + 7919 * rank)
+    host = make_inputs(shard, pin=True)
+    q, k, v, g, beta, initial = [x.to(device) if x is not None else None for x in host]
+    b, t, hk, hv = shard.shape
+    gate_fp32 = int(g.dtype == torch.float32)
+    if args.configuration is None:
+        selection = selection_for(q, v)
+        config, config_name = selection.configuration_id, selection.configuration
+    else:
+        config, config_name = configuration_id(args.configuration), args.configuration
+    out = torch.empty_like(v)
+    final = torch.empty(b, hv, 128, 128, device=device)
+    ws_bytes = lib.actlize_la_sm100_workspace_bytes(b, t, hk, hv, config)
+    workspace = torch.empty(ws_bytes, dtype=torch.uint8, device=device)
+    stream = torch.cuda.current_stream()
+
+    def forward(stage=0):
+        rc = lib.actlize_la_sm100_forward_prepared(
+            q.data_ptr(), k.data_ptr(), v.data_ptr(), g.data_ptr(), beta.data_ptr(),
+            initial.data_ptr() if initial is not None else None, out.data_ptr(), final.data_ptr(),
+            workspace.data_ptr(), ws_bytes, b, t, hk, hv, gate_fp32, config | stage, stream.cuda_stream)
+        if rc:
+            raise RuntimeError(f"forward_prepared failed with CUDA error {rc}")
+
+    def sync_all():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(fn, steps):
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        sync_all()
+        start.record(stream)
+        for _ in range(steps):
+            fn()
+        stop.record(stream)
+        sync_all()
+        elapsed = torch.tensor([start.elapsed_time(stop)], device=device)
+        if world > 1:
+            dist.all_reduce(elapsed, op=dist.ReduceOp.MAX)
+        return elapsed.item() / steps          # ms per step, max over ranks
+
+    for _ in range(args.warmup):
+        forward()
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    ms_step = timed(forward, args.steps)
+    ms_walk = timed(lambda: forward(0x20), args.steps)
+    ms_prepare = timed(lambda: forward(0x10), args.steps)
+    clocks = sampler.stop() if rank == 0 else None
+    forward()
+
+    # end to end through the host-buffer entry: pinned host tensors in, output + state back
+    arena_bytes = lib.actlize_la_sm100_host_arena_bytes(b, t, hk, hv, gate_fp32, int(initial is not None), 1, config)
+    del workspace
+    arena = torch.empty(arena_bytes, dtype=torch.uint8, device=device)
+    host_out = torch.empty(v.shape, dtype=torch.bfloat16).pin_memory()
+    host_final = torch.empty(b, hv, 128, 128).pin_memory()
+
+    def forward_host():
+        rc = lib.actlize_la_sm100_forward_host(
+            host[0].data_ptr(), host[1].data_ptr(), host[2].data_ptr(), host[3].data_ptr(), host[4].data_ptr(),
+            host[5].data_ptr() if host[5] is not None else None, host_out.data_ptr(), host_final.data_ptr(),
+            arena.data_ptr(), arena_bytes, b, t, hk, hv, gate_fp32, config, stream.cuda_stream)
+        if rc:
+            raise RuntimeError(f"forward_host failed with CUDA error {rc}")
+
+    e2e_steps = max(3, min(args.steps, 10))
+    forward_host()
+    ms_e2e = timed(forward_host, e2e_steps)
+    same = bool(torch.equal(host_out, out.cpu()))
+    h2d = sum(x.numel() * x.element_size() for x in host if x is not None)
+    d2h = host_out.numel() * 2 + host_final.numel() * 4
+
+    status = (ctypes.c_int * 4)()
+    lib.actlize_la_sm100_device_status(status, 0)
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+
+    hbm_peak, tensor_peak, peak_source = measured_peaks()
+    alg_bytes, alg_flops = algorithmic_bytes(shard), algorithmic_flops(shard)
+    achieved = alg_bytes / (ms_walk * 1e-3) / 1e9
+    roofline_ms = max(alg_bytes / (hbm_peak * 1e9), alg_flops / (tensor_peak * 1e12)) * 1e3
+    line = dict(
+        metric=METRIC, value=workload.tokens * world / (ms_step * 1e-3), unit=UNIT, n_gpus=world,
+        steps=args.steps, warmup=args.warmup, ms_per_step=ms_step, higher_is_better=True, scaling="weak",
+        vs_baseline=None, dtype="bf16 operands (state path as bf16 hi+lo pairs), f32 accumulate and state",
+        data="synthetic", config=config_dict(workload, world, config_name),
+        gpu_launches=args.steps * lib.actlize_la_sm100_launches_per_forward(config),
+        kernels_ms=dict(prepare=ms_prepare, walk=ms_walk, forward=ms_step),
+        roofline=dict(bound="hbm", kernel="walk", achieved=achieved, peak=hbm_peak, unit="GB/s",
+                      frac=achieved / hbm_peak, traffic=None, peak_source=peak_source,
+                      algorithmic_bytes=alg_bytes, algorithmic_flops=alg_flops,
+                      whole_forward_frac=roofline_ms / ms_step),
+        e2e=dict(value=workload.tokens * world / (ms_e2e * 1e-3), unit=UNIT, h2d_bytes_per_step=h2d,
+                 d2h_bytes_per_step=d2h, ms_per_step=ms_e2e, output_equals_device_path=same),
+        clocks=clocks, device_status=list(status))
+    if not args.skip_cpu_baseline:
+        reps = 10
+        line["cpu_baseline"] = {k2: v2 for k2, v2 in cpu_reference_run(
+            workload, reps, 1, f"{reps} repetitions of the full {workload.name} workload").items()
+            if k2 in ("value", "unit", "cores", "kind", "sample")}
+    print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

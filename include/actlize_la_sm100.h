@@ -33,6 +33,11 @@ extern "C" {
 /* Kernel configurations of the static shape table (see sm100_policy.json). */
 #define ACTLIZE_LA_SM100_CONFIG_SIMT 0      /* FP32 CUDA-core kernels: diagnostic / cross-check */
 #define ACTLIZE_LA_SM100_CONFIG_UMMA 1      /* tcgen05 + TMEM + TMA kernels */
+/* ids 2 and 3 mix the stages (2: CUDA-core prepare + tcgen05 walk, 3: the reverse) for diagnosis.
+ * OR-ing one of the following into `config` restricts forward_prepared to a single stage
+ * (per-kernel timing; the walk-only form needs a workspace filled by an earlier call). */
+#define ACTLIZE_LA_SM100_STAGE_PREPARE_ONLY 0x10
+#define ACTLIZE_LA_SM100_STAGE_WALK_ONLY 0x20
 
 /* ABI version of this library; the loader refuses a mismatch.
  * Counterpart: ala_abi_version in csrc/serving/abi.h:67-82. */

@@ -1,0 +1,248 @@
+"""Device parity of the cuda_sm100 forward against the CPU oracle and the golden fixtures.
+
+Every call goes through the C ABI (ctypes -> actlize_la_sm100_forward_prepared).  Tolerances
+are the ones stated for this path: output max-abs <= 2e-2 and relative-Frobenius <= 1e-2,
+final state relative-Frobenius <= 1e-3, all against the FP32 CPU reference path.
+Case list and negative controls follow the reference's device admission scripts
+(tests/run_sm90_hopper_cases.py:14-29, tools/run_sm90_gdn.py:95-103,
+tests/test_ppu_wy_backend.py:53-55, tests/test_ppu_default_device.py:112-120).
+"""
+import ctypes
+
+import pytest
+import torch
+
+from actlizela_b200.workloads import WORKLOADS, make_inputs
+from oracle import gdn_oracle as oracle
+from tests.cases import ALL_CASES, build_case
+
+pytestmark = pytest.mark.gpu
+
+OUT_MAX_ABS, OUT_REL_F, STATE_REL_F = 2e-2, 1e-2, 1e-3
+CONFIGS = ["simt", "umma"]
+
+
+@pytest.fixture(scope="module")
+def forward(native_library):
+    if not torch.cuda.is_available():
+        pytest.fail("the gpu tests need a CUDA device; there is no CPU fallback to test")
+    from actlizela_b200.sm100 import Sm100Forward
+    return Sm100Forward(native_library)
+
+
+def _to_device(tensors):
+    return [x.cuda() if x is not None else None for x in tensors]
+
+
+def _check(out, state, want_out, want_state, label):
+    out, want_out = out.float().cpu(), want_out.float().cpu()
+    assert torch.isfinite(out).all(), label
+    assert oracle.max_abs(out, want_out) <= OUT_MAX_ABS, (label, "out max-abs", oracle.max_abs(out, want_out))
+    if want_out.norm() > 0:
+        assert oracle.rel_frobenius(out, want_out) <= OUT_REL_F, (label, "out relF", oracle.rel_frobenius(out, want_out))
+    if want_state is not None:
+        rel = oracle.rel_frobenius(state.cpu(), want_state)
+        assert rel <= STATE_REL_F, (label, "state relF", rel)
+
+
+def _status(native_library):
+    buf = (ctypes.c_int * 4)()
+    assert native_library.lib.actlize_la_sm100_device_status(buf, 1) == 0
+    return list(buf)
+
+
+@pytest.mark.parametrize("configuration", CONFIGS)
+@pytest.mark.parametrize("case", ALL_CASES, ids=lambda c: c["name"])
+def test_golden_cases(case, configuration, forward, golden, native_library):
+    inputs = build_case(case)
+    want_out, want_state, _ = golden[case["name"]]
+    q, k, v, g, beta, init = _to_device(inputs)
+    out, state = forward(q, k, v, g, beta, init, True, configuration=configuration)
+    torch.cuda.synchronize()
+    assert _status(native_library)[0] == 0
+    _check(out, state, want_out, want_state, (case["name"], configuration))
+    # zero-output negative control: the criterion itself must be able to fail
+    assert oracle.rel_frobenius(torch.zeros_like(want_state), want_state) > STATE_REL_F
+
+
+@pytest.mark.parametrize("configuration", ["simt-prepare+umma-walk", "umma-prepare+simt-walk"])
+def test_stages_are_interchangeable(configuration, forward, golden):
+    case = next(c for c in ALL_CASES if c["name"] == "cfg3-scaled")
+    want_out, want_state, _ = golden[case["name"]]
+    q, k, v, g, beta, init = _to_device(build_case(case))
+    out, state = forward(q, k, v, g, beta, init, True, configuration=configuration)
+    _check(out, state, want_out, want_state, configuration)
+
+
+def _workspace_planes(native_library, inputs, config):
+    """Run one forward through the raw C ABI with a private workspace; return its planes."""
+    q, k, v, g, beta, init = inputs
+    b, t, hk, _ = q.shape
+    hv = v.shape[2]
+    lib = native_library.lib
+    native_library.configure(q.device)
+    nbytes = lib.actlize_la_sm100_workspace_bytes(b, t, hk, hv, config)
+    ws = torch.zeros(nbytes, dtype=torch.uint8, device="cuda")
+    out = torch.empty_like(v)
+    final = torch.empty(b, hv, 128, 128, device="cuda")
+    rc = lib.actlize_la_sm100_forward_prepared(
+        q.data_ptr(), k.data_ptr(), v.data_ptr(), g.data_ptr(), beta.data_ptr(),
+        init.data_ptr() if init is not None else None, out.data_ptr(), final.data_ptr(),
+        ws.data_ptr(), nbytes, b, t, hk, hv, int(g.dtype == torch.float32), config,
+        torch.cuda.current_stream().cuda_stream)
+    assert rc == 0
+    torch.cuda.synchronize()
+    n = b * hv * ((t + 63) // 64)
+    sizes = [("w_hi", n * 64 * 128 * 2, torch.bfloat16), ("w_lo", n * 64 * 128 * 2, torch.bfloat16),
+             ("u", n * 64 * 128 * 4, torch.float32), ("qs", n * 64 * 128 * 2, torch.bfloat16),
+             ("p", n * 64 * 64 * 2, torch.bfloat16), ("gates", n * 128 * 4, torch.float32)]
+    planes, off = {}, 0
+    for name, size, dtype in sizes:
+        planes[name] = ws[off:off + size].view(dtype).clone()
+        off += size
+    planes["w"] = planes["w_hi"].float() + planes["w_lo"].float()
+    planes["gates"] = planes["gates"].view(n, 128)[:, :65].contiguous()
+    return planes, out, final
+
+
+@pytest.mark.parametrize("name", ["cfg3-scaled", "cfg0-scaled", "tail65-initial"])
+def test_prepare_intermediates_match_the_oracle(name, native_library, forward):
+    case = next(c for c in ALL_CASES if c["name"] == name)
+    cpu = build_case(case)
+    _, _, im = oracle.wy_chunk_forward(*cpu[:5], cpu[5], return_intermediates=True)
+    t = cpu[0].shape[1]
+    for config in (0, 1):
+        planes, _, _ = _workspace_planes(native_library, _to_device(cpu), config)
+        w = planes["w"].view(*im["W"].shape).cpu()
+        u = planes["u"].view(*im["U"].shape).cpu()
+        p = planes["p"].float().view(*im["P"].shape).cpu()
+        assert oracle.rel_frobenius(w, im["W"]) < 2e-5, (name, config, "W")
+        assert oracle.rel_frobenius(u, im["U"]) < 2e-5, (name, config, "U")
+        assert oracle.rel_frobenius(p, im["P"]) < 4e-3, (name, config, "P")      # stored as BF16
+        prefix = im["prefix"]
+        valid_last = torch.full(prefix.shape[:3], 63, dtype=torch.long)
+        valid_last[..., -1] = (t - 1) % 64
+        last = prefix.gather(-1, valid_last[..., None])
+        gam = planes["gates"][:, 64].view(*prefix.shape[:3]).cpu()
+        assert oracle.rel_frobenius(gam, last[..., 0].exp()) < 1e-5, (name, config, "gamma")
+
+
+def test_output_only_equals_full_and_replay_is_bit_stable(forward):
+    case = next(c for c in ALL_CASES if c["name"] == "tail65-initial")
+    cpu = build_case(case)
+    dev = _to_device(cpu)
+    before = [x.clone() if x is not None else None for x in dev]
+    out, state = forward(*dev, True)
+    out_only, none = forward(*dev, False)
+    assert none is None and torch.equal(out, out_only)
+    for _ in range(8):
+        again, state_again = forward(*dev, True)
+        assert torch.equal(again, out) and torch.equal(state_again, state)
+    for a, b in zip(dev, before):
+        assert a is None or torch.equal(a, b), "inputs were modified"
+
+
+def test_grouped_heads_equal_expanded_heads_bitwise(forward):
+    case = next(c for c in ALL_CASES if c["name"] == "tail31-gva")
+    q, k, v, g, beta, init = _to_device(build_case(case))
+    ratio = v.shape[2] // q.shape[2]
+    out, state = forward(q, k, v, g, beta, init, True)
+    out_e, state_e = forward(q.repeat_interleave(ratio, 2).contiguous(),
+                             k.repeat_interleave(ratio, 2).contiguous(), v, g, beta, init, True)
+    assert torch.equal(out, out_e) and torch.equal(state, state_e)
+
+
+def test_transposed_initial_state_is_a_different_answer(forward, golden):
+    case = next(c for c in ALL_CASES if c["name"] == "cfg3-scaled")
+    _, want_state, _ = golden[case["name"]]
+    q, k, v, g, beta, init = _to_device(build_case(case))
+    _, state = forward(q, k, v, g, beta, init.transpose(-1, -2).contiguous(), True)
+    assert oracle.rel_frobenius(state.cpu(), want_state) > 10 * STATE_REL_F
+
+
+def _oracle_by_head_group(cpu, heads_per_call=8):
+    """FP32 reference over value-head slices (bounds host memory for the big shapes)."""
+    q, k, v, g, beta, init = cpu
+    ratio = v.shape[2] // q.shape[2]
+    outs, states = [], []
+    for v0 in range(0, v.shape[2], heads_per_call):
+        v1 = min(v.shape[2], v0 + heads_per_call)
+        h0, h1 = v0 // ratio, (v1 + ratio - 1) // ratio
+        o, s = oracle.chunk_forward_fp32(q[:, :, h0:h1], k[:, :, h0:h1], v[:, :, v0:v1], g[:, :, v0:v1],
+                                         beta[:, :, v0:v1], init[:, v0:v1] if init is not None else None, True)
+        outs.append(o)
+        states.append(s)
+    return torch.cat(outs, 2), torch.cat(states, 1)
+
+
+@pytest.mark.parametrize("name", ["cfg0", "headline", "cfg1", "cfg3"])
+def test_named_shapes_at_full_size(name, forward, native_library):
+    w = WORKLOADS[name]
+    cpu = make_inputs(w)
+    want_out, want_state = _oracle_by_head_group(cpu)
+    out, state = forward(*_to_device(cpu), True)
+    torch.cuda.synchronize()
+    assert _status(native_library)[0] == 0
+    _check(out, state, want_out, want_state, name)
+
+
+def test_cfg2_batch_sharded_shape(forward):
+    """B8 T4096 BF16 gate: device result for every batch, CPU reference for two of them."""
+    w = WORKLOADS["cfg2"]
+    cpu = make_inputs(w)
+    out, state = forward(*_to_device(cpu), True)
+    for b in (0, 7):
+        part = [x[b:b + 1] for x in cpu[:5]] + [cpu[5][b:b + 1]]
+        want_out, want_state = _oracle_by_head_group(part)
+        _check(out[b:b + 1], state[b:b + 1], want_out, want_state, ("cfg2", b))
+    # size-independent property: a batch element computed alone gives the same bits
+    solo_out, solo_state = forward(*[x[3:4].contiguous() for x in _to_device(cpu)], True)
+    assert torch.equal(solo_out, out[3:4]) and torch.equal(solo_state, state[3:4])
+
+
+def test_long_sequence_segment_chaining(forward):
+    """T=131072: the final state of a prefix fed as initial state of the rest equals the unsplit
+    run (chunk-aligned cut), and a head slice agrees with the CPU reference."""
+    w = WORKLOADS["cfg4"].sliced(key_heads=2, value_heads=4)
+    cpu = make_inputs(w)
+    dev = _to_device(cpu)
+    out, state = forward(*dev, True)
+    cut = 64 * 1000
+    head = [x[:, :cut].contiguous() for x in dev[:5]]
+    tail = [x[:, cut:].contiguous() for x in dev[:5]]
+    o1, s1 = forward(*head, dev[5], True)
+    o2, s2 = forward(*tail, s1, True)
+    assert torch.equal(torch.cat([o1, o2], 1), out) and torch.equal(s2, state)
+    want_out, want_state = oracle.chunk_forward_fp32(cpu[0][:, :, :1], cpu[1][:, :, :1], cpu[2][:, :, :2],
+                                                     cpu[3][:, :, :2], cpu[4][:, :, :2], cpu[5][:, :2], True)
+    _check(out[:, :, :2], state[:, :2], want_out, want_state, "cfg4-slice")
+
+
+def test_host_buffer_entry_matches_device_entry(native_library, forward):
+    case = next(c for c in ALL_CASES if c["name"] == "cfg1-scaled")
+    cpu = build_case(case)
+    q, k, v, g, beta, init = [x.contiguous() for x in cpu]
+    b, t, hk, _ = q.shape
+    hv = v.shape[2]
+    lib = native_library.lib
+    native_library.configure(torch.device("cuda:0"))
+    nbytes = lib.actlize_la_sm100_host_arena_bytes(b, t, hk, hv, 1, 1, 1, 1)
+    arena = torch.empty(nbytes, dtype=torch.uint8, device="cuda")
+    out = torch.empty_like(v)
+    final = torch.empty(b, hv, 128, 128)
+    rc = lib.actlize_la_sm100_forward_host(
+        q.data_ptr(), k.data_ptr(), v.data_ptr(), g.data_ptr(), beta.data_ptr(), init.data_ptr(),
+        out.data_ptr(), final.data_ptr(), arena.data_ptr(), nbytes, b, t, hk, hv, 1, 1,
+        torch.cuda.current_stream().cuda_stream)
+    assert rc == 0
+    dev_out, dev_state = forward(*_to_device(cpu), True, configuration="umma")
+    assert torch.equal(out, dev_out.cpu()) and torch.equal(final, dev_state.cpu())
+
+
+def test_apply_transition_kernel(native_library):
+    from actlizela_b200.sequence_parallel import native_apply_transition
+    gen = torch.Generator().manual_seed(5)
+    m, b, s = (torch.randn(2, 3, 128, 128, generator=gen).cuda() for _ in range(3))
+    got = native_apply_transition(m, b, s)
+    want = (m.double() @ s.double() + b.double()).float()
+    assert oracle.rel_frobenius(got.cpu(), want.cpu()) < 1e-6
