@@ -57,7 +57,7 @@ class ClockSampler:
         try:
             self.process = subprocess.Popen(
                 ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.QUERY}",
-                 "--format=csv,noheader,nounits", "-lms", "100"],
+                 "--format=csv,noheader,nounits", "-lms", "50"],
                 stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             threading.Thread(target=self._read, daemon=True).start()
         except OSError:
@@ -135,7 +135,7 @@ def reference_arm(args, workload):
 def main():
     ap = argparse.ArgumentParser(description=__doc__)
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--workload", default="headline")
     ap.add_argument("--configuration", default=None, help="diagnostic override of the policy table")
@@ -213,11 +213,11 @@ def main():
             dist.all_reduce(elapsed, op=dist.ReduceOp.MAX)
         return elapsed.item() / steps          # ms per step, max over ranks
 
-    for _ in range(args.warmup):
-        forward()
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()
+    for _ in range(args.warmup):
+        forward()
     ms_step = timed(forward, args.steps)
     ms_walk = timed(lambda: forward(0x20), args.steps)
     ms_prepare = timed(lambda: forward(0x10), args.steps)

@@ -160,14 +160,14 @@ def test_transposed_initial_state_is_a_different_answer(forward, golden):
     assert oracle.rel_frobenius(state.cpu(), want_state) > 10 * STATE_REL_F
 
 
-def _oracle_by_head_group(cpu, heads_per_call=8):
-    """FP32 reference over value-head slices (bounds host memory for the big shapes)."""
+def _oracle_by_head_group(cpu, key_heads_per_call=4):
+    """FP32 reference over slices of whole key-head groups (bounds host memory for big shapes)."""
     q, k, v, g, beta, init = cpu
     ratio = v.shape[2] // q.shape[2]
     outs, states = [], []
-    for v0 in range(0, v.shape[2], heads_per_call):
-        v1 = min(v.shape[2], v0 + heads_per_call)
-        h0, h1 = v0 // ratio, (v1 + ratio - 1) // ratio
+    for h0 in range(0, q.shape[2], key_heads_per_call):
+        h1 = min(q.shape[2], h0 + key_heads_per_call)
+        v0, v1 = h0 * ratio, h1 * ratio
         o, s = oracle.chunk_forward_fp32(q[:, :, h0:h1], k[:, :, h0:h1], v[:, :, v0:v1], g[:, :, v0:v1],
                                          beta[:, :, v0:v1], init[:, v0:v1] if init is not None else None, True)
         outs.append(o)
