@@ -112,6 +112,22 @@ int actlize_la_sm100_apply_transition(const float* transition, const float* offs
  * reference's serving ABI (csrc/serving/abi.h:8-17). */
 int actlize_la_sm100_device_status(int* status4, int reset);
 
+/* The same forward for callers that cannot allocate device memory (no counterpart in the
+ * reference): the workspace is a fixed array inside the library instead of a caller buffer.
+ * Meant for plugins inside a host framework that owns all allocations, or loops where a
+ * cudaMalloc is not acceptable.  B*Hv*ceil(T/64) must not exceed
+ * ACTLIZE_LA_SM100_STATIC_SCRATCH_MAX_BLOCKS, otherwise the call returns
+ * ACTLIZE_LA_SM100_ERROR_SCRATCH_TOO_SMALL and launches nothing.  The first call on a device does a
+ * one-time set-up there: make it before any stream capture.  All calls share the array, so calls
+ * that overlap on the GPU race; issue them one after the other.  Allocates nothing. */
+#define ACTLIZE_LA_SM100_STATIC_SCRATCH_MAX_BLOCKS 64
+#define ACTLIZE_LA_SM100_ERROR_SCRATCH_TOO_SMALL (-2)
+int actlize_la_sm100_forward_static_scratch(
+    const void* q, const void* k, const void* v, const void* g, const void* beta,
+    const float* initial, void* output, float* final_state,
+    int batch, int sequence, int key_heads, int value_heads, int gate_fp32, int config,
+    void* stream);
+
 /* Number of kernel launches one forward_prepared call issues for this configuration. */
 int actlize_la_sm100_launches_per_forward(int config);
 
