@@ -50,7 +50,7 @@ def render_policy_table(policy_path, out_path):
         % (data["id"], ids[data["default"]], rows))
 
 
-def build(out=None, compiler=None, verbose_ptxas=False, quiet=False):
+def build(out=None, compiler=None, verbose_ptxas=False, quiet=False, defines=()):
     out = Path(out) if out else PACKAGE / "_native"
     out.mkdir(parents=True, exist_ok=True)
     generated = out / "generated"
@@ -65,12 +65,12 @@ def build(out=None, compiler=None, verbose_ptxas=False, quiet=False):
         target="cuda_sm100", arch="sm_100a", abi_version=1, complete=False,
         compiler=str(compiler),
         compiler_version=subprocess.check_output([str(compiler), "--version"], text=True).strip().splitlines()[-1],
-        flags=FLAGS, policy_sha256=sha(policy_path),
+        flags=[*FLAGS, *(f"-D{d}" for d in defines)], policy_sha256=sha(policy_path),
         source_sha256={str(p.relative_to(ROOT)): sha(p) for p in [*sources, INCLUDE / "actlize_la_sm100.h"]})
     receipt = out / "build.json"
     receipt.write_text(json.dumps(identity, indent=2) + "\n")
     library = out / "libactlize_la_sm100.so"
-    command = [str(compiler), *FLAGS, "-shared", f"-I{INCLUDE}", f"-I{SOURCE}", f"-I{generated}",
+    command = [str(compiler), *identity["flags"], "-shared", f"-I{INCLUDE}", f"-I{SOURCE}", f"-I{generated}",
                *(["-Xptxas", "-v"] if verbose_ptxas else []),
                *(str(SOURCE / unit) for unit in UNITS), "-o", str(library)]
     if not quiet:
@@ -98,8 +98,9 @@ def main():
     ap.add_argument("--out", type=Path)
     ap.add_argument("--compiler", type=Path)
     ap.add_argument("--verbose-ptxas", action="store_true")
+    ap.add_argument("--define", action="append", default=[], help="extra -D macro (diagnostic builds)")
     args = ap.parse_args()
-    build(args.out, args.compiler, args.verbose_ptxas)
+    build(args.out, args.compiler, args.verbose_ptxas, defines=args.define)
     if args.verbose_ptxas:
         print((Path(args.out or PACKAGE / "_native") / "build.log").read_text())
 

@@ -107,6 +107,13 @@ constexpr int kPrepThreads = 128;
 constexpr int kPrepSmem = PrepLayout::kTotal + 1024;
 constexpr int kPrepTmemCols = 256;   // D1 [0,64)  DW [64,128)  DU [128,192)
 
+#ifdef GDN_SM100_PHASE_TIMING
+#define GDN_PSTAMP(slot) \
+  if (tid == 0) ws.gates[block * 128 + 80 + (slot)] = float((clock64() - t_begin) & 0xffffff)
+#else
+#define GDN_PSTAMP(slot)
+#endif
+
 __global__ void __launch_bounds__(kPrepThreads)
 prepare_umma_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                     const __grid_constant__ CUtensorMap tm_v, Inputs in, Geometry geo, Workspace ws) {
@@ -134,6 +141,9 @@ prepare_umma_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
   const int t0 = chunk * kChunk;
   const int valid = min(kChunk, geo.sequence - t0);
   const long long block = blockIdx.x;
+#ifdef GDN_SM100_PHASE_TIMING
+  const long long t_begin = clock64();
+#endif
 
   if (tid == 0) {
     mbar_init(bar_tma, 1);
@@ -158,6 +168,7 @@ prepare_umma_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = *tmem_slot;
+  GDN_PSTAMP(0);
 
   if (tid == 0) {
     mbar_arrive_expect_tx(bar_tma, 6 * kBox);
@@ -180,6 +191,7 @@ prepare_umma_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
 
   // ---- phase 2: D1 = [Q;K] K^T
   bool ok = mbar_wait(bar_tma, 0, abort, 1, chunk);
+  GDN_PSTAMP(1);
   if (tid == 0 && ok) {
     tc_fence_after();
     const uint32_t base = smem_u32(sm);
@@ -193,6 +205,7 @@ prepare_umma_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
   }
   ok = ok && mbar_wait(bar_mma, 0, abort, 2, chunk);
   tc_fence_after();
+  GDN_PSTAMP(2);
 
   // ---- phase 3: masks and decays on D1
   if (ok) {
@@ -234,6 +247,7 @@ prepare_umma_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
     }
   }
   __syncthreads();
+  GDN_PSTAMP(3);
 
   // ---- phase 4: inverse (warps 0,1) and scaled query (warps 2,3)
   if (ok && tid < 64) {
@@ -287,6 +301,7 @@ prepare_umma_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
     }
   }
   __syncthreads();
+  GDN_PSTAMP(4);
 
   // ---- phase 5: W^T and U^T
   if (tid == 0 && ok) {
@@ -314,6 +329,7 @@ prepare_umma_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
   }
   ok = ok && mbar_wait(bar_mma, 1, abort, 3, chunk);
   tc_fence_after();
+  GDN_PSTAMP(5);
 
   // ---- phase 6: write W (hi/lo), U, gate vector
   if (ok) {
@@ -346,6 +362,7 @@ prepare_umma_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
     if (tid < kChunk) ws.gates[block * 128 + tid] = (tid < valid) ? exp2f(last - s_pl2[tid]) : 0.f;
     if (tid == kChunk) ws.gates[block * 128 + kChunk] = exp2f(last);
   }
+  GDN_PSTAMP(6);
   if (!ok) {
     for (int i = 0; i < 20; ++i) __nanosleep(100000);   // let copies in flight land before the CTA leaves
   }
@@ -353,17 +370,19 @@ prepare_umma_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
   __syncthreads();
   if (warp == 0) tmem_dealloc(tmem, kPrepTmemCols);
 }
+#undef GDN_PSTAMP
 
 // ==================================================================================== walk kernel
-// One CTA per (batch, value head), 320 threads, one CTA per SM.  Tensor memory (512 columns):
+// One CTA per (batch, value head), 448 threads, one CTA per SM.  Tensor memory (512 columns):
 //   ACC_S  [  0,128)  St FP32 accumulator (pre-scaled by the chunk decay before the update MMA)
 //   OP_SH  [128,192)  St BF16 hi, packed pairs (A operand of W S and Q S)
 //   OP_SL  [192,256)  St BF16 lo
 //   ACC_WS [256,320)  (W S)^T FP32
 //   OP_NH  [320,352)  (N*rel)^T BF16 hi      OP_NL [352,384) lo      OP_N16 [384,416) N^T BF16
 //   ACC_O  [416,480)  O^T FP32
-// Roles: warps 0-3 state chain (decay/split of St, N = U - W S); warps 4-7 output epilogue;
-//        warp 8 TMA producer; warp 9 MMA issuer.
+// Roles: warps 0-7 state chain; a warp owns the 32 TMEM lanes of quarter (warp & 3) and, of every
+//        tile it touches, the column half (warp >> 2): decay + hi/lo split of St, N = U - W S.
+//        warps 8-11 output epilogue; warp 12 TMA producer; warp 13 MMA issuer.
 struct WalkLayout {
   static constexpr int kWH = 0, kWL = 2 * kBox, kQS = 4 * kBox, kK = 6 * kBox, kP = 8 * kBox;
   static constexpr int kGates = 9 * kBox;
@@ -373,10 +392,19 @@ struct WalkLayout {
   static constexpr int kBars = kStages * kStage;
   static constexpr int kTotal = kBars + 256;
 };
-constexpr int kWalkThreads = 320;
+constexpr int kChainWarps = 8, kOutWarp0 = 8, kTmaWarp = 12, kMmaWarp = 13;
+constexpr int kChainThreads = kChainWarps * 32;
+constexpr int kWalkThreads = 448;
 constexpr int kWalkSmem = WalkLayout::kTotal + 1024;
 constexpr uint32_t kAccS = 0, kOpSH = 128, kOpSL = 192, kAccWS = 256, kOpNH = 320, kOpNL = 352, kOpN16 = 384,
                    kAccO = 416;
+
+#ifdef GDN_SM100_PHASE_TIMING
+#define GDN_STAMP(slot)                                                                        \
+  if (tid == 0) ws.gates[(block0 + c) * 128 + 96 + (slot)] = float((clock64() - t_begin) & 0xffffff)
+#else
+#define GDN_STAMP(slot)
+#endif
 
 __global__ void __launch_bounds__(kWalkThreads, 1)
 walk_umma_kernel(const __grid_constant__ CUtensorMap tm_wh, const __grid_constant__ CUtensorMap tm_wl,
@@ -388,9 +416,9 @@ walk_umma_kernel(const __grid_constant__ CUtensorMap tm_wh, const __grid_constan
   uint64_t* bars = reinterpret_cast<uint64_t*>(sm + L::kBars);
   uint64_t* full = bars;                       // [kStages]
   uint64_t* empty = bars + L::kStages;         // [kStages]
-  uint64_t* bar_ops = bars + 2 * L::kStages;   // state operands written (128 arrivals)
+  uint64_t* bar_ops = bars + 2 * L::kStages;   // state operands written (chain threads arrive)
   uint64_t* bar_ws = bar_ops + 1;              // W S product complete
-  uint64_t* bar_opn = bar_ops + 2;             // N operands written (128 arrivals)
+  uint64_t* bar_opn = bar_ops + 2;             // N operands written (chain threads arrive)
   uint64_t* bar_s = bar_ops + 3;               // state update complete
   uint64_t* bar_o = bar_ops + 4;               // output accumulator complete
   uint64_t* bar_ofree = bar_ops + 5;           // output accumulator drained (128 arrivals)
@@ -404,22 +432,25 @@ walk_umma_kernel(const __grid_constant__ CUtensorMap tm_wh, const __grid_constan
   const int hk = hv / geo.group();
   const int chunks = geo.chunks();
   const long long block0 = (long long)bh * chunks;
+#ifdef GDN_SM100_PHASE_TIMING
+  const long long t_begin = clock64();
+#endif
 
   if (tid == 0) {
     for (int s = 0; s < L::kStages; ++s) {
       mbar_init(full + s, 1);
       mbar_init(empty + s, 1);
     }
-    mbar_init(bar_ops, 128);
+    mbar_init(bar_ops, kChainThreads);
     mbar_init(bar_ws, 1);
-    mbar_init(bar_opn, 128);
+    mbar_init(bar_opn, kChainThreads);
     mbar_init(bar_s, 1);
     mbar_init(bar_o, 1);
     mbar_init(bar_ofree, 128);
     *abort_word = 0;
     fence_barrier_init();
   }
-  if (warp == 9) {
+  if (warp == kMmaWarp) {
     tmem_alloc(tmem_slot, 512);
     tmem_relinquish();
   }
@@ -428,18 +459,20 @@ walk_umma_kernel(const __grid_constant__ CUtensorMap tm_wh, const __grid_constan
   tc_fence_after();
   const uint32_t tmem = *tmem_slot;
 
-  if (warp < 4) {
+  if (warp < kChainWarps) {
     // ------------------------------------------------------------------ state chain
-    const int v = tid;                                     // value row = TMEM lane
-    const uint32_t taddr = tmem + (uint32_t(warp * 32) << 16);
+    const int quarter = warp & 3, half = warp >> 2;
+    const int v = quarter * 32 + lane;                     // value row = TMEM lane
+    const uint32_t taddr = tmem + (uint32_t(quarter * 32) << 16);
     {
       const float* init = in.initial ? in.initial + (long long)bh * kDim * kDim + v : nullptr;
 #pragma unroll
-      for (int cg = 0; cg < 8; ++cg) {
-        uint32_t vals[16];
+      for (int part = 0; part < 2; ++part) {
+        uint32_t vals[32];
+        const int k0 = half * 64 + part * 32;
 #pragma unroll
-        for (int j = 0; j < 16; ++j) vals[j] = init ? __float_as_uint(init[(cg * 16 + j) * kDim]) : 0u;
-        tmem_st16(taddr + kAccS + cg * 16, vals);
+        for (int j = 0; j < 32; ++j) vals[j] = init ? __float_as_uint(init[(k0 + j) * kDim]) : 0u;
+        tmem_st32(taddr + kAccS + k0, vals);
       }
       tmem_wait_st();
     }
@@ -447,23 +480,24 @@ walk_umma_kernel(const __grid_constant__ CUtensorMap tm_wh, const __grid_constan
     for (int c = 0; c < chunks && ok; ++c) {
       const int s = c % L::kStages;
       const float* gates = reinterpret_cast<const float*>(sm + s * L::kStage + L::kGates);
-      const float* urow = ws.u + (block0 + c) * kChunk * kDim + v;
-      float u[64];
-#pragma unroll
-      for (int i = 0; i < 64; ++i) u[i] = __ldg(urow + i * kDim);
+      const float* urow = ws.u + ((block0 + c) * kChunk + half * 32) * kDim + v;
+      if (c + 1 < chunks)      // pull the next chunk's U rows of this warp towards L2
+        asm volatile("prefetch.global.L2 [%0];" ::"l"(urow + kChunk * kDim + lane * kDim - lane));
 
       if (c > 0) ok = mbar_wait(bar_s, (c - 1) & 1, abort, 10, c);
       ok = ok && mbar_wait(full + s, (c / L::kStages) & 1, abort, 11, c);
       if (!ok) break;
       tc_fence_after();
+      GDN_STAMP(0);
       const float gamma = gates[kChunk];
 #pragma unroll
-      for (int cg = 0; cg < 8; ++cg) {
-        uint32_t d[16], hi[8], lo[8];
-        tmem_ld16(taddr + kAccS + cg * 16, d);
+      for (int part = 0; part < 2; ++part) {
+        uint32_t d[32], hi[16], lo[16];
+        const int k0 = half * 64 + part * 32;
+        tmem_ld32(taddr + kAccS + k0, d);
         tmem_wait_ld();
 #pragma unroll
-        for (int j = 0; j < 16; j += 2) {
+        for (int j = 0; j < 32; j += 2) {
           const float s0 = __uint_as_float(d[j]), s1 = __uint_as_float(d[j + 1]);
           const uint32_t h = pack_bf16(s0, s1);
           hi[j >> 1] = h;
@@ -471,71 +505,82 @@ walk_umma_kernel(const __grid_constant__ CUtensorMap tm_wh, const __grid_constan
           d[j] = __float_as_uint(s0 * gamma);
           d[j + 1] = __float_as_uint(s1 * gamma);
         }
-        tmem_st16(taddr + kAccS + cg * 16, d);
-        tmem_st8(taddr + kOpSH + cg * 8, hi);
-        tmem_st8(taddr + kOpSL + cg * 8, lo);
+        tmem_st16(taddr + kOpSH + (k0 >> 1), hi);
+        tmem_st16(taddr + kOpSL + (k0 >> 1), lo);
+        tmem_st32(taddr + kAccS + k0, d);
       }
       tmem_wait_st();
       tc_fence_before();
       mbar_arrive(bar_ops);
+      GDN_STAMP(1);
+
+      float u[32];
+#pragma unroll
+      for (int i = 0; i < 32; ++i) u[i] = __ldg(urow + i * kDim);
 
       ok = mbar_wait(bar_ws, c & 1, abort, 12, c);
       if (!ok) break;
       tc_fence_after();
-#pragma unroll
-      for (int cg = 0; cg < 4; ++cg) {
-        uint32_t d[16], nh[8], nl[8], n16[8];
-        tmem_ld16(taddr + kAccWS + cg * 16, d);
+      GDN_STAMP(2);
+      {
+        uint32_t d[32], nh[16], nl[16], n16[16];
+        tmem_ld32(taddr + kAccWS + half * 32, d);
         tmem_wait_ld();
 #pragma unroll
-        for (int j = 0; j < 16; j += 2) {
-          const int i = cg * 16 + j;
-          const float n0 = u[i] - __uint_as_float(d[j]);
-          const float n1 = u[i + 1] - __uint_as_float(d[j + 1]);
+        for (int j = 0; j < 32; j += 2) {
+          const int i = half * 32 + j;
+          const float n0 = u[j] - __uint_as_float(d[j]);
+          const float n1 = u[j + 1] - __uint_as_float(d[j + 1]);
           const float r0 = n0 * gates[i], r1 = n1 * gates[i + 1];
           const uint32_t h = pack_bf16(r0, r1);
           nh[j >> 1] = h;
           nl[j >> 1] = pack_bf16(r0 - bf16_lo(h), r1 - bf16_hi(h));
           n16[j >> 1] = pack_bf16(n0, n1);
         }
-        tmem_st8(taddr + kOpNH + cg * 8, nh);
-        tmem_st8(taddr + kOpNL + cg * 8, nl);
-        tmem_st8(taddr + kOpN16 + cg * 8, n16);
+        tmem_st16(taddr + kOpNH + half * 16, nh);
+        tmem_st16(taddr + kOpNL + half * 16, nl);
+        tmem_st16(taddr + kOpN16 + half * 16, n16);
       }
       tmem_wait_st();
       tc_fence_before();
       mbar_arrive(bar_opn);
+      GDN_STAMP(3);
     }
     if (ok) ok = mbar_wait(bar_s, (chunks - 1) & 1, abort, 13, chunks);
     if (ok && in.final_state) {
       tc_fence_after();
       float* fin = in.final_state + (long long)bh * kDim * kDim + v;
 #pragma unroll
-      for (int cg = 0; cg < 8; ++cg) {
-        uint32_t d[16];
-        tmem_ld16(taddr + kAccS + cg * 16, d);
+      for (int part = 0; part < 2; ++part) {
+        uint32_t d[32];
+        const int k0 = half * 64 + part * 32;
+        tmem_ld32(taddr + kAccS + k0, d);
         tmem_wait_ld();
 #pragma unroll
-        for (int j = 0; j < 16; ++j) fin[(cg * 16 + j) * kDim] = __uint_as_float(d[j]);
+        for (int j = 0; j < 32; ++j) fin[(k0 + j) * kDim] = __uint_as_float(d[j]);
       }
     }
-  } else if (warp < 8) {
+  }  else if (warp < kTmaWarp) {
     // ------------------------------------------------------------------ output epilogue
-    const int v = tid - 128;
-    const uint32_t taddr = tmem + (uint32_t((warp - 4) * 32) << 16) + kAccO;
+    const int quarter = warp - kOutWarp0;
+    const int v = quarter * 32 + lane;
+    const uint32_t taddr = tmem + (uint32_t(quarter * 32) << 16) + kAccO;
     bool ok = true;
     for (int c = 0; c < chunks && ok; ++c) {
       ok = mbar_wait(bar_o, c & 1, abort, 20, c);
       if (!ok) break;
       tc_fence_after();
       uint32_t o[64];
-#pragma unroll
-      for (int cg = 0; cg < 4; ++cg) {
-        uint32_t d[16];
-        tmem_ld16(taddr + cg * 16, d);
+      {
+        uint32_t d0[32], d1[32];
+        tmem_ld32(taddr, d0);
+        tmem_ld32(taddr + 32, d1);
         tmem_wait_ld();
 #pragma unroll
-        for (int j = 0; j < 16; ++j) o[cg * 16 + j] = d[j];
+        for (int j = 0; j < 32; ++j) {
+          o[j] = d0[j];
+          o[32 + j] = d1[j];
+        }
       }
       tc_fence_before();
       mbar_arrive(bar_ofree);
@@ -547,7 +592,7 @@ walk_umma_kernel(const __grid_constant__ CUtensorMap tm_wh, const __grid_constan
       for (int i = 0; i < 64; ++i)
         if (i < valid) out[i * row] = __float2bfloat16_rn(__uint_as_float(o[i]));
     }
-  } else if (warp == 8) {
+  } else if (warp == kTmaWarp) {
     // ------------------------------------------------------------------ TMA producer
     if (lane == 0) {
       prefetch_tensormap(&tm_wh);
@@ -561,6 +606,7 @@ walk_umma_kernel(const __grid_constant__ CUtensorMap tm_wh, const __grid_constan
         uint8_t* st = sm + s * L::kStage;
         const int row = int((block0 + c) * kChunk);
         mbar_arrive_expect_tx(full + s, L::kTxBytes);
+        bulk_load(st + L::kGates, ws.gates + (block0 + c) * 128, 512, full + s);
         tma_load_2d(st + L::kWH, &tm_wh, full + s, 0, row);
         tma_load_2d(st + L::kWH + kBox, &tm_wh, full + s, 64, row);
         tma_load_2d(st + L::kWL, &tm_wl, full + s, 0, row);
@@ -570,7 +616,6 @@ walk_umma_kernel(const __grid_constant__ CUtensorMap tm_wh, const __grid_constan
         tma_load_4d(st + L::kK, &tm_k, full + s, 0, hk, c * kChunk, b);
         tma_load_4d(st + L::kK + kBox, &tm_k, full + s, 64, hk, c * kChunk, b);
         tma_load_2d(st + L::kP, &tm_p, full + s, 0, row);
-        bulk_load(st + L::kGates, ws.gates + (block0 + c) * 128, 512, full + s);
       }
     }
     __syncwarp();
@@ -583,7 +628,6 @@ walk_umma_kernel(const __grid_constant__ CUtensorMap tm_wh, const __grid_constan
         const uint32_t st = smem_u32(sm + s * L::kStage);
         ok = mbar_wait(full + s, (c / L::kStages) & 1, abort, 40, c) &&
              mbar_wait(bar_ops, c & 1, abort, 41, c);
-        if (ok && c > 0) ok = mbar_wait(bar_ofree, (c - 1) & 1, abort, 42, c);
         if (!ok) break;
         tc_fence_after();
         // (W S)^T = St W^T with St ~ SH + SL and W ~ WH + WL (the lo*lo term is dropped)
@@ -597,7 +641,10 @@ walk_umma_kernel(const __grid_constant__ CUtensorMap tm_wh, const __grid_constan
                    kIdescN64, (term | ks) != 0);
         }
         mma_commit(bar_ws);
-        // O^T = St Qs^T (old state, BF16 hi part)
+        // O^T = St Qs^T (old state, BF16 hi part); the previous chunk's O^T must have been drained
+        if (c > 0) ok = mbar_wait(bar_ofree, (c - 1) & 1, abort, 42, c);
+        if (!ok) break;
+        tc_fence_after();
 #pragma unroll
         for (int ks = 0; ks < 8; ++ks)
           mma_ts(tmem + kAccO, tmem + kOpSH + ks * 8,
@@ -630,8 +677,9 @@ walk_umma_kernel(const __grid_constant__ CUtensorMap tm_wh, const __grid_constan
   }
   tc_fence_before();
   __syncthreads();
-  if (warp == 9) tmem_dealloc(tmem, 512);
+  if (warp == kMmaWarp) tmem_dealloc(tmem, 512);
 }
+#undef GDN_STAMP
 
 }  // namespace
 
