@@ -87,20 +87,25 @@ __device__ __forceinline__ int swizzled_offset(int row, int col) {
 //   phase 1  TMA: Q, K chunk tiles (key head of the group) and V tile; gate prefix by two warps
 //   phase 2  D1[128x64] = [Q;K] K^T                                  (one tcgen05 product, 8 instructions)
 //   phase 3  rows 0..63  -> P = tril(QK^T * decay)/sqrt(128) -> BF16 -> workspace
-//            rows 64..127-> A = tril(beta_i KK^T * decay, -1) -> shared (transposed, FP32)
-//   phase 4  T = (I+A)^-1: one column per thread, right-looking substitution in registers
-//            (warps 0,1); scaled query rows -> workspace (warps 2,3)
+//            rows 64..127-> A = tril(beta_i KK^T * decay, -1) -> shared (FP32); scaled query rows -> workspace
+//   phase 4  T = (I+A)^-1 in FP32 on the CUDA cores, blocked: four 16x16 diagonal solves in registers, then
+//            T21 = -T22 (A21 T11) at block size 16 and 32 (the blocked scheme of the reference's
+//            tests/wy_cpu.py:21-41, with plain FP32 products instead of TF32x3)
 //            T diag(beta exp(p)) and T diag(beta) -> BF16 hi/lo K-major tiles in shared memory
 //   phase 5  W^T = K^T (T diag(beta exp p))^T,  U^T = V^T (T diag(beta))^T   (A = transposed K / V tiles)
 //   phase 6  accumulators -> W hi/lo BF16, U FP32, gate vector -> workspace
 struct PrepLayout {
   static constexpr int kQ0 = 0, kK0 = kBox, kQ1 = 2 * kBox, kK1 = 3 * kBox;   // [Q;K] stacked, two K atoms
   static constexpr int kV0 = 4 * kBox, kV1 = 5 * kBox;
-  static constexpr int kTwH = 6 * kBox, kTwL = 7 * kBox, kTuH = 8 * kBox, kTuL = 9 * kBox;
-  static constexpr int kAt = 10 * kBox;                   // float [64][68]: At[j][i] = A[i][j]
-  static constexpr int kAtStride = 68;
-  static constexpr int kVec = kAt + 64 * kAtStride * 4;   // float [4][64]: pl2, beta, beta*exp(p), exp(p)/sqrt(128)
-  static constexpr int kBars = kVec + 4 * 64 * 4;         // 2 mbarriers, tmem slot, abort flag, carry
+  static constexpr int kLd = 68;                           // row pitch (floats) of the FP32 64x64 matrices
+  static constexpr int kA = 6 * kBox;                      // float [64][68]: A, row-major
+  static constexpr int kTwH = 6 * kBox, kTwL = 7 * kBox;   // written after A is dead
+  static constexpr int kTuH = 6 * kBox + 18 * 1024, kTuL = kTuH + kBox;
+  static constexpr int kT = kTuL + kBox;                   // float [64][68]: T, row-major
+  static constexpr int kX = kQ0;                           // block products, reuse the Q boxes after phase 3
+  static constexpr int kLdX = 20, kLdX3 = 36;
+  static constexpr int kVec = kT + 64 * kLd * 4;           // float [4][64]: pl2, beta, beta*exp(p), exp(p)/sqrt(128)
+  static constexpr int kBars = kVec + 4 * 64 * 4;          // 2 mbarriers, tmem slot, abort flag, carry
   static constexpr int kTotal = kBars + 64;
 };
 constexpr int kPrepThreads = 128;
@@ -120,7 +125,9 @@ prepare_umma_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
   extern __shared__ uint8_t raw_smem[];
   uint8_t* sm = align1024(raw_smem);
   using L = PrepLayout;
-  float* sAt = reinterpret_cast<float*>(sm + L::kAt);
+  float* sA = reinterpret_cast<float*>(sm + L::kA);
+  float* sT = reinterpret_cast<float*>(sm + L::kT);
+  float* sX = reinterpret_cast<float*>(sm + L::kX);
   float* s_pl2 = reinterpret_cast<float*>(sm + L::kVec);
   float* s_beta = s_pl2 + 64;
   float* s_coefw = s_beta + 64;
@@ -207,7 +214,7 @@ prepare_umma_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
   tc_fence_after();
   GDN_PSTAMP(2);
 
-  // ---- phase 3: masks and decays on D1
+  // ---- phase 3: masks and decays on D1, scaled query rows
   if (ok) {
     const uint32_t taddr = tmem + (uint32_t(warp * 32) << 16);
     const int i = tid & 63;
@@ -233,59 +240,28 @@ prepare_umma_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
       }
     } else {
       const float bi = s_beta[i];
+      float* arow = sA + i * L::kLd;
 #pragma unroll
       for (int cg = 0; cg < 4; ++cg) {
         uint32_t d[16];
         tmem_ld16(taddr + cg * 16, d);
         tmem_wait_ld();
+        float a[16];
 #pragma unroll
         for (int jj = 0; jj < 16; ++jj) {
           const int j = cg * 16 + jj;
-          sAt[j * L::kAtStride + i] = (j < i) ? bi * __uint_as_float(d[jj]) * exp2f(pi - s_pl2[j]) : 0.f;
+          a[jj] = (j < i) ? bi * __uint_as_float(d[jj]) * exp2f(pi - s_pl2[j]) : 0.f;
         }
+#pragma unroll
+        for (int q4 = 0; q4 < 4; ++q4)
+          *reinterpret_cast<float4*>(arow + cg * 16 + q4 * 4) =
+              make_float4(a[q4 * 4], a[q4 * 4 + 1], a[q4 * 4 + 2], a[q4 * 4 + 3]);
       }
     }
-  }
-  __syncthreads();
-  GDN_PSTAMP(3);
-
-  // ---- phase 4: inverse (warps 0,1) and scaled query (warps 2,3)
-  if (ok && tid < 64) {
-    const int c = tid;
-    float x[64];
-#pragma unroll
-    for (int i = 0; i < 64; ++i) x[i] = (i == c) ? 1.f : 0.f;
-#pragma unroll
-    for (int j = 0; j < 63; ++j) {
-      const float xj = x[j];
-      const float* col = sAt + j * L::kAtStride;          // A[.][j], contiguous in the row index
-#pragma unroll
-      for (int i4 = ((j + 1) & ~3); i4 < 64; i4 += 4) {
-        const float4 a = *reinterpret_cast<const float4*>(col + i4);
-        if (i4 + 0 > j) x[i4 + 0] = fmaf(-a.x, xj, x[i4 + 0]);
-        if (i4 + 1 > j) x[i4 + 1] = fmaf(-a.y, xj, x[i4 + 1]);
-        if (i4 + 2 > j) x[i4 + 2] = fmaf(-a.z, xj, x[i4 + 2]);
-        if (i4 + 3 > j) x[i4 + 3] = fmaf(-a.w, xj, x[i4 + 3]);
-      }
-    }
-    const float cw = s_coefw[c], cu = s_beta[c];
-#pragma unroll
-    for (int i = 0; i < 64; ++i) {
-      __nv_bfloat16 hi, lo;
-      const int off = swizzled_offset(i, c);
-      split_bf16(x[i] * cw, hi, lo);
-      *reinterpret_cast<__nv_bfloat16*>(sm + L::kTwH + off) = hi;
-      *reinterpret_cast<__nv_bfloat16*>(sm + L::kTwL + off) = lo;
-      split_bf16(x[i] * cu, hi, lo);
-      *reinterpret_cast<__nv_bfloat16*>(sm + L::kTuH + off) = hi;
-      *reinterpret_cast<__nv_bfloat16*>(sm + L::kTuL + off) = lo;
-    }
-    fence_proxy_async_smem();
-  } else if (ok) {
-    const int row = tid - 64;
-    const float qs = s_qscale[row];
-#pragma unroll
-    for (int half = 0; half < 2; ++half) {
+    {
+      // scaled query: row = tid/2, one 64-wide half (= one TMA box row) per thread
+      const int row = tid >> 1, half = tid & 1;
+      const float qs = s_qscale[row];
       const uint8_t* src = sm + (half ? L::kQ1 : L::kQ0) + row * 128;
       __nv_bfloat16* dst = ws.qs + (block * kChunk + row) * kDim + half * 64;
 #pragma unroll
@@ -299,6 +275,141 @@ prepare_umma_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
         *reinterpret_cast<uint4*>(dst + cc * 8) = o;
       }
     }
+    for (int e = tid; e < 64 * L::kLd / 4; e += kPrepThreads)
+      reinterpret_cast<float4*>(sT)[e] = make_float4(0.f, 0.f, 0.f, 0.f);
+  }
+  __syncthreads();
+  GDN_PSTAMP(3);
+
+  // ---- phase 4: T = (I+A)^-1, blocked 16 -> 32 -> 64, all in FP32 on the CUDA cores
+  // level 1: the four 16x16 diagonal blocks, one column per thread (left-looking, in registers)
+  if (ok && tid < 64) {
+    const int blk = tid >> 4, c = tid & 15;
+    const float* a0 = sA + (blk * 16) * L::kLd + blk * 16;
+    float x[16];
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      float acc0 = (i == c) ? 1.f : 0.f, acc1 = 0.f;
+#pragma unroll
+      for (int j4 = 0; j4 < i; j4 += 4) {
+        const float4 a = *reinterpret_cast<const float4*>(a0 + i * L::kLd + j4);
+        if (j4 + 0 < i) acc0 = fmaf(-a.x, x[j4 + 0], acc0);
+        if (j4 + 1 < i) acc1 = fmaf(-a.y, x[j4 + 1], acc1);
+        if (j4 + 2 < i) acc0 = fmaf(-a.z, x[j4 + 2], acc0);
+        if (j4 + 3 < i) acc1 = fmaf(-a.w, x[j4 + 3], acc1);
+      }
+      x[i] = acc0 + acc1;
+    }
+    float* t0 = sT + (blk * 16) * L::kLd + blk * 16 + c;
+#pragma unroll
+    for (int i = 0; i < 16; ++i) t0[i * L::kLd] = x[i];
+  }
+  __syncthreads();
+  GDN_PSTAMP(7);
+  // level 2: inside each 32x32 diagonal block, T21 = -T22 (A21 T11) with 16x16 blocks
+  {
+    const int big = tid >> 6, i = (tid & 63) >> 2, cg = tid & 3;
+    const int o = big * 32;
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (ok) {
+      const float* arow = sA + (o + 16 + i) * L::kLd + o;
+#pragma unroll
+      for (int k = 0; k < 16; ++k) {
+        const float a = arow[k];
+        const float4 t = *reinterpret_cast<const float4*>(sT + (o + k) * L::kLd + o + cg * 4);
+        acc.x = fmaf(a, t.x, acc.x); acc.y = fmaf(a, t.y, acc.y);
+        acc.z = fmaf(a, t.z, acc.z); acc.w = fmaf(a, t.w, acc.w);
+      }
+      *reinterpret_cast<float4*>(sX + (big * 16 + i) * L::kLdX + cg * 4) = acc;
+    }
+    __syncthreads();
+    if (ok) {
+      acc = make_float4(0.f, 0.f, 0.f, 0.f);
+      const float* trow = sT + (o + 16 + i) * L::kLd + o + 16;
+#pragma unroll
+      for (int k = 0; k < 16; ++k) {
+        const float a = trow[k];
+        const float4 t = *reinterpret_cast<const float4*>(sX + (big * 16 + k) * L::kLdX + cg * 4);
+        acc.x = fmaf(a, t.x, acc.x); acc.y = fmaf(a, t.y, acc.y);
+        acc.z = fmaf(a, t.z, acc.z); acc.w = fmaf(a, t.w, acc.w);
+      }
+      *reinterpret_cast<float4*>(sT + (o + 16 + i) * L::kLd + o + cg * 4) =
+          make_float4(-acc.x, -acc.y, -acc.z, -acc.w);
+    }
+  }
+  __syncthreads();
+  GDN_PSTAMP(8);
+  // level 3: T21 = -T22 (A21 T11) with 32x32 blocks; thread -> row i, eight columns
+  {
+    const int i = tid >> 2, cg = tid & 3;
+    float acc[8];
+    if (ok) {
+#pragma unroll
+      for (int e = 0; e < 8; ++e) acc[e] = 0.f;
+      const float* arow = sA + (32 + i) * L::kLd;
+#pragma unroll 8
+      for (int k = 0; k < 32; ++k) {
+        const float a = arow[k];
+        const float4 t0 = *reinterpret_cast<const float4*>(sT + k * L::kLd + cg * 8);
+        const float4 t1 = *reinterpret_cast<const float4*>(sT + k * L::kLd + cg * 8 + 4);
+        acc[0] = fmaf(a, t0.x, acc[0]); acc[1] = fmaf(a, t0.y, acc[1]);
+        acc[2] = fmaf(a, t0.z, acc[2]); acc[3] = fmaf(a, t0.w, acc[3]);
+        acc[4] = fmaf(a, t1.x, acc[4]); acc[5] = fmaf(a, t1.y, acc[5]);
+        acc[6] = fmaf(a, t1.z, acc[6]); acc[7] = fmaf(a, t1.w, acc[7]);
+      }
+      float* xrow = sX + i * L::kLdX3 + cg * 8;
+      *reinterpret_cast<float4*>(xrow) = make_float4(acc[0], acc[1], acc[2], acc[3]);
+      *reinterpret_cast<float4*>(xrow + 4) = make_float4(acc[4], acc[5], acc[6], acc[7]);
+    }
+    __syncthreads();
+    if (ok) {
+#pragma unroll
+      for (int e = 0; e < 8; ++e) acc[e] = 0.f;
+      const float* trow = sT + (32 + i) * L::kLd + 32;
+#pragma unroll 8
+      for (int k = 0; k < 32; ++k) {
+        const float a = trow[k];
+        const float4 t0 = *reinterpret_cast<const float4*>(sX + k * L::kLdX3 + cg * 8);
+        const float4 t1 = *reinterpret_cast<const float4*>(sX + k * L::kLdX3 + cg * 8 + 4);
+        acc[0] = fmaf(a, t0.x, acc[0]); acc[1] = fmaf(a, t0.y, acc[1]);
+        acc[2] = fmaf(a, t0.z, acc[2]); acc[3] = fmaf(a, t0.w, acc[3]);
+        acc[4] = fmaf(a, t1.x, acc[4]); acc[5] = fmaf(a, t1.y, acc[5]);
+        acc[6] = fmaf(a, t1.z, acc[6]); acc[7] = fmaf(a, t1.w, acc[7]);
+      }
+      float* trow_out = sT + (32 + i) * L::kLd + cg * 8;
+      *reinterpret_cast<float4*>(trow_out) = make_float4(-acc[0], -acc[1], -acc[2], -acc[3]);
+      *reinterpret_cast<float4*>(trow_out + 4) = make_float4(-acc[4], -acc[5], -acc[6], -acc[7]);
+    }
+  }
+  __syncthreads();
+  GDN_PSTAMP(9);
+  // T diag(beta exp p) and T diag(beta) as BF16 hi/lo K-major tiles (these overwrite the A matrix)
+  if (ok) {
+    const int i = tid >> 1, c0 = (tid & 1) * 32;
+#pragma unroll
+    for (int g8 = 0; g8 < 4; ++g8) {
+      const int c = c0 + g8 * 8;
+      const float4 ta = *reinterpret_cast<const float4*>(sT + i * L::kLd + c);
+      const float4 tb = *reinterpret_cast<const float4*>(sT + i * L::kLd + c + 4);
+      const float t[8] = {ta.x, ta.y, ta.z, ta.w, tb.x, tb.y, tb.z, tb.w};
+      uint32_t wh[4], wl[4], uh[4], ul[4];
+#pragma unroll
+      for (int e = 0; e < 8; e += 2) {
+        const float w0 = t[e] * s_coefw[c + e], w1 = t[e + 1] * s_coefw[c + e + 1];
+        const float u0 = t[e] * s_beta[c + e], u1 = t[e + 1] * s_beta[c + e + 1];
+        const uint32_t hw = pack_bf16(w0, w1), hu = pack_bf16(u0, u1);
+        wh[e >> 1] = hw;
+        wl[e >> 1] = pack_bf16(w0 - bf16_lo(hw), w1 - bf16_hi(hw));
+        uh[e >> 1] = hu;
+        ul[e >> 1] = pack_bf16(u0 - bf16_lo(hu), u1 - bf16_hi(hu));
+      }
+      const int off = i * 128 + (((c >> 3) ^ (i & 7)) << 4);
+      *reinterpret_cast<uint4*>(sm + L::kTwH + off) = make_uint4(wh[0], wh[1], wh[2], wh[3]);
+      *reinterpret_cast<uint4*>(sm + L::kTwL + off) = make_uint4(wl[0], wl[1], wl[2], wl[3]);
+      *reinterpret_cast<uint4*>(sm + L::kTuH + off) = make_uint4(uh[0], uh[1], uh[2], uh[3]);
+      *reinterpret_cast<uint4*>(sm + L::kTuL + off) = make_uint4(ul[0], ul[1], ul[2], ul[3]);
+    }
+    fence_proxy_async_smem();
   }
   __syncthreads();
   GDN_PSTAMP(4);
@@ -402,8 +513,10 @@ constexpr uint32_t kAccS = 0, kOpSH = 128, kOpSL = 192, kAccWS = 256, kOpNH = 32
 #ifdef GDN_SM100_PHASE_TIMING
 #define GDN_STAMP(slot)                                                                        \
   if (tid == 0) ws.gates[(block0 + c) * 128 + 96 + (slot)] = float((clock64() - t_begin) & 0xffffff)
+#define GDN_MSTAMP(slot) ws.gates[(block0 + c) * 128 + 104 + (slot)] = float((clock64() - t_begin) & 0xffffff)
 #else
 #define GDN_STAMP(slot)
+#define GDN_MSTAMP(slot)
 #endif
 
 __global__ void __launch_bounds__(kWalkThreads, 1)
@@ -416,12 +529,12 @@ walk_umma_kernel(const __grid_constant__ CUtensorMap tm_wh, const __grid_constan
   uint64_t* bars = reinterpret_cast<uint64_t*>(sm + L::kBars);
   uint64_t* full = bars;                       // [kStages]
   uint64_t* empty = bars + L::kStages;         // [kStages]
-  uint64_t* bar_ops = bars + 2 * L::kStages;   // state operands written (chain threads arrive)
+  uint64_t* bar_ops = bars + 2 * L::kStages;   // state operands written (one arrival per chain warp)
   uint64_t* bar_ws = bar_ops + 1;              // W S product complete
-  uint64_t* bar_opn = bar_ops + 2;             // N operands written (chain threads arrive)
+  uint64_t* bar_opn = bar_ops + 2;             // N operands written (one arrival per chain warp)
   uint64_t* bar_s = bar_ops + 3;               // state update complete
   uint64_t* bar_o = bar_ops + 4;               // output accumulator complete
-  uint64_t* bar_ofree = bar_ops + 5;           // output accumulator drained (128 arrivals)
+  uint64_t* bar_ofree = bar_ops + 5;           // output accumulator drained (one arrival per output warp)
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_ops + 6);
   volatile int* abort_word = reinterpret_cast<volatile int*>(tmem_slot + 1);
   const AbortFlag abort{abort_word};
@@ -441,12 +554,12 @@ walk_umma_kernel(const __grid_constant__ CUtensorMap tm_wh, const __grid_constan
       mbar_init(full + s, 1);
       mbar_init(empty + s, 1);
     }
-    mbar_init(bar_ops, kChainThreads);
+    mbar_init(bar_ops, kChainWarps);
     mbar_init(bar_ws, 1);
-    mbar_init(bar_opn, kChainThreads);
+    mbar_init(bar_opn, kChainWarps);
     mbar_init(bar_s, 1);
     mbar_init(bar_o, 1);
-    mbar_init(bar_ofree, 128);
+    mbar_init(bar_ofree, 4);
     *abort_word = 0;
     fence_barrier_init();
   }
@@ -511,7 +624,8 @@ walk_umma_kernel(const __grid_constant__ CUtensorMap tm_wh, const __grid_constan
       }
       tmem_wait_st();
       tc_fence_before();
-      mbar_arrive(bar_ops);
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar_ops);
       GDN_STAMP(1);
 
       float u[32];
@@ -543,7 +657,8 @@ walk_umma_kernel(const __grid_constant__ CUtensorMap tm_wh, const __grid_constan
       }
       tmem_wait_st();
       tc_fence_before();
-      mbar_arrive(bar_opn);
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar_opn);
       GDN_STAMP(3);
     }
     if (ok) ok = mbar_wait(bar_s, (chunks - 1) & 1, abort, 13, chunks);
@@ -583,7 +698,8 @@ walk_umma_kernel(const __grid_constant__ CUtensorMap tm_wh, const __grid_constan
         }
       }
       tc_fence_before();
-      mbar_arrive(bar_ofree);
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar_ofree);
       const int t0 = c * kChunk;
       const int valid = min(kChunk, geo.sequence - t0);
       __nv_bfloat16* out = in.output + (((long long)b * geo.sequence + t0) * geo.value_heads + hv) * kDim + v;
@@ -630,6 +746,7 @@ walk_umma_kernel(const __grid_constant__ CUtensorMap tm_wh, const __grid_constan
              mbar_wait(bar_ops, c & 1, abort, 41, c);
         if (!ok) break;
         tc_fence_after();
+        GDN_MSTAMP(0);
         // (W S)^T = St W^T with St ~ SH + SL and W ~ WH + WL (the lo*lo term is dropped)
 #pragma unroll
         for (int term = 0; term < 3; ++term) {
@@ -641,6 +758,7 @@ walk_umma_kernel(const __grid_constant__ CUtensorMap tm_wh, const __grid_constan
                    kIdescN64, (term | ks) != 0);
         }
         mma_commit(bar_ws);
+        GDN_MSTAMP(1);
         // O^T = St Qs^T (old state, BF16 hi part); the previous chunk's O^T must have been drained
         if (c > 0) ok = mbar_wait(bar_ofree, (c - 1) & 1, abort, 42, c);
         if (!ok) break;
@@ -653,6 +771,7 @@ walk_umma_kernel(const __grid_constant__ CUtensorMap tm_wh, const __grid_constan
         ok = mbar_wait(bar_opn, c & 1, abort, 43, c);
         if (!ok) break;
         tc_fence_after();
+        GDN_MSTAMP(2);
         // St += (N*rel)^T K   (accumulator already holds gamma * St)
 #pragma unroll
         for (int term = 0; term < 2; ++term) {
@@ -662,6 +781,7 @@ walk_umma_kernel(const __grid_constant__ CUtensorMap tm_wh, const __grid_constan
                    smem_desc(st + L::kK + ks * 2048, kBox, 1024), kIdescN128BT, 1);
         }
         mma_commit(bar_s);
+        GDN_MSTAMP(3);
         // O^T += N^T P^T
 #pragma unroll
         for (int ks = 0; ks < 4; ++ks)
@@ -680,6 +800,7 @@ walk_umma_kernel(const __grid_constant__ CUtensorMap tm_wh, const __grid_constan
   if (warp == kMmaWarp) tmem_dealloc(tmem, 512);
 }
 #undef GDN_STAMP
+#undef GDN_MSTAMP
 
 }  // namespace
 
