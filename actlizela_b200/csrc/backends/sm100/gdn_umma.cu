@@ -74,6 +74,11 @@ __device__ __forceinline__ uint8_t* align1024(uint8_t* p) {
   return reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(p) + 1023) & ~uintptr_t(1023));
 }
 
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
 __device__ __forceinline__ float bf16_lo(uint32_t packed) { return __uint_as_float(packed << 16); }
 __device__ __forceinline__ float bf16_hi(uint32_t packed) { return __uint_as_float(packed & 0xffff0000u); }
 
@@ -83,7 +88,8 @@ __device__ __forceinline__ int swizzled_offset(int row, int col) {
 }
 
 // ================================================================================= prepare kernel
-// One CTA per (batch, value head, chunk) block, 128 threads, two CTAs per SM.
+// One CTA per (batch, value head, chunk) block, 256 threads, two CTAs per SM.  A warp owns the TMEM
+// lane quarter (warp & 3) and, of every accumulator it reads, the column half (warp >> 2).
 //   phase 1  TMA: Q, K chunk tiles (key head of the group) and V tile; gate prefix by two warps
 //   phase 2  D1[128x64] = [Q;K] K^T                                  (one tcgen05 product, 8 instructions)
 //   phase 3  rows 0..63  -> P = tril(QK^T * decay)/sqrt(128) -> BF16 -> workspace
@@ -108,7 +114,7 @@ struct PrepLayout {
   static constexpr int kBars = kVec + 4 * 64 * 4;          // 2 mbarriers, tmem slot, abort flag, carry
   static constexpr int kTotal = kBars + 64;
 };
-constexpr int kPrepThreads = 128;
+constexpr int kPrepThreads = 256;
 constexpr int kPrepSmem = PrepLayout::kTotal + 1024;
 constexpr int kPrepTmemCols = 256;   // D1 [0,64)  DW [64,128)  DU [128,192)
 
@@ -119,7 +125,7 @@ constexpr int kPrepTmemCols = 256;   // D1 [0,64)  DW [64,128)  DU [128,192)
 #define GDN_PSTAMP(slot)
 #endif
 
-__global__ void __launch_bounds__(kPrepThreads)
+__global__ void __launch_bounds__(kPrepThreads, 2)
 prepare_umma_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                     const __grid_constant__ CUtensorMap tm_v, Inputs in, Geometry geo, Workspace ws) {
   extern __shared__ uint8_t raw_smem[];
@@ -215,63 +221,66 @@ prepare_umma_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
   GDN_PSTAMP(2);
 
   // ---- phase 3: masks and decays on D1, scaled query rows
+  // warp -> TMEM lane quarter (warp & 3) and column half (warp >> 2) of the 64 columns
+  const int quarter = warp & 3, chalf = warp >> 2;
+  const int lrow = quarter * 32 + (tid & 31);          // accumulator row owned by this thread
+  const uint32_t taddr = tmem + (uint32_t(quarter * 32) << 16);
   if (ok) {
-    const uint32_t taddr = tmem + (uint32_t(warp * 32) << 16);
-    const int i = tid & 63;
+    const int i = lrow & 63, j0 = chalf * 32;
     const float pi = s_pl2[i];
-    if (tid < 64) {
-      __nv_bfloat16* prow = ws.p + (block * kChunk + i) * kChunk;
+    uint32_t d[32];
+    tmem_ld32(taddr + j0, d);
+    float pj[32];
 #pragma unroll
-      for (int cg = 0; cg < 4; ++cg) {
-        uint32_t d[16];
-        tmem_ld16(taddr + cg * 16, d);
-        tmem_wait_ld();
-        uint32_t packed[8];
+    for (int q4 = 0; q4 < 8; ++q4) {
+      const float4 t = *reinterpret_cast<const float4*>(s_pl2 + j0 + q4 * 4);
+      pj[q4 * 4] = t.x; pj[q4 * 4 + 1] = t.y; pj[q4 * 4 + 2] = t.z; pj[q4 * 4 + 3] = t.w;
+    }
+    tmem_wait_ld();
+    if (lrow < 64) {
+      uint32_t packed[16];
 #pragma unroll
-        for (int jj = 0; jj < 16; jj += 2) {
-          const int j = cg * 16 + jj;
-          const float a0 = (j <= i) ? __uint_as_float(d[jj]) * exp2f(pi - s_pl2[j]) * kScale : 0.f;
-          const float a1 = (j + 1 <= i) ? __uint_as_float(d[jj + 1]) * exp2f(pi - s_pl2[j + 1]) * kScale : 0.f;
-          packed[jj >> 1] = pack_bf16(a0, a1);
-        }
-        uint4* dst = reinterpret_cast<uint4*>(prow + cg * 16);
-        dst[0] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
-        dst[1] = make_uint4(packed[4], packed[5], packed[6], packed[7]);
+      for (int jj = 0; jj < 32; jj += 2) {
+        const int j = j0 + jj;
+        const float a0 = (j <= i) ? __uint_as_float(d[jj]) * fast_exp2(pi - pj[jj]) * kScale : 0.f;
+        const float a1 = (j + 1 <= i) ? __uint_as_float(d[jj + 1]) * fast_exp2(pi - pj[jj + 1]) * kScale : 0.f;
+        packed[jj >> 1] = pack_bf16(a0, a1);
       }
+      uint4* dst = reinterpret_cast<uint4*>(ws.p + (block * kChunk + i) * kChunk + j0);
+#pragma unroll
+      for (int q4 = 0; q4 < 4; ++q4)
+        dst[q4] = make_uint4(packed[q4 * 4], packed[q4 * 4 + 1], packed[q4 * 4 + 2], packed[q4 * 4 + 3]);
     } else {
       const float bi = s_beta[i];
-      float* arow = sA + i * L::kLd;
+      float* arow = sA + i * L::kLd + j0;
 #pragma unroll
-      for (int cg = 0; cg < 4; ++cg) {
-        uint32_t d[16];
-        tmem_ld16(taddr + cg * 16, d);
-        tmem_wait_ld();
-        float a[16];
+      for (int q4 = 0; q4 < 8; ++q4) {
+        float a[4];
 #pragma unroll
-        for (int jj = 0; jj < 16; ++jj) {
-          const int j = cg * 16 + jj;
-          a[jj] = (j < i) ? bi * __uint_as_float(d[jj]) * exp2f(pi - s_pl2[j]) : 0.f;
+        for (int e = 0; e < 4; ++e) {
+          const int jj = q4 * 4 + e;
+          a[e] = (j0 + jj < i) ? bi * __uint_as_float(d[jj]) * fast_exp2(pi - pj[jj]) : 0.f;
         }
-#pragma unroll
-        for (int q4 = 0; q4 < 4; ++q4)
-          *reinterpret_cast<float4*>(arow + cg * 16 + q4 * 4) =
-              make_float4(a[q4 * 4], a[q4 * 4 + 1], a[q4 * 4 + 2], a[q4 * 4 + 3]);
+        *reinterpret_cast<float4*>(arow + q4 * 4) = make_float4(a[0], a[1], a[2], a[3]);
       }
     }
     {
-      // scaled query: row = tid/2, one 64-wide half (= one TMA box row) per thread
-      const int row = tid >> 1, half = tid & 1;
+      // scaled query: row = tid/4, a quarter row (4 x 16 bytes of one TMA box row) per thread
+      const int row = tid >> 2, half = (tid >> 1) & 1, sub = tid & 1;
       const float qs = s_qscale[row];
       const uint8_t* src = sm + (half ? L::kQ1 : L::kQ0) + row * 128;
-      __nv_bfloat16* dst = ws.qs + (block * kChunk + row) * kDim + half * 64;
+      __nv_bfloat16* dst = ws.qs + (block * kChunk + row) * kDim + half * 64 + sub * 32;
+      uint4 v[4];
 #pragma unroll
-      for (int cc = 0; cc < 8; ++cc) {
-        const uint4 v = *reinterpret_cast<const uint4*>(src + ((cc ^ (row & 7)) << 4));
+      for (int cc = 0; cc < 4; ++cc)
+        v[cc] = *reinterpret_cast<const uint4*>(src + (((sub * 4 + cc) ^ (row & 7)) << 4));
+#pragma unroll
+      for (int cc = 0; cc < 4; ++cc) {
         uint4 o;
-        o.x = pack_bf16(bf16_lo(v.x) * qs, bf16_hi(v.x) * qs);
-        o.y = pack_bf16(bf16_lo(v.y) * qs, bf16_hi(v.y) * qs);
-        o.z = pack_bf16(bf16_lo(v.z) * qs, bf16_hi(v.z) * qs);
-        o.w = pack_bf16(bf16_lo(v.w) * qs, bf16_hi(v.w) * qs);
+        o.x = pack_bf16(bf16_lo(v[cc].x) * qs, bf16_hi(v[cc].x) * qs);
+        o.y = pack_bf16(bf16_lo(v[cc].y) * qs, bf16_hi(v[cc].y) * qs);
+        o.z = pack_bf16(bf16_lo(v[cc].z) * qs, bf16_hi(v[cc].z) * qs);
+        o.w = pack_bf16(bf16_lo(v[cc].w) * qs, bf16_hi(v[cc].w) * qs);
         *reinterpret_cast<uint4*>(dst + cc * 8) = o;
       }
     }
@@ -287,18 +296,25 @@ prepare_umma_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
     const int blk = tid >> 4, c = tid & 15;
     const float* a0 = sA + (blk * 16) * L::kLd + blk * 16;
     float x[16];
+    float4 cur[4], nxt[4] = {};
 #pragma unroll
     for (int i = 0; i < 16; ++i) {
+      // fetch the next row's lower-triangle part before the dependent FMA chain of this row
+#pragma unroll
+      for (int j4 = 0; j4 < i + 1 && i + 1 < 16; j4 += 4)
+        nxt[j4 >> 2] = *reinterpret_cast<const float4*>(a0 + (i + 1) * L::kLd + j4);
       float acc0 = (i == c) ? 1.f : 0.f, acc1 = 0.f;
 #pragma unroll
       for (int j4 = 0; j4 < i; j4 += 4) {
-        const float4 a = *reinterpret_cast<const float4*>(a0 + i * L::kLd + j4);
+        const float4 a = cur[j4 >> 2];
         if (j4 + 0 < i) acc0 = fmaf(-a.x, x[j4 + 0], acc0);
         if (j4 + 1 < i) acc1 = fmaf(-a.y, x[j4 + 1], acc1);
         if (j4 + 2 < i) acc0 = fmaf(-a.z, x[j4 + 2], acc0);
         if (j4 + 3 < i) acc1 = fmaf(-a.w, x[j4 + 3], acc1);
       }
       x[i] = acc0 + acc1;
+#pragma unroll
+      for (int q = 0; q < 4; ++q) cur[q] = nxt[q];
     }
     float* t0 = sT + (blk * 16) * L::kLd + blk * 16 + c;
 #pragma unroll
@@ -306,103 +322,131 @@ prepare_umma_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
   }
   __syncthreads();
   GDN_PSTAMP(7);
-  // level 2: inside each 32x32 diagonal block, T21 = -T22 (A21 T11) with 16x16 blocks
+  // level 2: inside each 32x32 diagonal block, T21 = -T22 (A21 T11) with 16x16 blocks;
+  // thread -> (block, row i, column pair)
   {
-    const int big = tid >> 6, i = (tid & 63) >> 2, cg = tid & 3;
+    const int big = tid >> 7, i = (tid & 127) >> 3, cg = tid & 7;
     const int o = big * 32;
-    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    float a[16];
+    float2 acc = make_float2(0.f, 0.f);
     if (ok) {
       const float* arow = sA + (o + 16 + i) * L::kLd + o;
+      float2 t[16];
+#pragma unroll
+      for (int q4 = 0; q4 < 4; ++q4) {
+        const float4 v = *reinterpret_cast<const float4*>(arow + q4 * 4);
+        a[q4 * 4] = v.x; a[q4 * 4 + 1] = v.y; a[q4 * 4 + 2] = v.z; a[q4 * 4 + 3] = v.w;
+      }
+#pragma unroll
+      for (int k = 0; k < 16; ++k) t[k] = *reinterpret_cast<const float2*>(sT + (o + k) * L::kLd + o + cg * 2);
 #pragma unroll
       for (int k = 0; k < 16; ++k) {
-        const float a = arow[k];
-        const float4 t = *reinterpret_cast<const float4*>(sT + (o + k) * L::kLd + o + cg * 4);
-        acc.x = fmaf(a, t.x, acc.x); acc.y = fmaf(a, t.y, acc.y);
-        acc.z = fmaf(a, t.z, acc.z); acc.w = fmaf(a, t.w, acc.w);
+        acc.x = fmaf(a[k], t[k].x, acc.x);
+        acc.y = fmaf(a[k], t[k].y, acc.y);
       }
-      *reinterpret_cast<float4*>(sX + (big * 16 + i) * L::kLdX + cg * 4) = acc;
+      *reinterpret_cast<float2*>(sX + (big * 16 + i) * L::kLdX + cg * 2) = acc;
     }
     __syncthreads();
     if (ok) {
-      acc = make_float4(0.f, 0.f, 0.f, 0.f);
       const float* trow = sT + (o + 16 + i) * L::kLd + o + 16;
+      float2 t[16];
+#pragma unroll
+      for (int q4 = 0; q4 < 4; ++q4) {
+        const float4 v = *reinterpret_cast<const float4*>(trow + q4 * 4);
+        a[q4 * 4] = v.x; a[q4 * 4 + 1] = v.y; a[q4 * 4 + 2] = v.z; a[q4 * 4 + 3] = v.w;
+      }
+#pragma unroll
+      for (int k = 0; k < 16; ++k) t[k] = *reinterpret_cast<const float2*>(sX + (big * 16 + k) * L::kLdX + cg * 2);
+      acc = make_float2(0.f, 0.f);
 #pragma unroll
       for (int k = 0; k < 16; ++k) {
-        const float a = trow[k];
-        const float4 t = *reinterpret_cast<const float4*>(sX + (big * 16 + k) * L::kLdX + cg * 4);
-        acc.x = fmaf(a, t.x, acc.x); acc.y = fmaf(a, t.y, acc.y);
-        acc.z = fmaf(a, t.z, acc.z); acc.w = fmaf(a, t.w, acc.w);
+        acc.x = fmaf(a[k], t[k].x, acc.x);
+        acc.y = fmaf(a[k], t[k].y, acc.y);
       }
-      *reinterpret_cast<float4*>(sT + (o + 16 + i) * L::kLd + o + cg * 4) =
-          make_float4(-acc.x, -acc.y, -acc.z, -acc.w);
+      *reinterpret_cast<float2*>(sT + (o + 16 + i) * L::kLd + o + cg * 2) = make_float2(-acc.x, -acc.y);
     }
   }
   __syncthreads();
   GDN_PSTAMP(8);
-  // level 3: T21 = -T22 (A21 T11) with 32x32 blocks; thread -> row i, eight columns
+  // level 3: T21 = -T22 (A21 T11) with 32x32 blocks; thread -> row i, four columns
   {
-    const int i = tid >> 2, cg = tid & 3;
-    float acc[8];
+    const int i = tid >> 3, cg = tid & 7;
+    float a[32];
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
     if (ok) {
-#pragma unroll
-      for (int e = 0; e < 8; ++e) acc[e] = 0.f;
       const float* arow = sA + (32 + i) * L::kLd;
-#pragma unroll 8
-      for (int k = 0; k < 32; ++k) {
-        const float a = arow[k];
-        const float4 t0 = *reinterpret_cast<const float4*>(sT + k * L::kLd + cg * 8);
-        const float4 t1 = *reinterpret_cast<const float4*>(sT + k * L::kLd + cg * 8 + 4);
-        acc[0] = fmaf(a, t0.x, acc[0]); acc[1] = fmaf(a, t0.y, acc[1]);
-        acc[2] = fmaf(a, t0.z, acc[2]); acc[3] = fmaf(a, t0.w, acc[3]);
-        acc[4] = fmaf(a, t1.x, acc[4]); acc[5] = fmaf(a, t1.y, acc[5]);
-        acc[6] = fmaf(a, t1.z, acc[6]); acc[7] = fmaf(a, t1.w, acc[7]);
+#pragma unroll
+      for (int q4 = 0; q4 < 8; ++q4) {
+        const float4 v = *reinterpret_cast<const float4*>(arow + q4 * 4);
+        a[q4 * 4] = v.x; a[q4 * 4 + 1] = v.y; a[q4 * 4 + 2] = v.z; a[q4 * 4 + 3] = v.w;
       }
-      float* xrow = sX + i * L::kLdX3 + cg * 8;
-      *reinterpret_cast<float4*>(xrow) = make_float4(acc[0], acc[1], acc[2], acc[3]);
-      *reinterpret_cast<float4*>(xrow + 4) = make_float4(acc[4], acc[5], acc[6], acc[7]);
+#pragma unroll
+      for (int k0 = 0; k0 < 32; k0 += 8) {
+        float4 t[8];
+#pragma unroll
+        for (int k = 0; k < 8; ++k) t[k] = *reinterpret_cast<const float4*>(sT + (k0 + k) * L::kLd + cg * 4);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+          acc.x = fmaf(a[k0 + k], t[k].x, acc.x); acc.y = fmaf(a[k0 + k], t[k].y, acc.y);
+          acc.z = fmaf(a[k0 + k], t[k].z, acc.z); acc.w = fmaf(a[k0 + k], t[k].w, acc.w);
+        }
+      }
+      *reinterpret_cast<float4*>(sX + i * L::kLdX3 + cg * 4) = acc;
     }
     __syncthreads();
     if (ok) {
-#pragma unroll
-      for (int e = 0; e < 8; ++e) acc[e] = 0.f;
       const float* trow = sT + (32 + i) * L::kLd + 32;
-#pragma unroll 8
-      for (int k = 0; k < 32; ++k) {
-        const float a = trow[k];
-        const float4 t0 = *reinterpret_cast<const float4*>(sX + k * L::kLdX3 + cg * 8);
-        const float4 t1 = *reinterpret_cast<const float4*>(sX + k * L::kLdX3 + cg * 8 + 4);
-        acc[0] = fmaf(a, t0.x, acc[0]); acc[1] = fmaf(a, t0.y, acc[1]);
-        acc[2] = fmaf(a, t0.z, acc[2]); acc[3] = fmaf(a, t0.w, acc[3]);
-        acc[4] = fmaf(a, t1.x, acc[4]); acc[5] = fmaf(a, t1.y, acc[5]);
-        acc[6] = fmaf(a, t1.z, acc[6]); acc[7] = fmaf(a, t1.w, acc[7]);
+#pragma unroll
+      for (int q4 = 0; q4 < 8; ++q4) {
+        const float4 v = *reinterpret_cast<const float4*>(trow + q4 * 4);
+        a[q4 * 4] = v.x; a[q4 * 4 + 1] = v.y; a[q4 * 4 + 2] = v.z; a[q4 * 4 + 3] = v.w;
       }
-      float* trow_out = sT + (32 + i) * L::kLd + cg * 8;
-      *reinterpret_cast<float4*>(trow_out) = make_float4(-acc[0], -acc[1], -acc[2], -acc[3]);
-      *reinterpret_cast<float4*>(trow_out + 4) = make_float4(-acc[4], -acc[5], -acc[6], -acc[7]);
+      acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+      for (int k0 = 0; k0 < 32; k0 += 8) {
+        float4 t[8];
+#pragma unroll
+        for (int k = 0; k < 8; ++k) t[k] = *reinterpret_cast<const float4*>(sX + (k0 + k) * L::kLdX3 + cg * 4);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+          acc.x = fmaf(a[k0 + k], t[k].x, acc.x); acc.y = fmaf(a[k0 + k], t[k].y, acc.y);
+          acc.z = fmaf(a[k0 + k], t[k].z, acc.z); acc.w = fmaf(a[k0 + k], t[k].w, acc.w);
+        }
+      }
+      *reinterpret_cast<float4*>(sT + (32 + i) * L::kLd + cg * 4) = make_float4(-acc.x, -acc.y, -acc.z, -acc.w);
     }
   }
   __syncthreads();
   GDN_PSTAMP(9);
-  // T diag(beta exp p) and T diag(beta) as BF16 hi/lo K-major tiles (these overwrite the A matrix)
+  // T diag(beta exp p) and T diag(beta) as BF16 hi/lo K-major tiles (these overwrite the A matrix);
+  // thread -> row i, sixteen columns
   if (ok) {
-    const int i = tid >> 1, c0 = (tid & 1) * 32;
+    const int i = tid >> 2, c0 = (tid & 3) * 16;
+    float t[16], cw[16], cu[16];
 #pragma unroll
-    for (int g8 = 0; g8 < 4; ++g8) {
-      const int c = c0 + g8 * 8;
-      const float4 ta = *reinterpret_cast<const float4*>(sT + i * L::kLd + c);
-      const float4 tb = *reinterpret_cast<const float4*>(sT + i * L::kLd + c + 4);
-      const float t[8] = {ta.x, ta.y, ta.z, ta.w, tb.x, tb.y, tb.z, tb.w};
+    for (int q4 = 0; q4 < 4; ++q4) {
+      const float4 tv = *reinterpret_cast<const float4*>(sT + i * L::kLd + c0 + q4 * 4);
+      const float4 wv = *reinterpret_cast<const float4*>(s_coefw + c0 + q4 * 4);
+      const float4 uv = *reinterpret_cast<const float4*>(s_beta + c0 + q4 * 4);
+      t[q4 * 4] = tv.x; t[q4 * 4 + 1] = tv.y; t[q4 * 4 + 2] = tv.z; t[q4 * 4 + 3] = tv.w;
+      cw[q4 * 4] = wv.x; cw[q4 * 4 + 1] = wv.y; cw[q4 * 4 + 2] = wv.z; cw[q4 * 4 + 3] = wv.w;
+      cu[q4 * 4] = uv.x; cu[q4 * 4 + 1] = uv.y; cu[q4 * 4 + 2] = uv.z; cu[q4 * 4 + 3] = uv.w;
+    }
+#pragma unroll
+    for (int g8 = 0; g8 < 2; ++g8) {
       uint32_t wh[4], wl[4], uh[4], ul[4];
 #pragma unroll
       for (int e = 0; e < 8; e += 2) {
-        const float w0 = t[e] * s_coefw[c + e], w1 = t[e + 1] * s_coefw[c + e + 1];
-        const float u0 = t[e] * s_beta[c + e], u1 = t[e + 1] * s_beta[c + e + 1];
+        const int x = g8 * 8 + e;
+        const float w0 = t[x] * cw[x], w1 = t[x + 1] * cw[x + 1];
+        const float u0 = t[x] * cu[x], u1 = t[x + 1] * cu[x + 1];
         const uint32_t hw = pack_bf16(w0, w1), hu = pack_bf16(u0, u1);
         wh[e >> 1] = hw;
         wl[e >> 1] = pack_bf16(w0 - bf16_lo(hw), w1 - bf16_hi(hw));
         uh[e >> 1] = hu;
         ul[e >> 1] = pack_bf16(u0 - bf16_lo(hu), u1 - bf16_hi(hu));
       }
+      const int c = c0 + g8 * 8;
       const int off = i * 128 + (((c >> 3) ^ (i & 7)) << 4);
       *reinterpret_cast<uint4*>(sm + L::kTwH + off) = make_uint4(wh[0], wh[1], wh[2], wh[3]);
       *reinterpret_cast<uint4*>(sm + L::kTwL + off) = make_uint4(wl[0], wl[1], wl[2], wl[3]);
@@ -442,36 +486,28 @@ prepare_umma_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
   tc_fence_after();
   GDN_PSTAMP(5);
 
-  // ---- phase 6: write W (hi/lo), U, gate vector
+  // ---- phase 6: write W (hi/lo), U, gate vector; thread -> accumulator row, 32 of the 64 token columns
   if (ok) {
-    const uint32_t taddr = tmem + (uint32_t(warp * 32) << 16);
-    __nv_bfloat16* whi = ws.w_hi + block * kChunk * kDim + tid;
-    __nv_bfloat16* wlo = ws.w_lo + block * kChunk * kDim + tid;
-    float* up = ws.u + block * kChunk * kDim + tid;
+    const int tk0 = chalf * 32;
+    __nv_bfloat16* whi = ws.w_hi + (block * kChunk + tk0) * kDim + lrow;
+    __nv_bfloat16* wlo = ws.w_lo + (block * kChunk + tk0) * kDim + lrow;
+    float* up = ws.u + (block * kChunk + tk0) * kDim + lrow;
+    uint32_t dw[32], du[32];
+    tmem_ld32(taddr + 64 + tk0, dw);
+    tmem_ld32(taddr + 128 + tk0, du);
+    tmem_wait_ld();
 #pragma unroll
-    for (int cg = 0; cg < 4; ++cg) {
-      uint32_t d[16];
-      tmem_ld16(taddr + 64 + cg * 16, d);
-      tmem_wait_ld();
-#pragma unroll
-      for (int jj = 0; jj < 16; ++jj) {
-        __nv_bfloat16 hi, lo;
-        split_bf16(__uint_as_float(d[jj]), hi, lo);
-        whi[(cg * 16 + jj) * kDim] = hi;
-        wlo[(cg * 16 + jj) * kDim] = lo;
-      }
+    for (int jj = 0; jj < 32; ++jj) {
+      __nv_bfloat16 hi, lo;
+      split_bf16(__uint_as_float(dw[jj]), hi, lo);
+      whi[jj * kDim] = hi;
+      wlo[jj * kDim] = lo;
     }
 #pragma unroll
-    for (int cg = 0; cg < 4; ++cg) {
-      uint32_t d[16];
-      tmem_ld16(taddr + 128 + cg * 16, d);
-      tmem_wait_ld();
-#pragma unroll
-      for (int jj = 0; jj < 16; ++jj) up[(cg * 16 + jj) * kDim] = __uint_as_float(d[jj]);
-    }
+    for (int jj = 0; jj < 32; ++jj) up[jj * kDim] = __uint_as_float(du[jj]);
     const float last = s_pl2[valid - 1];
-    if (tid < kChunk) ws.gates[block * 128 + tid] = (tid < valid) ? exp2f(last - s_pl2[tid]) : 0.f;
-    if (tid == kChunk) ws.gates[block * 128 + kChunk] = exp2f(last);
+    if (tid < kChunk) ws.gates[block * 128 + tid] = (tid < valid) ? fast_exp2(last - s_pl2[tid]) : 0.f;
+    if (tid == kChunk) ws.gates[block * 128 + kChunk] = fast_exp2(last);
   }
   GDN_PSTAMP(6);
   if (!ok) {
