@@ -57,6 +57,18 @@ int TensorMapEncoder::bf16_4d(CUtensorMap* map, const void* base, uint64_t d0, u
   return r == CUDA_SUCCESS ? 0 : int(cudaErrorInvalidValue);
 }
 
+int TensorMapEncoder::f32_2d(CUtensorMap* map, const void* base, uint64_t cols, uint64_t rows,
+                             uint32_t box_rows) const {
+  const cuuint64_t dims[2] = {cols, rows};
+  const cuuint64_t strides[1] = {cols * 4};
+  const cuuint32_t box[2] = {32, box_rows};
+  const cuuint32_t elem[2] = {1, 1};
+  CUresult r = encode(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<void*>(base), dims, strides, box,
+                      elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+                      CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : int(cudaErrorInvalidValue);
+}
+
 TensorMapEncoder& tensor_map_encoder() {
   static TensorMapEncoder encoder;
   return encoder;
@@ -69,10 +81,6 @@ constexpr int kBox = 8192;            // one TMA box: 64 rows x 128 bytes
 constexpr uint32_t kIdescN64 = idesc_bf16(128, 64, false, false);      // A K-major (smem or TMEM), B K-major
 constexpr uint32_t kIdescN64AT = idesc_bf16(128, 64, true, false);     // A MN-major (transposed smem tile)
 constexpr uint32_t kIdescN128BT = idesc_bf16(128, 128, false, true);   // B MN-major
-
-__device__ __forceinline__ uint8_t* align1024(uint8_t* p) {
-  return reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(p) + 1023) & ~uintptr_t(1023));
-}
 
 __device__ __forceinline__ float fast_exp2(float x) {
   float y;
@@ -99,7 +107,7 @@ __device__ __forceinline__ int swizzled_offset(int row, int col) {
 //            tests/wy_cpu.py:21-41, with plain FP32 products instead of TF32x3)
 //            T diag(beta exp(p)) and T diag(beta) -> BF16 hi/lo K-major tiles in shared memory
 //   phase 5  W^T = K^T (T diag(beta exp p))^T,  U^T = V^T (T diag(beta))^T   (A = transposed K / V tiles)
-//   phase 6  accumulators -> W hi/lo BF16, U FP32, gate vector -> workspace
+//   phase 6  accumulators -> W hi/lo BF16, U FP32 staged in shared memory, TMA stores; gate vector -> workspace
 struct PrepLayout {
   static constexpr int kQ0 = 0, kK0 = kBox, kQ1 = 2 * kBox, kK1 = 3 * kBox;   // [Q;K] stacked, two K atoms
   static constexpr int kV0 = 4 * kBox, kV1 = 5 * kBox;
@@ -127,9 +135,12 @@ constexpr int kPrepTmemCols = 256;   // D1 [0,64)  DW [64,128)  DU [128,192)
 
 __global__ void __launch_bounds__(kPrepThreads, 2)
 prepare_umma_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
-                    const __grid_constant__ CUtensorMap tm_v, Inputs in, Geometry geo, Workspace ws) {
-  extern __shared__ uint8_t raw_smem[];
-  uint8_t* sm = align1024(raw_smem);
+                    const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_wh,
+                    const __grid_constant__ CUtensorMap tm_wl, const __grid_constant__ CUtensorMap tm_u,
+                    Inputs in, Geometry geo, Workspace ws) {
+  // Indexing the declared array (no integer round trip) keeps these accesses in the shared state space.
+  extern __shared__ __align__(1024) uint8_t raw_smem[];
+  uint8_t* sm = raw_smem + ((1024u - (smem_u32(raw_smem) & 1023u)) & 1023u);
   using L = PrepLayout;
   float* sA = reinterpret_cast<float*>(sm + L::kA);
   float* sT = reinterpret_cast<float*>(sm + L::kT);
@@ -486,28 +497,45 @@ prepare_umma_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
   tc_fence_after();
   GDN_PSTAMP(5);
 
-  // ---- phase 6: write W (hi/lo), U, gate vector; thread -> accumulator row, 32 of the 64 token columns
+  // ---- phase 6: W (hi/lo) and U leave through shared memory and TMA stores; every input tile is dead
+  // by now, so the staging boxes reuse their space: W hi [0,16K), W lo [16K,32K), U [32K,64K).
   if (ok) {
     const int tk0 = chalf * 32;
-    __nv_bfloat16* whi = ws.w_hi + (block * kChunk + tk0) * kDim + lrow;
-    __nv_bfloat16* wlo = ws.w_lo + (block * kChunk + tk0) * kDim + lrow;
-    float* up = ws.u + (block * kChunk + tk0) * kDim + lrow;
     uint32_t dw[32], du[32];
     tmem_ld32(taddr + 64 + tk0, dw);
     tmem_ld32(taddr + 128 + tk0, du);
     tmem_wait_ld();
+    // lrow is the key (W) / value (U) index; W boxes are 128-byte swizzled [token][64 BF16], U boxes dense
+    // [token][32 FP32]
+    uint8_t* wbox = sm + (lrow >> 6) * kBox + ((lrow & 7) << 1);
+    const int wchunk = (lrow & 63) >> 3;
+    float* ubox = reinterpret_cast<float*>(sm + 4 * kBox + (lrow >> 5) * kBox) + (lrow & 31);
 #pragma unroll
     for (int jj = 0; jj < 32; ++jj) {
+      const int tok = tk0 + jj;
       __nv_bfloat16 hi, lo;
       split_bf16(__uint_as_float(dw[jj]), hi, lo);
-      whi[jj * kDim] = hi;
-      wlo[jj * kDim] = lo;
+      const int off = tok * 128 + ((wchunk ^ (tok & 7)) << 4);
+      *reinterpret_cast<__nv_bfloat16*>(wbox + off) = hi;
+      *reinterpret_cast<__nv_bfloat16*>(wbox + 2 * kBox + off) = lo;
+      ubox[tok * 32] = __uint_as_float(du[jj]);
     }
-#pragma unroll
-    for (int jj = 0; jj < 32; ++jj) up[jj * kDim] = __uint_as_float(du[jj]);
+    fence_proxy_async_smem();
     const float last = s_pl2[valid - 1];
     if (tid < kChunk) ws.gates[block * 128 + tid] = (tid < valid) ? fast_exp2(last - s_pl2[tid]) : 0.f;
     if (tid == kChunk) ws.gates[block * 128 + kChunk] = fast_exp2(last);
+  }
+  __syncthreads();
+  if (tid == 0 && ok) {
+    const int row = int(block * kChunk);
+    tma_store_2d(&tm_wh, sm, 0, row);
+    tma_store_2d(&tm_wh, sm + kBox, 64, row);
+    tma_store_2d(&tm_wl, sm + 2 * kBox, 0, row);
+    tma_store_2d(&tm_wl, sm + 3 * kBox, 64, row);
+#pragma unroll
+    for (int part = 0; part < 4; ++part) tma_store_2d(&tm_u, sm + (4 + part) * kBox, part * 32, row);
+    tma_store_commit();
+    tma_store_wait_read();
   }
   GDN_PSTAMP(6);
   if (!ok) {
@@ -559,8 +587,9 @@ __global__ void __launch_bounds__(kWalkThreads, 1)
 walk_umma_kernel(const __grid_constant__ CUtensorMap tm_wh, const __grid_constant__ CUtensorMap tm_wl,
                  const __grid_constant__ CUtensorMap tm_qs, const __grid_constant__ CUtensorMap tm_k,
                  const __grid_constant__ CUtensorMap tm_p, Inputs in, Geometry geo, Workspace ws) {
-  extern __shared__ uint8_t raw_smem[];
-  uint8_t* sm = align1024(raw_smem);
+  // Indexing the declared array (no integer round trip) keeps these accesses in the shared state space.
+  extern __shared__ __align__(1024) uint8_t raw_smem[];
+  uint8_t* sm = raw_smem + ((1024u - (smem_u32(raw_smem) & 1023u)) & 1023u);
   using L = WalkLayout;
   uint64_t* bars = reinterpret_cast<uint64_t*>(sm + L::kBars);
   uint64_t* full = bars;                       // [kStages]
@@ -853,11 +882,16 @@ int configure_umma() {
 int launch_prepare_umma(const Inputs& in, const Geometry& geo, const Workspace& ws, cudaStream_t stream) {
   TensorMapEncoder& enc = tensor_map_encoder();
   if (int rc = enc.init()) return rc;
-  CUtensorMap tm_q, tm_k, tm_v;
+  CUtensorMap tm_q, tm_k, tm_v, tm_wh, tm_wl, tm_u;
+  const uint64_t rows = uint64_t(geo.blocks()) * kChunk;
   if (int rc = enc.bf16_4d(&tm_q, in.q, kDim, geo.key_heads, geo.sequence, geo.batch, kChunk)) return rc;
   if (int rc = enc.bf16_4d(&tm_k, in.k, kDim, geo.key_heads, geo.sequence, geo.batch, kChunk)) return rc;
   if (int rc = enc.bf16_4d(&tm_v, in.v, kDim, geo.value_heads, geo.sequence, geo.batch, kChunk)) return rc;
-  prepare_umma_kernel<<<(unsigned)geo.blocks(), kPrepThreads, kPrepSmem, stream>>>(tm_q, tm_k, tm_v, in, geo, ws);
+  if (int rc = enc.bf16_2d(&tm_wh, ws.w_hi, kDim, rows, kChunk)) return rc;
+  if (int rc = enc.bf16_2d(&tm_wl, ws.w_lo, kDim, rows, kChunk)) return rc;
+  if (int rc = enc.f32_2d(&tm_u, ws.u, kDim, rows, kChunk)) return rc;
+  prepare_umma_kernel<<<(unsigned)geo.blocks(), kPrepThreads, kPrepSmem, stream>>>(tm_q, tm_k, tm_v, tm_wh, tm_wl,
+                                                                                  tm_u, in, geo, ws);
   return int(cudaGetLastError());
 }
 

@@ -102,6 +102,17 @@ __device__ __forceinline__ void bulk_load(void* dst, const void* src, uint32_t b
       ::"r"(smem_u32(dst)), "l"(src), "r"(bytes), "r"(smem_u32(bar))
       : "memory");
 }
+// TMA store shared -> global of one box; the issuing thread later commits and waits on the group.
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, const void* src, int x, int y) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
+               ::"l"(map), "r"(smem_u32(src)), "r"(x), "r"(y)
+               : "memory");
+}
+__device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// all committed stores of this thread have finished READING shared memory
+__device__ __forceinline__ void tma_store_wait_read() {
+  asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+}
 __device__ __forceinline__ void prefetch_tensormap(const CUtensorMap* map) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory");
 }
@@ -233,6 +244,8 @@ struct TensorMapEncoder {
   int bf16_2d(CUtensorMap* map, const void* base, uint64_t cols, uint64_t rows, uint32_t box_rows) const;
   int bf16_4d(CUtensorMap* map, const void* base, uint64_t d0, uint64_t d1, uint64_t d2, uint64_t d3,
               uint32_t box_rows_d2) const;
+  // FP32 matrix, box = 32 columns (128 bytes) x box_rows, no swizzle (dense box in shared memory)
+  int f32_2d(CUtensorMap* map, const void* base, uint64_t cols, uint64_t rows, uint32_t box_rows) const;
 };
 TensorMapEncoder& tensor_map_encoder();
 
