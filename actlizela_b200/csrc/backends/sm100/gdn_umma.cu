@@ -549,44 +549,58 @@ prepare_umma_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
 
 // ==================================================================================== walk kernel
 // One CTA per (batch, value head), 448 threads, one CTA per SM.  Tensor memory (512 columns):
-//   ACC_S  [  0,128)  St FP32 accumulator (pre-scaled by the chunk decay before the update MMA)
-//   OP_SH  [128,192)  St BF16 hi, packed pairs (A operand of W S and Q S)
-//   OP_SL  [192,256)  St BF16 lo
-//   ACC_WS [256,320)  (W S)^T FP32
-//   OP_NH  [320,352)  (N*rel)^T BF16 hi      OP_NL [352,384) lo      OP_N16 [384,416) N^T BF16
-//   ACC_O  [416,480)  O^T FP32
-// Roles: warps 0-7 state chain; a warp owns the 32 TMEM lanes of quarter (warp & 3) and, of every
-//        tile it touches, the column half (warp >> 2): decay + hi/lo split of St, N = U - W S.
+//   ACC_S [  0,128)  St FP32 accumulator (pre-scaled by the chunk decay before the update MMA)
+//   OP_SH [128,192)  St BF16 hi, packed pairs      OP_SL [192,256)  St BF16 lo
+//   ACC_Y [448,512)  (W_hi S_lo)^T: the low half of the state goes to its own accumulator so that the two
+//                    passes do not wait on each other's accumulate dependency
+//   ACC_X [256,448)  one 192-column product  S_hi^T [W_hi ; W_lo ; Qs]^T :
+//           [256,320) (W_hi S)^T   [320,384) (W_lo S)^T   [384,448) O^T (= ACC_O, later += N^T P^T)
+//         after N = U - W S has been formed, the first 128 columns are reused for the N operands of the
+//         16-token group ks:  (N*rel) hi at 256+16ks, lo at 256+16ks+8,  N (BF16) at 320+16ks
+// A tcgen05.mma with M = 128 occupies the tensor pipe for at least ~64 cycles whatever N is, so the chain
+// uses few, wide instructions: 16 per chunk for W S and Q S together (N = 192 and 128), 8 for the state
+// update (N = 128), 4 for P N.
+// Roles: warps 0-7 state chain; a warp owns the 32 TMEM lanes of quarter (warp & 3) and, of every tile it
+//        touches, the column half (warp >> 2).  Both chain steps are signalled in two halves so that the
+//        MMA issuer starts on the first half of the K range while the second half is still being written.
 //        warps 8-11 output epilogue; warp 12 TMA producer; warp 13 MMA issuer.
 struct WalkLayout {
-  static constexpr int kWH = 0, kWL = 2 * kBox, kQS = 4 * kBox, kK = 6 * kBox, kP = 8 * kBox;
+  // B operand of the wide product: per 64-wide K atom the rows [W_hi | W_lo | Qs] (3 boxes, contiguous)
+  static constexpr int kB0 = 0, kB1 = 3 * kBox;
+  static constexpr int kWH = 0, kWL = kBox, kQS = 2 * kBox;     // box offsets inside an atom
+  static constexpr int kK = 6 * kBox, kP = 8 * kBox;
   static constexpr int kGates = 9 * kBox;
   static constexpr int kStage = 9 * kBox + 1024;
-  static constexpr int kStages = 3;
+  static constexpr int kStages = 2;
   static constexpr int kTxBytes = 9 * kBox + 512;
-  static constexpr int kBars = kStages * kStage;
+  static constexpr int kOut = kStages * kStage;           // two staging tiles [64 tokens][128 values] BF16
+  static constexpr int kBars = kOut + 4 * kBox;
   static constexpr int kTotal = kBars + 256;
 };
 constexpr int kChainWarps = 8, kOutWarp0 = 8, kTmaWarp = 12, kMmaWarp = 13;
-constexpr int kChainThreads = kChainWarps * 32;
 constexpr int kWalkThreads = 448;
 constexpr int kWalkSmem = WalkLayout::kTotal + 1024;
-constexpr uint32_t kAccS = 0, kOpSH = 128, kOpSL = 192, kAccWS = 256, kOpNH = 320, kOpNL = 352, kOpN16 = 384,
-                   kAccO = 416;
+constexpr uint32_t kAccS = 0, kOpSH = 128, kOpSL = 192, kAccX = 256, kAccO = 384, kAccY = 448;
+constexpr uint32_t kIdescN192 = idesc_bf16(128, 192, false, false);
+constexpr uint32_t kIdescN128 = idesc_bf16(128, 128, false, false);
 
 #ifdef GDN_SM100_PHASE_TIMING
 #define GDN_STAMP(slot)                                                                        \
   if (tid == 0) ws.gates[(block0 + c) * 128 + 96 + (slot)] = float((clock64() - t_begin) & 0xffffff)
 #define GDN_MSTAMP(slot) ws.gates[(block0 + c) * 128 + 104 + (slot)] = float((clock64() - t_begin) & 0xffffff)
+#define GDN_OSTAMP(slot)                                                                       \
+  if (tid == kOutWarp0 * 32) ws.gates[(block0 + c) * 128 + 112 + (slot)] = float((clock64() - t_begin) & 0xffffff)
 #else
 #define GDN_STAMP(slot)
 #define GDN_MSTAMP(slot)
+#define GDN_OSTAMP(slot)
 #endif
 
 __global__ void __launch_bounds__(kWalkThreads, 1)
 walk_umma_kernel(const __grid_constant__ CUtensorMap tm_wh, const __grid_constant__ CUtensorMap tm_wl,
                  const __grid_constant__ CUtensorMap tm_qs, const __grid_constant__ CUtensorMap tm_k,
-                 const __grid_constant__ CUtensorMap tm_p, Inputs in, Geometry geo, Workspace ws) {
+                 const __grid_constant__ CUtensorMap tm_p, const __grid_constant__ CUtensorMap tm_out,
+                 Inputs in, Geometry geo, Workspace ws) {
   // Indexing the declared array (no integer round trip) keeps these accesses in the shared state space.
   extern __shared__ __align__(1024) uint8_t raw_smem[];
   uint8_t* sm = raw_smem + ((1024u - (smem_u32(raw_smem) & 1023u)) & 1023u);
@@ -594,13 +608,15 @@ walk_umma_kernel(const __grid_constant__ CUtensorMap tm_wh, const __grid_constan
   uint64_t* bars = reinterpret_cast<uint64_t*>(sm + L::kBars);
   uint64_t* full = bars;                       // [kStages]
   uint64_t* empty = bars + L::kStages;         // [kStages]
-  uint64_t* bar_ops = bars + 2 * L::kStages;   // state operands written (one arrival per chain warp)
-  uint64_t* bar_ws = bar_ops + 1;              // W S product complete
-  uint64_t* bar_opn = bar_ops + 2;             // N operands written (one arrival per chain warp)
-  uint64_t* bar_s = bar_ops + 3;               // state update complete
-  uint64_t* bar_o = bar_ops + 4;               // output accumulator complete
-  uint64_t* bar_ofree = bar_ops + 5;           // output accumulator drained (one arrival per output warp)
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_ops + 6);
+  uint64_t* bar_ops = bars + 2 * L::kStages;   // [2] state operands written, first / second K half
+  uint64_t* bar_opn = bar_ops + 2;             // [2] N operands written, first / second token half
+  uint64_t* bar_ws = bar_ops + 4;              // wide product complete
+  uint64_t* bar_s = bar_ops + 5;               // state update complete
+  uint64_t* bar_o = bar_ops + 6;               // output accumulator complete
+  uint64_t* bar_ofree = bar_ops + 7;           // output accumulator drained (one arrival per output warp)
+  uint64_t* bar_staged = bar_ops + 8;          // output tile staged in shared memory (one arrival per output warp)
+  uint64_t* bar_stfree = bar_ops + 9;          // an older output store has finished reading its staging tile
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_ops + 10);
   volatile int* abort_word = reinterpret_cast<volatile int*>(tmem_slot + 1);
   const AbortFlag abort{abort_word};
 
@@ -620,11 +636,15 @@ walk_umma_kernel(const __grid_constant__ CUtensorMap tm_wh, const __grid_constan
       mbar_init(empty + s, 1);
     }
     mbar_init(bar_ops, kChainWarps);
-    mbar_init(bar_ws, 1);
+    mbar_init(bar_ops + 1, kChainWarps);
     mbar_init(bar_opn, kChainWarps);
+    mbar_init(bar_opn + 1, kChainWarps);
+    mbar_init(bar_ws, 1);
     mbar_init(bar_s, 1);
     mbar_init(bar_o, 1);
     mbar_init(bar_ofree, 4);
+    mbar_init(bar_staged, 4);
+    mbar_init(bar_stfree, 1);
     *abort_word = 0;
     fence_barrier_init();
   }
@@ -686,11 +706,11 @@ walk_umma_kernel(const __grid_constant__ CUtensorMap tm_wh, const __grid_constan
         tmem_st16(taddr + kOpSH + (k0 >> 1), hi);
         tmem_st16(taddr + kOpSL + (k0 >> 1), lo);
         tmem_st32(taddr + kAccS + k0, d);
+        tmem_wait_st();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar_ops + part);
       }
-      tmem_wait_st();
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(bar_ops);
       GDN_STAMP(1);
 
       float u[32];
@@ -701,29 +721,35 @@ walk_umma_kernel(const __grid_constant__ CUtensorMap tm_wh, const __grid_constan
       if (!ok) break;
       tc_fence_after();
       GDN_STAMP(2);
-      {
-        uint32_t d[32], nh[16], nl[16], n16[16];
-        tmem_ld32(taddr + kAccWS + half * 32, d);
+#pragma unroll
+      for (int part = 0; part < 2; ++part) {
+        const int ks = half * 2 + part;                     // 16-token group
+        uint32_t dh[16], dl[16], dy[16], nh[8], nl[8], n16[8];
+        tmem_ld16(taddr + kAccX + ks * 16, dh);
+        tmem_ld16(taddr + kAccX + 64 + ks * 16, dl);
+        tmem_ld16(taddr + kAccY + ks * 16, dy);
         tmem_wait_ld();
 #pragma unroll
-        for (int j = 0; j < 32; j += 2) {
-          const int i = half * 32 + j;
-          const float n0 = u[j] - __uint_as_float(d[j]);
-          const float n1 = u[j + 1] - __uint_as_float(d[j + 1]);
+        for (int j = 0; j < 16; j += 2) {
+          const int i = ks * 16 + j;
+          const float n0 = u[part * 16 + j] -
+                           (__uint_as_float(dh[j]) + (__uint_as_float(dl[j]) + __uint_as_float(dy[j])));
+          const float n1 = u[part * 16 + j + 1] -
+                           (__uint_as_float(dh[j + 1]) + (__uint_as_float(dl[j + 1]) + __uint_as_float(dy[j + 1])));
           const float r0 = n0 * gates[i], r1 = n1 * gates[i + 1];
           const uint32_t h = pack_bf16(r0, r1);
           nh[j >> 1] = h;
           nl[j >> 1] = pack_bf16(r0 - bf16_lo(h), r1 - bf16_hi(h));
           n16[j >> 1] = pack_bf16(n0, n1);
         }
-        tmem_st16(taddr + kOpNH + half * 16, nh);
-        tmem_st16(taddr + kOpNL + half * 16, nl);
-        tmem_st16(taddr + kOpN16 + half * 16, n16);
+        tmem_st8(taddr + kAccX + ks * 16, nh);
+        tmem_st8(taddr + kAccX + ks * 16 + 8, nl);
+        tmem_st8(taddr + kAccX + 64 + ks * 16, n16);
+        tmem_wait_st();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar_opn + part);
       }
-      tmem_wait_st();
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(bar_opn);
       GDN_STAMP(3);
     }
     if (ok) ok = mbar_wait(bar_s, (chunks - 1) & 1, abort, 13, chunks);
@@ -750,6 +776,7 @@ walk_umma_kernel(const __grid_constant__ CUtensorMap tm_wh, const __grid_constan
       ok = mbar_wait(bar_o, c & 1, abort, 20, c);
       if (!ok) break;
       tc_fence_after();
+      GDN_OSTAMP(0);
       uint32_t o[64];
       {
         uint32_t d0[32], d1[32];
@@ -765,14 +792,34 @@ walk_umma_kernel(const __grid_constant__ CUtensorMap tm_wh, const __grid_constan
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(bar_ofree);
-      const int t0 = c * kChunk;
-      const int valid = min(kChunk, geo.sequence - t0);
-      __nv_bfloat16* out = in.output + (((long long)b * geo.sequence + t0) * geo.value_heads + hv) * kDim + v;
-      const long long row = (long long)geo.value_heads * kDim;
+      GDN_OSTAMP(1);
+      // stage the tile as two 128-byte-swizzled boxes [token][64 values] and hand it to a TMA store,
+      // which also clips the rows of a tail chunk at the sequence end
+      uint8_t* stage = sm + L::kOut + (c & 1) * 2 * kBox + (v >> 6) * kBox + ((v & 7) << 1);
+      const int chunk16 = (v & 63) >> 3;
+      // the store that used this buffer two chunks ago has been read out (signalled one chunk ago)
+      if (c > 0) ok = mbar_wait(bar_stfree, (c - 1) & 1, abort, 21, c);
+      if (!ok) break;
 #pragma unroll
       for (int i = 0; i < 64; ++i)
-        if (i < valid) out[i * row] = __float2bfloat16_rn(__uint_as_float(o[i]));
+        *reinterpret_cast<__nv_bfloat16*>(stage + i * 128 + ((chunk16 ^ (i & 7)) << 4)) =
+            __float2bfloat16_rn(__uint_as_float(o[i]));
+      fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar_staged);
+      if (tid == kOutWarp0 * 32) {
+        ok = mbar_wait(bar_staged, c & 1, abort, 22, c);
+        if (!ok) break;
+        const uint8_t* tile = sm + L::kOut + (c & 1) * 2 * kBox;
+        tma_store_4d(&tm_out, tile, 0, hv, c * kChunk, b);
+        tma_store_4d(&tm_out, tile + kBox, 64, hv, c * kChunk, b);
+        tma_store_commit();
+        tma_store_wait_read_keep1();
+        mbar_arrive(bar_stfree);
+      }
+      GDN_OSTAMP(2);
     }
+    if (tid == kOutWarp0 * 32) tma_store_wait_all();
   } else if (warp == kTmaWarp) {
     // ------------------------------------------------------------------ TMA producer
     if (lane == 0) {
@@ -788,12 +835,12 @@ walk_umma_kernel(const __grid_constant__ CUtensorMap tm_wh, const __grid_constan
         const int row = int((block0 + c) * kChunk);
         mbar_arrive_expect_tx(full + s, L::kTxBytes);
         bulk_load(st + L::kGates, ws.gates + (block0 + c) * 128, 512, full + s);
-        tma_load_2d(st + L::kWH, &tm_wh, full + s, 0, row);
-        tma_load_2d(st + L::kWH + kBox, &tm_wh, full + s, 64, row);
-        tma_load_2d(st + L::kWL, &tm_wl, full + s, 0, row);
-        tma_load_2d(st + L::kWL + kBox, &tm_wl, full + s, 64, row);
-        tma_load_2d(st + L::kQS, &tm_qs, full + s, 0, row);
-        tma_load_2d(st + L::kQS + kBox, &tm_qs, full + s, 64, row);
+        tma_load_2d(st + L::kB0 + L::kWH, &tm_wh, full + s, 0, row);
+        tma_load_2d(st + L::kB1 + L::kWH, &tm_wh, full + s, 64, row);
+        tma_load_2d(st + L::kB0 + L::kWL, &tm_wl, full + s, 0, row);
+        tma_load_2d(st + L::kB1 + L::kWL, &tm_wl, full + s, 64, row);
+        tma_load_2d(st + L::kB0 + L::kQS, &tm_qs, full + s, 0, row);
+        tma_load_2d(st + L::kB1 + L::kQS, &tm_qs, full + s, 64, row);
         tma_load_4d(st + L::kK, &tm_k, full + s, 0, hk, c * kChunk, b);
         tma_load_4d(st + L::kK + kBox, &tm_k, full + s, 64, hk, c * kChunk, b);
         tma_load_2d(st + L::kP, &tm_p, full + s, 0, row);
@@ -804,53 +851,62 @@ walk_umma_kernel(const __grid_constant__ CUtensorMap tm_wh, const __grid_constan
     // ------------------------------------------------------------------ MMA issuer
     if (lane == 0) {
       bool ok = true;
+      // Descriptors are built once per ring stage; inside the loop an operand step is one 64-bit add
+      // (the start-address field counts 16-byte units), which keeps the issuing thread's own instruction
+      // stream short: it is the only thread feeding the tensor pipe.
+      static_assert(L::kStages == 2, "descriptor cache below assumes a two-stage ring");
+      const uint32_t st0 = smem_u32(sm), st1 = st0 + L::kStage;
+      const uint64_t dB0[2] = {smem_desc(st0 + L::kB0, 16, 1024), smem_desc(st1 + L::kB0, 16, 1024)};
+      const uint64_t dB1[2] = {smem_desc(st0 + L::kB1, 16, 1024), smem_desc(st1 + L::kB1, 16, 1024)};
+      const uint64_t dK[2] = {smem_desc(st0 + L::kK, kBox, 1024), smem_desc(st1 + L::kK, kBox, 1024)};
+      const uint64_t dP[2] = {smem_desc(st0 + L::kP, 16, 1024), smem_desc(st1 + L::kP, 16, 1024)};
       for (int c = 0; c < chunks && ok; ++c) {
-        const int s = c % L::kStages;
-        const uint32_t st = smem_u32(sm + s * L::kStage);
-        ok = mbar_wait(full + s, (c / L::kStages) & 1, abort, 40, c) &&
-             mbar_wait(bar_ops, c & 1, abort, 41, c);
-        if (!ok) break;
-        tc_fence_after();
-        GDN_MSTAMP(0);
-        // (W S)^T = St W^T with St ~ SH + SL and W ~ WH + WL (the lo*lo term is dropped)
+        const int s = c & 1;
+        const uint64_t b0 = s ? dB0[1] : dB0[0], b1 = s ? dB1[1] : dB1[0];
+        const uint64_t kd = s ? dK[1] : dK[0], pd = s ? dP[1] : dP[0];
+        ok = mbar_wait(full + s, (c >> 1) & 1, abort, 40, c);
+        // the wide product overwrites O^T: the previous chunk's output must have been drained
+        if (ok && c > 0) ok = mbar_wait(bar_ofree, (c - 1) & 1, abort, 42, c);
+        // St [W_hi ; W_lo ; Qs]^T with St ~ SH + SL: the SH pass covers all 192 columns, the SL pass the
+        // 128 W columns.  K steps {0,1,4,5} become available first, {2,3,6,7} second.
 #pragma unroll
-        for (int term = 0; term < 3; ++term) {
-          const uint32_t a = tmem + (term == 1 ? kOpSL : kOpSH);
-          const uint32_t wb = st + (term == 2 ? L::kWL : L::kWH);
+        for (int part = 0; part < 2 && ok; ++part) {
+          ok = mbar_wait(bar_ops + part, c & 1, abort, 41, c);
+          if (!ok) break;
+          tc_fence_after();
 #pragma unroll
-          for (int ks = 0; ks < 8; ++ks)
-            mma_ts(tmem + kAccWS, a + ks * 8, smem_desc(wb + (ks >> 2) * kBox + (ks & 3) * 32, 16, 1024),
-                   kIdescN64, (term | ks) != 0);
+          for (int q = 0; q < 4; ++q) {
+            const int ks = (q >> 1) * 4 + part * 2 + (q & 1);
+            const uint64_t bdesc = ((ks >> 2) ? b1 : b0) + uint64_t((ks & 3) * 2);     // +32 bytes per K step
+            mma_ts(tmem + kAccX, tmem + kOpSH + ks * 8, bdesc, kIdescN192, (part | q) != 0);
+            mma_ts(tmem + kAccY, tmem + kOpSL + ks * 8, bdesc, kIdescN64, (part | q) != 0);
+          }
         }
+        if (!ok) break;
         mma_commit(bar_ws);
-        GDN_MSTAMP(1);
-        // O^T = St Qs^T (old state, BF16 hi part); the previous chunk's O^T must have been drained
-        if (c > 0) ok = mbar_wait(bar_ofree, (c - 1) & 1, abort, 42, c);
-        if (!ok) break;
-        tc_fence_after();
+        // St += (N*rel)^T K (accumulator already holds gamma * St); token groups {0,2} first, {1,3} second
 #pragma unroll
-        for (int ks = 0; ks < 8; ++ks)
-          mma_ts(tmem + kAccO, tmem + kOpSH + ks * 8,
-                 smem_desc(st + L::kQS + (ks >> 2) * kBox + (ks & 3) * 32, 16, 1024), kIdescN64, ks != 0);
-
-        ok = mbar_wait(bar_opn, c & 1, abort, 43, c);
-        if (!ok) break;
-        tc_fence_after();
-        GDN_MSTAMP(2);
-        // St += (N*rel)^T K   (accumulator already holds gamma * St)
+        for (int part = 0; part < 2 && ok; ++part) {
+          ok = mbar_wait(bar_opn + part, c & 1, abort, 43, c);
+          if (!ok) break;
+          tc_fence_after();
 #pragma unroll
-        for (int term = 0; term < 2; ++term) {
+          for (int h = 0; h < 2; ++h) {
+            const int ks = h * 2 + part;
+            const uint64_t kdesc = kd + uint64_t(ks * 128);                              // +2048 bytes per K step
+            mma_ts(tmem + kAccS, tmem + kAccX + ks * 16, kdesc, kIdescN128BT, 1);
+            mma_ts(tmem + kAccS, tmem + kAccX + ks * 16 + 8, kdesc, kIdescN128BT, 1);
+          }
+          if (part == 1) mma_commit(bar_s);
+          // O^T += N^T P^T for the same token groups; the first half runs while the chain warps still
+          // work on the second, so the output accumulator completes right behind the state update
 #pragma unroll
-          for (int ks = 0; ks < 4; ++ks)
-            mma_ts(tmem + kAccS, tmem + (term ? kOpNL : kOpNH) + ks * 8,
-                   smem_desc(st + L::kK + ks * 2048, kBox, 1024), kIdescN128BT, 1);
+          for (int h = 0; h < 2; ++h) {
+            const int ks = h * 2 + part;
+            mma_ts(tmem + kAccO, tmem + kAccX + 64 + ks * 16, pd + uint64_t(ks * 2), kIdescN64, 1);
+          }
         }
-        mma_commit(bar_s);
-        GDN_MSTAMP(3);
-        // O^T += N^T P^T
-#pragma unroll
-        for (int ks = 0; ks < 4; ++ks)
-          mma_ts(tmem + kAccO, tmem + kOpN16 + ks * 8, smem_desc(st + L::kP + ks * 32, 16, 1024), kIdescN64, 1);
+        if (!ok) break;
         mma_commit(bar_o);
         mma_commit(empty + s);
       }
@@ -866,6 +922,7 @@ walk_umma_kernel(const __grid_constant__ CUtensorMap tm_wh, const __grid_constan
 }
 #undef GDN_STAMP
 #undef GDN_MSTAMP
+#undef GDN_OSTAMP
 
 }  // namespace
 
@@ -899,14 +956,15 @@ int launch_walk_umma(const Inputs& in, const Geometry& geo, const Workspace& ws,
   TensorMapEncoder& enc = tensor_map_encoder();
   if (int rc = enc.init()) return rc;
   const uint64_t rows = uint64_t(geo.blocks()) * kChunk;
-  CUtensorMap tm_wh, tm_wl, tm_qs, tm_k, tm_p;
+  CUtensorMap tm_wh, tm_wl, tm_qs, tm_k, tm_p, tm_out;
+  if (int rc = enc.bf16_4d(&tm_out, in.output, kDim, geo.value_heads, geo.sequence, geo.batch, kChunk)) return rc;
   if (int rc = enc.bf16_2d(&tm_wh, ws.w_hi, kDim, rows, kChunk)) return rc;
   if (int rc = enc.bf16_2d(&tm_wl, ws.w_lo, kDim, rows, kChunk)) return rc;
   if (int rc = enc.bf16_2d(&tm_qs, ws.qs, kDim, rows, kChunk)) return rc;
   if (int rc = enc.bf16_4d(&tm_k, in.k, kDim, geo.key_heads, geo.sequence, geo.batch, kChunk)) return rc;
   if (int rc = enc.bf16_2d(&tm_p, ws.p, kChunk, rows, kChunk)) return rc;
   walk_umma_kernel<<<geo.batch * geo.value_heads, kWalkThreads, kWalkSmem, stream>>>(tm_wh, tm_wl, tm_qs, tm_k,
-                                                                                    tm_p, in, geo, ws);
+                                                                                    tm_p, tm_out, in, geo, ws);
   return int(cudaGetLastError());
 }
 
