@@ -560,10 +560,12 @@ prepare_umma_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
 // A tcgen05.mma with M = 128 occupies the tensor pipe for at least ~64 cycles whatever N is, so the chain
 // uses few, wide instructions: 16 per chunk for W S and Q S together (N = 192 and 128), 8 for the state
 // update (N = 128), 4 for P N.
-// Roles: warps 0-7 state chain; a warp owns the 32 TMEM lanes of quarter (warp & 3) and, of every tile it
-//        touches, the column half (warp >> 2).  Both chain steps are signalled in two halves so that the
-//        MMA issuer starts on the first half of the K range while the second half is still being written.
-//        warps 8-11 output epilogue; warp 12 TMA producer; warp 13 MMA issuer.
+// Roles: warp 0 MMA issuer and warp 1 TMA producer (the lowest warp ids: their short instruction streams
+//        sit on the critical path and must not queue behind the arithmetic of the chain warps);
+//        warps 4-11 state chain: a warp owns the 32 TMEM lanes of quarter (warp & 3) and, of every tile it
+//        touches, one column half.  Both chain steps are signalled in two halves so that the MMA issuer
+//        starts on the first half of the K range while the second half is still being written.
+//        warps 12-15 output epilogue; warps 2-3 idle.
 struct WalkLayout {
   // B operand of the wide product: per 64-wide K atom the rows [W_hi | W_lo | Qs] (3 boxes, contiguous)
   static constexpr int kB0 = 0, kB1 = 3 * kBox;
@@ -577,8 +579,8 @@ struct WalkLayout {
   static constexpr int kBars = kOut + 4 * kBox;
   static constexpr int kTotal = kBars + 256;
 };
-constexpr int kChainWarps = 8, kOutWarp0 = 8, kTmaWarp = 12, kMmaWarp = 13;
-constexpr int kWalkThreads = 448;
+constexpr int kMmaWarp = 0, kTmaWarp = 1, kChainWarp0 = 4, kChainWarps = 8, kOutWarp0 = 12;
+constexpr int kWalkThreads = 512;
 constexpr int kWalkSmem = WalkLayout::kTotal + 1024;
 constexpr uint32_t kAccS = 0, kOpSH = 128, kOpSL = 192, kAccX = 256, kAccO = 384, kAccY = 448;
 constexpr uint32_t kIdescN192 = idesc_bf16(128, 192, false, false);
@@ -586,7 +588,7 @@ constexpr uint32_t kIdescN128 = idesc_bf16(128, 128, false, false);
 
 #ifdef GDN_SM100_PHASE_TIMING
 #define GDN_STAMP(slot)                                                                        \
-  if (tid == 0) ws.gates[(block0 + c) * 128 + 96 + (slot)] = float((clock64() - t_begin) & 0xffffff)
+  if (tid == kChainWarp0 * 32) ws.gates[(block0 + c) * 128 + 96 + (slot)] = float((clock64() - t_begin) & 0xffffff)
 #define GDN_MSTAMP(slot) ws.gates[(block0 + c) * 128 + 104 + (slot)] = float((clock64() - t_begin) & 0xffffff)
 #define GDN_OSTAMP(slot)                                                                       \
   if (tid == kOutWarp0 * 32) ws.gates[(block0 + c) * 128 + 112 + (slot)] = float((clock64() - t_begin) & 0xffffff)
@@ -657,9 +659,9 @@ walk_umma_kernel(const __grid_constant__ CUtensorMap tm_wh, const __grid_constan
   tc_fence_after();
   const uint32_t tmem = *tmem_slot;
 
-  if (warp < kChainWarps) {
+  if (warp >= kChainWarp0 && warp < kChainWarp0 + kChainWarps) {
     // ------------------------------------------------------------------ state chain
-    const int quarter = warp & 3, half = warp >> 2;
+    const int quarter = warp & 3, half = (warp - kChainWarp0) >> 2;
     const int v = quarter * 32 + lane;                     // value row = TMEM lane
     const uint32_t taddr = tmem + (uint32_t(quarter * 32) << 16);
     {
@@ -708,9 +710,13 @@ walk_umma_kernel(const __grid_constant__ CUtensorMap tm_wh, const __grid_constan
         tmem_st32(taddr + kAccS + k0, d);
         tmem_wait_st();
         tc_fence_before();
+        // the wide product also overwrites O^T and reads the ring stage: this warp vouches for both before
+        // its first arrival, so the issuer has a single wait in front of the product
+        if (part == 0 && c > 0) ok = mbar_wait(bar_ofree, (c - 1) & 1, abort, 14, c);
         __syncwarp();
         if (lane == 0) mbar_arrive(bar_ops + part);
       }
+      if (!ok) break;
       GDN_STAMP(1);
 
       float u[32];
@@ -766,7 +772,7 @@ walk_umma_kernel(const __grid_constant__ CUtensorMap tm_wh, const __grid_constan
         for (int j = 0; j < 32; ++j) fin[(k0 + j) * kDim] = __uint_as_float(d[j]);
       }
     }
-  }  else if (warp < kTmaWarp) {
+  }  else if (warp >= kOutWarp0) {
     // ------------------------------------------------------------------ output epilogue
     const int quarter = warp - kOutWarp0;
     const int v = quarter * 32 + lane;
@@ -847,7 +853,7 @@ walk_umma_kernel(const __grid_constant__ CUtensorMap tm_wh, const __grid_constan
       }
     }
     __syncwarp();
-  } else {
+  } else if (warp == kMmaWarp) {
     // ------------------------------------------------------------------ MMA issuer
     if (lane == 0) {
       bool ok = true;
@@ -864,9 +870,6 @@ walk_umma_kernel(const __grid_constant__ CUtensorMap tm_wh, const __grid_constan
         const int s = c & 1;
         const uint64_t b0 = s ? dB0[1] : dB0[0], b1 = s ? dB1[1] : dB1[0];
         const uint64_t kd = s ? dK[1] : dK[0], pd = s ? dP[1] : dP[0];
-        ok = mbar_wait(full + s, (c >> 1) & 1, abort, 40, c);
-        // the wide product overwrites O^T: the previous chunk's output must have been drained
-        if (ok && c > 0) ok = mbar_wait(bar_ofree, (c - 1) & 1, abort, 42, c);
         // St [W_hi ; W_lo ; Qs]^T with St ~ SH + SL: the SH pass covers all 192 columns, the SL pass the
         // 128 W columns.  K steps {0,1,4,5} become available first, {2,3,6,7} second.
 #pragma unroll
