@@ -41,10 +41,11 @@ def render_policy_table(policy_path, out_path):
     data = json.loads(Path(policy_path).read_text())
     ids = data["configuration_ids"]
     rows = ",\n".join(
-        "  {%d, %d, %d, %d, %d}" % (*row["shape"], ids[row["configuration"]]) for row in data["rows"])
+        "  {%d, %d, %d, %d, %d, %d}" % (*row["shape"], ids[row["configuration"]], int(row.get("segments", 1)))
+        for row in data["rows"])
     out_path.write_text(
         "// generated from sm100_policy.json (%s); do not edit\n"
-        "struct PolicyRow { int b, t, hk, hv, config; };\n"
+        "struct PolicyRow { int b, t, hk, hv, config, segments; };\n"
         "constexpr int kPolicyDefault = %d;\n"
         "constexpr PolicyRow kPolicyRows[] = {\n%s\n};\n"
         % (data["id"], ids[data["default"]], rows))

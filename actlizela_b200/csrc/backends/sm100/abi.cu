@@ -25,9 +25,42 @@ bool geometry_ok(int b, int t, int hk, int hv) {
 // Bits 4 and 5 of `config` restrict a call to one stage (per-kernel timing and diagnosis):
 // 0x10 = prepare stage only, 0x20 = walk stage only (the workspace must already hold the
 // factors of the same inputs).
-constexpr int kStageMask = 0x30, kPrepareOnly = 0x10, kWalkOnly = 0x20;
+// Bits 8..15 hold the number of sequence segments (0 or 1 = one): the prepare kernels of later
+// segments then run next to the walk of earlier ones (tcgen05 configuration only).
+constexpr int kStageMask = 0x30, kPrepareOnly = 0x10, kWalkOnly = 0x20, kSegmentShift = 8, kMaxSegments = 16;
 bool config_ok(int config) {
-  return config >= 0 && (config & ~kStageMask) <= 3 && (config & kStageMask) != kStageMask;
+  const int segments = (config >> kSegmentShift) & 0xff;
+  return config >= 0 && (config & 0xf) <= 3 && (config & ~(kStageMask | 0xf | (0xff << kSegmentShift))) == 0 &&
+         (config & kStageMask) != kStageMask && segments <= kMaxSegments;
+}
+int segments_of(int config, const Geometry& geo) {
+  int segments = (config >> kSegmentShift) & 0xff;
+  if ((config & 0xf) != 1 || (config & kStageMask) || segments < 2) return 1;
+  const int chunks = geo.chunks();
+  return segments > chunks ? chunks : segments;
+}
+
+// Second stream and events of the segmented forward, created by configure() for the current device.
+struct SegmentStreams {
+  cudaStream_t walk = nullptr;
+  cudaEvent_t prepared[kMaxSegments] = {};
+  cudaEvent_t done = nullptr;
+};
+SegmentStreams g_streams[64];
+
+int create_segment_streams() {
+  int device = -1;
+  cudaError_t e = cudaGetDevice(&device);
+  if (e != cudaSuccess) return int(e);
+  if (device < 0 || device >= 64) return int(cudaErrorInvalidDevice);
+  SegmentStreams& ss = g_streams[device];
+  if (ss.walk) return 0;
+  int least = 0, greatest = 0;
+  if ((e = cudaDeviceGetStreamPriorityRange(&least, &greatest)) != cudaSuccess) return int(e);
+  if ((e = cudaStreamCreateWithPriority(&ss.walk, cudaStreamNonBlocking, greatest)) != cudaSuccess) return int(e);
+  for (cudaEvent_t& ev : ss.prepared)
+    if ((e = cudaEventCreateWithFlags(&ev, cudaEventDisableTiming)) != cudaSuccess) return int(e);
+  return int(cudaEventCreateWithFlags(&ss.done, cudaEventDisableTiming));
 }
 // bit 0: prepare stage uses tcgen05 (1) or CUDA cores (0); configuration ids:
 // 0 = simt/simt, 1 = umma/umma, 2 = simt prepare + umma walk, 3 = umma prepare + simt walk
@@ -74,24 +107,29 @@ extern "C" const char* actlize_la_sm100_numerical_contract(void) {
 
 extern "C" int actlize_la_sm100_configure(void) {
   if (int rc = configure_simt()) return rc;
-  return configure_umma();
+  if (int rc = configure_umma()) return rc;
+  return create_segment_streams();
 }
 
 extern "C" int actlize_la_sm100_select(int b, int t, int hk, int hv, int gate_fp32) {
   (void)gate_fp32;
   if (!geometry_ok(b, t, hk, hv)) return -1;
   for (const PolicyRow& row : kPolicyRows)
-    if (row.b == b && row.t == t && row.hk == hk && row.hv == hv) return row.config;
+    if (row.b == b && row.t == t && row.hk == hk && row.hv == hv) return row.config | (row.segments << kSegmentShift);
   return kPolicyDefault;
 }
 
 extern "C" long long actlize_la_sm100_workspace_bytes(int b, int t, int hk, int hv, int config) {
   if (!geometry_ok(b, t, hk, hv) || !config_ok(config)) return -1;
-  return workspace_bytes(Geometry{b, t, hk, hv});
+  const Geometry geo{b, t, hk, hv};
+  return workspace_bytes(geo, segments_of(config, geo));
 }
 
 extern "C" int actlize_la_sm100_launches_per_forward(int config) {
-  return !config_ok(config) ? -1 : (config & kStageMask) ? 1 : 2;
+  if (!config_ok(config)) return -1;
+  if (config & kStageMask) return 1;
+  const int segments = (config >> kSegmentShift) & 0xff;
+  return ((config & 0xf) == 1 && segments > 1) ? 2 * segments : 2;
 }
 
 extern "C" int actlize_la_sm100_device_status(int* status4, int reset) {
@@ -106,8 +144,9 @@ extern "C" int actlize_la_sm100_forward_prepared(
     int b, int t, int hk, int hv, int gate_fp32, int config, void* opaque_stream) {
   if (!q || !k || !v || !g || !beta || !output || !workspace) return int(cudaErrorInvalidValue);
   if (!geometry_ok(b, t, hk, hv) || !config_ok(config)) return int(cudaErrorInvalidValue);
-  const Geometry geo{b, t, hk, hv};
-  if (workspace_bytes_given < workspace_bytes(geo)) return int(cudaErrorInvalidValue);
+  Geometry geo{b, t, hk, hv};
+  const int segments = segments_of(config, geo);
+  if (workspace_bytes_given < workspace_bytes(geo, segments)) return int(cudaErrorInvalidValue);
   if ((reinterpret_cast<uintptr_t>(workspace) & 255) || (reinterpret_cast<uintptr_t>(q) & 15) ||
       (reinterpret_cast<uintptr_t>(k) & 15) || (reinterpret_cast<uintptr_t>(v) & 15) ||
       (reinterpret_cast<uintptr_t>(output) & 15))
@@ -119,6 +158,27 @@ extern "C" int actlize_la_sm100_forward_prepared(
                   initial, static_cast<__nv_bfloat16*>(output), final_state, gate_fp32 ? 1 : 0};
   const Workspace ws = carve_workspace(workspace, geo);
   cudaStream_t stream = static_cast<cudaStream_t>(opaque_stream);
+  if (segments > 1) {
+    // Prepare kernels of all segments go to the caller's stream back to back; the walks run in order on
+    // a high-priority second stream, each after its segment's prepare, so that a later segment is
+    // prepared on the SMs the walk leaves free.  The caller's stream finally waits for the last walk.
+    int device = -1;
+    cudaError_t e = cudaGetDevice(&device);
+    if (e != cudaSuccess) return int(e);
+    if (device < 0 || device >= 64 || !g_streams[device].walk) return int(cudaErrorNotReady);   // configure() first
+    SegmentStreams& ss = g_streams[device];
+    const int chunks = geo.chunks();
+    for (int i = 0; i < segments; ++i) {
+      geo.chunk_begin = int((long long)chunks * i / segments);
+      geo.chunk_count = int((long long)chunks * (i + 1) / segments) - geo.chunk_begin;
+      if (int rc = launch_prepare_umma(in, geo, ws, stream)) return rc;
+      if ((e = cudaEventRecord(ss.prepared[i], stream)) != cudaSuccess) return int(e);
+      if ((e = cudaStreamWaitEvent(ss.walk, ss.prepared[i], 0)) != cudaSuccess) return int(e);
+      if (int rc = launch_walk_umma(in, geo, ws, ss.walk)) return rc;
+    }
+    if ((e = cudaEventRecord(ss.done, ss.walk)) != cudaSuccess) return int(e);
+    return int(cudaStreamWaitEvent(stream, ss.done, 0));
+  }
   if (!(config & kWalkOnly)) {
     if (int rc = prepare_is_umma(config) ? launch_prepare_umma(in, geo, ws, stream)
                                          : launch_prepare_simt(in, geo, ws, stream))
@@ -134,7 +194,7 @@ struct Arena {
   long long q, k, v, g, beta, initial, output, final_state, workspace, total;
 };
 long long align256(long long x) { return (x + 255) & ~255LL; }
-Arena arena_layout(int b, int t, int hk, int hv, int gate_fp32, int has_initial, int has_final) {
+Arena arena_layout(int b, int t, int hk, int hv, int gate_fp32, int has_initial, int has_final, int config) {
   Arena a{};
   long long off = 0;
   auto take = [&](long long bytes) { long long at = off; off = align256(off + bytes); return at; };
@@ -145,7 +205,8 @@ Arena arena_layout(int b, int t, int hk, int hv, int gate_fp32, int has_initial,
   a.initial = has_initial ? take(st) : -1;
   a.output = take(vv);
   a.final_state = has_final ? take(st) : -1;
-  a.workspace = take(workspace_bytes(Geometry{b, t, hk, hv}));
+  const Geometry geo{b, t, hk, hv};
+  a.workspace = take(workspace_bytes(geo, segments_of(config, geo)));
   a.total = off;
   return a;
 }
@@ -154,7 +215,7 @@ Arena arena_layout(int b, int t, int hk, int hv, int gate_fp32, int has_initial,
 extern "C" long long actlize_la_sm100_host_arena_bytes(int b, int t, int hk, int hv, int gate_fp32,
                                                        int has_initial, int has_final, int config) {
   if (!geometry_ok(b, t, hk, hv) || !config_ok(config)) return -1;
-  return arena_layout(b, t, hk, hv, gate_fp32, has_initial, has_final).total;
+  return arena_layout(b, t, hk, hv, gate_fp32, has_initial, has_final, config).total;
 }
 
 extern "C" int actlize_la_sm100_forward_host(
@@ -165,7 +226,7 @@ extern "C" int actlize_la_sm100_forward_host(
   if (!q || !k || !v || !g || !beta || !output || !device_arena) return int(cudaErrorInvalidValue);
   if (!geometry_ok(b, t, hk, hv) || !config_ok(config)) return int(cudaErrorInvalidValue);
   if (reinterpret_cast<uintptr_t>(device_arena) & 255) return int(cudaErrorInvalidValue);
-  const Arena a = arena_layout(b, t, hk, hv, gate_fp32, initial != nullptr, final_state != nullptr);
+  const Arena a = arena_layout(b, t, hk, hv, gate_fp32, initial != nullptr, final_state != nullptr, config);
   if (device_arena_bytes < a.total) return int(cudaErrorInvalidValue);
   char* base = static_cast<char*>(device_arena);
   cudaStream_t stream = static_cast<cudaStream_t>(opaque_stream);

@@ -17,7 +17,12 @@ constexpr float kScale = 0.08838834764831845f;  // 1/sqrt(128), applied exactly 
 
 struct Geometry {
   int batch, sequence, key_heads, value_heads;
+  // A launch may cover a contiguous range of chunks only (sequence segment); 0 chunks = the whole sequence.
+  int chunk_begin = 0, chunk_count = 0;
   __host__ __device__ int chunks() const { return (sequence + kChunk - 1) / kChunk; }
+  __host__ __device__ int segment_chunks() const { return chunk_count ? chunk_count : chunks(); }
+  __host__ __device__ bool first_segment() const { return chunk_begin == 0; }
+  __host__ __device__ bool last_segment() const { return chunk_begin + segment_chunks() == chunks(); }
   __host__ __device__ int group() const { return value_heads / key_heads; }
   __host__ __device__ long long blocks() const {
     return (long long)batch * value_heads * chunks();
@@ -32,6 +37,8 @@ struct Geometry {
 //   p           BF16 [64][64]   tril(Q K^T * exp(prefix_i - prefix_j)) / sqrt(128)
 //   gates       FP32 [128]      [0,64): exp(prefix_last - prefix_i), 0 for padding rows;
 //                               [64]: exp(prefix_last); rest unused
+// plus, when the sequence is walked in segments, one FP32 [128][128] state per (batch, value head)
+// that carries the state from one segment's walk to the next (K-by-V order, like the public state).
 struct Workspace {
   __nv_bfloat16* w_hi;
   __nv_bfloat16* w_lo;
@@ -39,12 +46,16 @@ struct Workspace {
   __nv_bfloat16* qs;
   __nv_bfloat16* p;
   float* gates;
+  float* carry;
 };
 
 constexpr long long kBlockBytes =
     2LL * kChunk * kDim * 2 + kChunk * kDim * 4 + kChunk * kDim * 2 + kChunk * kChunk * 2 + 128 * 4;
 
-inline __host__ long long workspace_bytes(const Geometry& g) { return g.blocks() * kBlockBytes; }
+inline __host__ long long workspace_bytes(const Geometry& g, int segments = 1) {
+  return g.blocks() * kBlockBytes +
+         (segments > 1 ? (long long)g.batch * g.value_heads * kDim * kDim * 4 : 0);
+}
 
 // Carve the planes out of one caller-owned allocation (256-byte aligned base required).
 inline __host__ Workspace carve_workspace(void* base, const Geometry& g) {
@@ -56,7 +67,8 @@ inline __host__ Workspace carve_workspace(void* base, const Geometry& g) {
   w.u = reinterpret_cast<float*>(p);             p += n * kChunk * kDim * 4;
   w.qs = reinterpret_cast<__nv_bfloat16*>(p);    p += n * kChunk * kDim * 2;
   w.p = reinterpret_cast<__nv_bfloat16*>(p);     p += n * kChunk * kChunk * 2;
-  w.gates = reinterpret_cast<float*>(p);
+  w.gates = reinterpret_cast<float*>(p);         p += n * 128 * 4;
+  w.carry = reinterpret_cast<float*>(p);         // only backed by memory when segments > 1
   return w;
 }
 

@@ -157,14 +157,14 @@ prepare_umma_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
   const AbortFlag abort{abort_word};
 
   const int tid = threadIdx.x, warp = tid >> 5;
-  const int chunks = geo.chunks();
-  const int chunk = blockIdx.x % chunks;
-  const int bh = blockIdx.x / chunks;
+  const int chunks = geo.chunks(), seg_chunks = geo.segment_chunks();
+  const int chunk = geo.chunk_begin + blockIdx.x % seg_chunks;
+  const int bh = blockIdx.x / seg_chunks;
   const int b = bh / geo.value_heads, hv = bh % geo.value_heads;
   const int hk = hv / geo.group();
   const int t0 = chunk * kChunk;
   const int valid = min(kChunk, geo.sequence - t0);
-  const long long block = blockIdx.x;
+  const long long block = (long long)bh * chunks + chunk;
 #ifdef GDN_SM100_PHASE_TIMING
   const long long t_begin = clock64();
 #endif
@@ -626,8 +626,10 @@ walk_umma_kernel(const __grid_constant__ CUtensorMap tm_wh, const __grid_constan
   const int bh = blockIdx.x;
   const int b = bh / geo.value_heads, hv = bh % geo.value_heads;
   const int hk = hv / geo.group();
-  const int chunks = geo.chunks();
-  const long long block0 = (long long)bh * chunks;
+  const int chunks = geo.segment_chunks(), c0 = geo.chunk_begin;     // this launch walks chunks [c0, c0 + chunks)
+  const long long block0 = (long long)bh * geo.chunks() + c0;
+  const float* state_in = geo.first_segment() ? in.initial : ws.carry;
+  float* state_out = geo.last_segment() ? in.final_state : ws.carry;
 #ifdef GDN_SM100_PHASE_TIMING
   const long long t_begin = clock64();
 #endif
@@ -665,7 +667,7 @@ walk_umma_kernel(const __grid_constant__ CUtensorMap tm_wh, const __grid_constan
     const int v = quarter * 32 + lane;                     // value row = TMEM lane
     const uint32_t taddr = tmem + (uint32_t(quarter * 32) << 16);
     {
-      const float* init = in.initial ? in.initial + (long long)bh * kDim * kDim + v : nullptr;
+      const float* init = state_in ? state_in + (long long)bh * kDim * kDim + v : nullptr;
 #pragma unroll
       for (int part = 0; part < 2; ++part) {
         uint32_t vals[32];
@@ -759,9 +761,9 @@ walk_umma_kernel(const __grid_constant__ CUtensorMap tm_wh, const __grid_constan
       GDN_STAMP(3);
     }
     if (ok) ok = mbar_wait(bar_s, (chunks - 1) & 1, abort, 13, chunks);
-    if (ok && in.final_state) {
+    if (ok && state_out) {
       tc_fence_after();
-      float* fin = in.final_state + (long long)bh * kDim * kDim + v;
+      float* fin = state_out + (long long)bh * kDim * kDim + v;
 #pragma unroll
       for (int part = 0; part < 2; ++part) {
         uint32_t d[32];
@@ -817,8 +819,8 @@ walk_umma_kernel(const __grid_constant__ CUtensorMap tm_wh, const __grid_constan
         ok = mbar_wait(bar_staged, c & 1, abort, 22, c);
         if (!ok) break;
         const uint8_t* tile = sm + L::kOut + (c & 1) * 2 * kBox;
-        tma_store_4d(&tm_out, tile, 0, hv, c * kChunk, b);
-        tma_store_4d(&tm_out, tile + kBox, 64, hv, c * kChunk, b);
+        tma_store_4d(&tm_out, tile, 0, hv, (c0 + c) * kChunk, b);
+        tma_store_4d(&tm_out, tile + kBox, 64, hv, (c0 + c) * kChunk, b);
         tma_store_commit();
         tma_store_wait_read_keep1();
         mbar_arrive(bar_stfree);
@@ -847,8 +849,8 @@ walk_umma_kernel(const __grid_constant__ CUtensorMap tm_wh, const __grid_constan
         tma_load_2d(st + L::kB1 + L::kWL, &tm_wl, full + s, 64, row);
         tma_load_2d(st + L::kB0 + L::kQS, &tm_qs, full + s, 0, row);
         tma_load_2d(st + L::kB1 + L::kQS, &tm_qs, full + s, 64, row);
-        tma_load_4d(st + L::kK, &tm_k, full + s, 0, hk, c * kChunk, b);
-        tma_load_4d(st + L::kK + kBox, &tm_k, full + s, 64, hk, c * kChunk, b);
+        tma_load_4d(st + L::kK, &tm_k, full + s, 0, hk, (c0 + c) * kChunk, b);
+        tma_load_4d(st + L::kK + kBox, &tm_k, full + s, 64, hk, (c0 + c) * kChunk, b);
         tma_load_2d(st + L::kP, &tm_p, full + s, 0, row);
       }
     }
@@ -950,7 +952,7 @@ int launch_prepare_umma(const Inputs& in, const Geometry& geo, const Workspace& 
   if (int rc = enc.bf16_2d(&tm_wh, ws.w_hi, kDim, rows, kChunk)) return rc;
   if (int rc = enc.bf16_2d(&tm_wl, ws.w_lo, kDim, rows, kChunk)) return rc;
   if (int rc = enc.f32_2d(&tm_u, ws.u, kDim, rows, kChunk)) return rc;
-  prepare_umma_kernel<<<(unsigned)geo.blocks(), kPrepThreads, kPrepSmem, stream>>>(tm_q, tm_k, tm_v, tm_wh, tm_wl,
+  prepare_umma_kernel<<<(unsigned)((long long)geo.batch * geo.value_heads * geo.segment_chunks()), kPrepThreads, kPrepSmem, stream>>>(tm_q, tm_k, tm_v, tm_wh, tm_wl,
                                                                                   tm_u, in, geo, ws);
   return int(cudaGetLastError());
 }

@@ -82,6 +82,7 @@ extern "C" int actlize_la_sm100_forward_static_scratch(
   }
   void* scratch = nullptr;
   if (int rc = scratch_for_current_device(&scratch)) return rc;
+  // the built-in array has no room for the carry state of a segmented walk: always one segment here
   return actlize_la_sm100_forward_prepared(q, k, v, g, beta, initial, output, final_state, scratch,
-                                           kStaticBytes, b, t, hk, hv, gate_fp32, config, stream);
+                                           kStaticBytes, b, t, hk, hv, gate_fp32, config & 0xff, stream);
 }

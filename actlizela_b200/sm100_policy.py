@@ -28,6 +28,8 @@ def policy():
     keys = [tuple(r["shape"]) for r in rows]
     if len(set(keys)) != len(keys) or any(r["configuration"] not in data["configurations"] for r in rows):
         raise ValueError("duplicate or unknown SM100 policy row")
+    if any(not 1 <= int(r.get("segments", 1)) <= 16 for r in rows):
+        raise ValueError("SM100 policy row with an unsupported segment count")
     return data
 
 
@@ -40,10 +42,12 @@ class Selection:
     configuration: str
     basis: str
     policy_id: str
+    segments: int = 1     # sequence segments whose prepare overlaps the previous segment's walk
 
     @property
     def configuration_id(self):
-        return policy()["configuration_ids"][self.configuration]
+        """Native configuration word: kernel family in the low bits, segment count in bits 8..15."""
+        return policy()["configuration_ids"][self.configuration] | (self.segments << 8)
 
 
 def tensor_backend(q):
@@ -75,7 +79,8 @@ def select(shape, profile):
         return Selection(data["default"], "unmeasured-device-default", data["id"])
     for row in data["rows"]:
         if tuple(row["shape"]) == tuple(shape[:4]):
-            return Selection(row["configuration"], "b200-measured-shape", data["id"])
+            return Selection(row["configuration"], "b200-measured-shape", data["id"],
+                             int(row.get("segments", 1)))
     return Selection(data["default"], "unmeasured-shape-default", data["id"])
 
 

@@ -246,3 +246,18 @@ def test_apply_transition_kernel(native_library):
     got = native_apply_transition(m, b, s)
     want = (m.double() @ s.double() + b.double()).float()
     assert oracle.rel_frobenius(got.cpu(), want.cpu()) < 1e-6
+
+
+@pytest.mark.parametrize("configuration", ["umma-seg2", "umma-seg4", "umma-seg8"])
+def test_segmented_walk_equals_the_single_launch_bitwise(configuration, forward, native_library):
+    """Prepare of later segments overlaps the walk of earlier ones; the arithmetic is unchanged."""
+    w = WORKLOADS["cfg3"].sliced(batch=2, length=1000, key_heads=2, value_heads=8)     # 16 chunks, tail of 40
+    dev = _to_device(make_inputs(w))
+    out, state = forward(*dev, True, configuration="umma")
+    for _ in range(3):
+        seg_out, seg_state = forward(*dev, True, configuration=configuration)
+        assert torch.equal(seg_out, out) and torch.equal(seg_state, state)
+    seg_out, none = forward(*dev, False, configuration=configuration)
+    assert none is None and torch.equal(seg_out, out)
+    torch.cuda.synchronize()
+    assert _status(native_library)[0] == 0

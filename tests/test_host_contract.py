@@ -172,7 +172,10 @@ def test_native_select_agrees_with_python_policy(native_library):
     lib = native_library.lib
     ids = sm100_policy.policy()["configuration_ids"]
     for row in sm100_policy.policy()["rows"]:
-        assert lib.actlize_la_sm100_select(*row["shape"], 1) == ids[row["configuration"]]
+        want = ids[row["configuration"]] | (row.get("segments", 1) << 8)
+        assert lib.actlize_la_sm100_select(*row["shape"], 1) == want
+        profile_choice = sm100_policy.select((*row["shape"], 128, 128), B200)
+        assert profile_choice.configuration_id == want
     assert lib.actlize_la_sm100_select(3, 100, 2, 4, 0) == ids[sm100_policy.policy()["default"]]
     assert lib.actlize_la_sm100_select(1, 64, 3, 4, 0) < 0
     assert lib.actlize_la_sm100_select(0, 64, 1, 1, 0) < 0
@@ -183,6 +186,9 @@ def test_native_argument_rejection_without_a_device(native_library):
     invalid = 1   # cudaErrorInvalidValue
     n = lib.actlize_la_sm100_workspace_bytes(1, 8192, 16, 32, 1)
     assert n == 32 * 128 * (16384 * 2 + 32768 + 16384 + 8192 + 512)
+    # a segmented walk carries one FP32 128x128 state per (batch, value head) between segments
+    assert lib.actlize_la_sm100_workspace_bytes(1, 8192, 16, 32, 1 | (4 << 8)) == n + 32 * 65536
+    assert lib.actlize_la_sm100_launches_per_forward(1 | (4 << 8)) == 8
     assert lib.actlize_la_sm100_workspace_bytes(1, 64, 3, 4, 1) < 0
     assert lib.actlize_la_sm100_workspace_bytes(1, 64, 1, 1, 9) < 0
     args = [None] * 9 + [0, 1, 64, 1, 1, 1, 1, None]
