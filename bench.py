@@ -256,6 +256,9 @@ def main():
     hbm_peak, tensor_peak, peak_source = measured_peaks()
     alg_bytes, alg_flops = algorithmic_bytes(shard), algorithmic_flops(shard)
     achieved = alg_bytes / (ms_walk * 1e-3) / 1e9
+    # DRAM traffic of the walk kernel from the committed ncu capture (profiles/): 100.2 KB per
+    # (chunk, value head) block, scaled by the blocks of one whole-sequence launch
+    traffic = 100.2e3 * shard.batch * shard.value_heads * ((shard.length + 63) // 64) if config_name == "umma" else None
     roofline_ms = max(alg_bytes / (hbm_peak * 1e9), alg_flops / (tensor_peak * 1e12)) * 1e3
     line = dict(
         metric=METRIC, value=workload.tokens * world / (ms_step * 1e-3), unit=UNIT, n_gpus=world,
@@ -265,7 +268,7 @@ def main():
         gpu_launches=args.steps * lib.actlize_la_sm100_launches_per_forward(config),
         kernels_ms=dict(prepare=ms_prepare, walk=ms_walk, forward=ms_step),
         roofline=dict(bound="hbm", kernel="walk", achieved=achieved, peak=hbm_peak, unit="GB/s",
-                      frac=achieved / hbm_peak, traffic=None, peak_source=peak_source,
+                      frac=achieved / hbm_peak, traffic=traffic, peak_source=peak_source,
                       algorithmic_bytes=alg_bytes, algorithmic_flops=alg_flops,
                       whole_forward_frac=roofline_ms / ms_step),
         e2e=dict(value=workload.tokens * world / (ms_e2e * 1e-3), unit=UNIT, h2d_bytes_per_step=h2d,
