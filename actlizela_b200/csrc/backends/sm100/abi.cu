@@ -42,9 +42,12 @@ int segments_of(int config, const Geometry& geo) {
 
 // Second stream and events of the segmented forward, created by configure() for the current device.
 struct SegmentStreams {
-  cudaStream_t walk = nullptr;
+  cudaStream_t walk = nullptr;                    // high priority: the sequential chunk walks
+  cudaStream_t copy_in = nullptr, copy_out = nullptr;   // host-buffer entry: transfers next to compute
   cudaEvent_t prepared[kMaxSegments] = {};
-  cudaEvent_t done = nullptr;
+  cudaEvent_t arrived[kMaxSegments] = {};         // inputs of a segment are on the device
+  cudaEvent_t walked[kMaxSegments] = {};          // a segment's output tile rows are complete
+  cudaEvent_t done = nullptr, start = nullptr, copied = nullptr;
 };
 SegmentStreams g_streams[64];
 
@@ -58,8 +61,15 @@ int create_segment_streams() {
   int least = 0, greatest = 0;
   if ((e = cudaDeviceGetStreamPriorityRange(&least, &greatest)) != cudaSuccess) return int(e);
   if ((e = cudaStreamCreateWithPriority(&ss.walk, cudaStreamNonBlocking, greatest)) != cudaSuccess) return int(e);
-  for (cudaEvent_t& ev : ss.prepared)
-    if ((e = cudaEventCreateWithFlags(&ev, cudaEventDisableTiming)) != cudaSuccess) return int(e);
+  if ((e = cudaStreamCreateWithFlags(&ss.copy_in, cudaStreamNonBlocking)) != cudaSuccess) return int(e);
+  if ((e = cudaStreamCreateWithFlags(&ss.copy_out, cudaStreamNonBlocking)) != cudaSuccess) return int(e);
+  for (int i = 0; i < kMaxSegments; ++i) {
+    if ((e = cudaEventCreateWithFlags(&ss.prepared[i], cudaEventDisableTiming)) != cudaSuccess) return int(e);
+    if ((e = cudaEventCreateWithFlags(&ss.arrived[i], cudaEventDisableTiming)) != cudaSuccess) return int(e);
+    if ((e = cudaEventCreateWithFlags(&ss.walked[i], cudaEventDisableTiming)) != cudaSuccess) return int(e);
+  }
+  if ((e = cudaEventCreateWithFlags(&ss.start, cudaEventDisableTiming)) != cudaSuccess) return int(e);
+  if ((e = cudaEventCreateWithFlags(&ss.copied, cudaEventDisableTiming)) != cudaSuccess) return int(e);
   return int(cudaEventCreateWithFlags(&ss.done, cudaEventDisableTiming));
 }
 // bit 0: prepare stage uses tcgen05 (1) or CUDA cores (0); configuration ids:
@@ -233,6 +243,71 @@ extern "C" int actlize_la_sm100_forward_host(
   const long long qk = (long long)b * t * hk * kDim * 2, vv = (long long)b * t * hv * kDim * 2;
   const long long sc = (long long)b * t * hv, st = (long long)b * hv * kDim * kDim * 4;
   cudaError_t e;
+  {
+    Geometry geo{b, t, hk, hv};
+    const int segments = segments_of(config, geo);
+    if (segments > 1) {
+      // Pipelined form: the sequence is cut into the same chunk-aligned segments as the computation.
+      // Inputs of segment i+1 travel host -> device on one copy stream while segment i is prepared and
+      // walked, and finished output rows travel device -> host on another, so both PCIe directions and
+      // the SMs are busy at the same time.
+      int device = -1;
+      if ((e = cudaGetDevice(&device)) != cudaSuccess) return int(e);
+      if (device < 0 || device >= 64 || !g_streams[device].walk) return int(cudaErrorNotReady);   // configure() first
+      SegmentStreams& ss = g_streams[device];
+      const Inputs in{reinterpret_cast<const __nv_bfloat16*>(base + a.q), reinterpret_cast<const __nv_bfloat16*>(base + a.k),
+                      reinterpret_cast<const __nv_bfloat16*>(base + a.v), base + a.g,
+                      reinterpret_cast<const __nv_bfloat16*>(base + a.beta),
+                      initial ? reinterpret_cast<const float*>(base + a.initial) : nullptr,
+                      reinterpret_cast<__nv_bfloat16*>(base + a.output),
+                      final_state ? reinterpret_cast<float*>(base + a.final_state) : nullptr, gate_fp32 ? 1 : 0};
+      const Workspace ws = carve_workspace(base + a.workspace, geo);
+      const int chunks = geo.chunks();
+      const long long gate_bytes = gate_fp32 ? 4 : 2;
+      if ((e = cudaEventRecord(ss.start, stream)) != cudaSuccess) return int(e);
+      if ((e = cudaStreamWaitEvent(ss.copy_in, ss.start, 0)) != cudaSuccess) return int(e);
+      if ((e = cudaStreamWaitEvent(ss.copy_out, ss.start, 0)) != cudaSuccess) return int(e);
+      if (initial && (e = cudaMemcpyAsync(base + a.initial, initial, st, cudaMemcpyHostToDevice, ss.copy_in)) != cudaSuccess)
+        return int(e);
+      for (int i = 0; i < segments; ++i) {
+        geo.chunk_begin = int((long long)chunks * i / segments);
+        geo.chunk_count = int((long long)chunks * (i + 1) / segments) - geo.chunk_begin;
+        const long long t0 = (long long)geo.chunk_begin * kChunk;
+        const long long rows = ((long long)(geo.chunk_begin + geo.chunk_count) * kChunk < t ?
+                                (long long)(geo.chunk_begin + geo.chunk_count) * kChunk : t) - t0;
+        for (int bb = 0; bb < b; ++bb) {      // a segment is contiguous within one batch element
+          const long long tok = (long long)bb * t + t0;
+          struct { long long dst; const void* src; long long row; } parts[5] = {
+              {a.q, q, hk * kDim * 2LL}, {a.k, k, hk * kDim * 2LL}, {a.v, v, hv * kDim * 2LL},
+              {a.g, g, hv * gate_bytes}, {a.beta, beta, hv * 2LL}};
+          for (auto& part : parts)
+            if ((e = cudaMemcpyAsync(base + part.dst + tok * part.row, static_cast<const char*>(part.src) + tok * part.row,
+                                     rows * part.row, cudaMemcpyHostToDevice, ss.copy_in)) != cudaSuccess)
+              return int(e);
+        }
+        if ((e = cudaEventRecord(ss.arrived[i], ss.copy_in)) != cudaSuccess) return int(e);
+        if ((e = cudaStreamWaitEvent(stream, ss.arrived[i], 0)) != cudaSuccess) return int(e);
+        if (int rc = launch_prepare_umma(in, geo, ws, stream)) return rc;
+        if ((e = cudaEventRecord(ss.prepared[i], stream)) != cudaSuccess) return int(e);
+        if ((e = cudaStreamWaitEvent(ss.walk, ss.prepared[i], 0)) != cudaSuccess) return int(e);
+        if (int rc = launch_walk_umma(in, geo, ws, ss.walk)) return rc;
+        if ((e = cudaEventRecord(ss.walked[i], ss.walk)) != cudaSuccess) return int(e);
+        if ((e = cudaStreamWaitEvent(ss.copy_out, ss.walked[i], 0)) != cudaSuccess) return int(e);
+        for (int bb = 0; bb < b; ++bb) {
+          const long long off = ((long long)bb * t + t0) * hv * kDim * 2;
+          if ((e = cudaMemcpyAsync(static_cast<char*>(output) + off, base + a.output + off, rows * hv * kDim * 2,
+                                   cudaMemcpyDeviceToHost, ss.copy_out)) != cudaSuccess)
+            return int(e);
+        }
+      }
+      if (final_state &&
+          (e = cudaMemcpyAsync(final_state, base + a.final_state, st, cudaMemcpyDeviceToHost, ss.copy_out)) != cudaSuccess)
+        return int(e);
+      if ((e = cudaEventRecord(ss.copied, ss.copy_out)) != cudaSuccess) return int(e);
+      if ((e = cudaStreamWaitEvent(stream, ss.copied, 0)) != cudaSuccess) return int(e);
+      return int(cudaStreamSynchronize(stream));
+    }
+  }
 #define GDN_COPY(dst, src, bytes, kind) \
   if ((e = cudaMemcpyAsync(dst, src, bytes, kind, stream)) != cudaSuccess) return int(e)
   GDN_COPY(base + a.q, q, qk, cudaMemcpyHostToDevice);

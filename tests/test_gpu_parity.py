@@ -218,25 +218,30 @@ def test_long_sequence_segment_chaining(forward):
     _check(out[:, :, :2], state[:, :2], want_out, want_state, "cfg4-slice")
 
 
-def test_host_buffer_entry_matches_device_entry(native_library, forward):
-    case = next(c for c in ALL_CASES if c["name"] == "cfg1-scaled")
-    cpu = build_case(case)
-    q, k, v, g, beta, init = [x.contiguous() for x in cpu]
+@pytest.mark.parametrize("config", [1, 1 | (4 << 8)], ids=["one-shot", "pipelined-4-segments"])
+def test_host_buffer_entry_matches_device_entry(config, native_library, forward):
+    """Host tensors in, host tensors out; the segmented form overlaps the copies with the computation."""
+    w = WORKLOADS["cfg1"].sliced(batch=2, length=64 * 9 + 17, key_heads=1, value_heads=3)
+    cpu = [x.contiguous().pin_memory() for x in make_inputs(w)]
+    q, k, v, g, beta, init = cpu
     b, t, hk, _ = q.shape
     hv = v.shape[2]
     lib = native_library.lib
     native_library.configure(torch.device("cuda:0"))
-    nbytes = lib.actlize_la_sm100_host_arena_bytes(b, t, hk, hv, 1, 1, 1, 1)
+    nbytes = lib.actlize_la_sm100_host_arena_bytes(b, t, hk, hv, 1, 1, 1, config)
     arena = torch.empty(nbytes, dtype=torch.uint8, device="cuda")
-    out = torch.empty_like(v)
-    final = torch.empty(b, hv, 128, 128)
-    rc = lib.actlize_la_sm100_forward_host(
-        q.data_ptr(), k.data_ptr(), v.data_ptr(), g.data_ptr(), beta.data_ptr(), init.data_ptr(),
-        out.data_ptr(), final.data_ptr(), arena.data_ptr(), nbytes, b, t, hk, hv, 1, 1,
-        torch.cuda.current_stream().cuda_stream)
-    assert rc == 0
+    out = torch.empty_like(v).pin_memory()
+    final = torch.empty(b, hv, 128, 128).pin_memory()
     dev_out, dev_state = forward(*_to_device(cpu), True, configuration="umma")
-    assert torch.equal(out, dev_out.cpu()) and torch.equal(final, dev_state.cpu())
+    for _ in range(2):
+        out.zero_()
+        final.zero_()
+        rc = lib.actlize_la_sm100_forward_host(
+            q.data_ptr(), k.data_ptr(), v.data_ptr(), g.data_ptr(), beta.data_ptr(), init.data_ptr(),
+            out.data_ptr(), final.data_ptr(), arena.data_ptr(), nbytes, b, t, hk, hv, 1, config,
+            torch.cuda.current_stream().cuda_stream)
+        assert rc == 0
+        assert torch.equal(out, dev_out.cpu()) and torch.equal(final, dev_state.cpu())
 
 
 def test_apply_transition_kernel(native_library):
