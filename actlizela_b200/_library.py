@@ -39,6 +39,7 @@ EXPORTS = {
     "actlize_la_sm100_apply_transition": (_I, [_P] * 4 + [_I, _P]),
     "actlize_la_sm100_launches_per_forward": (_I, [_I]),
     "actlize_la_sm100_device_status": (_I, [_P, _I]),
+    "actlize_la_sm100_selftest_wait_timeout": (_I, [_I, _P]),
     "actlize_la_sm100_forward_static_scratch": (_I, [_P] * 8 + [_I] * 6 + [_P]),
 }
 

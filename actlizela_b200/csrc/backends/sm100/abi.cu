@@ -142,6 +142,10 @@ extern "C" int actlize_la_sm100_launches_per_forward(int config) {
   return ((config & 0xf) == 1 && segments > 1) ? 2 * segments : 2;
 }
 
+extern "C" int actlize_la_sm100_selftest_wait_timeout(int tag, void* stream) {
+  return launch_wait_timeout_selftest(tag, static_cast<cudaStream_t>(stream));
+}
+
 extern "C" int actlize_la_sm100_device_status(int* status4, int reset) {
   if (!status4) return int(cudaErrorInvalidValue);
   return read_device_status(status4, reset);

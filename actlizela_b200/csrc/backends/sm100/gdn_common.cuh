@@ -123,5 +123,6 @@ int launch_prepare_umma(const Inputs&, const Geometry&, const Workspace&, cudaSt
 int launch_walk_umma(const Inputs&, const Geometry&, const Workspace&, cudaStream_t);
 int configure_umma();
 int read_device_status(int* host_out4, int reset);
+int launch_wait_timeout_selftest(int tag, cudaStream_t);
 
 }  // namespace gdn_sm100

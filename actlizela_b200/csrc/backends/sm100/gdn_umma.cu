@@ -973,6 +973,31 @@ int launch_walk_umma(const Inputs& in, const Geometry& geo, const Workspace& ws,
   return int(cudaGetLastError());
 }
 
+namespace {
+// One CTA waits, with a small poll limit, on an mbarrier that nothing ever completes.  The wait must
+// give up, record (code 1, block 0, site 99, chunk `tag`) in the status word and let the kernel end.
+__global__ void wait_timeout_selftest_kernel(int tag, uint32_t polls) {
+  __shared__ uint64_t bar;
+  __shared__ int abort_word;
+  if (threadIdx.x == 0) {
+    mbar_init(&bar, 1);
+    abort_word = 0;
+    fence_barrier_init();
+  }
+  __syncthreads();
+  const AbortFlag abort{&abort_word};
+  bool completed = false;
+  for (uint32_t spin = 0; spin < polls && !completed; ++spin) completed = mbar_try_wait(&bar, 0);
+  if (!completed && threadIdx.x == 0) abort.raise(1, 99, tag);
+  __syncthreads();
+}
+}  // namespace
+
+int launch_wait_timeout_selftest(int tag, cudaStream_t stream) {
+  wait_timeout_selftest_kernel<<<1, 32, 0, stream>>>(tag, 1u << 12);
+  return int(cudaGetLastError());
+}
+
 int read_device_status(int* host_out4, int reset) {
   cudaError_t e = cudaMemcpyFromSymbol(host_out4, g_device_status, 4 * sizeof(int));
   if (e != cudaSuccess) return int(e);

@@ -112,6 +112,12 @@ int actlize_la_sm100_apply_transition(const float* transition, const float* offs
  * reference's serving ABI (csrc/serving/abi.h:8-17). */
 int actlize_la_sm100_device_status(int* status4, int reset);
 
+/* Failure-detection self-test: launches one small kernel whose bounded wait can never be satisfied
+ * (an mbarrier nothing arrives on, a few thousand polls).  The kernel gives up, writes
+ * (1, 0, 99, tag) to the status word read by actlize_la_sm100_device_status and ends normally: the
+ * context stays usable.  No counterpart in the reference, whose kernels wait without a limit. */
+int actlize_la_sm100_selftest_wait_timeout(int tag, void* stream);
+
 /* The same forward for callers that cannot allocate device memory (no counterpart in the
  * reference): the workspace is a fixed array inside the library instead of a caller buffer.
  * Meant for plugins inside a host framework that owns all allocations, or loops where a

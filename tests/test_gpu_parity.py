@@ -266,3 +266,67 @@ def test_segmented_walk_equals_the_single_launch_bitwise(configuration, forward,
     assert none is None and torch.equal(seg_out, out)
     torch.cuda.synchronize()
     assert _status(native_library)[0] == 0
+
+
+def test_bounded_wait_gives_up_and_reports(native_library, forward):
+    """A wait that can never be satisfied runs out, leaves a status record, and the context stays usable."""
+    lib = native_library.lib
+    assert _status(native_library)[0] == 0
+    assert lib.actlize_la_sm100_selftest_wait_timeout(4242, torch.cuda.current_stream().cuda_stream) == 0
+    torch.cuda.synchronize()
+    assert _status(native_library) == [1, 0, 99, 4242]
+    assert _status(native_library)[0] == 0            # reading with reset cleared it
+    case = next(c for c in ALL_CASES if c["name"] == "full64")
+    out, _ = forward(*_to_device(build_case(case)), True)        # the device still computes
+    assert torch.isfinite(out.float()).all()
+
+
+def test_forward_is_graph_capturable(native_library):
+    """forward_prepared (segmented: two streams joined by events) replays from a CUDA graph."""
+    w = WORKLOADS["cfg0"].sliced(length=1024, key_heads=2, value_heads=4)
+    q, k, v, g, beta, _ = _to_device(make_inputs(w))
+    b, t, hk, hv = w.shape
+    lib = native_library.lib
+    native_library.configure(q.device)          # per-device set-up happens before capture
+    config = 1 | (4 << 8)
+    nbytes = lib.actlize_la_sm100_workspace_bytes(b, t, hk, hv, config)
+    ws = torch.empty(nbytes, dtype=torch.uint8, device="cuda")
+    out = torch.empty_like(v)
+    final = torch.empty(b, hv, 128, 128, device="cuda")
+
+    def launch(stream):
+        assert lib.actlize_la_sm100_forward_prepared(
+            q.data_ptr(), k.data_ptr(), v.data_ptr(), g.data_ptr(), beta.data_ptr(), None, out.data_ptr(),
+            final.data_ptr(), ws.data_ptr(), nbytes, b, t, hk, hv, 1, config, stream.cuda_stream) == 0
+
+    launch(torch.cuda.current_stream())
+    torch.cuda.synchronize()
+    want_out, want_final = out.clone(), final.clone()
+    side, graph = torch.cuda.Stream(), torch.cuda.CUDAGraph()
+    with torch.cuda.stream(side):
+        side.wait_stream(torch.cuda.current_stream())
+        graph.capture_begin()
+        launch(side)
+        graph.capture_end()
+    for _ in range(3):
+        out.zero_()
+        final.zero_()
+        graph.replay()
+        torch.cuda.synchronize()
+        assert torch.equal(out, want_out) and torch.equal(final, want_final)
+
+
+@pytest.mark.parametrize("seed", range(6))
+def test_random_geometries(seed, forward):
+    """Randomly drawn small geometries (tails, grouped heads, both gate types, optional state)."""
+    gen = torch.Generator().manual_seed(7000 + seed)
+    pick = lambda *xs: xs[int(torch.randint(len(xs), (1,), generator=gen))]
+    hk = pick(1, 2, 3)
+    w = WORKLOADS[pick("cfg0", "cfg3")].sliced(
+        batch=pick(1, 2, 3), length=int(torch.randint(1, 700, (1,), generator=gen)), key_heads=hk,
+        value_heads=hk * pick(1, 2, 4), gate_dtype=pick("fp32", "bf16"), initial=pick(None, 0.0, 0.1),
+        seed=9000 + seed)
+    cpu = make_inputs(w)
+    want_out, want_state = oracle.chunk_forward_fp32(*cpu, output_final_state=True)
+    out, state = forward(*_to_device(cpu), True)
+    _check(out, state, want_out, want_state, ("random", seed, w.shape))
