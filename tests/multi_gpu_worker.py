@@ -1,8 +1,9 @@
 """Worker of tests/test_multi_gpu.py: one rank per GPU under torch.distributed.run.
 
 Checks, against the unsplit single-GPU forward on the same seeded inputs, that
-(1) the sequence-parallel forward returns bit-identical output segments and final state
-    (segments are chunk aligned, so chunking and rounding are the same), and
+(1) the sequence-parallel forward reproduces the output segments and the final state: bit-identical
+    on the first two ranks (segments are chunk aligned and the state is handed over as is), within
+    FP32 rounding of the affine hand-off `M S + b` on later ranks, and
 (2) the (batch, head)-sharded forward returns bit-identical slabs.
 Prints one line per rank that starts with "OK" or "FAIL".
 """
@@ -33,8 +34,14 @@ def main():
         part = [x[:, t0:t1].contiguous() for x in dev[:5]]
         out, final = gdn_forward_sequence_parallel(*part, dev[5] if rank == 0 else None, True)
         torch.cuda.synchronize()
-        ok = torch.equal(out, full_out[:, t0:t1])
-        ok = ok and ((final is None) if rank < world - 1 else torch.equal(final, full_state))
+        want = full_out[:, t0:t1].float()
+        rel_out = ((out.float() - want).norm() / want.norm()).item()
+        ok = torch.equal(out, full_out[:, t0:t1]) if rank < 2 else rel_out < 1e-3
+        if rank < world - 1:
+            ok = ok and final is None
+        else:
+            rel_state = ((final - full_state).norm() / full_state.norm()).item()
+            ok = ok and (torch.equal(final, full_state) if world == 2 else rel_state < 1e-5)
         pieces = gdn_forward_sharded(*dev, True, rank=rank, world_size=world)
         ok = ok and all(torch.equal(o, full_out[b0:b1, :, v0:v1]) and torch.equal(s, full_state[b0:b1, v0:v1])
                         for (b0, b1, v0, v1), o, s in pieces)
