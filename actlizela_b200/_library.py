@@ -40,6 +40,9 @@ EXPORTS = {
     "actlize_la_sm100_launches_per_forward": (_I, [_I]),
     "actlize_la_sm100_device_status": (_I, [_P, _I]),
     "actlize_la_sm100_selftest_wait_timeout": (_I, [_I, _P]),
+    "actlize_la_sm100_prepare_inputs": (_I, [_P, _LL] + [_P] * 9 + [_LL, _I, _I, _P]),
+    "actlize_la_sm100_decode_step": (_I, [_P] * 7 + [_I] * 4 + [_P]),
+    "actlize_la_sm100_rmsnorm_gated": (_I, [_P] * 4 + [_LL, _P]),
     "actlize_la_sm100_forward_static_scratch": (_I, [_P] * 8 + [_I] * 6 + [_P]),
 }
 
@@ -139,7 +142,13 @@ def _load(path, digest):
     return NativeLibrary(info)
 
 
-def load_library():
-    """The verified native library (cached by path and content hash)."""
-    info = get_library_info()
+@lru_cache(maxsize=None)
+def _load_selected(override):
+    info = get_library_info(override)
     return _load(info["library_path"], info["library_sha256"])
+
+
+def load_library():
+    """The verified native library.  Discovery, hashing and dlopen happen once per selection (the value of
+    the environment override); later calls are a dictionary look-up: no file I/O or hashing per call."""
+    return _load_selected(os.environ.get(ENVIRONMENT_OVERRIDE))

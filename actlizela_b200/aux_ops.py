@@ -1,0 +1,86 @@
+"""The steps either side of the chunked forward, on the same native library.
+
+* ``gdn_prepare_inputs``: Q/K L2 normalisation, gate activation and beta from a fused projection
+  (reference: csrc/serving/prefill.cu:45-70, csrc/serving/runtime.cuh:48-52).
+* ``gdn_decode_step``: one token on the FP32 ``[B,Hv,128,128]`` K-by-V state, in place
+  (reference: actlize_la/reference/gdn_chunk_ref.py:135-143; csrc/serving/gdn.cu:152).
+* ``rmsnorm_gated``: ``y * rsqrt(mean y^2 + 1e-6) * weight * silu(z)`` per 128-wide row
+  (reference: actlize_la.rmsnorm_gated, docs/OUTPUT_GATE.md:7-15).
+All three are single memory-bound kernels launched on the caller's current stream.
+"""
+from __future__ import annotations
+
+from ._library import load_library
+
+
+def _bf16_cuda(x, name, last=None):
+    import torch
+    if x.dtype != torch.bfloat16 or x.device.type != "cuda" or not x.is_contiguous():
+        raise ValueError(f"{name} must be a contiguous BF16 CUDA tensor")
+    if last is not None and x.shape[-1] != last:
+        raise ValueError(f"{name} must have a last dimension of {last}")
+
+
+def gdn_prepare_inputs(mixed, a, b, a_log, dt_bias, key_heads, value_heads):
+    """mixed [N, (2Hk+Hv)*128] BF16, a,b [N,Hv] BF16, a_log, dt_bias [Hv] FP32 ->
+    (q [N,Hk,128], k [N,Hk,128], v [N,Hv,128] BF16, g [N,Hv] FP32, beta [N,Hv] BF16)."""
+    import torch
+    _bf16_cuda(a, "a", value_heads)
+    _bf16_cuda(b, "b", value_heads)
+    if mixed.dtype != torch.bfloat16 or mixed.device.type != "cuda" or mixed.ndim != 2 or mixed.stride(1) != 1:
+        raise ValueError("mixed must be a 2-D BF16 CUDA tensor with unit inner stride")
+    n, width = mixed.shape
+    if width != (2 * key_heads + value_heads) * 128 or value_heads % key_heads:
+        raise ValueError("mixed must hold [q heads | k heads | v heads] x 128 and Hv % Hk == 0")
+    if a_log.dtype != torch.float32 or dt_bias.dtype != torch.float32 or a_log.numel() != value_heads:
+        raise ValueError("a_log and dt_bias must be FP32 [Hv]")
+    lib = load_library()
+    q = torch.empty(n, key_heads, 128, dtype=torch.bfloat16, device=mixed.device)
+    k = torch.empty_like(q)
+    v = torch.empty(n, value_heads, 128, dtype=torch.bfloat16, device=mixed.device)
+    g = torch.empty(n, value_heads, dtype=torch.float32, device=mixed.device)
+    beta = torch.empty(n, value_heads, dtype=torch.bfloat16, device=mixed.device)
+    with torch.cuda.device(mixed.device):
+        lib.check(lib.lib.actlize_la_sm100_prepare_inputs(
+            mixed.data_ptr(), mixed.stride(0), a.data_ptr(), b.data_ptr(), a_log.data_ptr(), dt_bias.data_ptr(),
+            q.data_ptr(), k.data_ptr(), v.data_ptr(), g.data_ptr(), beta.data_ptr(), n, key_heads, value_heads,
+            torch.cuda.current_stream().cuda_stream))
+    return q, k, v, g, beta
+
+
+def gdn_decode_step(q, k, v, g, beta, state):
+    """q,k [B,Hk,128], v [B,Hv,128] BF16, g [B,Hv] (BF16/FP32 natural-log decay), beta [B,Hv] BF16,
+    state FP32 [B,Hv,128,128] updated IN PLACE.  Returns the BF16 output [B,Hv,128]."""
+    import torch
+    for name, x in (("q", q), ("k", k), ("v", v), ("beta", beta)):
+        _bf16_cuda(x, name)
+    b_, hk = q.shape[0], q.shape[1]
+    hv = v.shape[1]
+    if tuple(state.shape) != (b_, hv, 128, 128) or state.dtype != torch.float32 or not state.is_contiguous():
+        raise ValueError("state must be contiguous FP32 [B,Hv,128,128] in K-by-V order")
+    if g.dtype not in (torch.bfloat16, torch.float32) or tuple(g.shape) != (b_, hv) or hv % hk:
+        raise ValueError("g must be BF16/FP32 [B,Hv] and Hv % Hk == 0")
+    lib = load_library()
+    out = torch.empty_like(v)
+    with torch.cuda.device(q.device):
+        lib.check(lib.lib.actlize_la_sm100_decode_step(
+            q.data_ptr(), k.data_ptr(), v.data_ptr(), g.data_ptr(), beta.data_ptr(), state.data_ptr(),
+            out.data_ptr(), b_, hk, hv, int(g.dtype == torch.float32), torch.cuda.current_stream().cuda_stream))
+    return out
+
+
+def rmsnorm_gated(y, z, weight):
+    """y, z [..., 128] BF16, weight [128] BF16 -> BF16 tensor shaped like y."""
+    import torch
+    _bf16_cuda(y, "y", 128)
+    _bf16_cuda(z, "z", 128)
+    _bf16_cuda(weight, "weight", 128)
+    if y.shape != z.shape or weight.numel() != 128:
+        raise ValueError("y and z must have the same shape and weight 128 entries")
+    lib = load_library()
+    out = torch.empty_like(y)
+    with torch.cuda.device(y.device):
+        lib.check(lib.lib.actlize_la_sm100_rmsnorm_gated(
+            y.data_ptr(), z.data_ptr(), weight.data_ptr(), out.data_ptr(), y.numel() // 128,
+            torch.cuda.current_stream().cuda_stream))
+    return out

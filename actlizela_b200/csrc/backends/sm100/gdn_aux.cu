@@ -1,0 +1,178 @@
+// Memory-bound companions of the chunked forward: the step before it (Q/K normalisation and gate
+// activation), the single-token decode step on the same state layout, and the gated RMSNorm after it.
+// Each is one streaming kernel whose roofline is HBM bandwidth; none needs tensor cores.
+//
+// Reference behaviour restated here (paths relative to the reference tree):
+//   prepare_inputs   csrc/serving/prefill.cu:45-70 and csrc/serving/runtime.cuh:48-52
+//                    (q,k <- x * rsqrt(sum x^2 + 1e-6) per 128-vector, v copied,
+//                     g = -exp(A_log) * softplus(a + dt_bias) with the z > 20 branch, beta = sigmoid(b))
+//   decode_step      actlize_la/reference/gdn_chunk_ref.py:135-143 (token recurrence), kernel analogue
+//                    csrc/serving/gdn.cu:152 (recurrent_gdn); state kept in the public K-by-V order
+//   rmsnorm_gated    csrc/output_gate/output_gate.cu:4-5,73-92 (out = y * rsqrt(mean y^2 + 1e-6) * w * silu(z))
+#include "actlize_la_sm100.h"
+#include "gdn_common.cuh"
+
+#include <climits>
+
+namespace gdn_sm100 {
+namespace {
+
+__device__ __forceinline__ float lo_bf16(uint32_t p) { return __uint_as_float(p << 16); }
+__device__ __forceinline__ float hi_bf16(uint32_t p) { return __uint_as_float(p & 0xffff0000u); }
+
+// 16 lanes per 128-wide head vector (8 BF16 = 16 bytes per lane), 16 vectors per 256-thread CTA.
+__global__ void __launch_bounds__(256)
+prepare_inputs_kernel(const __nv_bfloat16* __restrict__ mixed, long long mixed_stride,
+                      const __nv_bfloat16* __restrict__ a, const __nv_bfloat16* __restrict__ b,
+                      const float* __restrict__ a_log, const float* __restrict__ dt_bias,
+                      __nv_bfloat16* __restrict__ q, __nv_bfloat16* __restrict__ k, __nv_bfloat16* __restrict__ v,
+                      float* __restrict__ g, __nv_bfloat16* __restrict__ beta, long long tokens, int hk, int hv) {
+  const int heads = 2 * hk + hv;
+  const long long slot = (long long)blockIdx.x * 16 + (threadIdx.x >> 4);
+  const bool live = slot < tokens * heads;    // idle groups redo the last vector and store nothing
+  const long long vec = live ? slot : tokens * heads - 1;
+  const int lane = threadIdx.x & 15;
+  const long long token = vec / heads;
+  const int h = int(vec % heads);
+  const uint4 x = *reinterpret_cast<const uint4*>(mixed + token * mixed_stride + (long long)h * kDim + lane * 8);
+  if (h < 2 * hk) {
+    float f[8] = {lo_bf16(x.x), hi_bf16(x.x), lo_bf16(x.y), hi_bf16(x.y),
+                  lo_bf16(x.z), hi_bf16(x.z), lo_bf16(x.w), hi_bf16(x.w)};
+    float square = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) square = fmaf(f[i], f[i], square);
+#pragma unroll
+    for (int d = 8; d; d >>= 1) square += __shfl_xor_sync(0xffffffffu, square, d, 16);
+    const float factor = rsqrtf(square + 1e-6f);
+    uint4 o;
+    o.x = pack_bf16(f[0] * factor, f[1] * factor);
+    o.y = pack_bf16(f[2] * factor, f[3] * factor);
+    o.z = pack_bf16(f[4] * factor, f[5] * factor);
+    o.w = pack_bf16(f[6] * factor, f[7] * factor);
+    __nv_bfloat16* dst = (h < hk ? q : k) + (token * hk + (h % hk)) * kDim + lane * 8;
+    if (live) *reinterpret_cast<uint4*>(dst) = o;
+  } else {
+    const int vh = h - 2 * hk;
+    if (live) *reinterpret_cast<uint4*>(v + (token * hv + vh) * kDim + lane * 8) = x;
+    if (live && lane == 0) {
+      const long long at = token * hv + vh;
+      const float z = __bfloat162float(a[at]) + dt_bias[vh];
+      g[at] = -expf(a_log[vh]) * (z > 20.f ? z : log1pf(expf(z)));
+      beta[at] = __float2bfloat16_rn(1.f / (1.f + expf(-__bfloat162float(b[at]))));
+    }
+  }
+}
+
+// One CTA per (batch, value head), 256 threads: thread = (value column, half of the 128 key rows).  Its 64
+// state entries live in registers, so the state is read once and written once (128 KiB of traffic per
+// head and step); the two row halves meet through shared memory for k^T S and q^T S.
+__global__ void __launch_bounds__(256)
+decode_step_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k,
+                   const __nv_bfloat16* __restrict__ v, const void* __restrict__ g,
+                   const __nv_bfloat16* __restrict__ beta, float* __restrict__ state,
+                   __nv_bfloat16* __restrict__ out, int hk, int hv, int gate_fp32) {
+  __shared__ float sk[kDim], sq[kDim], partial[2][kDim];
+  const int bh = blockIdx.x, col = threadIdx.x & (kDim - 1), half = threadIdx.x >> 7;
+  const int bidx = bh / hv, vh = bh % hv;
+  const long long qk_at = ((long long)bidx * hk + vh / (hv / hk)) * kDim;
+  if (half == 0) sk[col] = __bfloat162float(k[qk_at + col]);
+  else sq[col] = __bfloat162float(q[qk_at + col]);
+  const float decay = expf(load_gate(g, bh, gate_fp32));
+  const float bt = __bfloat162float(beta[bh]);
+  const float value = __bfloat162float(v[(long long)bh * kDim + col]);
+  float* column = state + ((long long)bh * kDim + half * 64) * kDim + col;
+  float s[64];
+#pragma unroll
+  for (int r = 0; r < 64; ++r) s[r] = column[r * kDim] * decay;
+  __syncthreads();
+  const float* kk = sk + half * 64;
+  const float* qq = sq + half * 64;
+  float kv = 0.f;
+#pragma unroll
+  for (int r = 0; r < 64; ++r) kv = fmaf(kk[r], s[r], kv);
+  partial[half][col] = kv;
+  __syncthreads();
+  const float delta = bt * (value - (partial[0][col] + partial[1][col]));
+  float o = 0.f;
+#pragma unroll
+  for (int r = 0; r < 64; ++r) {
+    s[r] = fmaf(kk[r], delta, s[r]);
+    o = fmaf(qq[r], s[r], o);
+    column[r * kDim] = s[r];
+  }
+  __syncthreads();
+  partial[half][col] = o;
+  __syncthreads();
+  if (half == 0) out[(long long)bh * kDim + col] = __float2bfloat16_rn((partial[0][col] + partial[1][col]) * kScale);
+}
+
+// One warp per 128-wide row, 8 rows per CTA.
+__global__ void __launch_bounds__(256)
+rmsnorm_gated_kernel(const __nv_bfloat16* __restrict__ y, const __nv_bfloat16* __restrict__ z,
+                     const __nv_bfloat16* __restrict__ weight, __nv_bfloat16* __restrict__ out, long long rows) {
+  const long long row = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
+  if (row >= rows) return;
+  const int lane = threadIdx.x & 31;
+  const uint2 yy = *reinterpret_cast<const uint2*>(y + row * kDim + lane * 4);
+  const uint2 zz = *reinterpret_cast<const uint2*>(z + row * kDim + lane * 4);
+  const uint2 ww = *reinterpret_cast<const uint2*>(weight + lane * 4);
+  const float yf[4] = {lo_bf16(yy.x), hi_bf16(yy.x), lo_bf16(yy.y), hi_bf16(yy.y)};
+  const float zf[4] = {lo_bf16(zz.x), hi_bf16(zz.x), lo_bf16(zz.y), hi_bf16(zz.y)};
+  const float wf[4] = {lo_bf16(ww.x), hi_bf16(ww.x), lo_bf16(ww.y), hi_bf16(ww.y)};
+  float square = yf[0] * yf[0] + yf[1] * yf[1] + yf[2] * yf[2] + yf[3] * yf[3];
+#pragma unroll
+  for (int d = 16; d; d >>= 1) square += __shfl_xor_sync(0xffffffffu, square, d);
+  const float rstd = rsqrtf(square * (1.f / kDim) + 1e-6f);
+  float r[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) r[i] = yf[i] * rstd * wf[i] * (zf[i] / (1.f + expf(-zf[i])));
+  uint2 o;
+  o.x = pack_bf16(r[0], r[1]);
+  o.y = pack_bf16(r[2], r[3]);
+  *reinterpret_cast<uint2*>(out + row * kDim + lane * 4) = o;
+}
+
+}  // namespace
+}  // namespace gdn_sm100
+
+using namespace gdn_sm100;
+
+extern "C" int actlize_la_sm100_prepare_inputs(
+    const void* mixed, long long mixed_row_stride, const void* a, const void* b, const float* a_log,
+    const float* dt_bias, void* q, void* k, void* v, float* g, void* beta, long long tokens, int hk, int hv,
+    void* stream) {
+  if (!mixed || !a || !b || !a_log || !dt_bias || !q || !k || !v || !g || !beta) return int(cudaErrorInvalidValue);
+  if (tokens <= 0 || hk <= 0 || hv <= 0 || hv % hk || mixed_row_stride < (2LL * hk + hv) * kDim ||
+      (mixed_row_stride & 7) || (reinterpret_cast<uintptr_t>(mixed) & 15))
+    return int(cudaErrorInvalidValue);
+  const long long vectors = tokens * (2LL * hk + hv);
+  if ((vectors + 15) / 16 > INT_MAX) return int(cudaErrorInvalidValue);
+  prepare_inputs_kernel<<<(unsigned)((vectors + 15) / 16), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(mixed), mixed_row_stride, static_cast<const __nv_bfloat16*>(a),
+      static_cast<const __nv_bfloat16*>(b), a_log, dt_bias, static_cast<__nv_bfloat16*>(q),
+      static_cast<__nv_bfloat16*>(k), static_cast<__nv_bfloat16*>(v), g, static_cast<__nv_bfloat16*>(beta), tokens, hk, hv);
+  return int(cudaGetLastError());
+}
+
+extern "C" int actlize_la_sm100_decode_step(
+    const void* q, const void* k, const void* v, const void* g, const void* beta, float* state, void* output,
+    int batch, int hk, int hv, int gate_fp32, void* stream) {
+  if (!q || !k || !v || !g || !beta || !state || !output) return int(cudaErrorInvalidValue);
+  if (batch <= 0 || hk <= 0 || hv <= 0 || hv % hk || (long long)batch * hv > INT_MAX) return int(cudaErrorInvalidValue);
+  decode_step_kernel<<<batch * hv, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(q), static_cast<const __nv_bfloat16*>(k), static_cast<const __nv_bfloat16*>(v),
+      g, static_cast<const __nv_bfloat16*>(beta), state, static_cast<__nv_bfloat16*>(output), hk, hv, gate_fp32 ? 1 : 0);
+  return int(cudaGetLastError());
+}
+
+extern "C" int actlize_la_sm100_rmsnorm_gated(const void* y, const void* z, const void* weight, void* out,
+                                              long long rows, void* stream) {
+  if (!y || !z || !weight || !out || rows <= 0 || (rows + 7) / 8 > INT_MAX) return int(cudaErrorInvalidValue);
+  if ((reinterpret_cast<uintptr_t>(y) | reinterpret_cast<uintptr_t>(z) | reinterpret_cast<uintptr_t>(weight) |
+       reinterpret_cast<uintptr_t>(out)) & 7)
+    return int(cudaErrorInvalidValue);
+  rmsnorm_gated_kernel<<<(unsigned)((rows + 7) / 8), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(y), static_cast<const __nv_bfloat16*>(z),
+      static_cast<const __nv_bfloat16*>(weight), static_cast<__nv_bfloat16*>(out), rows);
+  return int(cudaGetLastError());
+}

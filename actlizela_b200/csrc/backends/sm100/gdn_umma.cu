@@ -174,11 +174,16 @@ prepare_umma_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
     mbar_init(bar_mma, 1);
     *abort_word = 0;
     fence_barrier_init();
-    prefetch_tensormap(&tm_q);
-    prefetch_tensormap(&tm_k);
-    prefetch_tensormap(&tm_v);
+    // the input tiles do not depend on tensor memory: start them before the allocation
+    mbar_arrive_expect_tx(bar_tma, 6 * kBox);
+    tma_load_4d(sm + L::kQ0, &tm_q, bar_tma, 0, hk, t0, b);
+    tma_load_4d(sm + L::kQ1, &tm_q, bar_tma, 64, hk, t0, b);
+    tma_load_4d(sm + L::kK0, &tm_k, bar_tma, 0, hk, t0, b);
+    tma_load_4d(sm + L::kK1, &tm_k, bar_tma, 64, hk, t0, b);
+    tma_load_4d(sm + L::kV0, &tm_v, bar_tma, 0, hv, t0, b);
+    tma_load_4d(sm + L::kV1, &tm_v, bar_tma, 64, hv, t0, b);
   }
-  if (warp == 0) {
+  if (warp == 1) {
     tmem_alloc(tmem_slot, kPrepTmemCols);
     tmem_relinquish();
   }
@@ -194,15 +199,6 @@ prepare_umma_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
   const uint32_t tmem = *tmem_slot;
   GDN_PSTAMP(0);
 
-  if (tid == 0) {
-    mbar_arrive_expect_tx(bar_tma, 6 * kBox);
-    tma_load_4d(sm + L::kQ0, &tm_q, bar_tma, 0, hk, t0, b);
-    tma_load_4d(sm + L::kQ1, &tm_q, bar_tma, 64, hk, t0, b);
-    tma_load_4d(sm + L::kK0, &tm_k, bar_tma, 0, hk, t0, b);
-    tma_load_4d(sm + L::kK1, &tm_k, bar_tma, 64, hk, t0, b);
-    tma_load_4d(sm + L::kV0, &tm_v, bar_tma, 0, hv, t0, b);
-    tma_load_4d(sm + L::kV1, &tm_v, bar_tma, 64, hv, t0, b);
-  }
   const float prefix = chunk_prefix64(gate, tid, carry);   // contains a __syncthreads
   if (tid < kChunk) {
     const float e = exp2f(prefix * kLog2e);
@@ -543,7 +539,7 @@ prepare_umma_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
   }
   tc_fence_before();
   __syncthreads();
-  if (warp == 0) tmem_dealloc(tmem, kPrepTmemCols);
+  if (warp == 1) tmem_dealloc(tmem, kPrepTmemCols);
 }
 #undef GDN_PSTAMP
 

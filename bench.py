@@ -132,6 +132,58 @@ def reference_arm(args, workload):
     print(json.dumps(line), flush=True)
 
 
+def aux_bench(args):
+    """Memory-bound neighbours of the forward: one JSON line with the achieved HBM fraction."""
+    import torch
+    from actlizela_b200 import gdn_decode_step, gdn_prepare_inputs, rmsnorm_gated
+    torch.cuda.set_device(0)
+    gen = torch.Generator().manual_seed(1)
+    hk, hv = 16, 32
+    if args.op == "decode":
+        batch = 256                              # 8192 states of 64 KiB: 537 MB, read once and written once
+        q = torch.randn(batch, hk, 128, generator=gen).to(torch.bfloat16).cuda()
+        v = torch.randn(batch, hv, 128, generator=gen).to(torch.bfloat16).cuda()
+        g = (-torch.rand(batch, hv, generator=gen)).cuda()
+        beta = torch.rand(batch, hv, generator=gen).to(torch.bfloat16).cuda()
+        state = torch.zeros(batch, hv, 128, 128, device="cuda")
+        call = lambda: gdn_decode_step(q, q, v, g, beta, state)
+        nbytes, units, unit = 2 * state.numel() * 4 + 2 * q.numel() * 2 + 2 * v.numel() * 2, batch, "tokens/s"
+        name = f"decode_step B{batch} Hk{hk} Hv{hv}"
+    elif args.op == "prepare_inputs":
+        n = 65536
+        mixed = torch.randn(n, (2 * hk + hv) * 128, generator=gen).to(torch.bfloat16).cuda()
+        a = torch.randn(n, hv, generator=gen).to(torch.bfloat16).cuda()
+        a_log, bias = torch.zeros(hv, device="cuda"), torch.zeros(hv, device="cuda")
+        call = lambda: gdn_prepare_inputs(mixed, a, a, a_log, bias, hk, hv)
+        nbytes, units, unit = 2 * mixed.numel() * 2 + n * hv * (2 + 2 + 4 + 2), n, "tokens/s"
+        name = f"prepare_inputs N{n} Hk{hk} Hv{hv}"
+    else:
+        rows = 65536 * hv
+        y = torch.randn(rows, 128, generator=gen).to(torch.bfloat16).cuda()
+        w = torch.ones(128, dtype=torch.bfloat16, device="cuda")
+        call = lambda: rmsnorm_gated(y, y, w)
+        nbytes, units, unit = 3 * y.numel() * 2, rows // hv, "tokens/s"
+        name = f"rmsnorm_gated rows{rows}"
+    for _ in range(max(3, args.warmup)):
+        call()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    start.record()
+    for _ in range(args.steps):
+        call()
+    stop.record()
+    torch.cuda.synchronize()
+    ms = start.elapsed_time(stop) / args.steps
+    peak, _, source = measured_peaks()
+    achieved = nbytes / (ms * 1e-3) / 1e9
+    print(json.dumps(dict(metric=f"{args.op} {unit}", value=units / (ms * 1e-3), unit=unit, n_gpus=1, steps=args.steps,
+                          warmup=max(3, args.warmup), ms_per_step=ms, higher_is_better=True, data="synthetic",
+                          config=dict(workload=name, l2="working set exceeds the 126 MB L2"),
+                          gpu_launches=args.steps,
+                          roofline=dict(bound="hbm", achieved=achieved, peak=peak, unit="GB/s", frac=achieved / peak,
+                                        traffic=None, peak_source=source, algorithmic_bytes=nbytes))), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser(description=__doc__)
     ap.add_argument("--gpus", type=int, default=1)
@@ -141,7 +193,11 @@ def main():
     ap.add_argument("--configuration", default=None, help="diagnostic override of the policy table")
     ap.add_argument("--impl", default="native", choices=("native", "reference"))
     ap.add_argument("--skip-cpu-baseline", action="store_true")
+    ap.add_argument("--op", default="forward", choices=("forward", "decode", "prepare_inputs", "rmsnorm_gated"),
+                    help="forward is the headline metric; the others time a neighbouring memory-bound kernel")
     args = ap.parse_args()
+    if args.op != "forward":
+        return aux_bench(args)
 
     from actlizela_b200.workloads import WORKLOADS, algorithmic_bytes, algorithmic_flops, make_inputs
     workload = WORKLOADS[args.workload]

@@ -105,6 +105,32 @@ int actlize_la_sm100_apply_transition(const float* transition, const float* offs
                                       const float* state_in, float* state_out,
                                       int blocks, void* stream);
 
+/* ---- the steps either side of the forward (memory-bound, one streaming kernel each) ---- */
+
+/* Step before: from a fused projection row [q heads | k heads | v heads] x 128 BF16 per token
+ * (row stride in elements), raw gate inputs a, b [tokens, Hv] BF16 and per-head A_log, dt_bias FP32:
+ * q,k <- x * rsqrt(sum x^2 + 1e-6) per head vector, v copied, g = -exp(A_log) * softplus(a + dt_bias)
+ * (FP32, natural log), beta = sigmoid(b) (BF16).  Outputs are the contiguous gdn_forward inputs.
+ * Replaces the packing kernel of the reference's prefill adapter (csrc/serving/prefill.cu:45-70,
+ * csrc/serving/runtime.cuh:48-52). */
+int actlize_la_sm100_prepare_inputs(
+    const void* mixed, long long mixed_row_stride, const void* a, const void* b, const float* a_log,
+    const float* dt_bias, void* q, void* k, void* v, float* g, void* beta, long long tokens,
+    int key_heads, int value_heads, void* stream);
+
+/* Single-token decode step on the same FP32 [B,Hv,128,128] K-by-V state, updated in place:
+ * S <- exp(g) S; d = beta (v - k^T S); S <- S + k d^T; out = q^T S / sqrt(128).
+ * q,k [B,Hk,128], v,out [B,Hv,128] BF16, g,beta [B,Hv].  Equals gdn_forward with T = 1.
+ * Replaces the recurrent kernel of the reference's serving library (csrc/serving/gdn.cu:152). */
+int actlize_la_sm100_decode_step(
+    const void* q, const void* k, const void* v, const void* g, const void* beta, float* state, void* output,
+    int batch, int key_heads, int value_heads, int gate_fp32, void* stream);
+
+/* Step after: out = y * rsqrt(mean(y^2) + 1e-6) * weight * silu(z) per 128-wide row, BF16.
+ * Replaces rmsnorm_gated (csrc/output_gate/output_gate.cu:4-5,73-92). */
+int actlize_la_sm100_rmsnorm_gated(const void* y, const void* z, const void* weight, void* out,
+                                   long long rows, void* stream);
+
 /* Diagnostic word written by a kernel whose bounded wait ran out (all waits on barriers are
  * bounded; a kernel that gives up drains, frees its tensor memory and returns): status4[0] = 0
  * when healthy else a failure code, [1] block index, [2] wait site, [3] chunk.  Synchronises the

@@ -224,3 +224,29 @@ def segment_transition(k, g, beta, dtype=torch.float64):
     eye = torch.eye(d, dtype=dtype).expand(b, hv, d, d).contiguous()
     _, m = recurrent_forward(k, k, zero_v, g, beta, initial_state=eye, dtype=dtype)
     return m
+
+
+# --------------------------------------------------------------------------- neighbouring steps
+def prepare_inputs_ref(mixed, a, b, a_log, dt_bias, key_heads, value_heads):
+    """The step before the forward, as the reference's serving path defines it
+    (tests/serving_reference.py:11-23; csrc/serving/prefill.cu:45-70, runtime.cuh:48-52):
+    q,k = x / sqrt(sum x^2 + 1e-6) rounded to BF16 (no 1/sqrt(128): the forward applies it),
+    v copied, g = -exp(A_log) * softplus(a + dt_bias) in FP32, beta = sigmoid(b) rounded to BF16."""
+    n = mixed.shape[0]
+    x = mixed.float()
+    hk, hv = key_heads, value_heads
+    q = x[:, :hk * 128].reshape(n, hk, 128)
+    k = x[:, hk * 128:2 * hk * 128].reshape(n, hk, 128)
+    v = mixed[:, 2 * hk * 128:].reshape(n, hv, 128)
+    q = (q / torch.sqrt(q.square().sum(-1, keepdim=True) + 1e-6)).to(torch.bfloat16)
+    k = (k / torch.sqrt(k.square().sum(-1, keepdim=True) + 1e-6)).to(torch.bfloat16)
+    g = -a_log.float().exp() * F.softplus(a.float() + dt_bias.float(), threshold=20)
+    beta = b.float().sigmoid().to(torch.bfloat16)
+    return q, k, v.clone(), g, beta
+
+
+def rmsnorm_gated_ref(y, z, weight, eps=1e-6):
+    """tests/test_output_gate.py:12-16 restated: RMSNorm(y) * weight * silu(z), FP32 math, input dtype out."""
+    yf = y.float()
+    normed = yf * torch.rsqrt(yf.square().mean(-1, keepdim=True) + eps)
+    return (normed * weight.float() * F.silu(z.float())).to(y.dtype)

@@ -71,3 +71,15 @@ def build_case(case):
     if case["initial"]:
         initial = 0.005 * torch.randn(b, hv, 128, 128, generator=torch.Generator().manual_seed(17))
     return q, k, v, g, beta, initial
+
+
+def prestep_case():
+    """Raw projection inputs of the step before the forward (shapes of tests/serving_reference.py:7-23)."""
+    gen = torch.Generator().manual_seed(4711)
+    hk, hv, n = 2, 4, 70
+    mixed = torch.randn(n, (2 * hk + hv) * 128, generator=gen).to(torch.bfloat16)
+    a = torch.randn(n, hv, generator=gen).to(torch.bfloat16)
+    b = torch.randn(n, hv, generator=gen).to(torch.bfloat16)
+    a_log = torch.randn(hv, generator=gen) * 0.5
+    dt_bias = torch.randn(hv, generator=gen)
+    return mixed, a, b, a_log, dt_bias, hk, hv

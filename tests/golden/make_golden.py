@@ -91,6 +91,23 @@ def main():
                            fp32_vs_fp64_state_rel_frobenius=oracle.rel_frobenius(ref_state, dbl_state),
                            fp32_vs_fp64_out_rel_frobenius=oracle.rel_frobenius(ref_out.double(), dbl_out))
         print(f"{name:28s} ok  state relF(fp32 ref vs fp64)={index[name]['fp32_vs_fp64_state_rel_frobenius']:.2e}")
+    # ---- the step before the forward: the reference's serving recurrence on raw projection inputs
+    from serving_reference import gdn_reference
+    from tests.cases import prestep_case
+    mixed, a, b, a_log, dt_bias, hk, hv = prestep_case()
+    ref_out, ref_state_vk, _, ref_key, ref_decay = gdn_reference(
+        mixed, a, b, a_log, dt_bias, torch.zeros(hv, 128, 128), hk)
+    q, k, v, g, beta = oracle.prepare_inputs_ref(mixed, a, b, a_log, dt_bias, hk, hv)
+    assert (k.float() - ref_key).abs().max() <= 2 ** -8 * ref_key.abs().max()          # BF16 rounding of k only
+    assert oracle.rel_frobenius(g.exp(), ref_decay) < 1e-6
+    mine_out, mine_state = oracle.recurrent_forward(q[None], k[None], v[None], g[None], beta[None], None)
+    assert oracle.max_abs(mine_out[0], ref_out.double()) < 2e-2
+    assert oracle.rel_frobenius(mine_state[0].transpose(-1, -2), ref_state_vk.double()) < 1e-2   # ref state is V-by-K
+    arrays["prestep.key_f32"] = ref_key.numpy()
+    arrays["prestep.decay_f32"] = ref_decay.numpy()
+    arrays["prestep.out_bf16"] = ref_out.view(torch.int16).numpy()
+    print("prestep                      ok")
+
     np.savez_compressed(args.out, **arrays)
     args.out.with_suffix(".json").write_text(json.dumps(
         dict(schema=1, torch=torch.__version__, cases=index), indent=1, sort_keys=True) + "\n")

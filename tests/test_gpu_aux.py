@@ -1,0 +1,101 @@
+"""Device parity of the steps either side of the forward and of the packed-sequence wrapper."""
+import pytest
+import torch
+
+from oracle import gdn_oracle as oracle
+from tests.cases import prestep_case
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module", autouse=True)
+def _library(native_library):
+    if not torch.cuda.is_available():
+        pytest.fail("the gpu tests need a CUDA device; there is no CPU fallback to test")
+
+
+def test_prepare_inputs_matches_oracle():
+    from actlizela_b200 import gdn_prepare_inputs
+    mixed, a, b, a_log, dt_bias, hk, hv = prestep_case()
+    want = oracle.prepare_inputs_ref(mixed, a, b, a_log, dt_bias, hk, hv)
+    got = gdn_prepare_inputs(mixed.cuda(), a.cuda(), b.cuda(), a_log.cuda(), dt_bias.cuda(), hk, hv)
+    for name, x, y in zip(("q", "k", "v", "g", "beta"), got, want):
+        x, y = x.float().cpu(), y.float()
+        # identical up to one BF16 ulp where rsqrt / exp differ in the last FP32 bit
+        assert (x - y).abs().max() <= 2 ** -7 * y.abs().max() + 1e-6, name
+        assert oracle.rel_frobenius(x, y) < 1e-3, name
+    assert torch.equal(got[2].cpu(), want[2])          # v is a copy
+
+
+@pytest.mark.parametrize("batch,hk,hv,gate", [(1, 1, 1, torch.float32), (3, 2, 8, torch.bfloat16), (16, 16, 32, torch.float32)])
+def test_decode_step_matches_recurrence(batch, hk, hv, gate):
+    from actlizela_b200 import gdn_decode_step
+    gen = torch.Generator().manual_seed(batch * 100 + hv)
+    norm = torch.nn.functional.normalize
+    q = norm(torch.randn(batch, hk, 128, generator=gen), dim=-1).to(torch.bfloat16)
+    k = norm(torch.randn(batch, hk, 128, generator=gen), dim=-1).to(torch.bfloat16)
+    v = torch.randn(batch, hv, 128, generator=gen).to(torch.bfloat16)
+    g = torch.nn.functional.logsigmoid(torch.randn(batch, hv, generator=gen) + 2).to(gate)
+    beta = torch.sigmoid(torch.randn(batch, hv, generator=gen)).to(torch.bfloat16)
+    state = torch.randn(batch, hv, 128, 128, generator=gen) * 0.3
+    dev_state = state.cuda()
+    for step in range(3):                      # three tokens in a row on the same state
+        want_out, want_state = oracle.recurrent_forward(q[:, None], k[:, None], v[:, None], g[:, None],
+                                                        beta[:, None], state, dtype=torch.float64)
+        out = gdn_decode_step(q.cuda(), k.cuda(), v.cuda(), g.cuda(), beta.cuda(), dev_state)
+        assert oracle.max_abs(out.float().cpu(), want_out[:, 0]) <= 2e-2
+        assert oracle.rel_frobenius(out.float().cpu(), want_out[:, 0]) <= 1e-2
+        assert oracle.rel_frobenius(dev_state.cpu(), want_state) <= 1e-5
+        state = want_state.float()
+        dev_state.copy_(state)
+
+
+def test_decode_step_equals_forward_with_one_token():
+    from actlizela_b200 import gdn_decode_step, gdn_forward
+    gen = torch.Generator().manual_seed(11)
+    q = torch.nn.functional.normalize(torch.randn(2, 1, 2, 128, generator=gen), dim=-1).to(torch.bfloat16).cuda()
+    k = torch.nn.functional.normalize(torch.randn(2, 1, 2, 128, generator=gen), dim=-1).to(torch.bfloat16).cuda()
+    v = torch.randn(2, 1, 4, 128, generator=gen).to(torch.bfloat16).cuda()
+    g = (-torch.rand(2, 1, 4, generator=gen)).cuda()
+    beta = torch.rand(2, 1, 4, generator=gen).to(torch.bfloat16).cuda()
+    state = (torch.randn(2, 4, 128, 128, generator=gen) * 0.2).cuda()
+    out_f, state_f = gdn_forward(q, k, v, g, beta, state, True)
+    mine = state.clone()
+    out_d = gdn_decode_step(q[:, 0].contiguous(), k[:, 0].contiguous(), v[:, 0].contiguous(),
+                            g[:, 0].contiguous(), beta[:, 0].contiguous(), mine)
+    assert oracle.max_abs(out_d.float(), out_f[:, 0].float()) <= 2e-2
+    assert oracle.rel_frobenius(mine.cpu(), state_f.cpu()) <= 1e-3
+
+
+def test_rmsnorm_gated_matches_oracle():
+    from actlizela_b200 import rmsnorm_gated
+    gen = torch.Generator().manual_seed(3)
+    y = torch.randn(1000, 32, 128, generator=gen).to(torch.bfloat16)
+    z = torch.randn(1000, 32, 128, generator=gen).to(torch.bfloat16)
+    w = (1 + 0.1 * torch.randn(128, generator=gen)).to(torch.bfloat16)
+    want = oracle.rmsnorm_gated_ref(y, z, w)
+    got = rmsnorm_gated(y.cuda(), z.cuda(), w.cuda()).cpu()
+    assert oracle.rel_frobenius(got.float(), want.float()) < 1e-2       # the reference's own criterion
+    assert (got.float() - want.float()).abs().max() <= 2 ** -7 * want.float().abs().max()
+
+
+def test_varlen_matches_per_sequence_oracle():
+    from actlizela_b200 import gdn_forward_varlen
+    from actlizela_b200.workloads import WORKLOADS, make_inputs
+    lengths = [130, 1, 64, 0, 257, 63]
+    bounds = [0]
+    for n in lengths:
+        bounds.append(bounds[-1] + n)
+    w = WORKLOADS["cfg3"].sliced(batch=1, length=bounds[-1], key_heads=2, value_heads=4, initial=None)
+    q, k, v, g, beta, _ = make_inputs(w)
+    init = 0.1 * torch.randn(len(lengths), 4, 128, 128, generator=torch.Generator().manual_seed(5))
+    out, finals = gdn_forward_varlen(q.cuda(), k.cuda(), v.cuda(), g.cuda(), beta.cuda(), bounds, init.cuda(), True)
+    for i, (t0, t1) in enumerate(zip(bounds, bounds[1:])):
+        if t1 == t0:
+            assert torch.equal(finals[i].cpu(), init[i])
+            continue
+        want_out, want_state = oracle.chunk_forward_fp32(q[:, t0:t1], k[:, t0:t1], v[:, t0:t1], g[:, t0:t1],
+                                                         beta[:, t0:t1], init[i:i + 1], True)
+        assert oracle.max_abs(out[:, t0:t1].float().cpu(), want_out.float()) <= 2e-2
+        assert oracle.rel_frobenius(out[:, t0:t1].float().cpu(), want_out.float()) <= 1e-2
+        assert oracle.rel_frobenius(finals[i:i + 1].cpu(), want_state) <= 1e-3

@@ -249,3 +249,13 @@ def test_build_entry_and_arch_guard_are_present():
     assert "__CUDA_ARCH__ != 1000" in common and "#error" in common
     receipt = json.loads((ROOT / "actlizela_b200/_native/build.json").read_text())
     assert "arch=compute_100a,code=sm_100a" in receipt["flags"]
+
+
+def test_no_file_io_or_hashing_per_call(native_library):
+    """After the first load, resolving the library must not touch the file system
+    (the reference tests the same property: tests/test_gdn_route.py:112-117)."""
+    first = _library.load_library()
+    with mock.patch.object(_library, "_sha", side_effect=AssertionError("hashing on the call path")), \
+            mock.patch.object(_library.Path, "is_file", side_effect=AssertionError("file system on the call path")):
+        for _ in range(3):
+            assert _library.load_library() is first

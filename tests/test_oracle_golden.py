@@ -101,3 +101,19 @@ def test_segment_chaining_and_affine_transition():
     m = oracle.segment_transition(tail[1], tail[3], tail[4])
     _, b_tail = oracle.recurrent_forward(*tail, None)
     assert oracle.rel_frobenius(m @ s1 + b_tail, full_state) < 1e-12
+
+
+def test_prestep_oracle_matches_reference_fixture():
+    """Q/K normalisation, gate activation and beta against the reference's serving recurrence."""
+    import numpy as np
+    from pathlib import Path
+    from tests.cases import prestep_case
+    arrays = np.load(Path(__file__).with_name("golden") / "golden_cases.npz")
+    mixed, a, b, a_log, dt_bias, hk, hv = prestep_case()
+    q, k, v, g, beta = oracle.prepare_inputs_ref(mixed, a, b, a_log, dt_bias, hk, hv)
+    key = torch.from_numpy(arrays["prestep.key_f32"])
+    assert (k.float() - key).abs().max() <= 2 ** -8 * key.abs().max()
+    assert oracle.rel_frobenius(g.exp(), torch.from_numpy(arrays["prestep.decay_f32"])) < 1e-6
+    out, _ = oracle.recurrent_forward(q[None], k[None], v[None], g[None], beta[None], None)
+    ref_out = torch.from_numpy(arrays["prestep.out_bf16"].copy()).view(torch.bfloat16)
+    assert oracle.max_abs(out[0], ref_out.double()) < 2e-2
