@@ -106,30 +106,37 @@ decode_step_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
   if (half == 0) out[(long long)bh * kDim + col] = __float2bfloat16_rn((partial[0][col] + partial[1][col]) * kScale);
 }
 
-// One warp per 128-wide row, 8 rows per CTA.
+// 16 lanes per 128-wide row (16 bytes per lane and tensor), 16 rows per 256-thread CTA.
 __global__ void __launch_bounds__(256)
 rmsnorm_gated_kernel(const __nv_bfloat16* __restrict__ y, const __nv_bfloat16* __restrict__ z,
                      const __nv_bfloat16* __restrict__ weight, __nv_bfloat16* __restrict__ out, long long rows) {
-  const long long row = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
-  if (row >= rows) return;
-  const int lane = threadIdx.x & 31;
-  const uint2 yy = *reinterpret_cast<const uint2*>(y + row * kDim + lane * 4);
-  const uint2 zz = *reinterpret_cast<const uint2*>(z + row * kDim + lane * 4);
-  const uint2 ww = *reinterpret_cast<const uint2*>(weight + lane * 4);
-  const float yf[4] = {lo_bf16(yy.x), hi_bf16(yy.x), lo_bf16(yy.y), hi_bf16(yy.y)};
-  const float zf[4] = {lo_bf16(zz.x), hi_bf16(zz.x), lo_bf16(zz.y), hi_bf16(zz.y)};
-  const float wf[4] = {lo_bf16(ww.x), hi_bf16(ww.x), lo_bf16(ww.y), hi_bf16(ww.y)};
-  float square = yf[0] * yf[0] + yf[1] * yf[1] + yf[2] * yf[2] + yf[3] * yf[3];
+  const long long slot = (long long)blockIdx.x * 16 + (threadIdx.x >> 4);
+  const bool live = slot < rows;               // idle groups redo the last row and store nothing
+  const long long row = live ? slot : rows - 1;
+  const int lane = threadIdx.x & 15;
+  const uint4 yy = *reinterpret_cast<const uint4*>(y + row * kDim + lane * 8);
+  const uint4 zz = *reinterpret_cast<const uint4*>(z + row * kDim + lane * 8);
+  const uint4 ww = *reinterpret_cast<const uint4*>(weight + lane * 8);
+  const uint32_t yp[4] = {yy.x, yy.y, yy.z, yy.w}, zp[4] = {zz.x, zz.y, zz.z, zz.w}, wp[4] = {ww.x, ww.y, ww.z, ww.w};
+  float yf[8], square = 0.f;
 #pragma unroll
-  for (int d = 16; d; d >>= 1) square += __shfl_xor_sync(0xffffffffu, square, d);
+  for (int i = 0; i < 4; ++i) {
+    yf[2 * i] = lo_bf16(yp[i]);
+    yf[2 * i + 1] = hi_bf16(yp[i]);
+    square = fmaf(yf[2 * i], yf[2 * i], fmaf(yf[2 * i + 1], yf[2 * i + 1], square));
+  }
+#pragma unroll
+  for (int d = 8; d; d >>= 1) square += __shfl_xor_sync(0xffffffffu, square, d, 16);
   const float rstd = rsqrtf(square * (1.f / kDim) + 1e-6f);
-  float r[4];
+  uint32_t packed[4];
 #pragma unroll
-  for (int i = 0; i < 4; ++i) r[i] = yf[i] * rstd * wf[i] * (zf[i] / (1.f + expf(-zf[i])));
-  uint2 o;
-  o.x = pack_bf16(r[0], r[1]);
-  o.y = pack_bf16(r[2], r[3]);
-  *reinterpret_cast<uint2*>(out + row * kDim + lane * 4) = o;
+  for (int i = 0; i < 4; ++i) {
+    const float z0 = lo_bf16(zp[i]), z1 = hi_bf16(zp[i]);
+    const float r0 = yf[2 * i] * rstd * lo_bf16(wp[i]) * (z0 / (1.f + expf(-z0)));
+    const float r1 = yf[2 * i + 1] * rstd * hi_bf16(wp[i]) * (z1 / (1.f + expf(-z1)));
+    packed[i] = pack_bf16(r0, r1);
+  }
+  if (live) *reinterpret_cast<uint4*>(out + row * kDim + lane * 8) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
 }
 
 }  // namespace
@@ -167,11 +174,11 @@ extern "C" int actlize_la_sm100_decode_step(
 
 extern "C" int actlize_la_sm100_rmsnorm_gated(const void* y, const void* z, const void* weight, void* out,
                                               long long rows, void* stream) {
-  if (!y || !z || !weight || !out || rows <= 0 || (rows + 7) / 8 > INT_MAX) return int(cudaErrorInvalidValue);
+  if (!y || !z || !weight || !out || rows <= 0 || (rows + 15) / 16 > INT_MAX) return int(cudaErrorInvalidValue);
   if ((reinterpret_cast<uintptr_t>(y) | reinterpret_cast<uintptr_t>(z) | reinterpret_cast<uintptr_t>(weight) |
-       reinterpret_cast<uintptr_t>(out)) & 7)
+       reinterpret_cast<uintptr_t>(out)) & 15)
     return int(cudaErrorInvalidValue);
-  rmsnorm_gated_kernel<<<(unsigned)((rows + 7) / 8), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+  rmsnorm_gated_kernel<<<(unsigned)((rows + 15) / 16), 256, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const __nv_bfloat16*>(y), static_cast<const __nv_bfloat16*>(z),
       static_cast<const __nv_bfloat16*>(weight), static_cast<__nv_bfloat16*>(out), rows);
   return int(cudaGetLastError());
