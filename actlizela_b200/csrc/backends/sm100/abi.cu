@@ -30,12 +30,12 @@ bool geometry_ok(int b, int t, int hk, int hv) {
 constexpr int kStageMask = 0x30, kPrepareOnly = 0x10, kWalkOnly = 0x20, kSegmentShift = 8, kMaxSegments = 16;
 bool config_ok(int config) {
   const int segments = (config >> kSegmentShift) & 0xff;
-  return config >= 0 && (config & 0xf) <= 3 && (config & ~(kStageMask | 0xf | (0xff << kSegmentShift))) == 0 &&
+  return config >= 0 && (config & 0xf) <= 4 && (config & ~(kStageMask | 0xf | (0xff << kSegmentShift))) == 0 &&
          (config & kStageMask) != kStageMask && segments <= kMaxSegments;
 }
 int segments_of(int config, const Geometry& geo) {
   int segments = (config >> kSegmentShift) & 0xff;
-  if ((config & 0xf) != 1 || (config & kStageMask) || segments < 2) return 1;
+  if (((config & 0xf) != 1 && (config & 0xf) != 4) || (config & kStageMask) || segments < 2) return 1;
   const int chunks = geo.chunks();
   return segments > chunks ? chunks : segments;
 }
@@ -74,8 +74,16 @@ int create_segment_streams() {
 }
 // bit 0: prepare stage uses tcgen05 (1) or CUDA cores (0); configuration ids:
 // 0 = simt/simt, 1 = umma/umma, 2 = simt prepare + umma walk, 3 = umma prepare + simt walk
-bool prepare_is_umma(int config) { return (config & 3) == 1 || (config & 3) == 3; }
-bool walk_is_umma(int config) { return (config & 3) == 1 || (config & 3) == 2; }
+// 4 = chained tensor-core pair (prepare also emits G and the decay-scaled W; see gdn_chain.cu)
+bool is_chain(int config) { return (config & 0xf) == 4; }
+bool prepare_is_umma(int config) { return (config & 0xf) == 1 || (config & 0xf) == 3; }
+bool walk_is_umma(int config) { return (config & 0xf) == 1 || (config & 0xf) == 2; }
+int launch_prepare_tc(int config, const Inputs& in, const Geometry& geo, const Workspace& ws, cudaStream_t stream) {
+  return is_chain(config) ? launch_prepare_chain(in, geo, ws, stream) : launch_prepare_umma(in, geo, ws, stream);
+}
+int launch_walk_tc(int config, const Inputs& in, const Geometry& geo, const Workspace& ws, cudaStream_t stream) {
+  return is_chain(config) ? launch_walk_chain(in, geo, ws, stream) : launch_walk_umma(in, geo, ws, stream);
+}
 
 __global__ void apply_transition_kernel(const float* __restrict__ m, const float* __restrict__ off,
                                         const float* __restrict__ s_in, float* __restrict__ s_out) {
@@ -118,6 +126,7 @@ extern "C" const char* actlize_la_sm100_numerical_contract(void) {
 extern "C" int actlize_la_sm100_configure(void) {
   if (int rc = configure_simt()) return rc;
   if (int rc = configure_umma()) return rc;
+  if (int rc = configure_chain()) return rc;
   return create_segment_streams();
 }
 
@@ -132,14 +141,14 @@ extern "C" int actlize_la_sm100_select(int b, int t, int hk, int hv, int gate_fp
 extern "C" long long actlize_la_sm100_workspace_bytes(int b, int t, int hk, int hv, int config) {
   if (!geometry_ok(b, t, hk, hv) || !config_ok(config)) return -1;
   const Geometry geo{b, t, hk, hv};
-  return workspace_bytes(geo, segments_of(config, geo));
+  return workspace_bytes(geo, segments_of(config, geo), is_chain(config));
 }
 
 extern "C" int actlize_la_sm100_launches_per_forward(int config) {
   if (!config_ok(config)) return -1;
   if (config & kStageMask) return 1;
   const int segments = (config >> kSegmentShift) & 0xff;
-  return ((config & 0xf) == 1 && segments > 1) ? 2 * segments : 2;
+  return (((config & 0xf) == 1 || (config & 0xf) == 4) && segments > 1) ? 2 * segments : 2;
 }
 
 extern "C" int actlize_la_sm100_selftest_wait_timeout(int tag, void* stream) {
@@ -160,7 +169,7 @@ extern "C" int actlize_la_sm100_forward_prepared(
   if (!geometry_ok(b, t, hk, hv) || !config_ok(config)) return int(cudaErrorInvalidValue);
   Geometry geo{b, t, hk, hv};
   const int segments = segments_of(config, geo);
-  if (workspace_bytes_given < workspace_bytes(geo, segments)) return int(cudaErrorInvalidValue);
+  if (workspace_bytes_given < workspace_bytes(geo, segments, is_chain(config))) return int(cudaErrorInvalidValue);
   if ((reinterpret_cast<uintptr_t>(workspace) & 255) || (reinterpret_cast<uintptr_t>(q) & 15) ||
       (reinterpret_cast<uintptr_t>(k) & 15) || (reinterpret_cast<uintptr_t>(v) & 15) ||
       (reinterpret_cast<uintptr_t>(output) & 15))
@@ -170,7 +179,7 @@ extern "C" int actlize_la_sm100_forward_prepared(
   const Inputs in{static_cast<const __nv_bfloat16*>(q), static_cast<const __nv_bfloat16*>(k),
                   static_cast<const __nv_bfloat16*>(v), g, static_cast<const __nv_bfloat16*>(beta),
                   initial, static_cast<__nv_bfloat16*>(output), final_state, gate_fp32 ? 1 : 0};
-  const Workspace ws = carve_workspace(workspace, geo);
+  const Workspace ws = carve_workspace(workspace, geo, is_chain(config));
   cudaStream_t stream = static_cast<cudaStream_t>(opaque_stream);
   if (segments > 1) {
     // Prepare kernels of all segments go to the caller's stream back to back; the walks run in order on
@@ -185,22 +194,24 @@ extern "C" int actlize_la_sm100_forward_prepared(
     for (int i = 0; i < segments; ++i) {
       geo.chunk_begin = int((long long)chunks * i / segments);
       geo.chunk_count = int((long long)chunks * (i + 1) / segments) - geo.chunk_begin;
-      if (int rc = launch_prepare_umma(in, geo, ws, stream)) return rc;
+      if (int rc = launch_prepare_tc(config, in, geo, ws, stream)) return rc;
       if ((e = cudaEventRecord(ss.prepared[i], stream)) != cudaSuccess) return int(e);
       if ((e = cudaStreamWaitEvent(ss.walk, ss.prepared[i], 0)) != cudaSuccess) return int(e);
-      if (int rc = launch_walk_umma(in, geo, ws, ss.walk)) return rc;
+      if (int rc = launch_walk_tc(config, in, geo, ws, ss.walk)) return rc;
     }
     if ((e = cudaEventRecord(ss.done, ss.walk)) != cudaSuccess) return int(e);
     return int(cudaStreamWaitEvent(stream, ss.done, 0));
   }
   if (!(config & kWalkOnly)) {
-    if (int rc = prepare_is_umma(config) ? launch_prepare_umma(in, geo, ws, stream)
-                                         : launch_prepare_simt(in, geo, ws, stream))
+    if (int rc = is_chain(config)          ? launch_prepare_chain(in, geo, ws, stream)
+                 : prepare_is_umma(config) ? launch_prepare_umma(in, geo, ws, stream)
+                                           : launch_prepare_simt(in, geo, ws, stream))
       return rc;
   }
   if (config & kPrepareOnly) return 0;
-  return walk_is_umma(config) ? launch_walk_umma(in, geo, ws, stream)
-                              : launch_walk_simt(in, geo, ws, stream);
+  return is_chain(config)       ? launch_walk_chain(in, geo, ws, stream)
+         : walk_is_umma(config) ? launch_walk_umma(in, geo, ws, stream)
+                                : launch_walk_simt(in, geo, ws, stream);
 }
 
 namespace {
@@ -220,7 +231,7 @@ Arena arena_layout(int b, int t, int hk, int hv, int gate_fp32, int has_initial,
   a.output = take(vv);
   a.final_state = has_final ? take(st) : -1;
   const Geometry geo{b, t, hk, hv};
-  a.workspace = take(workspace_bytes(geo, segments_of(config, geo)));
+  a.workspace = take(workspace_bytes(geo, segments_of(config, geo), is_chain(config)));
   a.total = off;
   return a;
 }
@@ -265,7 +276,7 @@ extern "C" int actlize_la_sm100_forward_host(
                       initial ? reinterpret_cast<const float*>(base + a.initial) : nullptr,
                       reinterpret_cast<__nv_bfloat16*>(base + a.output),
                       final_state ? reinterpret_cast<float*>(base + a.final_state) : nullptr, gate_fp32 ? 1 : 0};
-      const Workspace ws = carve_workspace(base + a.workspace, geo);
+      const Workspace ws = carve_workspace(base + a.workspace, geo, is_chain(config));
       const int chunks = geo.chunks();
       const long long gate_bytes = gate_fp32 ? 4 : 2;
       if ((e = cudaEventRecord(ss.start, stream)) != cudaSuccess) return int(e);
@@ -291,10 +302,10 @@ extern "C" int actlize_la_sm100_forward_host(
         }
         if ((e = cudaEventRecord(ss.arrived[i], ss.copy_in)) != cudaSuccess) return int(e);
         if ((e = cudaStreamWaitEvent(stream, ss.arrived[i], 0)) != cudaSuccess) return int(e);
-        if (int rc = launch_prepare_umma(in, geo, ws, stream)) return rc;
+        if (int rc = launch_prepare_tc(config, in, geo, ws, stream)) return rc;
         if ((e = cudaEventRecord(ss.prepared[i], stream)) != cudaSuccess) return int(e);
         if ((e = cudaStreamWaitEvent(ss.walk, ss.prepared[i], 0)) != cudaSuccess) return int(e);
-        if (int rc = launch_walk_umma(in, geo, ws, ss.walk)) return rc;
+        if (int rc = launch_walk_tc(config, in, geo, ws, ss.walk)) return rc;
         if ((e = cudaEventRecord(ss.walked[i], ss.walk)) != cudaSuccess) return int(e);
         if ((e = cudaStreamWaitEvent(ss.copy_out, ss.walked[i], 0)) != cudaSuccess) return int(e);
         for (int bb = 0; bb < b; ++bb) {

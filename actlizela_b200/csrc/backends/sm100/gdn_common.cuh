@@ -37,6 +37,9 @@ struct Geometry {
 //   p           BF16 [64][64]   tril(Q K^T * exp(prefix_i - prefix_j)) / sqrt(128)
 //   gates       FP32 [128]      [0,64): exp(prefix_last - prefix_i), 0 for padding rows;
 //                               [64]: exp(prefix_last); rest unused
+//   g_hi, g_lo  BF16 [64][64]   only written by the chained configuration: G = W K_prev^T (token of this chunk,
+//                               token of the previous chunk), split G ~= hi + lo; in that configuration w_hi/w_lo
+//                               hold W scaled by the previous chunk's total decay (1 for the first chunk of a launch)
 // plus, when the sequence is walked in segments, one FP32 [128][128] state per (batch, value head)
 // that carries the state from one segment's walk to the next (K-by-V order, like the public state).
 struct Workspace {
@@ -46,19 +49,22 @@ struct Workspace {
   __nv_bfloat16* qs;
   __nv_bfloat16* p;
   float* gates;
+  __nv_bfloat16* g_hi;
+  __nv_bfloat16* g_lo;
   float* carry;
 };
 
 constexpr long long kBlockBytes =
     2LL * kChunk * kDim * 2 + kChunk * kDim * 4 + kChunk * kDim * 2 + kChunk * kChunk * 2 + 128 * 4;
+constexpr long long kChainBlockBytes = 2LL * kChunk * kChunk * 2;     // g_hi, g_lo: chained configuration only
 
-inline __host__ long long workspace_bytes(const Geometry& g, int segments = 1) {
-  return g.blocks() * kBlockBytes +
+inline __host__ long long workspace_bytes(const Geometry& g, int segments = 1, bool chained = false) {
+  return g.blocks() * (kBlockBytes + (chained ? kChainBlockBytes : 0)) +
          (segments > 1 ? (long long)g.batch * g.value_heads * kDim * kDim * 4 : 0);
 }
 
 // Carve the planes out of one caller-owned allocation (256-byte aligned base required).
-inline __host__ Workspace carve_workspace(void* base, const Geometry& g) {
+inline __host__ Workspace carve_workspace(void* base, const Geometry& g, bool chained = false) {
   char* p = static_cast<char*>(base);
   const long long n = g.blocks();
   Workspace w;
@@ -68,6 +74,11 @@ inline __host__ Workspace carve_workspace(void* base, const Geometry& g) {
   w.qs = reinterpret_cast<__nv_bfloat16*>(p);    p += n * kChunk * kDim * 2;
   w.p = reinterpret_cast<__nv_bfloat16*>(p);     p += n * kChunk * kChunk * 2;
   w.gates = reinterpret_cast<float*>(p);         p += n * 128 * 4;
+  w.g_hi = w.g_lo = nullptr;
+  if (chained) {
+    w.g_hi = reinterpret_cast<__nv_bfloat16*>(p);  p += n * kChunk * kChunk * 2;
+    w.g_lo = reinterpret_cast<__nv_bfloat16*>(p);  p += n * kChunk * kChunk * 2;
+  }
   w.carry = reinterpret_cast<float*>(p);         // only backed by memory when segments > 1
   return w;
 }
@@ -122,6 +133,11 @@ int configure_simt();
 int launch_prepare_umma(const Inputs&, const Geometry&, const Workspace&, cudaStream_t);
 int launch_walk_umma(const Inputs&, const Geometry&, const Workspace&, cudaStream_t);
 int configure_umma();
+// chained configuration: the prepare stage also emits G and the decay-scaled W, and the walk forms
+// W S of chunk c+1 from the state of chunk c-1's end plus G (N*rel) without waiting for the new state
+int launch_prepare_chain(const Inputs&, const Geometry&, const Workspace&, cudaStream_t);
+int launch_walk_chain(const Inputs&, const Geometry&, const Workspace&, cudaStream_t);
+int configure_chain();
 int read_device_status(int* host_out4, int reset);
 int launch_wait_timeout_selftest(int tag, cudaStream_t);
 

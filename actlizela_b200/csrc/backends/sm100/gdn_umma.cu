@@ -108,6 +108,10 @@ __device__ __forceinline__ int swizzled_offset(int row, int col) {
 //            T diag(beta exp(p)) and T diag(beta) -> BF16 hi/lo K-major tiles in shared memory
 //   phase 5  W^T = K^T (T diag(beta exp p))^T,  U^T = V^T (T diag(beta))^T   (A = transposed K / V tiles)
 //   phase 6  accumulators -> W hi/lo BF16, U FP32 staged in shared memory, TMA stores; gate vector -> workspace
+// Chained variant (kChained): W is multiplied by the previous chunk's total decay (clamped below at 2^-100 so
+// that it can be divided out again; 1 for the first chunk of the launch) before it is split, and
+//   phase 7  G = W K_prev^T / scale from the staged [W_hi ; W_lo] tiles (one M = 128 product whose two lane
+//            halves are added through shared memory) -> BF16 hi/lo -> workspace
 struct PrepLayout {
   static constexpr int kQ0 = 0, kK0 = kBox, kQ1 = 2 * kBox, kK1 = 3 * kBox;   // [Q;K] stacked, two K atoms
   static constexpr int kV0 = 4 * kBox, kV1 = 5 * kBox;
@@ -119,12 +123,16 @@ struct PrepLayout {
   static constexpr int kX = kQ0;                           // block products, reuse the Q boxes after phase 3
   static constexpr int kLdX = 20, kLdX3 = 36;
   static constexpr int kVec = kT + 64 * kLd * 4;           // float [4][64]: pl2, beta, beta*exp(p), exp(p)/sqrt(128)
-  static constexpr int kBars = kVec + 4 * 64 * 4;          // 2 mbarriers, tmem slot, abort flag, carry
+  static constexpr int kBars = kVec + 4 * 64 * 4;          // 2 mbarriers, tmem slot, abort flag, carry, 2 sums
   static constexpr int kTotal = kBars + 64;
+  // chained variant: previous chunk's K tile (two boxes) lands on T once T is dead; the lane halves of the
+  // G product are added through a float [64][64] scratch on the dead T diag(beta) tiles
+  static constexpr int kKprev = kT, kGsum = kTuH;
+  static_assert(kKprev % 1024 == 0 && 2 * kBox <= 64 * kLd * 4, "previous K tile must fit on T, box aligned");
 };
 constexpr int kPrepThreads = 256;
 constexpr int kPrepSmem = PrepLayout::kTotal + 1024;
-constexpr int kPrepTmemCols = 256;   // D1 [0,64)  DW [64,128)  DU [128,192)
+constexpr int kPrepTmemCols = 256;   // D1 [0,64)  DW [64,128)  DU [128,192)  DG [192,256)
 
 #ifdef GDN_SM100_PHASE_TIMING
 #define GDN_PSTAMP(slot) \
@@ -133,6 +141,7 @@ constexpr int kPrepTmemCols = 256;   // D1 [0,64)  DW [64,128)  DU [128,192)
 #define GDN_PSTAMP(slot)
 #endif
 
+template <bool kChained>
 __global__ void __launch_bounds__(kPrepThreads, 2)
 prepare_umma_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                     const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_wh,
@@ -192,6 +201,17 @@ prepare_umma_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
     const long long gi = ((long long)b * geo.sequence + t0 + tid) * geo.value_heads + hv;
     gate = load_gate(in.g, gi, in.gate_fp32);
     beta = __bfloat162float(in.beta[gi]);
+  }
+  if (kChained && warp >= 2 && warp < 4) {
+    // total log-decay of the previous chunk (always a full chunk), summed by warps 2 and 3
+    float prev = 0.f;
+    if (chunk > geo.chunk_begin) {
+      const long long gi = ((long long)b * geo.sequence + t0 - kChunk + (tid - 64)) * geo.value_heads + hv;
+      prev = load_gate(in.g, gi, in.gate_fp32);
+    }
+#pragma unroll
+    for (int d = 16; d > 0; d >>= 1) prev += __shfl_xor_sync(0xffffffffu, prev, d);
+    if ((tid & 31) == 0) carry[warp - 1] = prev;
   }
   tc_fence_before();
   __syncthreads();
@@ -469,6 +489,12 @@ prepare_umma_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
   if (tid == 0 && ok) {
     tc_fence_after();
     const uint32_t base = smem_u32(sm);
+    if (kChained) {
+      // T is dead: fetch the previous chunk's K tile onto it (rows before the sequence start read as zero)
+      mbar_arrive_expect_tx(bar_tma, 2 * kBox);
+      tma_load_4d(sm + L::kKprev, &tm_k, bar_tma, 0, hk, t0 - kChunk, b);
+      tma_load_4d(sm + L::kKprev + kBox, &tm_k, bar_tma, 64, hk, t0 - kChunk, b);
+    }
 #pragma unroll
     for (int part = 0; part < 2; ++part) {
 #pragma unroll
@@ -494,7 +520,10 @@ prepare_umma_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
   GDN_PSTAMP(5);
 
   // ---- phase 6: W (hi/lo) and U leave through shared memory and TMA stores; every input tile is dead
-  // by now, so the staging boxes reuse their space: W hi [0,16K), W lo [16K,32K), U [32K,64K).
+  // by now, so the staging boxes reuse their space: per 64-wide key atom [W hi | W lo] (0, 8K | 16K, 24K),
+  // U [32K,64K).
+  float w_scale = 1.f;
+  if (kChained && chunk > geo.chunk_begin) w_scale = fmaxf(exp2f((carry[1] + carry[2]) * kLog2e), 0x1p-100f);
   if (ok) {
     const int tk0 = chalf * 32;
     uint32_t dw[32], du[32];
@@ -503,17 +532,17 @@ prepare_umma_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
     tmem_wait_ld();
     // lrow is the key (W) / value (U) index; W boxes are 128-byte swizzled [token][64 BF16], U boxes dense
     // [token][32 FP32]
-    uint8_t* wbox = sm + (lrow >> 6) * kBox + ((lrow & 7) << 1);
+    uint8_t* wbox = sm + (lrow >> 6) * 2 * kBox + ((lrow & 7) << 1);
     const int wchunk = (lrow & 63) >> 3;
     float* ubox = reinterpret_cast<float*>(sm + 4 * kBox + (lrow >> 5) * kBox) + (lrow & 31);
 #pragma unroll
     for (int jj = 0; jj < 32; ++jj) {
       const int tok = tk0 + jj;
       __nv_bfloat16 hi, lo;
-      split_bf16(__uint_as_float(dw[jj]), hi, lo);
+      split_bf16(__uint_as_float(dw[jj]) * w_scale, hi, lo);
       const int off = tok * 128 + ((wchunk ^ (tok & 7)) << 4);
       *reinterpret_cast<__nv_bfloat16*>(wbox + off) = hi;
-      *reinterpret_cast<__nv_bfloat16*>(wbox + 2 * kBox + off) = lo;
+      *reinterpret_cast<__nv_bfloat16*>(wbox + kBox + off) = lo;
       ubox[tok * 32] = __uint_as_float(du[jj]);
     }
     fence_proxy_async_smem();
@@ -522,17 +551,74 @@ prepare_umma_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
     if (tid == kChunk) ws.gates[block * 128 + kChunk] = fast_exp2(last);
   }
   __syncthreads();
+  if (kChained) {
+    // ---- phase 7: G = (W_hi + W_lo) K_prev^T: A = the staged [W_hi ; W_lo] rows (M = 128), B = previous K tile
+    if (ok) ok = mbar_wait(bar_tma, 1, abort, 4, chunk);
+    if (tid == 0 && ok) {
+      tc_fence_after();
+      const uint32_t base = smem_u32(sm);
+#pragma unroll
+      for (int ks = 0; ks < 8; ++ks) {
+        const uint32_t a = base + (ks >> 2) * 2 * kBox + (ks & 3) * 32;
+        const uint32_t bb = base + L::kKprev + (ks >> 2) * kBox + (ks & 3) * 32;
+        mma_ss(tmem + 192, smem_desc(a, 16, 1024), smem_desc(bb, 16, 1024), kIdescN64, ks > 0);
+      }
+      mma_commit(bar_mma);
+    }
+  }
   if (tid == 0 && ok) {
     const int row = int(block * kChunk);
     tma_store_2d(&tm_wh, sm, 0, row);
-    tma_store_2d(&tm_wh, sm + kBox, 64, row);
-    tma_store_2d(&tm_wl, sm + 2 * kBox, 0, row);
+    tma_store_2d(&tm_wh, sm + 2 * kBox, 64, row);
+    tma_store_2d(&tm_wl, sm + kBox, 0, row);
     tma_store_2d(&tm_wl, sm + 3 * kBox, 64, row);
 #pragma unroll
     for (int part = 0; part < 4; ++part) tma_store_2d(&tm_u, sm + (4 + part) * kBox, part * 32, row);
     tma_store_commit();
-    tma_store_wait_read();
   }
+  if (kChained) {
+    ok = ok && mbar_wait(bar_mma, 0, abort, 5, chunk);
+    tc_fence_after();
+    // lanes 64..127 hold the W_lo part of row (lane - 64): hand it to the thread of the W_hi row through a
+    // float [64][64] scratch (16-byte slots XOR-swizzled by the row so that a warp's stores spread over banks)
+    float* gsum = reinterpret_cast<float*>(sm + L::kGsum);
+    const int grow = lrow & 63, slot0 = chalf * 8;
+    uint32_t dg[32];
+    if (ok) {
+      tmem_ld32(taddr + 192 + chalf * 32, dg);
+      tmem_wait_ld();
+      if (lrow >= 64) {
+#pragma unroll
+        for (int q4 = 0; q4 < 8; ++q4)
+          *reinterpret_cast<uint4*>(gsum + grow * 64 + (((slot0 + q4) ^ (grow & 15)) << 2)) =
+              make_uint4(dg[q4 * 4], dg[q4 * 4 + 1], dg[q4 * 4 + 2], dg[q4 * 4 + 3]);
+      }
+    }
+    __syncthreads();
+    if (ok && lrow < 64) {
+      const float inv = 1.f / w_scale;
+      uint32_t gh[16], gl[16];
+#pragma unroll
+      for (int q4 = 0; q4 < 8; ++q4) {
+        const float4 o = *reinterpret_cast<const float4*>(gsum + grow * 64 + (((slot0 + q4) ^ (grow & 15)) << 2));
+        const float g0 = (__uint_as_float(dg[q4 * 4]) + o.x) * inv, g1 = (__uint_as_float(dg[q4 * 4 + 1]) + o.y) * inv;
+        const float g2 = (__uint_as_float(dg[q4 * 4 + 2]) + o.z) * inv, g3 = (__uint_as_float(dg[q4 * 4 + 3]) + o.w) * inv;
+        const uint32_t h0 = pack_bf16(g0, g1), h1 = pack_bf16(g2, g3);
+        gh[q4 * 2] = h0;
+        gh[q4 * 2 + 1] = h1;
+        gl[q4 * 2] = pack_bf16(g0 - bf16_lo(h0), g1 - bf16_hi(h0));
+        gl[q4 * 2 + 1] = pack_bf16(g2 - bf16_lo(h1), g3 - bf16_hi(h1));
+      }
+      uint4* dh = reinterpret_cast<uint4*>(ws.g_hi + (block * kChunk + grow) * kChunk + chalf * 32);
+      uint4* dl = reinterpret_cast<uint4*>(ws.g_lo + (block * kChunk + grow) * kChunk + chalf * 32);
+#pragma unroll
+      for (int q4 = 0; q4 < 4; ++q4) {
+        dh[q4] = make_uint4(gh[q4 * 4], gh[q4 * 4 + 1], gh[q4 * 4 + 2], gh[q4 * 4 + 3]);
+        dl[q4] = make_uint4(gl[q4 * 4], gl[q4 * 4 + 1], gl[q4 * 4 + 2], gl[q4 * 4 + 3]);
+      }
+    }
+  }
+  if (tid == 0 && ok) tma_store_wait_read();
   GDN_PSTAMP(6);
   if (!ok) {
     for (int i = 0; i < 20; ++i) __nanosleep(100000);   // let copies in flight land before the CTA leaves
@@ -930,14 +1016,17 @@ walk_umma_kernel(const __grid_constant__ CUtensorMap tm_wh, const __grid_constan
 // ======================================================================================= launchers
 int configure_umma() {
   if (int rc = tensor_map_encoder().init()) return rc;
-  cudaError_t e = cudaFuncSetAttribute(prepare_umma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+  cudaError_t e = cudaFuncSetAttribute(prepare_umma_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        kPrepSmem);
+  if (e != cudaSuccess) return int(e);
+  e = cudaFuncSetAttribute(prepare_umma_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kPrepSmem);
   if (e != cudaSuccess) return int(e);
   e = cudaFuncSetAttribute(walk_umma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kWalkSmem);
   return int(e);
 }
 
-int launch_prepare_umma(const Inputs& in, const Geometry& geo, const Workspace& ws, cudaStream_t stream) {
+namespace {
+int launch_prepare_tc(const Inputs& in, const Geometry& geo, const Workspace& ws, cudaStream_t stream, bool chained) {
   TensorMapEncoder& enc = tensor_map_encoder();
   if (int rc = enc.init()) return rc;
   CUtensorMap tm_q, tm_k, tm_v, tm_wh, tm_wl, tm_u;
@@ -948,9 +1037,20 @@ int launch_prepare_umma(const Inputs& in, const Geometry& geo, const Workspace& 
   if (int rc = enc.bf16_2d(&tm_wh, ws.w_hi, kDim, rows, kChunk)) return rc;
   if (int rc = enc.bf16_2d(&tm_wl, ws.w_lo, kDim, rows, kChunk)) return rc;
   if (int rc = enc.f32_2d(&tm_u, ws.u, kDim, rows, kChunk)) return rc;
-  prepare_umma_kernel<<<(unsigned)((long long)geo.batch * geo.value_heads * geo.segment_chunks()), kPrepThreads, kPrepSmem, stream>>>(tm_q, tm_k, tm_v, tm_wh, tm_wl,
-                                                                                  tm_u, in, geo, ws);
+  const unsigned grid = (unsigned)((long long)geo.batch * geo.value_heads * geo.segment_chunks());
+  if (chained)
+    prepare_umma_kernel<true><<<grid, kPrepThreads, kPrepSmem, stream>>>(tm_q, tm_k, tm_v, tm_wh, tm_wl, tm_u, in, geo, ws);
+  else
+    prepare_umma_kernel<false><<<grid, kPrepThreads, kPrepSmem, stream>>>(tm_q, tm_k, tm_v, tm_wh, tm_wl, tm_u, in, geo, ws);
   return int(cudaGetLastError());
+}
+}  // namespace
+
+int launch_prepare_umma(const Inputs& in, const Geometry& geo, const Workspace& ws, cudaStream_t stream) {
+  return launch_prepare_tc(in, geo, ws, stream, false);
+}
+int launch_prepare_chain(const Inputs& in, const Geometry& geo, const Workspace& ws, cudaStream_t stream) {
+  return launch_prepare_tc(in, geo, ws, stream, true);
 }
 
 int launch_walk_umma(const Inputs& in, const Geometry& geo, const Workspace& ws, cudaStream_t stream) {

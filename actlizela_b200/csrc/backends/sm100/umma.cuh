@@ -66,14 +66,31 @@ struct AbortFlag {
 
 // Bounded wait for the phase with the given parity.  Returns false after a time-out or when
 // another role of this CTA has already given up.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, const AbortFlag& abort,
-                                          int site, int chunk) {
+// The polling loop is one shared out-of-line routine: inlined at the ~40 wait sites of a warp-specialised kernel
+// it made up a third of the kernel's code, and the issuing threads, which run their code alone, then paid an
+// instruction-cache miss at nearly every wait.
+static __device__ __noinline__ bool mbar_wait_poll(uint32_t bar_addr, uint32_t parity, volatile int* flag, int site,
+                                            int chunk) {
+  const AbortFlag abort{flag};
   for (uint32_t spin = 0; spin < kSpinLimit; ++spin) {
-    if (mbar_try_wait(bar, parity)) return true;
+    uint32_t done;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(done)
+        : "r"(bar_addr), "r"(parity)
+        : "memory");
+    if (done) return true;
     if ((spin & 255u) == 255u && abort.raised()) return false;
   }
   abort.raise(1, site, chunk);
   return false;
+}
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, const AbortFlag& abort,
+                                          int site, int chunk) {
+  if (mbar_try_wait(bar, parity)) return true;
+  return mbar_wait_poll(smem_u32(bar), parity, abort.flag, site, chunk);
 }
 
 // generic-proxy writes to shared memory -> visible to the async proxy (TMA, tcgen05.mma)

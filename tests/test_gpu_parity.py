@@ -19,7 +19,7 @@ from tests.cases import ALL_CASES, build_case
 pytestmark = pytest.mark.gpu
 
 OUT_MAX_ABS, OUT_REL_F, STATE_REL_F = 2e-2, 1e-2, 1e-3
-CONFIGS = ["simt", "umma"]
+CONFIGS = ["simt", "umma", "chain"]
 
 
 @pytest.fixture(scope="module")
@@ -266,6 +266,25 @@ def test_segmented_walk_equals_the_single_launch_bitwise(configuration, forward,
     assert none is None and torch.equal(seg_out, out)
     torch.cuda.synchronize()
     assert _status(native_library)[0] == 0
+
+
+@pytest.mark.parametrize("configuration", ["chain-seg2", "chain-seg4", "chain-seg8"])
+def test_segmented_chained_walk(configuration, forward, native_library):
+    """The chained walk starts every launch from the plain W S product, so a segmented run differs from the
+    single launch by rounding only; both stay inside the criterion against the oracle."""
+    w = WORKLOADS["cfg3"].sliced(batch=2, length=1000, key_heads=2, value_heads=8)     # 16 chunks, tail of 40
+    cpu = make_inputs(w)
+    dev = _to_device(cpu)
+    want_out, want_state = oracle.wy_chunk_forward(*cpu)
+    out, state = forward(*dev, True, configuration="chain")
+    seg_out, seg_state = forward(*dev, True, configuration=configuration)
+    again_out, again_state = forward(*dev, True, configuration=configuration)
+    torch.cuda.synchronize()
+    assert _status(native_library)[0] == 0
+    assert torch.equal(seg_out, again_out) and torch.equal(seg_state, again_state)
+    _check(out, state, want_out, want_state, "chain")
+    _check(seg_out, seg_state, want_out, want_state, configuration)
+    assert oracle.rel_frobenius(seg_state.cpu(), state.cpu()) < 1e-4
 
 
 def test_bounded_wait_gives_up_and_reports(native_library, forward):
