@@ -215,6 +215,18 @@ extern "C" int actlize_la_sm100_forward_prepared(
 }
 
 namespace {
+// Segment boundaries of the host-buffer entry.  The transfers bound that path; what cannot overlap them is the last
+// segment's compute and copy-out, so the segments taper towards the end (cumulative fraction 1 - (1 - i/n)^2:
+// 44 %, 31 %, 19 %, 6 % for four) instead of being equal.  Every segment keeps at least one chunk.
+int tapered_begin(int chunks, int i, int segments) {
+  if (i >= segments) return chunks;
+  const double rest = 1.0 - double(i) / segments;
+  int begin = int(chunks * (1.0 - rest * rest) + 0.5);
+  if (begin < i) begin = i;
+  if (begin > chunks - (segments - i)) begin = chunks - (segments - i);
+  return begin;
+}
+
 struct Arena {
   long long q, k, v, g, beta, initial, output, final_state, workspace, total;
 };
@@ -285,8 +297,8 @@ extern "C" int actlize_la_sm100_forward_host(
       if (initial && (e = cudaMemcpyAsync(base + a.initial, initial, st, cudaMemcpyHostToDevice, ss.copy_in)) != cudaSuccess)
         return int(e);
       for (int i = 0; i < segments; ++i) {
-        geo.chunk_begin = int((long long)chunks * i / segments);
-        geo.chunk_count = int((long long)chunks * (i + 1) / segments) - geo.chunk_begin;
+        geo.chunk_begin = tapered_begin(chunks, i, segments);
+        geo.chunk_count = tapered_begin(chunks, i + 1, segments) - geo.chunk_begin;
         const long long t0 = (long long)geo.chunk_begin * kChunk;
         const long long rows = ((long long)(geo.chunk_begin + geo.chunk_count) * kChunk < t ?
                                 (long long)(geo.chunk_begin + geo.chunk_count) * kChunk : t) - t0;

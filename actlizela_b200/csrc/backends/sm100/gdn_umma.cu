@@ -939,63 +939,71 @@ walk_umma_kernel(const __grid_constant__ CUtensorMap tm_wh, const __grid_constan
     __syncwarp();
   } else if (warp == kMmaWarp) {
     // ------------------------------------------------------------------ MMA issuer
+    // The issuing thread is a latency-bound scalar program: the loop holds no data-dependent branch but one check
+    // of the wait results per chunk (a wait that gave up lets the rest of that chunk's instructions run on stale
+    // operands, which is harmless: the launch is already failed), and the base addresses are broadcast so that
+    // the compiler knows they are warp-uniform.
+    const uint32_t tm = __shfl_sync(0xffffffffu, tmem, 0);
+    const uint32_t st0 = __shfl_sync(0xffffffffu, smem_u32(sm), 0);
     if (lane == 0) {
       bool ok = true;
-      // Descriptors are built once per ring stage; inside the loop an operand step is one 64-bit add
-      // (the start-address field counts 16-byte units), which keeps the issuing thread's own instruction
-      // stream short: it is the only thread feeding the tensor pipe.
-      static_assert(L::kStages == 2, "descriptor cache below assumes a two-stage ring");
-      const uint32_t st0 = smem_u32(sm), st1 = st0 + L::kStage;
-      const uint64_t dB0[2] = {smem_desc(st0 + L::kB0, 16, 1024), smem_desc(st1 + L::kB0, 16, 1024)};
-      const uint64_t dB1[2] = {smem_desc(st0 + L::kB1, 16, 1024), smem_desc(st1 + L::kB1, 16, 1024)};
-      const uint64_t dK[2] = {smem_desc(st0 + L::kK, kBox, 1024), smem_desc(st1 + L::kK, kBox, 1024)};
-      const uint64_t dP[2] = {smem_desc(st0 + L::kP, 16, 1024), smem_desc(st1 + L::kP, 16, 1024)};
+      // Descriptors of ring stage 0; stage 1 is a constant further on (the start-address field counts 16-byte units).
+      static_assert(L::kStages == 2 && L::kStage % 16 == 0, "descriptor arithmetic below assumes a two-stage ring");
+      const uint64_t dB0 = smem_desc(st0 + L::kB0, 16, 1024), dB1 = smem_desc(st0 + L::kB1, 16, 1024);
+      const uint64_t dK = smem_desc(st0 + L::kK, kBox, 1024), dP = smem_desc(st0 + L::kP, 16, 1024);
       for (int c = 0; c < chunks && ok; ++c) {
-        const int s = c & 1;
-        const uint64_t b0 = s ? dB0[1] : dB0[0], b1 = s ? dB1[1] : dB1[0];
-        const uint64_t kd = s ? dK[1] : dK[0], pd = s ? dP[1] : dP[0];
+        const uint64_t stage = uint64_t((c & 1) * (L::kStage >> 4));
+        const uint64_t b0 = dB0 + stage, b1 = dB1 + stage, kd = dK + stage, pd = dP + stage;
         // St [W_hi ; W_lo ; Qs]^T with St ~ SH + SL: the SH pass covers all 192 columns, the SL pass the
         // 128 W columns.  K steps {0,1,4,5} become available first, {2,3,6,7} second.
+        ok = mbar_wait(bar_ops, c & 1, abort, 41, c);
+        tc_fence_after();
 #pragma unroll
-        for (int part = 0; part < 2 && ok; ++part) {
-          ok = mbar_wait(bar_ops + part, c & 1, abort, 41, c);
-          if (!ok) break;
-          tc_fence_after();
-#pragma unroll
-          for (int q = 0; q < 4; ++q) {
-            const int ks = (q >> 1) * 4 + part * 2 + (q & 1);
-            const uint64_t bdesc = ((ks >> 2) ? b1 : b0) + uint64_t((ks & 3) * 2);     // +32 bytes per K step
-            mma_ts(tmem + kAccX, tmem + kOpSH + ks * 8, bdesc, kIdescN192, (part | q) != 0);
-            mma_ts(tmem + kAccY, tmem + kOpSL + ks * 8, bdesc, kIdescN64, (part | q) != 0);
-          }
+        for (int q = 0; q < 4; ++q) {
+          const int ks = (q >> 1) * 4 + (q & 1);
+          const uint64_t bdesc = ((ks >> 2) ? b1 : b0) + uint64_t((ks & 3) * 2);     // +32 bytes per K step
+          mma_ts(tm + kAccX, tm + kOpSH + ks * 8, bdesc, kIdescN192, q != 0);
+          mma_ts(tm + kAccY, tm + kOpSL + ks * 8, bdesc, kIdescN64, q != 0);
         }
-        if (!ok) break;
+        ok &= mbar_wait(bar_ops + 1, c & 1, abort, 41, c);
+        tc_fence_after();
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          const int ks = (q >> 1) * 4 + 2 + (q & 1);
+          const uint64_t bdesc = ((ks >> 2) ? b1 : b0) + uint64_t((ks & 3) * 2);
+          mma_ts(tm + kAccX, tm + kOpSH + ks * 8, bdesc, kIdescN192, 1);
+          mma_ts(tm + kAccY, tm + kOpSL + ks * 8, bdesc, kIdescN64, 1);
+        }
         mma_commit(bar_ws);
-        // St += (N*rel)^T K (accumulator already holds gamma * St); token groups {0,2} first, {1,3} second
+        // St += (N*rel)^T K (accumulator already holds gamma * St); token groups {0,2} first, {1,3} second;
+        // O^T += N^T P^T for the same token groups: the first half runs while the chain warps still work on the
+        // second, so the output accumulator completes right behind the state update
+        ok &= mbar_wait(bar_opn, c & 1, abort, 43, c);
+        tc_fence_after();
 #pragma unroll
-        for (int part = 0; part < 2 && ok; ++part) {
-          ok = mbar_wait(bar_opn + part, c & 1, abort, 43, c);
-          if (!ok) break;
-          tc_fence_after();
-#pragma unroll
-          for (int h = 0; h < 2; ++h) {
-            const int ks = h * 2 + part;
-            const uint64_t kdesc = kd + uint64_t(ks * 128);                              // +2048 bytes per K step
-            mma_ts(tmem + kAccS, tmem + kAccX + ks * 16, kdesc, kIdescN128BT, 1);
-            mma_ts(tmem + kAccS, tmem + kAccX + ks * 16 + 8, kdesc, kIdescN128BT, 1);
-          }
-          if (part == 1) mma_commit(bar_s);
-          // O^T += N^T P^T for the same token groups; the first half runs while the chain warps still
-          // work on the second, so the output accumulator completes right behind the state update
-#pragma unroll
-          for (int h = 0; h < 2; ++h) {
-            const int ks = h * 2 + part;
-            mma_ts(tmem + kAccO, tmem + kAccX + 64 + ks * 16, pd + uint64_t(ks * 2), kIdescN64, 1);
-          }
+        for (int h = 0; h < 2; ++h) {
+          const int ks = h * 2;
+          const uint64_t kdesc = kd + uint64_t(ks * 128);                              // +2048 bytes per K step
+          mma_ts(tm + kAccS, tm + kAccX + ks * 16, kdesc, kIdescN128BT, 1);
+          mma_ts(tm + kAccS, tm + kAccX + ks * 16 + 8, kdesc, kIdescN128BT, 1);
         }
-        if (!ok) break;
+#pragma unroll
+        for (int h = 0; h < 2; ++h) mma_ts(tm + kAccO, tm + kAccX + 64 + h * 32, pd + uint64_t(h * 4), kIdescN64, 1);
+        ok &= mbar_wait(bar_opn + 1, c & 1, abort, 43, c);
+        tc_fence_after();
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          const int ks = h * 2 + 1;
+          const uint64_t kdesc = kd + uint64_t(ks * 128);
+          mma_ts(tm + kAccS, tm + kAccX + ks * 16, kdesc, kIdescN128BT, 1);
+          mma_ts(tm + kAccS, tm + kAccX + ks * 16 + 8, kdesc, kIdescN128BT, 1);
+        }
+        mma_commit(bar_s);
+#pragma unroll
+        for (int h = 0; h < 2; ++h)
+          mma_ts(tm + kAccO, tm + kAccX + 64 + (h * 2 + 1) * 16, pd + uint64_t((h * 2 + 1) * 2), kIdescN64, 1);
         mma_commit(bar_o);
-        mma_commit(empty + s);
+        mma_commit(empty + (c & 1));
       }
     }
     __syncwarp();

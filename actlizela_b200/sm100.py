@@ -15,7 +15,7 @@ from .sm100_policy import policy, selection_for
 
 MATH_CONTRACT = "wy-splitbf16-state-bf16-out-sm100-v1"
 _DIAGNOSTIC_IDS = {"simt": 0, "umma": 1, "simt-prepare+umma-walk": 2, "umma-prepare+simt-walk": 3,
-                   "umma-seg2": 1 | (2 << 8), "umma-seg4": 1 | (4 << 8), "umma-seg8": 1 | (8 << 8),
+                   "umma-seg2": 1 | (2 << 8), "umma-seg4": 1 | (4 << 8), "umma-seg8": 1 | (8 << 8), "umma-seg16": 1 | (16 << 8),
                    "chain": 4, "chain-seg2": 4 | (2 << 8), "chain-seg4": 4 | (4 << 8), "chain-seg8": 4 | (8 << 8)}
 
 
