@@ -6,6 +6,7 @@
 #include "gdn_common.cuh"
 
 #include <climits>
+#include <vector>
 
 namespace gdn_sm100 {
 namespace {
@@ -212,6 +213,59 @@ extern "C" int actlize_la_sm100_forward_prepared(
   return is_chain(config)       ? launch_walk_chain(in, geo, ws, stream)
          : walk_is_umma(config) ? launch_walk_umma(in, geo, ws, stream)
                                 : launch_walk_simt(in, geo, ws, stream);
+}
+
+// ---------------------------------------------------------------------------------- packed sequences
+namespace {
+long long align256_ll(long long x) { return (x + 255) & ~255LL; }
+long long varlen_table_bytes(int n_seqs) { return align256_ll(2LL * (n_seqs + 1) * (long long)sizeof(int)); }
+}  // namespace
+
+extern "C" long long actlize_la_sm100_varlen_workspace_bytes(long long total_tokens, int n_seqs, int hk, int hv) {
+  if (total_tokens <= 0 || total_tokens > INT_MAX || n_seqs <= 0 || !geometry_ok(1, int(total_tokens), hk, hv)) return -1;
+  // every sequence starts a new chunk, so each may add one partly filled chunk to ceil(total / 64)
+  const long long max_chunks = (total_tokens + kChunk - 1) / kChunk + n_seqs;
+  if (max_chunks * hv > INT_MAX / kChunk || (long long)n_seqs * hv > INT_MAX / 4) return -1;
+  return varlen_table_bytes(n_seqs) + max_chunks * hv * kBlockBytes;
+}
+
+extern "C" int actlize_la_sm100_forward_varlen(
+    const void* q, const void* k, const void* v, const void* g, const void* beta,
+    const float* initial_states, void* output, float* final_states,
+    void* workspace, long long workspace_bytes_given,
+    const int* cu_seqlens_host, int n_seqs, int hk, int hv, int gate_fp32, void* opaque_stream) {
+  if (!q || !k || !v || !g || !beta || !output || !workspace || !cu_seqlens_host) return int(cudaErrorInvalidValue);
+  if (n_seqs <= 0 || cu_seqlens_host[0] != 0) return int(cudaErrorInvalidValue);
+  for (int i = 0; i < n_seqs; ++i)
+    if (cu_seqlens_host[i + 1] < cu_seqlens_host[i]) return int(cudaErrorInvalidValue);
+  const int total = cu_seqlens_host[n_seqs];
+  const long long need = actlize_la_sm100_varlen_workspace_bytes(total, n_seqs, hk, hv);
+  if (need < 0 || workspace_bytes_given < need) return int(cudaErrorInvalidValue);
+  if ((reinterpret_cast<uintptr_t>(workspace) & 255) || (reinterpret_cast<uintptr_t>(q) & 15) ||
+      (reinterpret_cast<uintptr_t>(k) & 15) || (reinterpret_cast<uintptr_t>(v) & 15) ||
+      (reinterpret_cast<uintptr_t>(output) & 15))
+    return int(cudaErrorInvalidValue);
+  // offsets table: cu_seqlens[0..n] then chunk_prefix[0..n]
+  std::vector<int> table(2 * (n_seqs + 1));
+  int chunks = 0;
+  for (int i = 0; i <= n_seqs; ++i) {
+    table[i] = cu_seqlens_host[i];
+    table[n_seqs + 1 + i] = chunks;
+    if (i < n_seqs) chunks += (cu_seqlens_host[i + 1] - cu_seqlens_host[i] + kChunk - 1) / kChunk;
+  }
+  cudaStream_t stream = static_cast<cudaStream_t>(opaque_stream);
+  // pageable source: the runtime has staged the bytes when the call returns, so `table` may go out of scope
+  cudaError_t e = cudaMemcpyAsync(workspace, table.data(), table.size() * sizeof(int), cudaMemcpyHostToDevice, stream);
+  if (e != cudaSuccess) return int(e);
+  Geometry geo{n_seqs, total, hk, hv};
+  geo.varlen = static_cast<const int*>(workspace);
+  geo.total_chunks = chunks;
+  const Inputs in{static_cast<const __nv_bfloat16*>(q), static_cast<const __nv_bfloat16*>(k),
+                  static_cast<const __nv_bfloat16*>(v), g, static_cast<const __nv_bfloat16*>(beta),
+                  initial_states, static_cast<__nv_bfloat16*>(output), final_states, gate_fp32 ? 1 : 0};
+  const Workspace ws = carve_workspace(static_cast<char*>(workspace) + varlen_table_bytes(n_seqs), geo);
+  if (int rc = launch_prepare_umma(in, geo, ws, stream)) return rc;
+  return launch_walk_umma(in, geo, ws, stream);
 }
 
 namespace {

@@ -19,15 +19,32 @@ struct Geometry {
   int batch, sequence, key_heads, value_heads;
   // A launch may cover a contiguous range of chunks only (sequence segment); 0 chunks = the whole sequence.
   int chunk_begin = 0, chunk_count = 0;
-  __host__ __device__ int chunks() const { return (sequence + kChunk - 1) / kChunk; }
+  // Packed variable-length mode (tcgen05 kernels only): the tensors are [1, sequence = total tokens, H, ...],
+  // `batch` is the number of sequences and `varlen` points at 2 (batch + 1) device integers: the token offsets
+  // cu_seqlens[0..batch] followed by the chunk offsets chunk_prefix[0..batch] (every sequence starts a new chunk);
+  // `total_chunks` = chunk_prefix[batch].  Workspace blocks are then indexed hv * total_chunks + global chunk.
+  const int* varlen = nullptr;
+  int total_chunks = 0;
+  __host__ __device__ int chunks() const { return varlen ? total_chunks : (sequence + kChunk - 1) / kChunk; }
   __host__ __device__ int segment_chunks() const { return chunk_count ? chunk_count : chunks(); }
   __host__ __device__ bool first_segment() const { return chunk_begin == 0; }
   __host__ __device__ bool last_segment() const { return chunk_begin + segment_chunks() == chunks(); }
   __host__ __device__ int group() const { return value_heads / key_heads; }
   __host__ __device__ long long blocks() const {
-    return (long long)batch * value_heads * chunks();
+    return varlen ? (long long)value_heads * total_chunks : (long long)batch * value_heads * chunks();
   }
 };
+
+// Packed mode: the sequence that owns global chunk `gchunk` (largest s with chunk_prefix[s] <= gchunk; empty
+// sequences share their successor's offset and are skipped by the search).
+__device__ __forceinline__ int varlen_sequence_of(const int* chunk_prefix, int count, int gchunk) {
+  int lo = 0, hi = count;          // invariant: chunk_prefix[lo] <= gchunk < chunk_prefix[hi]
+  while (hi - lo > 1) {
+    const int mid = (lo + hi) >> 1;
+    if (chunk_prefix[mid] <= gchunk) lo = mid; else hi = mid;
+  }
+  return lo;
+}
 
 // Workspace: structure-of-arrays planes, one entry per (batch, value head, chunk) block,
 // block index = (b * Hv + hv) * chunks + c.  Per block:

@@ -167,13 +167,24 @@ prepare_umma_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
 
   const int tid = threadIdx.x, warp = tid >> 5;
   const int chunks = geo.chunks(), seg_chunks = geo.segment_chunks();
-  const int chunk = geo.chunk_begin + blockIdx.x % seg_chunks;
+  int chunk = geo.chunk_begin + blockIdx.x % seg_chunks;      // chunk index inside its sequence
   const int bh = blockIdx.x / seg_chunks;
-  const int b = bh / geo.value_heads, hv = bh % geo.value_heads;
+  const int b = bh / geo.value_heads, hv = bh % geo.value_heads;     // packed mode: bh = hv, b = 0
   const int hk = hv / geo.group();
-  const int t0 = chunk * kChunk;
-  const int valid = min(kChunk, geo.sequence - t0);
-  const long long block = (long long)bh * chunks + chunk;
+  int t0 = chunk * kChunk, t_end = geo.sequence;
+  long long block = (long long)bh * chunks + chunk;
+  if (geo.varlen) {
+    // packed sequences: the grid runs over (value head, global chunk); rows behind the sequence end belong to the
+    // next sequence and are neutralised by beta = 0 / zero gate weights exactly like zero-filled padding rows
+    const int gchunk = chunk;
+    const int* prefix = geo.varlen + geo.batch + 1;
+    const int seq = varlen_sequence_of(prefix, geo.batch, gchunk);
+    chunk = gchunk - prefix[seq];
+    t0 = geo.varlen[seq] + chunk * kChunk;
+    t_end = geo.varlen[seq + 1];
+    block = (long long)hv * chunks + gchunk;
+  }
+  const int valid = min(kChunk, t_end - t0);
 #ifdef GDN_SM100_PHASE_TIMING
   const long long t_begin = clock64();
 #endif
@@ -706,10 +717,22 @@ walk_umma_kernel(const __grid_constant__ CUtensorMap tm_wh, const __grid_constan
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int bh = blockIdx.x;
-  const int b = bh / geo.value_heads, hv = bh % geo.value_heads;
+  int b = bh / geo.value_heads;
+  const int hv = bh % geo.value_heads;
   const int hk = hv / geo.group();
-  const int chunks = geo.segment_chunks(), c0 = geo.chunk_begin;     // this launch walks chunks [c0, c0 + chunks)
-  const long long block0 = (long long)bh * geo.chunks() + c0;
+  int chunks = geo.segment_chunks();                 // this launch walks `chunks` chunks from token t_first on
+  int t_first = geo.chunk_begin * kChunk, tail_valid = kChunk;
+  long long block0 = (long long)bh * geo.chunks() + geo.chunk_begin;
+  if (geo.varlen) {
+    // packed sequences: one CTA per (sequence, value head); states are indexed by bh = sequence * Hv + hv
+    const int seq = b;
+    const int* prefix = geo.varlen + geo.batch + 1;
+    chunks = prefix[seq + 1] - prefix[seq];
+    t_first = geo.varlen[seq];
+    tail_valid = geo.varlen[seq + 1] - t_first - (chunks - 1) * kChunk;     // rows of the sequence's last chunk
+    block0 = (long long)hv * geo.total_chunks + prefix[seq];
+    b = 0;
+  }
   const float* state_in = geo.first_segment() ? in.initial : ws.carry;
   float* state_out = geo.last_segment() ? in.final_state : ws.carry;
 #ifdef GDN_SM100_PHASE_TIMING
@@ -842,7 +865,7 @@ walk_umma_kernel(const __grid_constant__ CUtensorMap tm_wh, const __grid_constan
       }
       GDN_STAMP(3);
     }
-    if (ok) ok = mbar_wait(bar_s, (chunks - 1) & 1, abort, 13, chunks);
+    if (ok && chunks > 0) ok = mbar_wait(bar_s, (chunks - 1) & 1, abort, 13, chunks);
     if (ok && state_out) {
       tc_fence_after();
       float* fin = state_out + (long long)bh * kDim * kDim + v;
@@ -883,6 +906,16 @@ walk_umma_kernel(const __grid_constant__ CUtensorMap tm_wh, const __grid_constan
       __syncwarp();
       if (lane == 0) mbar_arrive(bar_ofree);
       GDN_OSTAMP(1);
+      if (geo.varlen && c == chunks - 1 && tail_valid < kChunk) {
+        // packed mode, ragged end of a sequence: the rows behind it belong to the next sequence, so the tile
+        // cannot leave through a clipping TMA store; this is the sequence's last chunk, nothing follows it
+        __nv_bfloat16* out = in.output + ((long long)(t_first + c * kChunk) * geo.value_heads + hv) * kDim + v;
+        const long long row = (long long)geo.value_heads * kDim;
+#pragma unroll
+        for (int i = 0; i < 64; ++i)
+          if (i < tail_valid) out[i * row] = __float2bfloat16_rn(__uint_as_float(o[i]));
+        break;
+      }
       // stage the tile as two 128-byte-swizzled boxes [token][64 values] and hand it to a TMA store,
       // which also clips the rows of a tail chunk at the sequence end
       uint8_t* stage = sm + L::kOut + (c & 1) * 2 * kBox + (v >> 6) * kBox + ((v & 7) << 1);
@@ -901,8 +934,8 @@ walk_umma_kernel(const __grid_constant__ CUtensorMap tm_wh, const __grid_constan
         ok = mbar_wait(bar_staged, c & 1, abort, 22, c);
         if (!ok) break;
         const uint8_t* tile = sm + L::kOut + (c & 1) * 2 * kBox;
-        tma_store_4d(&tm_out, tile, 0, hv, (c0 + c) * kChunk, b);
-        tma_store_4d(&tm_out, tile + kBox, 64, hv, (c0 + c) * kChunk, b);
+        tma_store_4d(&tm_out, tile, 0, hv, t_first + c * kChunk, b);
+        tma_store_4d(&tm_out, tile + kBox, 64, hv, t_first + c * kChunk, b);
         tma_store_commit();
         tma_store_wait_read_keep1();
         mbar_arrive(bar_stfree);
@@ -931,8 +964,8 @@ walk_umma_kernel(const __grid_constant__ CUtensorMap tm_wh, const __grid_constan
         tma_load_2d(st + L::kB1 + L::kWL, &tm_wl, full + s, 64, row);
         tma_load_2d(st + L::kB0 + L::kQS, &tm_qs, full + s, 0, row);
         tma_load_2d(st + L::kB1 + L::kQS, &tm_qs, full + s, 64, row);
-        tma_load_4d(st + L::kK, &tm_k, full + s, 0, hk, (c0 + c) * kChunk, b);
-        tma_load_4d(st + L::kK + kBox, &tm_k, full + s, 64, hk, (c0 + c) * kChunk, b);
+        tma_load_4d(st + L::kK, &tm_k, full + s, 0, hk, t_first + c * kChunk, b);
+        tma_load_4d(st + L::kK + kBox, &tm_k, full + s, 64, hk, t_first + c * kChunk, b);
         tma_load_2d(st + L::kP, &tm_p, full + s, 0, row);
       }
     }
@@ -1039,13 +1072,13 @@ int launch_prepare_tc(const Inputs& in, const Geometry& geo, const Workspace& ws
   if (int rc = enc.init()) return rc;
   CUtensorMap tm_q, tm_k, tm_v, tm_wh, tm_wl, tm_u;
   const uint64_t rows = uint64_t(geo.blocks()) * kChunk;
-  if (int rc = enc.bf16_4d(&tm_q, in.q, kDim, geo.key_heads, geo.sequence, geo.batch, kChunk)) return rc;
-  if (int rc = enc.bf16_4d(&tm_k, in.k, kDim, geo.key_heads, geo.sequence, geo.batch, kChunk)) return rc;
-  if (int rc = enc.bf16_4d(&tm_v, in.v, kDim, geo.value_heads, geo.sequence, geo.batch, kChunk)) return rc;
+  if (int rc = enc.bf16_4d(&tm_q, in.q, kDim, geo.key_heads, geo.sequence, geo.varlen ? 1 : geo.batch, kChunk)) return rc;
+  if (int rc = enc.bf16_4d(&tm_k, in.k, kDim, geo.key_heads, geo.sequence, geo.varlen ? 1 : geo.batch, kChunk)) return rc;
+  if (int rc = enc.bf16_4d(&tm_v, in.v, kDim, geo.value_heads, geo.sequence, geo.varlen ? 1 : geo.batch, kChunk)) return rc;
   if (int rc = enc.bf16_2d(&tm_wh, ws.w_hi, kDim, rows, kChunk)) return rc;
   if (int rc = enc.bf16_2d(&tm_wl, ws.w_lo, kDim, rows, kChunk)) return rc;
   if (int rc = enc.f32_2d(&tm_u, ws.u, kDim, rows, kChunk)) return rc;
-  const unsigned grid = (unsigned)((long long)geo.batch * geo.value_heads * geo.segment_chunks());
+  const unsigned grid = (unsigned)((geo.varlen ? 1LL : (long long)geo.batch) * geo.value_heads * geo.segment_chunks());
   if (chained)
     prepare_umma_kernel<true><<<grid, kPrepThreads, kPrepSmem, stream>>>(tm_q, tm_k, tm_v, tm_wh, tm_wl, tm_u, in, geo, ws);
   else
@@ -1066,11 +1099,11 @@ int launch_walk_umma(const Inputs& in, const Geometry& geo, const Workspace& ws,
   if (int rc = enc.init()) return rc;
   const uint64_t rows = uint64_t(geo.blocks()) * kChunk;
   CUtensorMap tm_wh, tm_wl, tm_qs, tm_k, tm_p, tm_out;
-  if (int rc = enc.bf16_4d(&tm_out, in.output, kDim, geo.value_heads, geo.sequence, geo.batch, kChunk)) return rc;
+  if (int rc = enc.bf16_4d(&tm_out, in.output, kDim, geo.value_heads, geo.sequence, geo.varlen ? 1 : geo.batch, kChunk)) return rc;
   if (int rc = enc.bf16_2d(&tm_wh, ws.w_hi, kDim, rows, kChunk)) return rc;
   if (int rc = enc.bf16_2d(&tm_wl, ws.w_lo, kDim, rows, kChunk)) return rc;
   if (int rc = enc.bf16_2d(&tm_qs, ws.qs, kDim, rows, kChunk)) return rc;
-  if (int rc = enc.bf16_4d(&tm_k, in.k, kDim, geo.key_heads, geo.sequence, geo.batch, kChunk)) return rc;
+  if (int rc = enc.bf16_4d(&tm_k, in.k, kDim, geo.key_heads, geo.sequence, geo.varlen ? 1 : geo.batch, kChunk)) return rc;
   if (int rc = enc.bf16_2d(&tm_p, ws.p, kChunk, rows, kChunk)) return rc;
   walk_umma_kernel<<<geo.batch * geo.value_heads, kWalkThreads, kWalkSmem, stream>>>(tm_wh, tm_wl, tm_qs, tm_k,
                                                                                     tm_p, tm_out, in, geo, ws);

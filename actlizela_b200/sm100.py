@@ -107,6 +107,40 @@ class Sm100Forward:
                 int(g.dtype == torch.float32), config, stream))
         return out, final
 
+    def varlen(self, q, k, v, g, beta, cu_seqlens, initial_states=None, output_final_state=True):
+        """Packed sequences in one prepare and one walk launch (actlize_la_sm100_forward_varlen)."""
+        import ctypes
+        import torch
+        b, total, hk, hv = _validate(q, k, v, g, beta, None)
+        bounds = [int(x) for x in cu_seqlens]
+        n = len(bounds) - 1
+        if b != 1 or n < 1 or bounds[0] != 0 or bounds[-1] != total:
+            raise ValueError("varlen expects batch 1 and cu_seqlens running from 0 to the token count")
+        if any(b1 < b0 for b0, b1 in zip(bounds, bounds[1:])):
+            raise ValueError("cu_seqlens must be non-decreasing")
+        if initial_states is not None:
+            if (tuple(initial_states.shape) != (n, hv, 128, 128) or initial_states.dtype != torch.float32
+                    or initial_states.device != q.device or not initial_states.is_contiguous()):
+                raise ValueError("initial_states must be contiguous FP32 [N,Hv,128,128] on the inputs' device")
+        self.library.configure(q.device)
+        out = torch.empty_like(v)
+        final = (torch.empty((n, hv, 128, 128), dtype=torch.float32, device=q.device)
+                 if output_final_state else None)
+        lib = self.library.lib
+        nbytes = lib.actlize_la_sm100_varlen_workspace_bytes(total, n, hk, hv)
+        if nbytes < 0:
+            raise ValueError("geometry exceeds the native grid limits")
+        workspace = self._workspace(q.device, nbytes)
+        offsets = (ctypes.c_int * (n + 1))(*bounds)
+        with torch.cuda.device(q.device):
+            stream = torch.cuda.current_stream().cuda_stream
+            self.library.check(lib.actlize_la_sm100_forward_varlen(
+                q.data_ptr(), k.data_ptr(), v.data_ptr(), g.data_ptr(), beta.data_ptr(),
+                initial_states.data_ptr() if initial_states is not None else None,
+                out.data_ptr(), final.data_ptr() if final is not None else None,
+                workspace.data_ptr(), nbytes, offsets, n, hk, hv, int(g.dtype == torch.float32), stream))
+        return out, final
+
 
 _FORWARD = {}
 

@@ -157,6 +157,21 @@ def aux_bench(args):
         call = lambda: gdn_prepare_inputs(mixed, a, a, a_log, bias, hk, hv)
         nbytes, units, unit = 2 * mixed.numel() * 2 + n * hv * (2 + 2 + 4 + 2), n, "tokens/s"
         name = f"prepare_inputs N{n} Hk{hk} Hv{hv}"
+    elif args.op == "varlen":
+        # 64 packed prefill requests with seeded ragged lengths (mean 256 tokens); per token and value head the same
+        # algorithmic bytes as the fixed-shape forward
+        from actlizela_b200 import gdn_forward_varlen
+        from actlizela_b200.workloads import Workload, make_inputs
+        lengths = torch.randint(1, 512, (64,), generator=gen).tolist()
+        bounds = [0]
+        for n in lengths:
+            bounds.append(bounds[-1] + n)
+        w = Workload("varlen", 1, bounds[-1], hk, hv)
+        q, k, v, g, beta, _ = [x.cuda() if x is not None else None for x in make_inputs(w)]
+        call = lambda: gdn_forward_varlen(q, k, v, g, beta, bounds, None, True)
+        nbytes = (2 * q.numel() + 2 * v.numel()) * 2 + g.numel() * 4 + beta.numel() * 2 + 64 * hv * 128 * 128 * 4
+        units, unit = bounds[-1], "tokens/s"
+        name = f"varlen 64 sequences {bounds[-1]} tokens Hk{hk} Hv{hv}"
     else:
         rows = 65536 * hv
         y = torch.randn(rows, 128, generator=gen).to(torch.bfloat16).cuda()
@@ -179,7 +194,7 @@ def aux_bench(args):
     print(json.dumps(dict(metric=f"{args.op} {unit}", value=units / (ms * 1e-3), unit=unit, n_gpus=1, steps=args.steps,
                           warmup=max(3, args.warmup), ms_per_step=ms, higher_is_better=True, data="synthetic",
                           config=dict(workload=name, l2="working set exceeds the 126 MB L2"),
-                          gpu_launches=args.steps,
+                          gpu_launches=args.steps * (2 if args.op == "varlen" else 1),
                           roofline=dict(bound="hbm", achieved=achieved, peak=peak, unit="GB/s", frac=achieved / peak,
                                         traffic=None, peak_source=source, algorithmic_bytes=nbytes))), flush=True)
 
@@ -193,7 +208,7 @@ def main():
     ap.add_argument("--configuration", default=None, help="diagnostic override of the policy table")
     ap.add_argument("--impl", default="native", choices=("native", "reference"))
     ap.add_argument("--skip-cpu-baseline", action="store_true")
-    ap.add_argument("--op", default="forward", choices=("forward", "decode", "prepare_inputs", "rmsnorm_gated"),
+    ap.add_argument("--op", default="forward", choices=("forward", "decode", "prepare_inputs", "rmsnorm_gated", "varlen"),
                     help="forward is the headline metric; the others time a neighbouring memory-bound kernel")
     args = ap.parse_args()
     if args.op != "forward":

@@ -149,6 +149,23 @@ int actlize_la_sm100_device_status(int* status4, int reset);
  * context stays usable.  No counterpart in the reference, whose kernels wait without a limit. */
 int actlize_la_sm100_selftest_wait_timeout(int tag, void* stream);
 
+/* Packed variable-length sequences: q,k [1,total,Hk,128], v [1,total,Hv,128], g/beta [1,total,Hv] hold n_seqs
+ * sequences back to back; cu_seqlens_host[0..n_seqs] (HOST integers, 0 = first, total = last, non-decreasing)
+ * marks the boundaries; initial_states / final_states are FP32 [n_seqs,Hv,128,128] (nullable).  Every sequence
+ * is chunked from its own start, an empty sequence passes its state through.  The reference has no such entry:
+ * its serving prefill pads the requests into a fixed [R,W] batch first (csrc/serving/prefill.cu:196-255,
+ * csrc/serving/abi.h:48-56); this entry removes the padding.  Two launches (tcgen05 prepare + walk) on `stream`
+ * plus one small host-to-device copy of the offsets table (from pageable memory: not for stream capture).
+ * Rows behind a sequence's end inside its last chunk are the next sequence's tokens; they are multiplied by
+ * exact zeros, so all inputs must be finite.  `workspace` needs actlize_la_sm100_varlen_workspace_bytes(...)
+ * bytes, 256-byte aligned.  Returns 0 or a cudaError_t value. */
+long long actlize_la_sm100_varlen_workspace_bytes(long long total_tokens, int n_seqs, int hk, int hv);
+int actlize_la_sm100_forward_varlen(
+    const void* q, const void* k, const void* v, const void* g, const void* beta,
+    const float* initial_states, void* output, float* final_states,
+    void* workspace, long long workspace_bytes,
+    const int* cu_seqlens_host, int n_seqs, int hk, int hv, int gate_fp32, void* stream);
+
 /* The same forward for callers that cannot allocate device memory (no counterpart in the
  * reference): the workspace is a fixed array inside the library instead of a caller buffer.
  * Meant for plugins inside a host framework that owns all allocations, or loops where a

@@ -99,3 +99,48 @@ def test_varlen_matches_per_sequence_oracle():
         assert oracle.max_abs(out[:, t0:t1].float().cpu(), want_out.float()) <= 2e-2
         assert oracle.rel_frobenius(out[:, t0:t1].float().cpu(), want_out.float()) <= 1e-2
         assert oracle.rel_frobenius(finals[i:i + 1].cpu(), want_state) <= 1e-3
+
+
+@pytest.mark.parametrize("lengths", [[130, 1, 64, 0, 257, 63], [5], [64, 64], [0, 200, 0], [1] * 9, [700, 3, 129]])
+def test_native_varlen_equals_the_per_sequence_forward_bitwise(lengths):
+    """One prepare and one walk launch for all sequences give the bits of N fixed-shape forwards: the rows behind a
+    ragged sequence end (the next sequence's tokens) only ever meet exact zeros."""
+    from actlizela_b200 import gdn_forward_varlen
+    from actlizela_b200.workloads import WORKLOADS, make_inputs
+    bounds = [0]
+    for n in lengths:
+        bounds.append(bounds[-1] + n)
+    w = WORKLOADS["cfg1"].sliced(batch=1, length=bounds[-1], key_heads=2, value_heads=6, initial=None)   # group of 3
+    q, k, v, g, beta, _ = [x.cuda() if x is not None else None for x in make_inputs(w)]
+    init = (0.1 * torch.randn(len(lengths), 6, 128, 128, generator=torch.Generator().manual_seed(7))).cuda()
+    for initial in (init, None):
+        out, finals = gdn_forward_varlen(q, k, v, g, beta, bounds, initial, True)
+        ref_out, ref_finals = gdn_forward_varlen(q, k, v, g, beta, bounds, initial, True, per_sequence=True,
+                                                 algorithm="wy_sm100", backend="cuda_sm100", configuration="umma")
+        torch.cuda.synchronize()
+        assert torch.equal(out, ref_out)
+        assert torch.equal(finals, ref_finals)
+        out_only, none = gdn_forward_varlen(q, k, v, g, beta, bounds, initial, False)
+        assert none is None and torch.equal(out_only, out)
+
+
+def test_native_varlen_rejects_bad_offsets(native_library):
+    from actlizela_b200 import gdn_forward_varlen
+    from actlizela_b200.workloads import WORKLOADS, make_inputs
+    w = WORKLOADS["cfg3"].sliced(batch=1, length=100, key_heads=1, value_heads=2, initial=None)
+    q, k, v, g, beta, _ = [x.cuda() if x is not None else None for x in make_inputs(w)]
+    for bad in ([0, 50], [1, 100], [0, 60, 40, 100], [0]):
+        with pytest.raises(ValueError):
+            gdn_forward_varlen(q, k, v, g, beta, bad)
+    # the C entry checks on its own as well
+    import ctypes
+    lib = native_library.lib
+    nbytes = lib.actlize_la_sm100_varlen_workspace_bytes(100, 2, 1, 2)
+    ws = torch.empty(nbytes, dtype=torch.uint8, device="cuda")
+    out = torch.empty_like(v)
+    offsets = (ctypes.c_int * 3)(0, 70, 60)
+    rc = lib.actlize_la_sm100_forward_varlen(q.data_ptr(), k.data_ptr(), v.data_ptr(), g.data_ptr(), beta.data_ptr(), None,
+                                             out.data_ptr(), None, ws.data_ptr(), nbytes, offsets, 2, 1, 2, 1,
+                                             torch.cuda.current_stream().cuda_stream)
+    assert rc != 0
+    assert lib.actlize_la_sm100_varlen_workspace_bytes(0, 1, 1, 2) < 0
