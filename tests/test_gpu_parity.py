@@ -349,3 +349,30 @@ def test_random_geometries(seed, forward):
     want_out, want_state = oracle.chunk_forward_fp32(*cpu, output_final_state=True)
     out, state = forward(*_to_device(cpu), True)
     _check(out, state, want_out, want_state, ("random", seed, w.shape))
+
+
+@pytest.mark.parametrize("configuration", ["umma", "chain", "chain-seg4"])
+@pytest.mark.parametrize("gate", ["none", "strong", "underflow", "mixed"])
+def test_extreme_gates(gate, configuration, forward, native_library):
+    """Gate ranges beyond the benchmark distributions: no decay at all, a decay that empties the state within a
+    chunk, one whose chunk product underflows FP32 (the chained configuration divides a clamped decay out of G),
+    and a mixture of these per head."""
+    w = WORKLOADS["cfg3"].sliced(batch=1, length=520, key_heads=2, value_heads=4, initial=0.1, seed=4242)
+    q, k, v, g, beta, init = make_inputs(w)
+    gen = torch.Generator().manual_seed(99)
+    if gate == "none":
+        g = torch.zeros_like(g)
+    elif gate == "strong":
+        g = -2.0 * torch.rand(g.shape, generator=gen)
+    elif gate == "underflow":
+        g = -2.0 - 3.0 * torch.rand(g.shape, generator=gen)          # chunk sums near -220: exp underflows
+    else:
+        g = torch.stack([torch.zeros(g.shape[:2]), -0.01 * torch.rand(g.shape[:2], generator=gen),
+                         -3.0 * torch.rand(g.shape[:2], generator=gen), -6.0 * torch.ones(g.shape[:2])], dim=-1)
+    cpu = (q, k, v, g.float().contiguous(), beta, init)
+    want_out, want_state = oracle.wy_chunk_forward(*cpu)
+    out, state = forward(*_to_device(cpu), True, configuration=configuration)
+    torch.cuda.synchronize()
+    assert _status(native_library)[0] == 0
+    assert torch.isfinite(state).all()
+    _check(out, state, want_out, want_state, ("extreme gate", gate, configuration))
