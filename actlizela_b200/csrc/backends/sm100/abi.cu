@@ -28,11 +28,17 @@ bool geometry_ok(int b, int t, int hk, int hv) {
 // factors of the same inputs).
 // Bits 8..15 hold the number of sequence segments (0 or 1 = one): the prepare kernels of later
 // segments then run next to the walk of earlier ones (tcgen05 configuration only).
+// Bits 6 and 7 modify a walk-only call of the tcgen05 configuration (sequence-parallel scheme):
+// 0x40 = treat U as zero (state-transition pass), 0x80 = stop each (batch, value head) walk once the decay
+// accumulated since its start is below exp(-40) (no final state is written then).
 constexpr int kStageMask = 0x30, kPrepareOnly = 0x10, kWalkOnly = 0x20, kSegmentShift = 8, kMaxSegments = 16;
+constexpr int kWalkFlagMask = 0xc0, kHomogeneousBit = 0x40, kUntilDecayedBit = 0x80;
 bool config_ok(int config) {
   const int segments = (config >> kSegmentShift) & 0xff;
-  return config >= 0 && (config & 0xf) <= 4 && (config & ~(kStageMask | 0xf | (0xff << kSegmentShift))) == 0 &&
-         (config & kStageMask) != kStageMask && segments <= kMaxSegments;
+  if (config < 0 || (config & 0xf) > 4 || (config & ~(kStageMask | kWalkFlagMask | 0xf | (0xff << kSegmentShift))) != 0)
+    return false;
+  if ((config & kWalkFlagMask) && ((config & 0xf) != 1 || (config & kStageMask) != kWalkOnly)) return false;
+  return (config & kStageMask) != kStageMask && segments <= kMaxSegments;
 }
 int segments_of(int config, const Geometry& geo) {
   int segments = (config >> kSegmentShift) & 0xff;
@@ -136,7 +142,19 @@ extern "C" int actlize_la_sm100_select(int b, int t, int hk, int hv, int gate_fp
   if (!geometry_ok(b, t, hk, hv)) return -1;
   for (const PolicyRow& row : kPolicyRows)
     if (row.b == b && row.t == t && row.hk == hk && row.hv == hv) return row.config | (row.segments << kSegmentShift);
-  return kPolicyDefault;
+  // no measured row: integer rule fitted to the measured ones (sm100_policy.py::default_segments is the same)
+  const long long heads = (long long)b * hv, chunks = (t + kChunk - 1) / kChunk;
+  int segments = 1;
+  if (heads > 148) {
+    segments = 1;
+  } else if (heads > 64) {
+    segments = chunks >= 16 ? 2 : 1;
+  } else {
+    int root = 0;
+    while ((long long)(root + 1) * (root + 1) <= chunks / 8) ++root;
+    segments = root < 1 ? 1 : (root > 8 ? 8 : root);
+  }
+  return kPolicyDefault | (kPolicyDefault == 1 ? segments << kSegmentShift : 0);
 }
 
 extern "C" long long actlize_la_sm100_workspace_bytes(int b, int t, int hk, int hv, int config) {
@@ -177,9 +195,11 @@ extern "C" int actlize_la_sm100_forward_prepared(
     return int(cudaErrorInvalidValue);
   if (output == workspace || (void*)final_state == workspace || (void*)final_state == output)
     return int(cudaErrorInvalidValue);
+  if ((config & kUntilDecayedBit) && final_state) return int(cudaErrorInvalidValue);   // a cut-short walk has no final state
   const Inputs in{static_cast<const __nv_bfloat16*>(q), static_cast<const __nv_bfloat16*>(k),
                   static_cast<const __nv_bfloat16*>(v), g, static_cast<const __nv_bfloat16*>(beta),
-                  initial, static_cast<__nv_bfloat16*>(output), final_state, gate_fp32 ? 1 : 0};
+                  initial, static_cast<__nv_bfloat16*>(output), final_state, gate_fp32 ? 1 : 0,
+                  ((config & kHomogeneousBit) ? kWalkHomogeneous : 0) | ((config & kUntilDecayedBit) ? kWalkUntilDecayed : 0)};
   const Workspace ws = carve_workspace(workspace, geo, is_chain(config));
   cudaStream_t stream = static_cast<cudaStream_t>(opaque_stream);
   if (segments > 1) {

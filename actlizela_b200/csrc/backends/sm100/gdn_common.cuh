@@ -110,7 +110,14 @@ struct Inputs {
   __nv_bfloat16* output;
   float* final_state;     // nullable
   int gate_fp32;
+  // tcgen05 walk only, for the sequence-parallel scheme:
+  //   kWalkHomogeneous  treat U as zero (the state-transition pass: V = 0)
+  //   kWalkUntilDecayed stop a (batch, value head) walk at the first chunk boundary where the decay accumulated
+  //                     since the walk's start is below exp(-40); later outputs are left as they are
+  int walk_flags = 0;
 };
+constexpr int kWalkHomogeneous = 1, kWalkUntilDecayed = 2;
+constexpr float kDecayedLog2 = -40.f * 1.4426950408889634f;
 
 __device__ __forceinline__ float load_gate(const void* g, long long index, int gate_fp32) {
   return gate_fp32 ? static_cast<const float*>(g)[index]

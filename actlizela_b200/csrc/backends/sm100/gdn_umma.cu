@@ -713,6 +713,7 @@ walk_umma_kernel(const __grid_constant__ CUtensorMap tm_wh, const __grid_constan
   uint64_t* bar_stfree = bar_ops + 9;          // an older output store has finished reading its staging tile
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_ops + 10);
   volatile int* abort_word = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  int* limit_slot = reinterpret_cast<int*>(tmem_slot + 2);
   const AbortFlag abort{abort_word};
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -761,10 +762,30 @@ walk_umma_kernel(const __grid_constant__ CUtensorMap tm_wh, const __grid_constan
     tmem_alloc(tmem_slot, 512);
     tmem_relinquish();
   }
+  if ((in.walk_flags & kWalkUntilDecayed) && warp == kTmaWarp) {
+    // first chunk boundary at which the accumulated decay is below exp(-40): 32 chunks per step, the per-chunk
+    // decay exp(p_last) is word 64 of the chunk's gate vector
+    float total = 0.f;
+    int stop = chunks;
+    for (int c0 = 0; c0 < chunks && stop == chunks; c0 += 32) {
+      const int c = c0 + lane;
+      float x = c < chunks ? log2f(ws.gates[(block0 + c) * 128 + kChunk]) : 0.f;
+#pragma unroll
+      for (int d = 1; d < 32; d <<= 1) {
+        const float y = __shfl_up_sync(0xffffffffu, x, d);
+        if (lane >= d) x += y;
+      }
+      const unsigned below = __ballot_sync(0xffffffffu, c < chunks && total + x < kDecayedLog2);
+      if (below) stop = c0 + __ffs(below);          // chunks [0, stop) are walked
+      total += __shfl_sync(0xffffffffu, x, 31);
+    }
+    if (lane == 0) *limit_slot = stop;
+  }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = *tmem_slot;
+  if (in.walk_flags & kWalkUntilDecayed) chunks = *limit_slot;
 
   if (warp >= kChainWarp0 && warp < kChainWarp0 + kChainWarps) {
     // ------------------------------------------------------------------ state chain
@@ -828,7 +849,7 @@ walk_umma_kernel(const __grid_constant__ CUtensorMap tm_wh, const __grid_constan
 
       float u[32];
 #pragma unroll
-      for (int i = 0; i < 32; ++i) u[i] = __ldg(urow + i * kDim);
+      for (int i = 0; i < 32; ++i) u[i] = (in.walk_flags & kWalkHomogeneous) ? 0.f : __ldg(urow + i * kDim);
 
       ok = mbar_wait(bar_ws, c & 1, abort, 12, c);
       if (!ok) break;

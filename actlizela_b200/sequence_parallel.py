@@ -45,46 +45,101 @@ def native_apply_transition(m, b, s):
     return out
 
 
+_DECAYED = -40.0      # natural log: below this a segment's transition matrix is treated as zero
+
+
+def _neighbour(group, rank):
+    import torch.distributed as dist
+    return dist.get_global_rank(group, rank) if group else rank
+
+
 def gdn_forward_sequence_parallel(q, k, v, g, beta, initial_state=None, output_final_state=True, *,
-                                  group=None, forward_fn=None, apply_transition=None,
-                                  **forward_options):
+                                  group=None, forward_fn=None, apply_transition=None, segment_fn=None,
+                                  until_decayed=False, **forward_options):
     """Forward over a sequence split across the ranks of ``group``.
 
     Every rank passes ITS OWN contiguous segment (q,k [B,Tr,Hk,128] ...), segments in rank
     order, every segment except the last a multiple of 64 tokens.  ``initial_state`` is read on
     rank 0 only.  Returns (output of the local segment, final state on the LAST rank or None).
+
+    On CUDA tensors the ranks behind the first prepare their segment once and walk it several times
+    (``Sm100Forward.prepare_segment``): offset and transition pass next to each other, then, once the incoming
+    state has arrived, the final pass.  ``until_decayed=True`` replaces that final pass by a walk over the leading
+    chunks only, those the incoming state still reaches with a weight above exp(-40) (valid when every chunk
+    transition is a contraction, which holds for L2-normalised keys and beta in [0, 1]); the remaining rows keep
+    the zero-state outputs and the final state comes from ``M S_in + b``.  ``forward_fn`` (any complete forward)
+    selects the generic three-pass form instead; ``segment_fn`` substitutes the prepared-segment factory.
     """
     import torch.distributed as dist
+    rank, world = dist.get_rank(group), dist.get_world_size(group)
+    b, t, _, d = q.shape
+    hv = v.shape[2]
+    staged = forward_fn is None and (segment_fn is not None or q.is_cuda)
     if forward_fn is None:
         from .gdn_interface import gdn_forward as forward_fn
     if apply_transition is None:
         apply_transition = native_apply_transition if q.is_cuda else _torch_apply_transition
-    rank, world = dist.get_rank(group), dist.get_world_size(group)
-    b, t, _, d = q.shape
-    hv = v.shape[2]
     if world == 1:
         return forward_fn(q, k, v, g, beta, initial_state, output_final_state, **forward_options)
     if rank < world - 1 and t % 64:
         raise ValueError("every segment but the last must be a multiple of 64 tokens")
-
     state_shape = (b, hv, d, d)
+    last = rank == world - 1
+
     if rank == 0:
-        incoming = initial_state
-    else:
-        transition = offset = None
-        if rank < world - 1:
-            # (M_r, b_r): two state-only passes over the local segment
-            _, offset = forward_fn(q, k, v, g, beta, None, True, **forward_options)
-            eye = torch.eye(d, dtype=torch.float32, device=q.device).expand(state_shape).contiguous()
-            _, transition = forward_fn(q, k, torch.zeros_like(v), g, beta, eye, True, **forward_options)
+        # the first segment starts from the caller's state; its final state is the next rank's incoming state
+        out, final = forward_fn(q, k, v, g, beta, initial_state, True, **forward_options)
+        dist.send(final, dst=_neighbour(group, 1), group=group)
+        return out, None
+
+    if staged:
+        if forward_options:
+            raise ValueError("forward options apply to the generic form (forward_fn) only")
+        if segment_fn is None:
+            from .sm100 import load_sm100
+            segment_fn = load_sm100().prepare_segment
+        segment = segment_fn(q, k, v, g, beta)
         incoming = torch.empty(state_shape, dtype=torch.float32, device=q.device)
-        dist.recv(incoming, src=dist.get_global_rank(group, rank - 1) if group else rank - 1, group=group)
-        if rank < world - 1:
+        source, target = _neighbour(group, rank - 1), (None if last else _neighbour(group, rank + 1))
+        # the whole segment's decay, per batch and value head: one small reduction and one host read
+        if until_decayed and bool((g.float().sum(dim=1).max() < _DECAYED).item()):
+            # M_r is below exp(-40): the outgoing state is b_r whatever comes in, so it leaves at once and all
+            # hand-offs of the job overlap; the incoming state only reaches the leading chunks of the output
+            offset = segment.offset_pipelined()
+            ops = [dist.P2POp(dist.irecv, incoming, source, group)]
+            if not last:
+                ops.append(dist.P2POp(dist.isend, offset, target, group))
+            for work in dist.batch_isend_irecv(ops):
+                work.wait()
+            out = segment.finish_decayed(incoming)
+            return out, (offset if (last and output_final_state) else None)
+        offset = transition = None
+        if not last or until_decayed:
+            offset, transition = segment.offset_and_transition(
+                need_transition=not last or bool(output_final_state))
+        else:
+            segment.prepare()
+        dist.recv(incoming, src=source, group=group)
+        if not last:
             outgoing = apply_transition(transition, offset, incoming)
-            dist.send(outgoing, dst=dist.get_global_rank(group, rank + 1) if group else rank + 1, group=group)
-    # rank 0's final state is the next rank's incoming state; the last rank's is the result
-    want_final = True if rank == 0 else bool(output_final_state and rank == world - 1)
-    out, final = forward_fn(q, k, v, g, beta, incoming, want_final, **forward_options)
-    if rank == 0:
-        dist.send(final, dst=dist.get_global_rank(group, 1) if group else 1, group=group)
-    return out, (final if (output_final_state and rank == world - 1) else None)
+            dist.send(outgoing, dst=target, group=group)
+        if until_decayed:
+            out = segment.finish_decayed(incoming)
+            final = apply_transition(transition, offset, incoming) if (last and output_final_state) else None
+        else:
+            out, final = segment.finish(incoming, bool(last and output_final_state))
+        return out, (final if (last and output_final_state) else None)
+
+    transition = offset = None
+    if not last:
+        # (M_r, b_r): two state-only passes over the local segment
+        _, offset = forward_fn(q, k, v, g, beta, None, True, **forward_options)
+        eye = torch.eye(d, dtype=torch.float32, device=q.device).expand(state_shape).contiguous()
+        _, transition = forward_fn(q, k, torch.zeros_like(v), g, beta, eye, True, **forward_options)
+    incoming = torch.empty(state_shape, dtype=torch.float32, device=q.device)
+    dist.recv(incoming, src=_neighbour(group, rank - 1), group=group)
+    if not last:
+        outgoing = apply_transition(transition, offset, incoming)
+        dist.send(outgoing, dst=_neighbour(group, rank + 1), group=group)
+    out, final = forward_fn(q, k, v, g, beta, incoming, bool(output_final_state and last), **forward_options)
+    return out, (final if (output_final_state and last) else None)

@@ -107,6 +107,10 @@ class Sm100Forward:
                 int(g.dtype == torch.float32), config, stream))
         return out, final
 
+    def prepare_segment(self, q, k, v, g, beta):
+        """Run the prepare stage once and return a handle on which several walks can follow."""
+        return PreparedSegment(self, q, k, v, g, beta)
+
     def varlen(self, q, k, v, g, beta, cu_seqlens, initial_states=None, output_final_state=True):
         """Packed sequences in one prepare and one walk launch (actlize_la_sm100_forward_varlen)."""
         import ctypes
@@ -140,6 +144,93 @@ class Sm100Forward:
                 out.data_ptr(), final.data_ptr() if final is not None else None,
                 workspace.data_ptr(), nbytes, offsets, n, hk, hv, int(g.dtype == torch.float32), stream))
         return out, final
+
+
+class PreparedSegment:
+    """The WY factors of one token segment in a workspace of its own, and the walks over them.
+
+    Used by the sequence-parallel scheme: the factors do not depend on the recurrent state, so the offset pass
+    (zero state), the transition pass (identity state, U treated as zero) and the final pass (true incoming state)
+    share the prepare work.  Built on stage-restricted calls of ``actlize_la_sm100_forward_prepared`` (tcgen05
+    configuration); nothing is launched before the first method call.
+    """
+    _CONFIG, _PREPARE, _WALK, _HOMOGENEOUS, _UNTIL_DECAYED = 1, 0x10, 0x20, 0x40, 0x80
+
+    def __init__(self, owner, q, k, v, g, beta):
+        import torch
+        self.dims = _validate(q, k, v, g, beta, None)
+        self.owner, self.tensors = owner, (q, k, v, g, beta)
+        b, t, hk, hv = self.dims
+        owner.library.configure(q.device)
+        self.pipelined_config = selection_for(q, v).configuration_id       # the policy's segmented form
+        self.nbytes = max(owner.workspace_bytes(b, t, hk, hv, self._CONFIG),
+                          owner.workspace_bytes(b, t, hk, hv, self.pipelined_config))
+        self.workspace = torch.empty(self.nbytes, dtype=torch.uint8, device=q.device)
+        self.output = torch.empty_like(v)
+        self._side = None
+
+    def _launch(self, config, initial, output, final):
+        import torch
+        q, k, v, g, beta = self.tensors
+        b, t, hk, hv = self.dims
+        with torch.cuda.device(q.device):
+            self.owner.library.check(self.owner.library.lib.actlize_la_sm100_forward_prepared(
+                q.data_ptr(), k.data_ptr(), v.data_ptr(), g.data_ptr(), beta.data_ptr(),
+                initial.data_ptr() if initial is not None else None, output.data_ptr(),
+                final.data_ptr() if final is not None else None, self.workspace.data_ptr(), self.nbytes,
+                b, t, hk, hv, int(g.dtype == torch.float32), config, torch.cuda.current_stream().cuda_stream))
+
+    def _state(self):
+        import torch
+        b, _, _, hv = self.dims
+        return torch.empty((b, hv, 128, 128), dtype=torch.float32, device=self.output.device)
+
+    def offset_pipelined(self):
+        """b_r (final state from a zero state) through the complete, segmented forward: prepare of later
+        segments next to the walk of earlier ones.  Leaves the zero-state outputs in ``self.output`` and the
+        factors of the whole segment in the workspace."""
+        offset = self._state()
+        self._launch(self.pipelined_config, None, self.output, offset)
+        return offset
+
+    def offset_and_transition(self, need_transition=True):
+        """(b_r, M_r) of ``S_out = M_r S_in + b_r``; the zero-state outputs stay in ``self.output``.
+        One prepare launch, then the two walks next to each other on two streams (a walk occupies B*Hv SMs)."""
+        import torch
+        self._launch(self._CONFIG | self._PREPARE, None, self.output, None)
+        offset, transition = self._state(), None
+        if need_transition:
+            b, _, _, hv = self.dims
+            current = torch.cuda.current_stream()
+            if self._side is None:
+                self._side = torch.cuda.Stream(device=self.output.device)
+            self._side.wait_stream(current)
+            with torch.cuda.stream(self._side):
+                eye = torch.eye(128, dtype=torch.float32, device=self.output.device).expand(b, hv, 128, 128).contiguous()
+                transition, scratch = self._state(), torch.empty_like(self.output)
+                self._launch(self._CONFIG | self._WALK | self._HOMOGENEOUS, eye, scratch, transition)
+                for x in (eye, transition, scratch):
+                    x.record_stream(self._side)
+        self._launch(self._CONFIG | self._WALK, None, self.output, offset)
+        if need_transition:
+            torch.cuda.current_stream().wait_stream(self._side)
+        return offset, transition
+
+    def prepare(self):
+        """Only the factors (for a rank that has nothing else to do before its incoming state arrives)."""
+        self._launch(self._CONFIG | self._PREPARE, None, self.output, None)
+
+    def finish(self, incoming, output_final_state=True):
+        """The ordinary walk from the true incoming state over prepared factors: (output, final state or None)."""
+        final = self._state() if output_final_state else None
+        self._launch(self._CONFIG | self._WALK, incoming, self.output, final)
+        return self.output, final
+
+    def finish_decayed(self, incoming):
+        """Rewrite only the leading chunks of ``self.output`` (those the incoming state still reaches, decay
+        above exp(-40) per batch and value head); valid after one of the offset passes."""
+        self._launch(self._CONFIG | self._WALK | self._UNTIL_DECAYED, incoming, self.output, None)
+        return self.output
 
 
 _FORWARD = {}

@@ -50,6 +50,19 @@ class Selection:
         return policy()["configuration_ids"][self.configuration] | (self.segments << 8)
 
 
+def default_segments(batch, length, value_heads):
+    """Segment count for a shape without a measured row; integer rule fitted to the measured rows (the walk of a
+    segment occupies B*Hv SMs, the prepare of the next segment runs on the rest): few heads -> isqrt(chunks/8)
+    clamped to 1..8, up to one head per SM -> 2, more -> 1.  The native selector computes the same."""
+    from math import isqrt
+    heads, chunks = batch * value_heads, (length + 63) // 64
+    if heads > 148:
+        return 1
+    if heads > 64:
+        return 2 if chunks >= 16 else 1
+    return max(1, min(8, isqrt(chunks // 8)))
+
+
 def tensor_backend(q):
     """Device tensor -> backend name; only capability (10,0) is admitted, nothing is guessed."""
     device = getattr(q, "device", None)
@@ -81,7 +94,8 @@ def select(shape, profile):
         if tuple(row["shape"]) == tuple(shape[:4]):
             return Selection(row["configuration"], "b200-measured-shape", data["id"],
                              int(row.get("segments", 1)))
-    return Selection(data["default"], "unmeasured-shape-default", data["id"])
+    return Selection(data["default"], "unmeasured-shape-default", data["id"],
+                     default_segments(shape[0], shape[1], shape[3]))
 
 
 def selection_for(q, v, *, mode="device", sm_count=None):

@@ -199,6 +199,74 @@ def aux_bench(args):
                                         traffic=None, peak_source=source, algorithmic_bytes=nbytes))), flush=True)
 
 
+def sequence_parallel_bench(args, workload):
+    """Strong scaling of ONE long sequence over the ranks (sequence-parallel scheme): every rank owns a contiguous
+    token segment; the state travels rank to rank as `M S + b` over NCCL send/recv.  N = 1 is the plain forward."""
+    import torch
+    import torch.distributed as dist
+    from actlizela_b200 import gdn_forward
+    from actlizela_b200.sequence_parallel import gdn_forward_sequence_parallel, segment_bounds
+    from actlizela_b200.workloads import algorithmic_bytes, make_inputs
+    rank, world, local = (int(os.environ.get(k, d)) for k, d in (("RANK", "0"), ("WORLD_SIZE", "1"), ("LOCAL_RANK", "0")))
+    if world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}; launch with torch.distributed.run")
+    torch.cuda.set_device(local)
+    device = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+    t0, t1 = segment_bounds(workload.length, world)[rank]
+    # the rank's own segment, drawn from the workload's distributions with a per-rank seed (synthetic data: only
+    # the first rank gets the workload's initial state)
+    part = workload.sliced(length=t1 - t0, seed=workload.seed + 7919 * rank,
+                           initial=workload.initial if rank == 0 else None)
+    q, k, v, g, beta, initial = [x.to(device) if x is not None else None for x in make_inputs(part)]
+
+    def step():
+        if world == 1:
+            return gdn_forward(q, k, v, g, beta, initial, True)
+        return gdn_forward_sequence_parallel(q, k, v, g, beta, initial, True, until_decayed=args.until_decayed)
+
+    def sync_all():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+            torch.cuda.synchronize()
+
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    for _ in range(max(3, args.warmup)):
+        step()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    sync_all()
+    start.record()
+    for _ in range(args.steps):
+        step()
+    stop.record()
+    sync_all()
+    elapsed = torch.tensor([start.elapsed_time(stop)], device=device)
+    if world > 1:
+        dist.all_reduce(elapsed, op=dist.ReduceOp.MAX)
+    ms = elapsed.item() / args.steps
+    clocks = sampler.stop() if rank == 0 else None
+    if rank == 0:
+        peak, _, source = measured_peaks()
+        nbytes = algorithmic_bytes(workload)
+        achieved = nbytes / (ms * 1e-3) / 1e9
+        print(json.dumps(dict(
+            metric=METRIC, value=workload.tokens / (ms * 1e-3), unit=UNIT, n_gpus=world, steps=args.steps,
+            warmup=max(3, args.warmup), ms_per_step=ms, higher_is_better=True, scaling="strong", vs_baseline=None,
+            dtype="bf16 operands (state path as bf16 hi+lo pairs), f32 accumulate and state", data="synthetic",
+            config=dict(workload=f"{workload.name} B{workload.batch} T{workload.length} Hk{workload.key_heads} "
+                                 f"Hv{workload.value_heads}", parallelism=f"sp{world}",
+                        until_decayed=bool(args.until_decayed), l2="inputs exceed the 126 MB L2"),
+            roofline=dict(bound="hbm", achieved=achieved, peak=peak * world, unit="GB/s", frac=achieved / (peak * world),
+                          traffic=None, peak_source=source, algorithmic_bytes=nbytes),
+            e2e=None, clocks=clocks, gpu_launches=None)), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser(description=__doc__)
     ap.add_argument("--gpus", type=int, default=1)
@@ -210,9 +278,17 @@ def main():
     ap.add_argument("--skip-cpu-baseline", action="store_true")
     ap.add_argument("--op", default="forward", choices=("forward", "decode", "prepare_inputs", "rmsnorm_gated", "varlen"),
                     help="forward is the headline metric; the others time a neighbouring memory-bound kernel")
+    ap.add_argument("--parallelism", default="shard", choices=("shard", "sp"),
+                    help="shard: every rank one per-GPU workload (weak scaling, the headline form); sp: one sequence "
+                         "split over the ranks (strong scaling, e.g. --workload cfg4)")
+    ap.add_argument("--until-decayed", action="store_true",
+                    help="sp only: final pass over the leading chunks the incoming state still reaches")
     args = ap.parse_args()
     if args.op != "forward":
         return aux_bench(args)
+    if args.parallelism == "sp":
+        from actlizela_b200.workloads import WORKLOADS
+        return sequence_parallel_bench(args, WORKLOADS[args.workload])
 
     from actlizela_b200.workloads import WORKLOADS, algorithmic_bytes, algorithmic_flops, make_inputs
     workload = WORKLOADS[args.workload]

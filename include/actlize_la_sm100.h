@@ -38,6 +38,15 @@ extern "C" {
  * (per-kernel timing; the walk-only form needs a workspace filled by an earlier call). */
 #define ACTLIZE_LA_SM100_STAGE_PREPARE_ONLY 0x10
 #define ACTLIZE_LA_SM100_STAGE_WALK_ONLY 0x20
+/* id 4: chained tensor-core pair (the prepare stage also emits G = W K_prev^T; experimental, not in the table).
+ * Two modifiers of a walk-only call of configuration 1, used by the sequence-parallel scheme (several walks over
+ * one prepared workspace): WALK_HOMOGENEOUS treats U as zero, which with the identity as initial state yields the
+ * state-transition matrix of the segment; WALK_UNTIL_DECAYED stops every (batch, value head) walk at the first chunk
+ * boundary where the decay accumulated since the segment start is below exp(-40), leaving later output rows
+ * untouched (final_state must be NULL). */
+#define ACTLIZE_LA_SM100_CONFIG_CHAIN 4
+#define ACTLIZE_LA_SM100_WALK_HOMOGENEOUS 0x40
+#define ACTLIZE_LA_SM100_WALK_UNTIL_DECAYED 0x80
 
 /* ABI version of this library; the loader refuses a mismatch.
  * Counterpart: ala_abi_version in csrc/serving/abi.h:67-82. */

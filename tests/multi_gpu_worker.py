@@ -45,6 +45,20 @@ def main():
         pieces = gdn_forward_sharded(*dev, True, rank=rank, world_size=world)
         ok = ok and all(torch.equal(o, full_out[b0:b1, :, v0:v1]) and torch.equal(s, full_state[b0:b1, v0:v1])
                         for (b0, b1, v0, v1), o, s in pieces)
+        # decayed form: with the benchmark gate the incoming state is gone after a few chunks of a segment, so the
+        # ranks behind the first rewrite only those and keep the zero-state rows elsewhere
+        w2 = WORKLOADS["cfg0"].sliced(batch=1, length=64 * 48 + 10, key_heads=2, value_heads=4, initial=0.1)
+        dev2 = [x.cuda() if x is not None else None for x in make_inputs(w2)]
+        full_out2, full_state2 = gdn_forward(*dev2, output_final_state=True)
+        s0, s1 = segment_bounds(w2.length, world)[rank]
+        part2 = [x[:, s0:s1].contiguous() for x in dev2[:5]]
+        out2, final2 = gdn_forward_sequence_parallel(*part2, dev2[5] if rank == 0 else None, True, until_decayed=True)
+        torch.cuda.synchronize()
+        want2 = full_out2[:, s0:s1].float()
+        ok = ok and ((out2.float() - want2).norm() / want2.norm()).item() < 1e-3
+        ok = ok and (out2.float() - want2).abs().max().item() < 2e-2
+        if rank == world - 1:
+            ok = ok and ((final2 - full_state2).norm() / full_state2.norm()).item() < 1e-4
         print(f"{'OK' if ok else 'FAIL'} rank {rank} of {world}: tokens [{t0},{t1}), "
               f"slabs {[p[0] for p in pieces]}", flush=True)
         dist.barrier()

@@ -176,7 +176,14 @@ def test_native_select_agrees_with_python_policy(native_library):
         assert lib.actlize_la_sm100_select(*row["shape"], 1) == want
         profile_choice = sm100_policy.select((*row["shape"], 128, 128), B200)
         assert profile_choice.configuration_id == want
-    assert lib.actlize_la_sm100_select(3, 100, 2, 4, 0) == ids[sm100_policy.policy()["default"]]
+    # shapes without a measured row: the default configuration with the rule's segment count, same on both sides
+    for shape in [(3, 100, 2, 4), (1, 65536, 16, 32), (1, 16384, 16, 32), (2, 4096, 8, 48), (16, 8192, 16, 32),
+                  (1, 511, 1, 1), (1, 513, 1, 64), (3, 1025, 16, 48), (1, 1 << 20, 1, 2)]:
+        want = sm100_policy.select((*shape, 128, 128), B200)
+        assert want.basis == "unmeasured-shape-default"
+        assert lib.actlize_la_sm100_select(*shape, 0) == want.configuration_id, shape
+    assert sm100_policy.default_segments(1, 65536, 32) == 8 and sm100_policy.default_segments(1, 16384, 32) == 5
+    assert sm100_policy.default_segments(3, 100, 4) == 1 and sm100_policy.default_segments(16, 8192, 32) == 1
     assert lib.actlize_la_sm100_select(1, 64, 3, 4, 0) < 0
     assert lib.actlize_la_sm100_select(0, 64, 1, 1, 0) < 0
 

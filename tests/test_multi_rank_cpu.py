@@ -22,6 +22,49 @@ def _oracle_forward(q, k, v, g, beta, initial_state=None, output_final_state=Tru
     return out.to(torch.float32), (state.to(torch.float32) if output_final_state else None)
 
 
+class _OracleSegment:
+    """CPU stand-in for Sm100Forward.prepare_segment: same methods, the oracle instead of the kernels."""
+
+    def __init__(self, q, k, v, g, beta):
+        self.tensors = (q, k, v, g, beta)
+        self.output = None
+
+    def prepare(self):
+        pass
+
+    def offset_pipelined(self):
+        return self.offset_and_transition(need_transition=False)[0]
+
+    def offset_and_transition(self, need_transition=True):
+        q, k, v, g, beta = self.tensors
+        self.output, offset = _oracle_forward(q, k, v, g, beta, None)
+        transition = None
+        if need_transition:
+            eye = torch.eye(128).expand(q.shape[0], v.shape[2], 128, 128).contiguous()
+            _, transition = _oracle_forward(q, k, torch.zeros_like(v), g, beta, eye)
+        return offset, transition
+
+    def finish(self, incoming, output_final_state=True):
+        return _oracle_forward(*self.tensors, incoming, output_final_state)
+
+    def finish_decayed(self, incoming):
+        """Rewrite, per (batch, value head), the chunks up to and including the first one at whose end the decay
+        accumulated since the segment start is below exp(-40): the walk kernel's rule."""
+        q, k, v, g, beta = self.tensors
+        full, _ = _oracle_forward(q, k, v, g, beta, incoming)
+        total = g.double().cumsum(1)                                   # [B, T, Hv]
+        chunks = (q.shape[1] + 63) // 64
+        for b in range(q.shape[0]):
+            for h in range(v.shape[2]):
+                stop = chunks
+                for c in range(chunks):
+                    if total[b, min(q.shape[1], (c + 1) * 64) - 1, h] < -40.0:
+                        stop = c + 1
+                        break
+                self.output[b, :stop * 64, h] = full[b, :stop * 64, h]
+        return self.output
+
+
 def test_shard_plan_covers_every_unit_exactly_once():
     for batch, hk, world in [(8, 16, 8), (8, 16, 2), (1, 16, 8), (3, 5, 4), (2, 2, 8), (1, 1, 2)]:
         seen = []
@@ -70,10 +113,23 @@ def _worker(rank, world, port, mode, result_queue):
             assert covered.item() == 2 * 4
             result_queue.put((rank, worst))
         else:
+            if mode.startswith("sp-decayed"):
+                # strong decay: the incoming state is gone within the first chunks of a segment; the weaker variant
+                # does not empty a whole segment, so the transition matrix is still exchanged
+                g = g * (25.0 if mode == "sp-decayed" else 4.0)
+                want_out, want_state = _oracle_forward(q, k, v, g, beta, init)
             t0, t1 = segment_bounds(q.shape[1], world)[rank]
             part = [x[:, t0:t1].contiguous() for x in (q, k, v, g, beta)]
-            out, final = gdn_forward_sequence_parallel(
-                *part, init if rank == 0 else None, True, forward_fn=_oracle_forward)
+            if mode == "sp":
+                out, final = gdn_forward_sequence_parallel(
+                    *part, init if rank == 0 else None, True, forward_fn=_oracle_forward)
+            else:
+                # the staged form: prepared segment walked several times; rank 0 still runs a complete forward
+                import actlizela_b200.gdn_interface as interface
+                interface.gdn_forward = _oracle_forward
+                out, final = gdn_forward_sequence_parallel(
+                    *part, init if rank == 0 else None, True, segment_fn=_OracleSegment,
+                    until_decayed=mode.startswith("sp-decayed"))
             worst = oracle.max_abs(out, want_out[:, t0:t1])
             if rank == world - 1:
                 worst = max(worst, oracle.rel_frobenius(final, want_state))
@@ -84,7 +140,8 @@ def _worker(rank, world, port, mode, result_queue):
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("mode,world", [("shard", 2), ("sp", 2), ("sp", 3)])
+@pytest.mark.parametrize("mode,world", [("shard", 2), ("sp", 2), ("sp", 3), ("sp-staged", 2), ("sp-staged", 3),
+                                        ("sp-decayed", 3), ("sp-decayed-partly", 3)])
 def test_two_rank_paths_match_the_unsplit_run(mode, world):
     ctx = mp.get_context("spawn")
     queue = ctx.Queue()
