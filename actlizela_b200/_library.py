@@ -43,6 +43,8 @@ EXPORTS = {
     "actlize_la_sm100_prepare_inputs": (_I, [_P, _LL] + [_P] * 9 + [_LL, _I, _I, _P]),
     "actlize_la_sm100_decode_step": (_I, [_P] * 7 + [_I] * 4 + [_P]),
     "actlize_la_sm100_rmsnorm_gated": (_I, [_P] * 4 + [_LL, _P]),
+    "actlize_la_sm100_verify_step": (_I, [_P] * 8 + [_I] * 5 + [_P]),
+    "actlize_la_sm100_commit_step": (_I, [_P] * 5 + [_I] * 5 + [_P]),
     "actlize_la_sm100_forward_static_scratch": (_I, [_P] * 8 + [_I] * 6 + [_P]),
     "actlize_la_sm100_varlen_workspace_bytes": (_LL, [_LL, _I, _I, _I]),
     "actlize_la_sm100_forward_varlen": (_I, [_P] * 9 + [_LL, _P] + [_I] * 4 + [_P]),

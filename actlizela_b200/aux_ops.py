@@ -69,6 +69,57 @@ def gdn_decode_step(q, k, v, g, beta, state):
     return out
 
 
+def _check_step_inputs(k, v, g, beta, state, width_axis):
+    import torch
+    b_, w, hk = k.shape[0], k.shape[1], k.shape[2]
+    hv = v.shape[2] if v is not None else g.shape[2]
+    if tuple(state.shape) != (b_, hv, 128, 128) or state.dtype != torch.float32 or not state.is_contiguous():
+        raise ValueError("state must be contiguous FP32 [B,Hv,128,128] in K-by-V order")
+    if g.dtype not in (torch.bfloat16, torch.float32) or tuple(g.shape) != (b_, w, hv) or hv % hk or not g.is_contiguous():
+        raise ValueError("g must be contiguous BF16/FP32 [B,W,Hv] and Hv % Hk == 0")
+    if not 1 <= w <= 64:
+        raise ValueError("the step width must be 1..64 tokens")
+    return b_, w, hk, hv
+
+
+def gdn_verify_step(q, k, v, g, beta, state):
+    """Speculative-decoding verify: q,k [B,W,Hk,128], v [B,W,Hv,128] BF16, g,beta [B,W,Hv]; ``state`` FP32
+    [B,Hv,128,128] is READ ONLY.  Returns (out [B,W,Hv,128] BF16, delta [B,W,Hv,128] FP32); ``gdn_commit_step``
+    applies the accepted prefix (the reference's verify/commit pair, csrc/serving/gdn.cu:152-217,255-300,
+    without its slot pool)."""
+    import torch
+    for name, x in (("q", q), ("k", k), ("v", v), ("beta", beta)):
+        _bf16_cuda(x, name)
+    b_, w, hk, hv = _check_step_inputs(k, v, g, beta, state, 1)
+    lib = load_library()
+    out = torch.empty_like(v)
+    delta = torch.empty(v.shape, dtype=torch.float32, device=v.device)
+    with torch.cuda.device(q.device):
+        lib.check(lib.lib.actlize_la_sm100_verify_step(
+            q.data_ptr(), k.data_ptr(), v.data_ptr(), g.data_ptr(), beta.data_ptr(), state.data_ptr(),
+            out.data_ptr(), delta.data_ptr(), b_, w, hk, hv, int(g.dtype == torch.float32),
+            torch.cuda.current_stream().cuda_stream))
+    return out, delta
+
+
+def gdn_commit_step(k, g, delta, counts, state):
+    """Apply the first ``counts[b]`` (int32 device tensor [B], 0..W) recorded updates of a verify step to ``state``
+    in place: S <- e^{g_t} S + k_t delta_t^T."""
+    import torch
+    _bf16_cuda(k, "k")
+    b_, w, hk, hv = _check_step_inputs(k, None, g, None, state, 1)
+    if tuple(delta.shape) != (b_, w, hv, 128) or delta.dtype != torch.float32 or not delta.is_contiguous():
+        raise ValueError("delta must be contiguous FP32 [B,W,Hv,128]")
+    if counts.dtype != torch.int32 or tuple(counts.shape) != (b_,) or counts.device != state.device:
+        raise ValueError("counts must be an int32 device tensor [B]")
+    lib = load_library()
+    with torch.cuda.device(k.device):
+        lib.check(lib.lib.actlize_la_sm100_commit_step(
+            k.data_ptr(), g.data_ptr(), delta.data_ptr(), counts.data_ptr(), state.data_ptr(), b_, w, hk, hv,
+            int(g.dtype == torch.float32), torch.cuda.current_stream().cuda_stream))
+    return state
+
+
 def rmsnorm_gated(y, z, weight):
     """y, z [..., 128] BF16, weight [128] BF16 -> BF16 tensor shaped like y."""
     import torch

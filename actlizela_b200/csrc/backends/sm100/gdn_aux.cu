@@ -106,6 +106,90 @@ decode_step_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
   if (half == 0) out[(long long)bh * kDim + col] = __float2bfloat16_rn((partial[0][col] + partial[1][col]) * kScale);
 }
 
+// Verify step (speculative decoding): `width` draft tokens per request run through the same recurrence with the
+// state held in registers and NOT written back; besides the outputs it records delta_t = beta_t (v_t - k_t^T S),
+// from which commit_step_kernel later applies the accepted prefix.  Thread layout as in decode_step_kernel; the
+// arithmetic per token is the decode step's, operation for operation.
+__global__ void __launch_bounds__(256)
+verify_step_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k,
+                   const __nv_bfloat16* __restrict__ v, const void* __restrict__ g,
+                   const __nv_bfloat16* __restrict__ beta, const float* __restrict__ state,
+                   __nv_bfloat16* __restrict__ out, float* __restrict__ delta_out, int width, int hk, int hv,
+                   int gate_fp32) {
+  __shared__ float sk[2][kDim], sq[2][kDim], partial[2][kDim];
+  const int bh = blockIdx.x, col = threadIdx.x & (kDim - 1), half = threadIdx.x >> 7;
+  const int bidx = bh / hv, vh = bh % hv, kh = vh / (hv / hk);
+  const float* column = state + ((long long)bh * kDim + half * 64) * kDim + col;
+  float s[64];
+#pragma unroll
+  for (int r = 0; r < 64; ++r) s[r] = column[r * kDim];
+  for (int t = 0; t < width; ++t) {
+    const long long token = (long long)bidx * width + t;
+    const long long qk_at = (token * hk + kh) * kDim, head = token * hv + vh;
+    float* skt = sk[t & 1];
+    float* sqt = sq[t & 1];
+    if (half == 0) skt[col] = __bfloat162float(k[qk_at + col]);
+    else sqt[col] = __bfloat162float(q[qk_at + col]);
+    const float decay = expf(load_gate(g, head, gate_fp32));
+    const float bt = __bfloat162float(beta[head]);
+    const float value = __bfloat162float(v[head * kDim + col]);
+#pragma unroll
+    for (int r = 0; r < 64; ++r) s[r] *= decay;
+    __syncthreads();
+    const float* kk = skt + half * 64;
+    const float* qq = sqt + half * 64;
+    float kv = 0.f;
+#pragma unroll
+    for (int r = 0; r < 64; ++r) kv = fmaf(kk[r], s[r], kv);
+    partial[half][col] = kv;
+    __syncthreads();
+    const float delta = bt * (value - (partial[0][col] + partial[1][col]));
+    float o = 0.f;
+#pragma unroll
+    for (int r = 0; r < 64; ++r) {
+      s[r] = fmaf(kk[r], delta, s[r]);
+      o = fmaf(qq[r], s[r], o);
+    }
+    __syncthreads();
+    partial[half][col] = o;
+    __syncthreads();
+    if (half == 0) {
+      out[head * kDim + col] = __float2bfloat16_rn((partial[0][col] + partial[1][col]) * kScale);
+      delta_out[head * kDim + col] = delta;
+    }
+    __syncthreads();      // `partial` is rewritten by the next token
+  }
+}
+
+// Commit: apply the first counts[b] recorded updates, S <- e^{g_t} S + k_t delta_t^T, to the state in place.
+__global__ void __launch_bounds__(256)
+commit_step_kernel(const __nv_bfloat16* __restrict__ k, const void* __restrict__ g,
+                   const float* __restrict__ delta, const int* __restrict__ counts, float* __restrict__ state,
+                   int width, int hk, int hv, int gate_fp32) {
+  __shared__ float sk[2][kDim];
+  const int bh = blockIdx.x, col = threadIdx.x & (kDim - 1), half = threadIdx.x >> 7;
+  const int bidx = bh / hv, vh = bh % hv, kh = vh / (hv / hk);
+  const int count = min(max(counts[bidx], 0), width);
+  if (count == 0) return;
+  float* column = state + ((long long)bh * kDim + half * 64) * kDim + col;
+  float s[64];
+#pragma unroll
+  for (int r = 0; r < 64; ++r) s[r] = column[r * kDim];
+  for (int t = 0; t < count; ++t) {
+    const long long token = (long long)bidx * width + t;
+    const long long head = token * hv + vh;
+    if (half == 0) sk[t & 1][col] = __bfloat162float(k[(token * hk + kh) * kDim + col]);
+    const float decay = expf(load_gate(g, head, gate_fp32));
+    const float d = delta[head * kDim + col];
+    __syncthreads();
+    const float* kk = sk[t & 1] + half * 64;
+#pragma unroll
+    for (int r = 0; r < 64; ++r) s[r] = fmaf(kk[r], d, s[r] * decay);
+  }
+#pragma unroll
+  for (int r = 0; r < 64; ++r) column[r * kDim] = s[r];
+}
+
 // 16 lanes per 128-wide row (16 bytes per lane and tensor), 16 rows per 256-thread CTA.
 __global__ void __launch_bounds__(256)
 rmsnorm_gated_kernel(const __nv_bfloat16* __restrict__ y, const __nv_bfloat16* __restrict__ z,
@@ -169,6 +253,30 @@ extern "C" int actlize_la_sm100_decode_step(
   decode_step_kernel<<<batch * hv, 256, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const __nv_bfloat16*>(q), static_cast<const __nv_bfloat16*>(k), static_cast<const __nv_bfloat16*>(v),
       g, static_cast<const __nv_bfloat16*>(beta), state, static_cast<__nv_bfloat16*>(output), hk, hv, gate_fp32 ? 1 : 0);
+  return int(cudaGetLastError());
+}
+
+extern "C" int actlize_la_sm100_verify_step(
+    const void* q, const void* k, const void* v, const void* g, const void* beta, const float* state, void* output,
+    float* delta, int batch, int width, int hk, int hv, int gate_fp32, void* stream) {
+  if (!q || !k || !v || !g || !beta || !state || !output || !delta) return int(cudaErrorInvalidValue);
+  if (batch <= 0 || width <= 0 || width > 64 || hk <= 0 || hv <= 0 || hv % hk || (long long)batch * hv > INT_MAX)
+    return int(cudaErrorInvalidValue);
+  verify_step_kernel<<<batch * hv, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(q), static_cast<const __nv_bfloat16*>(k), static_cast<const __nv_bfloat16*>(v),
+      g, static_cast<const __nv_bfloat16*>(beta), state, static_cast<__nv_bfloat16*>(output), delta, width, hk, hv,
+      gate_fp32 ? 1 : 0);
+  return int(cudaGetLastError());
+}
+
+extern "C" int actlize_la_sm100_commit_step(const void* k, const void* g, const float* delta, const int* counts,
+                                            float* state, int batch, int width, int hk, int hv, int gate_fp32,
+                                            void* stream) {
+  if (!k || !g || !delta || !counts || !state) return int(cudaErrorInvalidValue);
+  if (batch <= 0 || width <= 0 || width > 64 || hk <= 0 || hv <= 0 || hv % hk || (long long)batch * hv > INT_MAX)
+    return int(cudaErrorInvalidValue);
+  commit_step_kernel<<<batch * hv, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(k), g, delta, counts, state, width, hk, hv, gate_fp32 ? 1 : 0);
   return int(cudaGetLastError());
 }
 

@@ -140,6 +140,18 @@ int actlize_la_sm100_decode_step(
     const void* q, const void* k, const void* v, const void* g, const void* beta, float* state, void* output,
     int batch, int key_heads, int value_heads, int gate_fp32, void* stream);
 
+/* Speculative-decoding pair on the same K-by-V state (the reference's verify / commit, csrc/serving/gdn.cu:152-217 and
+ * 255-300, without its slot pool and transaction records): verify_step runs `width` (1..64) draft tokens per
+ * request through the recurrence, q,k [B,W,Hk,128], v [B,W,Hv,128], g,beta [B,W,Hv], reads `state` without
+ * writing it, and returns the outputs [B,W,Hv,128] BF16 and delta_t = beta_t (v_t - k_t^T S) as FP32 [B,W,Hv,128];
+ * commit_step then applies the first counts[b] (int32 on the device, clamped to 0..width) recorded updates
+ * S <- e^{g_t} S + k_t delta_t^T in place.  verify + commit of all W tokens equals W decode steps bit for bit. */
+int actlize_la_sm100_verify_step(
+    const void* q, const void* k, const void* v, const void* g, const void* beta, const float* state, void* output,
+    float* delta, int batch, int width, int hk, int hv, int gate_fp32, void* stream);
+int actlize_la_sm100_commit_step(const void* k, const void* g, const float* delta, const int* counts, float* state,
+                                 int batch, int width, int hk, int hv, int gate_fp32, void* stream);
+
 /* Step after: out = y * rsqrt(mean(y^2) + 1e-6) * weight * silu(z) per 128-wide row, BF16.
  * Replaces rmsnorm_gated (csrc/output_gate/output_gate.cu:4-5,73-92). */
 int actlize_la_sm100_rmsnorm_gated(const void* y, const void* z, const void* weight, void* out,

@@ -144,3 +144,43 @@ def test_native_varlen_rejects_bad_offsets(native_library):
                                              torch.cuda.current_stream().cuda_stream)
     assert rc != 0
     assert lib.actlize_la_sm100_varlen_workspace_bytes(0, 1, 1, 2) < 0
+
+
+def test_verify_and_commit_steps():
+    """Verify runs W draft tokens without touching the state; committing all of them equals W decode steps bit for
+    bit, committing a prefix equals the oracle recurrence over that prefix."""
+    from actlizela_b200 import gdn_commit_step, gdn_decode_step, gdn_verify_step
+    gen = torch.Generator().manual_seed(11)
+    b, w, hk, hv = 3, 5, 2, 6
+    q = torch.nn.functional.normalize(torch.randn(b, w, hk, 128, generator=gen), dim=-1).to(torch.bfloat16)
+    k = torch.nn.functional.normalize(torch.randn(b, w, hk, 128, generator=gen), dim=-1).to(torch.bfloat16)
+    v = torch.randn(b, w, hv, 128, generator=gen).to(torch.bfloat16)
+    g = -torch.rand(b, w, hv, generator=gen)
+    beta = torch.rand(b, w, hv, generator=gen).to(torch.bfloat16)
+    state0 = 0.1 * torch.randn(b, hv, 128, 128, generator=gen)
+    dev = [x.cuda() for x in (q, k, v, g, beta)]
+    state = state0.cuda()
+    out, delta = gdn_verify_step(*dev, state)
+    assert torch.equal(state.cpu(), state0)                                   # read only
+    want_out, _ = oracle.recurrent_forward(q, k, v, g, beta, state0)
+    assert oracle.max_abs(out.float().cpu(), want_out.float()) < 2e-2
+    # W decode steps on a copy
+    stepped = state0.cuda()
+    for t in range(w):
+        o = gdn_decode_step(dev[0][:, t].contiguous(), dev[1][:, t].contiguous(), dev[2][:, t].contiguous(),
+                            dev[3][:, t].contiguous(), dev[4][:, t].contiguous(), stepped)
+        assert torch.equal(o, out[:, t])
+    full = gdn_commit_step(dev[1], dev[3], delta, torch.full((b,), w, dtype=torch.int32, device="cuda"), state0.cuda())
+    assert torch.equal(full, stepped)
+    # accepted prefixes of different lengths, including none
+    counts = torch.tensor([0, 2, 5], dtype=torch.int32)
+    partial = gdn_commit_step(dev[1], dev[3], delta, counts.cuda(), state0.cuda()).cpu()
+    for i, n in enumerate(counts.tolist()):
+        if n == 0:
+            assert torch.equal(partial[i], state0[i])
+            continue
+        _, want = oracle.recurrent_forward(q[i:i + 1, :n], k[i:i + 1, :n], v[i:i + 1, :n], g[i:i + 1, :n],
+                                           beta[i:i + 1, :n], state0[i:i + 1])
+        assert oracle.rel_frobenius(partial[i:i + 1], want) < 1e-5
+    with pytest.raises(ValueError):
+        gdn_commit_step(dev[1], dev[3], delta, counts.cuda().long(), state)
