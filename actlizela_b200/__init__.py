@@ -23,6 +23,7 @@ _MODULES = {
     "gdn_forward_varlen": "varlen",
     "gdn_prepare_inputs": "aux_ops",
     "gdn_decode_step": "aux_ops",
+    "gdn_forward_projections": "aux_ops",
     "gdn_verify_step": "aux_ops",
     "gdn_commit_step": "aux_ops",
     "rmsnorm_gated": "aux_ops",

@@ -46,6 +46,8 @@ EXPORTS = {
     "actlize_la_sm100_verify_step": (_I, [_P] * 8 + [_I] * 5 + [_P]),
     "actlize_la_sm100_commit_step": (_I, [_P] * 5 + [_I] * 5 + [_P]),
     "actlize_la_sm100_forward_static_scratch": (_I, [_P] * 8 + [_I] * 6 + [_P]),
+    "actlize_la_sm100_projections_workspace_bytes": (_LL, [_I] * 5),
+    "actlize_la_sm100_forward_projections": (_I, [_P, _LL] + [_P] * 8 + [_LL] + [_I] * 5 + [_P]),
     "actlize_la_sm100_varlen_workspace_bytes": (_LL, [_LL, _I, _I, _I]),
     "actlize_la_sm100_forward_varlen": (_I, [_P] * 9 + [_LL, _P] + [_I] * 4 + [_P]),
 }

@@ -69,6 +69,51 @@ def gdn_decode_step(q, k, v, g, beta, state):
     return out
 
 
+def gdn_forward_projections(mixed, a, b, a_log, dt_bias, key_heads, value_heads, initial_state=None,
+                            output_final_state=True):
+    """The forward straight from the layer's projection outputs: ``mixed`` BF16 [B,T,(2Hk+Hv)*128] laid out
+    [q heads | k heads | v heads], ``a``, ``b`` BF16 [B,T,Hv], ``a_log``, ``dt_bias`` FP32 [Hv].  Normalisation
+    and gate activation happen inside the prepare kernel; the result equals ``gdn_prepare_inputs`` followed by
+    ``gdn_forward`` bit for bit.  Returns (out [B,T,Hv,128] BF16, final state or None)."""
+    import torch
+    from .sm100 import load_sm100
+    from .sm100_policy import select
+    from .device import device_profile
+    hk, hv = key_heads, value_heads
+    if mixed.ndim != 3 or mixed.shape[2] != (2 * hk + hv) * 128 or hv % hk:
+        raise ValueError("mixed must be [B,T,(2Hk+Hv)*128] with Hv % Hk == 0")
+    _bf16_cuda(mixed, "mixed")
+    _bf16_cuda(a, "a")
+    _bf16_cuda(b, "b")
+    bsz, t = mixed.shape[0], mixed.shape[1]
+    if tuple(a.shape) != (bsz, t, hv) or tuple(b.shape) != (bsz, t, hv):
+        raise ValueError("a and b must be [B,T,Hv]")
+    for name, x in (("a_log", a_log), ("dt_bias", dt_bias)):
+        if x.dtype != torch.float32 or x.numel() != hv or x.device != mixed.device or not x.is_contiguous():
+            raise ValueError(f"{name} must be contiguous FP32 [Hv] on the inputs' device")
+    if initial_state is not None and (tuple(initial_state.shape) != (bsz, hv, 128, 128) or
+                                      initial_state.dtype != torch.float32 or not initial_state.is_contiguous()):
+        raise ValueError("initial_state must be contiguous FP32 [B,Hv,128,128]")
+    owner = load_sm100()
+    owner.library.configure(mixed.device)
+    lib = owner.library.lib
+    config = select((bsz, t, hk, hv, 128, 128), device_profile(mixed.device.index)).configuration_id
+    nbytes = lib.actlize_la_sm100_projections_workspace_bytes(bsz, t, hk, hv, config)
+    if nbytes < 0:
+        raise ValueError("geometry exceeds the native grid limits")
+    workspace = owner._workspace(mixed.device, nbytes)
+    out = torch.empty((bsz, t, hv, 128), dtype=torch.bfloat16, device=mixed.device)
+    final = (torch.empty((bsz, hv, 128, 128), dtype=torch.float32, device=mixed.device)
+             if output_final_state else None)
+    with torch.cuda.device(mixed.device):
+        owner.library.check(lib.actlize_la_sm100_forward_projections(
+            mixed.data_ptr(), mixed.shape[2], a.data_ptr(), b.data_ptr(), a_log.data_ptr(), dt_bias.data_ptr(),
+            initial_state.data_ptr() if initial_state is not None else None, out.data_ptr(),
+            final.data_ptr() if final is not None else None, workspace.data_ptr(), nbytes, bsz, t, hk, hv, config,
+            torch.cuda.current_stream().cuda_stream))
+    return out, final
+
+
 def _check_step_inputs(k, v, g, beta, state, width_axis):
     import torch
     b_, w, hk = k.shape[0], k.shape[1], k.shape[2]

@@ -86,6 +86,7 @@ bool is_chain(int config) { return (config & 0xf) == 4; }
 bool prepare_is_umma(int config) { return (config & 0xf) == 1 || (config & 0xf) == 3; }
 bool walk_is_umma(int config) { return (config & 0xf) == 1 || (config & 0xf) == 2; }
 int launch_prepare_tc(int config, const Inputs& in, const Geometry& geo, const Workspace& ws, cudaStream_t stream) {
+  if (in.mixed) return launch_prepare_fused(in, geo, ws, stream);
   return is_chain(config) ? launch_prepare_chain(in, geo, ws, stream) : launch_prepare_umma(in, geo, ws, stream);
 }
 int launch_walk_tc(int config, const Inputs& in, const Geometry& geo, const Workspace& ws, cudaStream_t stream) {
@@ -179,6 +180,10 @@ extern "C" int actlize_la_sm100_device_status(int* status4, int reset) {
   return read_device_status(status4, reset);
 }
 
+namespace {
+int run_forward(const Inputs& in, Geometry geo, const Workspace& ws, int config, int segments, cudaStream_t stream);
+}
+
 extern "C" int actlize_la_sm100_forward_prepared(
     const void* q, const void* k, const void* v, const void* g, const void* beta,
     const float* initial, void* output, float* final_state,
@@ -201,7 +206,11 @@ extern "C" int actlize_la_sm100_forward_prepared(
                   initial, static_cast<__nv_bfloat16*>(output), final_state, gate_fp32 ? 1 : 0,
                   ((config & kHomogeneousBit) ? kWalkHomogeneous : 0) | ((config & kUntilDecayedBit) ? kWalkUntilDecayed : 0)};
   const Workspace ws = carve_workspace(workspace, geo, is_chain(config));
-  cudaStream_t stream = static_cast<cudaStream_t>(opaque_stream);
+  return run_forward(in, geo, ws, config, segments, static_cast<cudaStream_t>(opaque_stream));
+}
+
+namespace {
+int run_forward(const Inputs& in, Geometry geo, const Workspace& ws, int config, int segments, cudaStream_t stream) {
   if (segments > 1) {
     // Prepare kernels of all segments go to the caller's stream back to back; the walks run in order on
     // a high-priority second stream, each after its segment's prepare, so that a later segment is
@@ -224,7 +233,8 @@ extern "C" int actlize_la_sm100_forward_prepared(
     return int(cudaStreamWaitEvent(stream, ss.done, 0));
   }
   if (!(config & kWalkOnly)) {
-    if (int rc = is_chain(config)          ? launch_prepare_chain(in, geo, ws, stream)
+    if (int rc = in.mixed                  ? launch_prepare_fused(in, geo, ws, stream)
+                 : is_chain(config)        ? launch_prepare_chain(in, geo, ws, stream)
                  : prepare_is_umma(config) ? launch_prepare_umma(in, geo, ws, stream)
                                            : launch_prepare_simt(in, geo, ws, stream))
       return rc;
@@ -233,6 +243,48 @@ extern "C" int actlize_la_sm100_forward_prepared(
   return is_chain(config)       ? launch_walk_chain(in, geo, ws, stream)
          : walk_is_umma(config) ? launch_walk_umma(in, geo, ws, stream)
                                 : launch_walk_simt(in, geo, ws, stream);
+}
+}  // namespace
+
+// --------------------------------------------------------------- forward on raw projection outputs
+extern "C" long long actlize_la_sm100_projections_workspace_bytes(int b, int t, int hk, int hv, int config) {
+  if (!geometry_ok(b, t, hk, hv) || !config_ok(config) || (config & 0xf) != 1 || (config & (kStageMask | kWalkFlagMask)))
+    return -1;
+  const Geometry geo{b, t, hk, hv};
+  // the ordinary workspace plus the normalised keys [B][T][Hk][128] BF16
+  return ((workspace_bytes(geo, segments_of(config, geo)) + 255) & ~255LL) + (long long)b * t * hk * kDim * 2;
+}
+
+extern "C" int actlize_la_sm100_forward_projections(
+    const void* mixed, long long mixed_row_stride, const void* a, const void* b_act, const float* a_log,
+    const float* dt_bias, const float* initial, void* output, float* final_state,
+    void* workspace, long long workspace_bytes_given,
+    int b, int t, int hk, int hv, int config, void* opaque_stream) {
+  if (!mixed || !a || !b_act || !a_log || !dt_bias || !output || !workspace) return int(cudaErrorInvalidValue);
+  const long long need = actlize_la_sm100_projections_workspace_bytes(b, t, hk, hv, config);
+  if (need < 0 || workspace_bytes_given < need) return int(cudaErrorInvalidValue);
+  if (mixed_row_stride < (2LL * hk + hv) * kDim || (mixed_row_stride & 7) || (long long)b * t > INT_MAX ||
+      (reinterpret_cast<uintptr_t>(mixed) & 15) || (reinterpret_cast<uintptr_t>(workspace) & 255) ||
+      (reinterpret_cast<uintptr_t>(output) & 15))
+    return int(cudaErrorInvalidValue);
+  Geometry geo{b, t, hk, hv};
+  const int segments = segments_of(config, geo);
+  const Workspace ws = carve_workspace(workspace, geo);
+  Inputs in{};
+  in.k_norm = reinterpret_cast<__nv_bfloat16*>(static_cast<char*>(workspace) +
+                                               ((workspace_bytes(geo, segments) + 255) & ~255LL));
+  in.k = in.k_norm;                 // what the walk reads
+  in.initial = initial;
+  in.output = static_cast<__nv_bfloat16*>(output);
+  in.final_state = final_state;
+  in.gate_fp32 = 1;
+  in.mixed = static_cast<const __nv_bfloat16*>(mixed);
+  in.mixed_stride = mixed_row_stride;
+  in.act_a = static_cast<const __nv_bfloat16*>(a);
+  in.act_b = static_cast<const __nv_bfloat16*>(b_act);
+  in.a_log = a_log;
+  in.dt_bias = dt_bias;
+  return run_forward(in, geo, ws, config, segments, static_cast<cudaStream_t>(opaque_stream));
 }
 
 // ---------------------------------------------------------------------------------- packed sequences

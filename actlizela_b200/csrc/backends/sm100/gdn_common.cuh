@@ -115,6 +115,17 @@ struct Inputs {
   //   kWalkUntilDecayed stop a (batch, value head) walk at the first chunk boundary where the decay accumulated
   //                     since the walk's start is below exp(-40); later outputs are left as they are
   int walk_flags = 0;
+  // Fused input preparation (tcgen05 prepare kernel only): q, k, v are then read from the packed projection
+  // rows `mixed` [B*T][mixed_stride] = [q heads | k heads | v heads] x 128, normalised in shared memory; the gate and
+  // beta come from the raw activations `act_a`, `act_b` [B*T][Hv] with the per-head constants `a_log`, `dt_bias`;
+  // the normalised keys are written to `k_norm` [B][T][Hk][128] for the walk (which gets it as its `k`).
+  const __nv_bfloat16* mixed = nullptr;
+  long long mixed_stride = 0;
+  const __nv_bfloat16* act_a = nullptr;
+  const __nv_bfloat16* act_b = nullptr;
+  const float* a_log = nullptr;
+  const float* dt_bias = nullptr;
+  __nv_bfloat16* k_norm = nullptr;
 };
 constexpr int kWalkHomogeneous = 1, kWalkUntilDecayed = 2;
 constexpr float kDecayedLog2 = -40.f * 1.4426950408889634f;
@@ -155,6 +166,7 @@ int launch_prepare_simt(const Inputs&, const Geometry&, const Workspace&, cudaSt
 int launch_walk_simt(const Inputs&, const Geometry&, const Workspace&, cudaStream_t);
 int configure_simt();
 int launch_prepare_umma(const Inputs&, const Geometry&, const Workspace&, cudaStream_t);
+int launch_prepare_fused(const Inputs&, const Geometry&, const Workspace&, cudaStream_t);   // Inputs::mixed etc. set
 int launch_walk_umma(const Inputs&, const Geometry&, const Workspace&, cudaStream_t);
 int configure_umma();
 // chained configuration: the prepare stage also emits G and the decay-scaled W, and the walk forms

@@ -141,7 +141,10 @@ constexpr int kPrepTmemCols = 256;   // D1 [0,64)  DW [64,128)  DU [128,192)  DG
 #define GDN_PSTAMP(slot)
 #endif
 
-template <bool kChained>
+// Fused variant (kFused): the tiles come from the packed projection rows (tm_q is a 2-D map over them, tm_k the 4-D
+// map of the normalised-key plane that the walk reads); Q and K rows are L2-normalised in shared memory with the
+// arithmetic of the separate input-preparation kernel (16 lanes per row), gate and beta are activated on load.
+template <bool kChained, bool kFused>
 __global__ void __launch_bounds__(kPrepThreads, 2)
 prepare_umma_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                     const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_wh,
@@ -196,12 +199,25 @@ prepare_umma_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
     fence_barrier_init();
     // the input tiles do not depend on tensor memory: start them before the allocation
     mbar_arrive_expect_tx(bar_tma, 6 * kBox);
-    tma_load_4d(sm + L::kQ0, &tm_q, bar_tma, 0, hk, t0, b);
-    tma_load_4d(sm + L::kQ1, &tm_q, bar_tma, 64, hk, t0, b);
-    tma_load_4d(sm + L::kK0, &tm_k, bar_tma, 0, hk, t0, b);
-    tma_load_4d(sm + L::kK1, &tm_k, bar_tma, 64, hk, t0, b);
-    tma_load_4d(sm + L::kV0, &tm_v, bar_tma, 0, hv, t0, b);
-    tma_load_4d(sm + L::kV1, &tm_v, bar_tma, 64, hv, t0, b);
+    if (kFused) {
+      // packed rows [q heads | k heads | v heads]; rows behind the batch element's end belong to the next one
+      // (or read as zero behind the last) and are neutralised by beta = 0 / zero gate weights
+      const int row = b * geo.sequence + t0;
+      const int xq = hk * kDim, xk = (geo.key_heads + hk) * kDim, xv = (2 * geo.key_heads + hv) * kDim;
+      tma_load_2d(sm + L::kQ0, &tm_q, bar_tma, xq, row);
+      tma_load_2d(sm + L::kQ1, &tm_q, bar_tma, xq + 64, row);
+      tma_load_2d(sm + L::kK0, &tm_q, bar_tma, xk, row);
+      tma_load_2d(sm + L::kK1, &tm_q, bar_tma, xk + 64, row);
+      tma_load_2d(sm + L::kV0, &tm_q, bar_tma, xv, row);
+      tma_load_2d(sm + L::kV1, &tm_q, bar_tma, xv + 64, row);
+    } else {
+      tma_load_4d(sm + L::kQ0, &tm_q, bar_tma, 0, hk, t0, b);
+      tma_load_4d(sm + L::kQ1, &tm_q, bar_tma, 64, hk, t0, b);
+      tma_load_4d(sm + L::kK0, &tm_k, bar_tma, 0, hk, t0, b);
+      tma_load_4d(sm + L::kK1, &tm_k, bar_tma, 64, hk, t0, b);
+      tma_load_4d(sm + L::kV0, &tm_v, bar_tma, 0, hv, t0, b);
+      tma_load_4d(sm + L::kV1, &tm_v, bar_tma, 64, hv, t0, b);
+    }
   }
   if (warp == 1) {
     tmem_alloc(tmem_slot, kPrepTmemCols);
@@ -210,8 +226,15 @@ prepare_umma_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
   float gate = 0.f, beta = 0.f;
   if (tid < valid) {
     const long long gi = ((long long)b * geo.sequence + t0 + tid) * geo.value_heads + hv;
-    gate = load_gate(in.g, gi, in.gate_fp32);
-    beta = __bfloat162float(in.beta[gi]);
+    if (kFused) {
+      // g = -exp(A_log) softplus(a + dt_bias) (z > 20 branch), beta = sigmoid(b) rounded to BF16
+      const float z = __bfloat162float(in.act_a[gi]) + in.dt_bias[hv];
+      gate = -expf(in.a_log[hv]) * (z > 20.f ? z : log1pf(expf(z)));
+      beta = __bfloat162float(__float2bfloat16_rn(1.f / (1.f + expf(-__bfloat162float(in.act_b[gi])))));
+    } else {
+      gate = load_gate(in.g, gi, in.gate_fp32);
+      beta = __bfloat162float(in.beta[gi]);
+    }
   }
   if (kChained && warp >= 2 && warp < 4) {
     // total log-decay of the previous chunk (always a full chunk), summed by warps 2 and 3
@@ -243,6 +266,38 @@ prepare_umma_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
   // ---- phase 2: D1 = [Q;K] K^T
   bool ok = mbar_wait(bar_tma, 0, abort, 1, chunk);
   GDN_PSTAMP(1);
+  if (kFused) {
+    // L2-normalise the 64 Q and 64 K rows in place: 16 lanes per row (8 BF16 = one swizzled 16-byte slot each),
+    // 16 rows per pass; x * rsqrt(sum x^2 + 1e-6) rounded to BF16
+    if (ok) {
+      const int lane16 = tid & 15;
+#pragma unroll
+      for (int pass = 0; pass < 8; ++pass) {
+        const int r = pass * 16 + (tid >> 4), row = r & 63;
+        uint8_t* slot = sm + (r < 64 ? (lane16 < 8 ? L::kQ0 : L::kQ1) : (lane16 < 8 ? L::kK0 : L::kK1)) + row * 128 +
+                        (((lane16 & 7) ^ (row & 7)) << 4);
+        const uint4 x = *reinterpret_cast<const uint4*>(slot);
+        const float f[8] = {bf16_lo(x.x), bf16_hi(x.x), bf16_lo(x.y), bf16_hi(x.y),
+                            bf16_lo(x.z), bf16_hi(x.z), bf16_lo(x.w), bf16_hi(x.w)};
+        float square = 0.f;
+#pragma unroll
+        for (int e = 0; e < 8; ++e) square = fmaf(f[e], f[e], square);
+#pragma unroll
+        for (int d = 8; d; d >>= 1) square += __shfl_xor_sync(0xffffffffu, square, d, 16);
+        const float factor = rsqrtf(square + 1e-6f);
+        *reinterpret_cast<uint4*>(slot) = make_uint4(pack_bf16(f[0] * factor, f[1] * factor), pack_bf16(f[2] * factor, f[3] * factor),
+                                                     pack_bf16(f[4] * factor, f[5] * factor), pack_bf16(f[6] * factor, f[7] * factor));
+      }
+      fence_proxy_async_smem();
+    }
+    __syncthreads();
+    // the walk reads the normalised keys: one CTA per key-head group stores the tile (rows behind T are clipped)
+    if (tid == 0 && ok && hv % geo.group() == 0) {
+      tma_store_4d(&tm_k, sm + L::kK0, 0, hk, t0, b);
+      tma_store_4d(&tm_k, sm + L::kK1, 64, hk, t0, b);
+      tma_store_commit();
+    }
+  }
   if (tid == 0 && ok) {
     tc_fence_after();
     const uint32_t base = smem_u32(sm);
@@ -524,6 +579,7 @@ prepare_umma_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
         mma_ss(tmem + 128, a, bb, kIdescN64AT, (part | ks) != 0);
       }
     }
+    if (kFused) tma_store_wait_read();      // the key tile's store has left shared memory before staging reuses it
     mma_commit(bar_mma);
   }
   ok = ok && mbar_wait(bar_mma, 1, abort, 3, chunk);
@@ -1078,10 +1134,12 @@ walk_umma_kernel(const __grid_constant__ CUtensorMap tm_wh, const __grid_constan
 // ======================================================================================= launchers
 int configure_umma() {
   if (int rc = tensor_map_encoder().init()) return rc;
-  cudaError_t e = cudaFuncSetAttribute(prepare_umma_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+  cudaError_t e = cudaFuncSetAttribute(prepare_umma_kernel<false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        kPrepSmem);
   if (e != cudaSuccess) return int(e);
-  e = cudaFuncSetAttribute(prepare_umma_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kPrepSmem);
+  e = cudaFuncSetAttribute(prepare_umma_kernel<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kPrepSmem);
+  if (e != cudaSuccess) return int(e);
+  e = cudaFuncSetAttribute(prepare_umma_kernel<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kPrepSmem);
   if (e != cudaSuccess) return int(e);
   e = cudaFuncSetAttribute(walk_umma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kWalkSmem);
   return int(e);
@@ -1093,17 +1151,28 @@ int launch_prepare_tc(const Inputs& in, const Geometry& geo, const Workspace& ws
   if (int rc = enc.init()) return rc;
   CUtensorMap tm_q, tm_k, tm_v, tm_wh, tm_wl, tm_u;
   const uint64_t rows = uint64_t(geo.blocks()) * kChunk;
-  if (int rc = enc.bf16_4d(&tm_q, in.q, kDim, geo.key_heads, geo.sequence, geo.varlen ? 1 : geo.batch, kChunk)) return rc;
-  if (int rc = enc.bf16_4d(&tm_k, in.k, kDim, geo.key_heads, geo.sequence, geo.varlen ? 1 : geo.batch, kChunk)) return rc;
-  if (int rc = enc.bf16_4d(&tm_v, in.v, kDim, geo.value_heads, geo.sequence, geo.varlen ? 1 : geo.batch, kChunk)) return rc;
+  const bool fused = in.mixed != nullptr;
+  if (fused) {
+    if (chained || geo.varlen) return int(cudaErrorInvalidValue);
+    // one 2-D map over the packed projection rows; the 4-D map of the normalised-key plane is the store target
+    if (int rc = enc.bf16_2d(&tm_q, in.mixed, uint64_t(in.mixed_stride), uint64_t(geo.batch) * geo.sequence, kChunk)) return rc;
+    if (int rc = enc.bf16_4d(&tm_k, in.k_norm, kDim, geo.key_heads, geo.sequence, geo.batch, kChunk)) return rc;
+    tm_v = tm_q;
+  } else {
+    if (int rc = enc.bf16_4d(&tm_q, in.q, kDim, geo.key_heads, geo.sequence, geo.varlen ? 1 : geo.batch, kChunk)) return rc;
+    if (int rc = enc.bf16_4d(&tm_k, in.k, kDim, geo.key_heads, geo.sequence, geo.varlen ? 1 : geo.batch, kChunk)) return rc;
+    if (int rc = enc.bf16_4d(&tm_v, in.v, kDim, geo.value_heads, geo.sequence, geo.varlen ? 1 : geo.batch, kChunk)) return rc;
+  }
   if (int rc = enc.bf16_2d(&tm_wh, ws.w_hi, kDim, rows, kChunk)) return rc;
   if (int rc = enc.bf16_2d(&tm_wl, ws.w_lo, kDim, rows, kChunk)) return rc;
   if (int rc = enc.f32_2d(&tm_u, ws.u, kDim, rows, kChunk)) return rc;
   const unsigned grid = (unsigned)((geo.varlen ? 1LL : (long long)geo.batch) * geo.value_heads * geo.segment_chunks());
-  if (chained)
-    prepare_umma_kernel<true><<<grid, kPrepThreads, kPrepSmem, stream>>>(tm_q, tm_k, tm_v, tm_wh, tm_wl, tm_u, in, geo, ws);
+  if (fused)
+    prepare_umma_kernel<false, true><<<grid, kPrepThreads, kPrepSmem, stream>>>(tm_q, tm_k, tm_v, tm_wh, tm_wl, tm_u, in, geo, ws);
+  else if (chained)
+    prepare_umma_kernel<true, false><<<grid, kPrepThreads, kPrepSmem, stream>>>(tm_q, tm_k, tm_v, tm_wh, tm_wl, tm_u, in, geo, ws);
   else
-    prepare_umma_kernel<false><<<grid, kPrepThreads, kPrepSmem, stream>>>(tm_q, tm_k, tm_v, tm_wh, tm_wl, tm_u, in, geo, ws);
+    prepare_umma_kernel<false, false><<<grid, kPrepThreads, kPrepSmem, stream>>>(tm_q, tm_k, tm_v, tm_wh, tm_wl, tm_u, in, geo, ws);
   return int(cudaGetLastError());
 }
 }  // namespace
@@ -1113,6 +1182,10 @@ int launch_prepare_umma(const Inputs& in, const Geometry& geo, const Workspace& 
 }
 int launch_prepare_chain(const Inputs& in, const Geometry& geo, const Workspace& ws, cudaStream_t stream) {
   return launch_prepare_tc(in, geo, ws, stream, true);
+}
+int launch_prepare_fused(const Inputs& in, const Geometry& geo, const Workspace& ws, cudaStream_t stream) {
+  if (!in.mixed || !in.act_a || !in.act_b || !in.a_log || !in.dt_bias || !in.k_norm) return int(cudaErrorInvalidValue);
+  return launch_prepare_tc(in, geo, ws, stream, false);
 }
 
 int launch_walk_umma(const Inputs& in, const Geometry& geo, const Workspace& ws, cudaStream_t stream) {

@@ -157,6 +157,17 @@ def aux_bench(args):
         call = lambda: gdn_prepare_inputs(mixed, a, a, a_log, bias, hk, hv)
         nbytes, units, unit = 2 * mixed.numel() * 2 + n * hv * (2 + 2 + 4 + 2), n, "tokens/s"
         name = f"prepare_inputs N{n} Hk{hk} Hv{hv}"
+    elif args.op == "projections":
+        # the headline shape from the layer's raw projection outputs: input preparation fused into the prepare kernel
+        from actlizela_b200 import gdn_forward_projections
+        t = 8192
+        mixed = torch.randn(1, t, (2 * hk + hv) * 128, generator=gen).to(torch.bfloat16).cuda()
+        a = torch.randn(1, t, hv, generator=gen).to(torch.bfloat16).cuda()
+        a_log, bias = torch.zeros(hv, device="cuda"), torch.zeros(hv, device="cuda")
+        call = lambda: gdn_forward_projections(mixed, a, a, a_log, bias, hk, hv, None, True)
+        nbytes = mixed.numel() * 2 + 2 * a.numel() * 2 + t * hv * 256 + hv * 65536
+        units, unit = t, "tokens/s"
+        name = f"forward on projections B1 T{t} Hk{hk} Hv{hv}"
     elif args.op == "varlen":
         # 64 packed prefill requests with seeded ragged lengths (mean 256 tokens); per token and value head the same
         # algorithmic bytes as the fixed-shape forward
@@ -194,7 +205,7 @@ def aux_bench(args):
     print(json.dumps(dict(metric=f"{args.op} {unit}", value=units / (ms * 1e-3), unit=unit, n_gpus=1, steps=args.steps,
                           warmup=max(3, args.warmup), ms_per_step=ms, higher_is_better=True, data="synthetic",
                           config=dict(workload=name, l2="working set exceeds the 126 MB L2"),
-                          gpu_launches=args.steps * (2 if args.op == "varlen" else 1),
+                          gpu_launches=args.steps * (2 if args.op == "varlen" else 8 if args.op == "projections" else 1),
                           roofline=dict(bound="hbm", achieved=achieved, peak=peak, unit="GB/s", frac=achieved / peak,
                                         traffic=None, peak_source=source, algorithmic_bytes=nbytes))), flush=True)
 
@@ -276,7 +287,7 @@ def main():
     ap.add_argument("--configuration", default=None, help="diagnostic override of the policy table")
     ap.add_argument("--impl", default="native", choices=("native", "reference"))
     ap.add_argument("--skip-cpu-baseline", action="store_true")
-    ap.add_argument("--op", default="forward", choices=("forward", "decode", "prepare_inputs", "rmsnorm_gated", "varlen"),
+    ap.add_argument("--op", default="forward", choices=("forward", "decode", "prepare_inputs", "rmsnorm_gated", "varlen", "projections"),
                     help="forward is the headline metric; the others time a neighbouring memory-bound kernel")
     ap.add_argument("--parallelism", default="shard", choices=("shard", "sp"),
                     help="shard: every rank one per-GPU workload (weak scaling, the headline form); sp: one sequence "

@@ -170,6 +170,22 @@ int actlize_la_sm100_device_status(int* status4, int reset);
  * context stays usable.  No counterpart in the reference, whose kernels wait without a limit. */
 int actlize_la_sm100_selftest_wait_timeout(int tag, void* stream);
 
+/* The forward on the raw projection outputs of the layer: the step before the path (Q/K L2-normalisation, gate
+ * activation g = -exp(A_log) softplus(a + dt_bias), beta = sigmoid(b); csrc/serving/prefill.cu:45-70,
+ * csrc/serving/runtime.cuh:48-52) is done inside the tcgen05 prepare kernel instead of by a kernel of its own
+ * (actlize_la_sm100_prepare_inputs): `mixed` is BF16 [B*T][mixed_row_stride] with the row layout
+ * [Hk q vectors | Hk k vectors | Hv v vectors] x 128, `a` and `b` are BF16 [B*T][Hv], `a_log`, `dt_bias` FP32 [Hv].
+ * Same results, bit for bit, as prepare_inputs followed by forward_prepared with an FP32 gate.  `config` as returned
+ * by actlize_la_sm100_select (tcgen05 configuration, segments allowed, no stage bits); the workspace
+ * (actlize_la_sm100_projections_workspace_bytes) also holds the normalised keys for the walk.  Rows behind a batch
+ * element's end inside its last chunk are the next element's tokens and meet exact zeros: inputs must be finite. */
+long long actlize_la_sm100_projections_workspace_bytes(int b, int t, int hk, int hv, int config);
+int actlize_la_sm100_forward_projections(
+    const void* mixed, long long mixed_row_stride, const void* a, const void* b_act, const float* a_log,
+    const float* dt_bias, const float* initial, void* output, float* final_state,
+    void* workspace, long long workspace_bytes,
+    int b, int t, int hk, int hv, int config, void* stream);
+
 /* Packed variable-length sequences: q,k [1,total,Hk,128], v [1,total,Hv,128], g/beta [1,total,Hv] hold n_seqs
  * sequences back to back; cu_seqlens_host[0..n_seqs] (HOST integers, 0 = first, total = last, non-decreasing)
  * marks the boundaries; initial_states / final_states are FP32 [n_seqs,Hv,128,128] (nullable).  Every sequence

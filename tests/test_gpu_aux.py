@@ -184,3 +184,30 @@ def test_verify_and_commit_steps():
         assert oracle.rel_frobenius(partial[i:i + 1], want) < 1e-5
     with pytest.raises(ValueError):
         gdn_commit_step(dev[1], dev[3], delta, counts.cuda().long(), state)
+
+
+@pytest.mark.parametrize("shape", [(1, 300, 2, 4), (3, 200, 2, 6), (2, 64, 1, 1), (1, 2048, 16, 32)])
+def test_forward_on_projections_equals_prepare_then_forward(shape):
+    """Normalisation and gate activation inside the prepare kernel give the bits of the separate input-preparation
+    kernel followed by the forward (batch tails read the next element's rows, which only meet exact zeros)."""
+    from actlizela_b200 import gdn_forward, gdn_forward_projections, gdn_prepare_inputs
+    bsz, t, hk, hv = shape
+    gen = torch.Generator().manual_seed(21 + t)
+    mixed = torch.randn(bsz, t, (2 * hk + hv) * 128, generator=gen).to(torch.bfloat16).cuda()
+    a = torch.randn(bsz, t, hv, generator=gen).to(torch.bfloat16).cuda()
+    b = torch.randn(bsz, t, hv, generator=gen).to(torch.bfloat16).cuda()
+    a_log = (0.5 * torch.randn(hv, generator=gen)).cuda()
+    dt_bias = (0.5 * torch.randn(hv, generator=gen)).cuda()
+    init = (0.1 * torch.randn(bsz, hv, 128, 128, generator=gen)).cuda()
+    q, k, v, g, beta = gdn_prepare_inputs(mixed.view(bsz * t, -1), a.view(bsz * t, hv), b.view(bsz * t, hv), a_log,
+                                          dt_bias, hk, hv)
+    view = lambda x, h: x.view(bsz, t, h, 128)
+    for initial in (init, None):
+        want_out, want_state = gdn_forward(view(q, hk), view(k, hk), view(v, hv), g.view(bsz, t, hv),
+                                           beta.view(bsz, t, hv), initial, True)
+        out, state = gdn_forward_projections(mixed, a, b, a_log, dt_bias, hk, hv, initial, True)
+        torch.cuda.synchronize()
+        assert torch.equal(out, want_out)
+        assert torch.equal(state, want_state)
+    out_only, none = gdn_forward_projections(mixed, a, b, a_log, dt_bias, hk, hv, None, False)
+    assert none is None and torch.equal(out_only, out)
