@@ -894,8 +894,9 @@ walk_umma_kernel(const __grid_constant__ CUtensorMap tm_wh, const __grid_constan
         tmem_st32(taddr + kAccS + k0, d);
         tmem_wait_st();
         tc_fence_before();
-        // the wide product also overwrites O^T and reads the ring stage: this warp vouches for both before
-        // its first arrival, so the issuer has a single wait in front of the product
+        // the products overwrite O^T and read the ring stage: this warp vouches for both before its first
+        // arrival, so the issuer has a single wait in front of them (waiting for the drained output on the
+        // issuer itself would hold up the state update behind it)
         if (part == 0 && c > 0) ok = mbar_wait(bar_ofree, (c - 1) & 1, abort, 14, c);
         __syncwarp();
         if (lane == 0) mbar_arrive(bar_ops + part);
@@ -1064,15 +1065,17 @@ walk_umma_kernel(const __grid_constant__ CUtensorMap tm_wh, const __grid_constan
       for (int c = 0; c < chunks && ok; ++c) {
         const uint64_t stage = uint64_t((c & 1) * (L::kStage >> 4));
         const uint64_t b0 = dB0 + stage, b1 = dB1 + stage, kd = dK + stage, pd = dP + stage;
-        // St [W_hi ; W_lo ; Qs]^T with St ~ SH + SL: the SH pass covers all 192 columns, the SL pass the
-        // 128 W columns.  K steps {0,1,4,5} become available first, {2,3,6,7} second.
+        // St [W_hi ; W_lo]^T with St ~ SH + SL (the SL pass only against W_hi, into its own accumulator).  K steps
+        // {0,1,4,5} of the split become available first, {2,3,6,7} second.  The chain waits for this product only;
+        // the state part of the output, St Qs^T, reads the same operands and is issued behind the commit, so that
+        // it runs while the chain warps form N.
         ok = mbar_wait(bar_ops, c & 1, abort, 41, c);
         tc_fence_after();
 #pragma unroll
         for (int q = 0; q < 4; ++q) {
           const int ks = (q >> 1) * 4 + (q & 1);
           const uint64_t bdesc = ((ks >> 2) ? b1 : b0) + uint64_t((ks & 3) * 2);     // +32 bytes per K step
-          mma_ts(tm + kAccX, tm + kOpSH + ks * 8, bdesc, kIdescN192, q != 0);
+          mma_ts(tm + kAccX, tm + kOpSH + ks * 8, bdesc, kIdescN128, q != 0);
           mma_ts(tm + kAccY, tm + kOpSL + ks * 8, bdesc, kIdescN64, q != 0);
         }
         ok &= mbar_wait(bar_ops + 1, c & 1, abort, 41, c);
@@ -1081,13 +1084,15 @@ walk_umma_kernel(const __grid_constant__ CUtensorMap tm_wh, const __grid_constan
         for (int q = 0; q < 4; ++q) {
           const int ks = (q >> 1) * 4 + 2 + (q & 1);
           const uint64_t bdesc = ((ks >> 2) ? b1 : b0) + uint64_t((ks & 3) * 2);
-          mma_ts(tm + kAccX, tm + kOpSH + ks * 8, bdesc, kIdescN192, 1);
+          mma_ts(tm + kAccX, tm + kOpSH + ks * 8, bdesc, kIdescN128, 1);
           mma_ts(tm + kAccY, tm + kOpSL + ks * 8, bdesc, kIdescN64, 1);
         }
         mma_commit(bar_ws);
-        // St += (N*rel)^T K (accumulator already holds gamma * St); token groups {0,2} first, {1,3} second;
-        // O^T += N^T P^T for the same token groups: the first half runs while the chain warps still work on the
-        // second, so the output accumulator completes right behind the state update
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks)
+          mma_ts(tm + kAccO, tm + kOpSH + ks * 8, ((ks >> 2) ? b1 : b0) + uint64_t((ks & 3) * 2 + (L::kQS >> 4)),
+                 kIdescN64, ks != 0);
+        // St += (N*rel)^T K (accumulator already holds gamma * St); token groups {0,2} first, {1,3} second
         ok &= mbar_wait(bar_opn, c & 1, abort, 43, c);
         tc_fence_after();
 #pragma unroll
@@ -1097,8 +1102,6 @@ walk_umma_kernel(const __grid_constant__ CUtensorMap tm_wh, const __grid_constan
           mma_ts(tm + kAccS, tm + kAccX + ks * 16, kdesc, kIdescN128BT, 1);
           mma_ts(tm + kAccS, tm + kAccX + ks * 16 + 8, kdesc, kIdescN128BT, 1);
         }
-#pragma unroll
-        for (int h = 0; h < 2; ++h) mma_ts(tm + kAccO, tm + kAccX + 64 + h * 32, pd + uint64_t(h * 4), kIdescN64, 1);
         ok &= mbar_wait(bar_opn + 1, c & 1, abort, 43, c);
         tc_fence_after();
 #pragma unroll
@@ -1109,9 +1112,10 @@ walk_umma_kernel(const __grid_constant__ CUtensorMap tm_wh, const __grid_constan
           mma_ts(tm + kAccS, tm + kAccX + ks * 16 + 8, kdesc, kIdescN128BT, 1);
         }
         mma_commit(bar_s);
+        // O^T += N^T P^T behind the state update: the next chunk's split waits for that, not for the output
 #pragma unroll
-        for (int h = 0; h < 2; ++h)
-          mma_ts(tm + kAccO, tm + kAccX + 64 + (h * 2 + 1) * 16, pd + uint64_t((h * 2 + 1) * 2), kIdescN64, 1);
+        for (int ks = 0; ks < 4; ++ks)
+          mma_ts(tm + kAccO, tm + kAccX + 64 + ks * 16, pd + uint64_t(ks * 2), kIdescN64, 1);
         mma_commit(bar_o);
         mma_commit(empty + (c & 1));
       }
