@@ -3,7 +3,7 @@
 
 Run where the reference checkout is available:
 
-    python tests/golden/make_golden.py [--reference /path/to/actlizeLA]
+    python tests/golden/make_golden.py --reference /path/to/actlizeLA
 
 For every case it (1) builds the seeded inputs, (2) runs the reference's own CPU path
 (``actlize_la.reference.gdn_chunk_ref.torch_chunk_gated_delta_rule`` in FP32, with q/k
@@ -44,7 +44,7 @@ def digest(tensors):
 
 def main():
     ap = argparse.ArgumentParser(description=__doc__)
-    ap.add_argument("--reference", type=Path, default=Path("/root/reference"))
+    ap.add_argument("--reference", type=Path, required=True, help="checkout of the reference project")
     ap.add_argument("--out", type=Path, default=Path(__file__).with_name("golden_cases.npz"))
     args = ap.parse_args()
     sys.path[:0] = [str(args.reference), str(args.reference / "tests")]
