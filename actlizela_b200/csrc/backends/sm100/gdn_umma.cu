@@ -697,18 +697,17 @@ prepare_umma_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
 #undef GDN_PSTAMP
 
 // ==================================================================================== walk kernel
-// One CTA per (batch, value head), 448 threads, one CTA per SM.  Tensor memory (512 columns):
+// One CTA per (batch, value head), 512 threads, one CTA per SM.  Tensor memory (512 columns):
 //   ACC_S [  0,128)  St FP32 accumulator (pre-scaled by the chunk decay before the update MMA)
 //   OP_SH [128,192)  St BF16 hi, packed pairs      OP_SL [192,256)  St BF16 lo
-//   ACC_Y [448,512)  (W_hi S_lo)^T: the low half of the state goes to its own accumulator so that the two
-//                    passes do not wait on each other's accumulate dependency
-//   ACC_X [256,448)  one 192-column product  S_hi^T [W_hi ; W_lo ; Qs]^T :
-//           [256,320) (W_hi S)^T   [320,384) (W_lo S)^T   [384,448) O^T (= ACC_O, later += N^T P^T)
-//         after N = U - W S has been formed, the first 128 columns are reused for the N operands of the
+//   ACC_X [256,384)  S_hi^T [W_hi ; W_lo]^T, with S_lo^T W_hi^T added to the first half:
+//           [256,320) (W_hi S)^T   [320,384) (W_lo S_hi)^T
+//         after N = U - W S has been formed, the columns are reused for the N operands of the
 //         16-token group ks:  (N*rel) hi at 256+16ks, lo at 256+16ks+8,  N (BF16) at 320+16ks
-// A tcgen05.mma with M = 128 occupies the tensor pipe for at least ~64 cycles whatever N is, so the chain
-// uses few, wide instructions: 16 per chunk for W S and Q S together (N = 192 and 128), 8 for the state
-// update (N = 128), 4 for P N.
+//   ACC_O [384,448) and [448,512)  O^T = S_hi^T Qs^T + N^T P^T, alternating by chunk: the epilogue drains one
+//         while the next chunk's products fill the other
+// Per chunk: 16 instructions for W S (N = 128 and 64), on which the chain waits; 8 for S Qs and 4 for P N, issued
+// behind the commits the chain waits for; 8 for the state update (N = 128).
 // Roles: warp 0 MMA issuer and warp 1 TMA producer (the lowest warp ids: their short instruction streams
 //        sit on the critical path and must not queue behind the arithmetic of the chain warps);
 //        warps 4-11 state chain: a warp owns the 32 TMEM lanes of quarter (warp & 3) and, of every tile it
@@ -731,7 +730,7 @@ struct WalkLayout {
 constexpr int kMmaWarp = 0, kTmaWarp = 1, kChainWarp0 = 4, kChainWarps = 8, kOutWarp0 = 12;
 constexpr int kWalkThreads = 512;
 constexpr int kWalkSmem = WalkLayout::kTotal + 1024;
-constexpr uint32_t kAccS = 0, kOpSH = 128, kOpSL = 192, kAccX = 256, kAccO = 384, kAccY = 448;
+constexpr uint32_t kAccS = 0, kOpSH = 128, kOpSL = 192, kAccX = 256, kAccO = 384;   // ACC_O: two buffers of 64
 constexpr uint32_t kIdescN192 = idesc_bf16(128, 192, false, false);
 constexpr uint32_t kIdescN128 = idesc_bf16(128, 128, false, false);
 
@@ -764,10 +763,10 @@ walk_umma_kernel(const __grid_constant__ CUtensorMap tm_wh, const __grid_constan
   uint64_t* bar_ws = bar_ops + 4;              // wide product complete
   uint64_t* bar_s = bar_ops + 5;               // state update complete
   uint64_t* bar_o = bar_ops + 6;               // output accumulator complete
-  uint64_t* bar_ofree = bar_ops + 7;           // output accumulator drained (one arrival per output warp)
+  uint64_t* bar_ofree = bar_ops + 10;          // [2] output accumulator (c & 1) drained (one arrival per output warp)
   uint64_t* bar_staged = bar_ops + 8;          // output tile staged in shared memory (one arrival per output warp)
   uint64_t* bar_stfree = bar_ops + 9;          // an older output store has finished reading its staging tile
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_ops + 10);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_ops + 12);
   volatile int* abort_word = reinterpret_cast<volatile int*>(tmem_slot + 1);
   int* limit_slot = reinterpret_cast<int*>(tmem_slot + 2);
   const AbortFlag abort{abort_word};
@@ -809,6 +808,7 @@ walk_umma_kernel(const __grid_constant__ CUtensorMap tm_wh, const __grid_constan
     mbar_init(bar_s, 1);
     mbar_init(bar_o, 1);
     mbar_init(bar_ofree, 4);
+    mbar_init(bar_ofree + 1, 4);
     mbar_init(bar_staged, 4);
     mbar_init(bar_stfree, 1);
     *abort_word = 0;
@@ -894,10 +894,9 @@ walk_umma_kernel(const __grid_constant__ CUtensorMap tm_wh, const __grid_constan
         tmem_st32(taddr + kAccS + k0, d);
         tmem_wait_st();
         tc_fence_before();
-        // the products overwrite O^T and read the ring stage: this warp vouches for both before its first
-        // arrival, so the issuer has a single wait in front of them (waiting for the drained output on the
-        // issuer itself would hold up the state update behind it)
-        if (part == 0 && c > 0) ok = mbar_wait(bar_ofree, (c - 1) & 1, abort, 14, c);
+        // the products overwrite one O^T buffer (last used two chunks ago) and read the ring stage: this warp
+        // vouches for both before its first arrival, so the issuer has a single wait in front of them
+        if (part == 0 && c > 1) ok = mbar_wait(bar_ofree + (c & 1), ((c >> 1) - 1) & 1, abort, 14, c);
         __syncwarp();
         if (lane == 0) mbar_arrive(bar_ops + part);
       }
@@ -915,18 +914,15 @@ walk_umma_kernel(const __grid_constant__ CUtensorMap tm_wh, const __grid_constan
 #pragma unroll
       for (int part = 0; part < 2; ++part) {
         const int ks = half * 2 + part;                     // 16-token group
-        uint32_t dh[16], dl[16], dy[16], nh[8], nl[8], n16[8];
+        uint32_t dh[16], dl[16], nh[8], nl[8], n16[8];
         tmem_ld16(taddr + kAccX + ks * 16, dh);
         tmem_ld16(taddr + kAccX + 64 + ks * 16, dl);
-        tmem_ld16(taddr + kAccY + ks * 16, dy);
         tmem_wait_ld();
 #pragma unroll
         for (int j = 0; j < 16; j += 2) {
           const int i = ks * 16 + j;
-          const float n0 = u[part * 16 + j] -
-                           (__uint_as_float(dh[j]) + (__uint_as_float(dl[j]) + __uint_as_float(dy[j])));
-          const float n1 = u[part * 16 + j + 1] -
-                           (__uint_as_float(dh[j + 1]) + (__uint_as_float(dl[j + 1]) + __uint_as_float(dy[j + 1])));
+          const float n0 = u[part * 16 + j] - (__uint_as_float(dh[j]) + __uint_as_float(dl[j]));
+          const float n1 = u[part * 16 + j + 1] - (__uint_as_float(dh[j + 1]) + __uint_as_float(dl[j + 1]));
           const float r0 = n0 * gates[i], r1 = n1 * gates[i + 1];
           const uint32_t h = pack_bf16(r0, r1);
           nh[j >> 1] = h;
@@ -961,13 +957,14 @@ walk_umma_kernel(const __grid_constant__ CUtensorMap tm_wh, const __grid_constan
     // ------------------------------------------------------------------ output epilogue
     const int quarter = warp - kOutWarp0;
     const int v = quarter * 32 + lane;
-    const uint32_t taddr = tmem + (uint32_t(quarter * 32) << 16) + kAccO;
+    const uint32_t tbase = tmem + (uint32_t(quarter * 32) << 16) + kAccO;
     bool ok = true;
     for (int c = 0; c < chunks && ok; ++c) {
       ok = mbar_wait(bar_o, c & 1, abort, 20, c);
       if (!ok) break;
       tc_fence_after();
       GDN_OSTAMP(0);
+      const uint32_t taddr = tbase + (c & 1) * 64;
       uint32_t o[64];
       {
         uint32_t d0[32], d1[32];
@@ -982,7 +979,7 @@ walk_umma_kernel(const __grid_constant__ CUtensorMap tm_wh, const __grid_constan
       }
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(bar_ofree);
+      if (lane == 0) mbar_arrive(bar_ofree + (c & 1));
       GDN_OSTAMP(1);
       if (geo.varlen && c == chunks - 1 && tail_valid < kChunk) {
         // packed mode, ragged end of a sequence: the rows behind it belong to the next sequence, so the tile
@@ -1065,6 +1062,7 @@ walk_umma_kernel(const __grid_constant__ CUtensorMap tm_wh, const __grid_constan
       for (int c = 0; c < chunks && ok; ++c) {
         const uint64_t stage = uint64_t((c & 1) * (L::kStage >> 4));
         const uint64_t b0 = dB0 + stage, b1 = dB1 + stage, kd = dK + stage, pd = dP + stage;
+        const uint32_t acc_o = tm + kAccO + (c & 1) * 64;
         // St [W_hi ; W_lo]^T with St ~ SH + SL (the SL pass only against W_hi, into its own accumulator).  K steps
         // {0,1,4,5} of the split become available first, {2,3,6,7} second.  The chain waits for this product only;
         // the state part of the output, St Qs^T, reads the same operands and is issued behind the commit, so that
@@ -1076,7 +1074,7 @@ walk_umma_kernel(const __grid_constant__ CUtensorMap tm_wh, const __grid_constan
           const int ks = (q >> 1) * 4 + (q & 1);
           const uint64_t bdesc = ((ks >> 2) ? b1 : b0) + uint64_t((ks & 3) * 2);     // +32 bytes per K step
           mma_ts(tm + kAccX, tm + kOpSH + ks * 8, bdesc, kIdescN128, q != 0);
-          mma_ts(tm + kAccY, tm + kOpSL + ks * 8, bdesc, kIdescN64, q != 0);
+          mma_ts(tm + kAccX, tm + kOpSL + ks * 8, bdesc, kIdescN64, 1);
         }
         ok &= mbar_wait(bar_ops + 1, c & 1, abort, 41, c);
         tc_fence_after();
@@ -1085,12 +1083,12 @@ walk_umma_kernel(const __grid_constant__ CUtensorMap tm_wh, const __grid_constan
           const int ks = (q >> 1) * 4 + 2 + (q & 1);
           const uint64_t bdesc = ((ks >> 2) ? b1 : b0) + uint64_t((ks & 3) * 2);
           mma_ts(tm + kAccX, tm + kOpSH + ks * 8, bdesc, kIdescN128, 1);
-          mma_ts(tm + kAccY, tm + kOpSL + ks * 8, bdesc, kIdescN64, 1);
+          mma_ts(tm + kAccX, tm + kOpSL + ks * 8, bdesc, kIdescN64, 1);
         }
         mma_commit(bar_ws);
 #pragma unroll
         for (int ks = 0; ks < 8; ++ks)
-          mma_ts(tm + kAccO, tm + kOpSH + ks * 8, ((ks >> 2) ? b1 : b0) + uint64_t((ks & 3) * 2 + (L::kQS >> 4)),
+          mma_ts(acc_o, tm + kOpSH + ks * 8, ((ks >> 2) ? b1 : b0) + uint64_t((ks & 3) * 2 + (L::kQS >> 4)),
                  kIdescN64, ks != 0);
         // St += (N*rel)^T K (accumulator already holds gamma * St); token groups {0,2} first, {1,3} second
         ok &= mbar_wait(bar_opn, c & 1, abort, 43, c);
@@ -1115,7 +1113,7 @@ walk_umma_kernel(const __grid_constant__ CUtensorMap tm_wh, const __grid_constan
         // O^T += N^T P^T behind the state update: the next chunk's split waits for that, not for the output
 #pragma unroll
         for (int ks = 0; ks < 4; ++ks)
-          mma_ts(tm + kAccO, tm + kAccX + 64 + ks * 16, pd + uint64_t(ks * 2), kIdescN64, 1);
+          mma_ts(acc_o, tm + kAccX + 64 + ks * 16, pd + uint64_t(ks * 2), kIdescN64, 1);
         mma_commit(bar_o);
         mma_commit(empty + (c & 1));
       }
