@@ -49,7 +49,8 @@ int segments_of(int config, const Geometry& geo) {
 
 // Second stream and events of the segmented forward, created by configure() for the current device.
 struct SegmentStreams {
-  cudaStream_t walk = nullptr;                    // high priority: the sequential chunk walks
+  cudaStream_t walk = nullptr;                    // high priority: the sequential chunk walks (host-buffer entry)
+  cudaStream_t prepare = nullptr;                 // low priority: prepare kernels of the segments behind the first
   cudaStream_t copy_in = nullptr, copy_out = nullptr;   // host-buffer entry: transfers next to compute
   cudaEvent_t prepared[kMaxSegments] = {};
   cudaEvent_t arrived[kMaxSegments] = {};         // inputs of a segment are on the device
@@ -68,6 +69,7 @@ int create_segment_streams() {
   int least = 0, greatest = 0;
   if ((e = cudaDeviceGetStreamPriorityRange(&least, &greatest)) != cudaSuccess) return int(e);
   if ((e = cudaStreamCreateWithPriority(&ss.walk, cudaStreamNonBlocking, greatest)) != cudaSuccess) return int(e);
+  if ((e = cudaStreamCreateWithPriority(&ss.prepare, cudaStreamNonBlocking, least)) != cudaSuccess) return int(e);
   if ((e = cudaStreamCreateWithFlags(&ss.copy_in, cudaStreamNonBlocking)) != cudaSuccess) return int(e);
   if ((e = cudaStreamCreateWithFlags(&ss.copy_out, cudaStreamNonBlocking)) != cudaSuccess) return int(e);
   for (int i = 0; i < kMaxSegments; ++i) {
@@ -212,22 +214,33 @@ extern "C" int actlize_la_sm100_forward_prepared(
 namespace {
 int run_forward(const Inputs& in, Geometry geo, const Workspace& ws, int config, int segments, cudaStream_t stream) {
   if (segments > 1) {
-    // Prepare kernels of all segments go to the caller's stream back to back; the walks run in order on
-    // a high-priority second stream, each after its segment's prepare, so that a later segment is
-    // prepared on the SMs the walk leaves free.  The caller's stream finally waits for the last walk.
+    // Three streams.  The caller's: the first segment's prepare, then its walk, which so follows without an event
+    // hop and claims its SMs before the second prepare kernel fills the device.  A second one (normal priority): the
+    // prepare kernels of the later segments, forked behind the first prepare.  A high-priority third: the later
+    // walks, each behind the previous walk and its own segment's prepare; as a walk ends, the next takes over its
+    // SMs ahead of pending prepare blocks.  The caller's stream finally waits for the last walk.
     int device = -1;
     cudaError_t e = cudaGetDevice(&device);
     if (e != cudaSuccess) return int(e);
-    if (device < 0 || device >= 64 || !g_streams[device].walk) return int(cudaErrorNotReady);   // configure() first
+    if (device < 0 || device >= 64 || !g_streams[device].prepare) return int(cudaErrorNotReady);   // configure() first
     SegmentStreams& ss = g_streams[device];
     const int chunks = geo.chunks();
     for (int i = 0; i < segments; ++i) {
       geo.chunk_begin = int((long long)chunks * i / segments);
       geo.chunk_count = int((long long)chunks * (i + 1) / segments) - geo.chunk_begin;
-      if (int rc = launch_prepare_tc(config, in, geo, ws, stream)) return rc;
-      if ((e = cudaEventRecord(ss.prepared[i], stream)) != cudaSuccess) return int(e);
-      if ((e = cudaStreamWaitEvent(ss.walk, ss.prepared[i], 0)) != cudaSuccess) return int(e);
-      if (int rc = launch_walk_tc(config, in, geo, ws, ss.walk)) return rc;
+      if (i == 0) {
+        if (int rc = launch_prepare_tc(config, in, geo, ws, stream)) return rc;
+        if ((e = cudaEventRecord(ss.start, stream)) != cudaSuccess) return int(e);
+        if ((e = cudaStreamWaitEvent(ss.prepare, ss.start, 0)) != cudaSuccess) return int(e);
+        if (int rc = launch_walk_tc(config, in, geo, ws, stream)) return rc;
+        if ((e = cudaEventRecord(ss.walked[0], stream)) != cudaSuccess) return int(e);
+        if ((e = cudaStreamWaitEvent(ss.walk, ss.walked[0], 0)) != cudaSuccess) return int(e);
+      } else {
+        if (int rc = launch_prepare_tc(config, in, geo, ws, ss.prepare)) return rc;
+        if ((e = cudaEventRecord(ss.prepared[i], ss.prepare)) != cudaSuccess) return int(e);
+        if ((e = cudaStreamWaitEvent(ss.walk, ss.prepared[i], 0)) != cudaSuccess) return int(e);
+        if (int rc = launch_walk_tc(config, in, geo, ws, ss.walk)) return rc;
+      }
     }
     if ((e = cudaEventRecord(ss.done, ss.walk)) != cudaSuccess) return int(e);
     return int(cudaStreamWaitEvent(stream, ss.done, 0));

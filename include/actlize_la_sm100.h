@@ -82,10 +82,10 @@ long long actlize_la_sm100_workspace_bytes(int batch, int sequence, int key_head
 /* Complete forward on caller-owned buffers: prepare kernel (per-chunk gate prefix, decay-masked
  * K.K^T, unit-lower-triangular inverse, WY factors) followed by the sequential chunk walk.
  * `config` is the value returned by actlize_la_sm100_select: kernel family in bits 0..3, number of
- * sequence segments in bits 8..15.  With more than one segment the walks run on a library-owned
- * high-priority stream that is forked from and joined back into `stream` with events (so the call stays
- * asynchronous and capturable); those streams and events exist once per device, therefore two segmented
- * calls on the same device must not be in flight at the same time on different streams.
+ * sequence segments in bits 8..15.  With more than one segment the prepare kernels and walks of the segments
+ * behind the first run on two library-owned streams that are forked from and joined back into `stream` with
+ * events (so the call stays asynchronous and capturable); those streams and events exist once per device,
+ * therefore two segmented calls on the same device must not be in flight at the same time on different streams.
  * Replaces actlize_la_ppu15_forward_prepared / actlize_la_ppu10_forward_prepared
  * (csrc/backends/ppu15/launch.h:12-17, csrc/backends/ppu10/launch.h:11-14). */
 int actlize_la_sm100_forward_prepared(
