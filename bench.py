@@ -96,6 +96,9 @@ def cpu_reference_run(workload, steps, warmup, sample_note):
     import torch
     from actlizela_b200.workloads import make_inputs
     from oracle import gdn_oracle as oracle
+    # all host threads, also under torch.distributed.run (which exports OMP_NUM_THREADS=1 for multi-rank jobs)
+    usable = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
+    torch.set_num_threads(max(1, usable))
     inputs = make_inputs(workload)
     for _ in range(warmup):
         oracle.chunk_forward_fp32(*inputs, output_final_state=True)
