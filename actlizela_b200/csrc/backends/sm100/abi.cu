@@ -148,10 +148,8 @@ extern "C" int actlize_la_sm100_select(int b, int t, int hk, int hv, int gate_fp
   // no measured row: integer rule fitted to the measured ones (sm100_policy.py::default_segments is the same)
   const long long heads = (long long)b * hv, chunks = (t + kChunk - 1) / kChunk;
   int segments = 1;
-  if (heads > 148) {
+  if (heads > 64) {
     segments = 1;
-  } else if (heads > 64) {
-    segments = chunks >= 16 ? 2 : 1;
   } else {
     int root = 0;
     while ((long long)(root + 1) * (root + 1) <= chunks / 8) ++root;

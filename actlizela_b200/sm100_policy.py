@@ -52,14 +52,12 @@ class Selection:
 
 def default_segments(batch, length, value_heads):
     """Segment count for a shape without a measured row; integer rule fitted to the measured rows (the walk of a
-    segment occupies B*Hv SMs, the prepare of the next segment runs on the rest): few heads -> isqrt(chunks/8)
-    clamped to 1..8, up to one head per SM -> 2, more -> 1.  The native selector computes the same."""
+    segment occupies B*Hv SMs, the prepare of the next segment runs on the rest): up to 64 heads -> isqrt(chunks/8)
+    clamped to 1..8, more -> 1.  The native selector computes the same."""
     from math import isqrt
     heads, chunks = batch * value_heads, (length + 63) // 64
-    if heads > 148:
-        return 1
     if heads > 64:
-        return 2 if chunks >= 16 else 1
+        return 1
     return max(1, min(8, isqrt(chunks // 8)))
 
 
