@@ -87,6 +87,18 @@ __device__ __forceinline__ float fast_exp2(float x) {
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
+// Packed FP32 pairs (two IEEE round-to-nearest operations per instruction on sm_100): the arithmetic of the walk's
+// chain warps is bound by instruction issue, and these halve its floating-point instruction count bit for bit.
+#define GDN_F32X2(name, op)                                                                                      \
+  __device__ __forceinline__ void name(float& x0, float& x1, float a0, float a1, float b0, float b1) {          \
+    asm("{\n\t.reg .b64 a, b, c;\n\tmov.b64 a, {%2, %3};\n\tmov.b64 b, {%4, %5};\n\t" op                       \
+        ".rn.f32x2 c, a, b;\n\tmov.b64 {%0, %1}, c;\n\t}"                                                       \
+        : "=f"(x0), "=f"(x1) : "f"(a0), "f"(a1), "f"(b0), "f"(b1));                                              \
+  }
+GDN_F32X2(add2, "add")
+GDN_F32X2(sub2, "sub")
+GDN_F32X2(mul2, "mul")
+#undef GDN_F32X2
 __device__ __forceinline__ float bf16_lo(uint32_t packed) { return __uint_as_float(packed << 16); }
 __device__ __forceinline__ float bf16_hi(uint32_t packed) { return __uint_as_float(packed & 0xffff0000u); }
 
@@ -885,9 +897,12 @@ walk_umma_kernel(const __grid_constant__ CUtensorMap tm_wh, const __grid_constan
           const float s0 = __uint_as_float(d[j]), s1 = __uint_as_float(d[j + 1]);
           const uint32_t h = pack_bf16(s0, s1);
           hi[j >> 1] = h;
-          lo[j >> 1] = pack_bf16(s0 - bf16_lo(h), s1 - bf16_hi(h));
-          d[j] = __float_as_uint(s0 * gamma);
-          d[j + 1] = __float_as_uint(s1 * gamma);
+          float l0, l1, g0, g1;
+          sub2(l0, l1, s0, s1, bf16_lo(h), bf16_hi(h));
+          lo[j >> 1] = pack_bf16(l0, l1);
+          mul2(g0, g1, s0, s1, gamma, gamma);
+          d[j] = __float_as_uint(g0);
+          d[j + 1] = __float_as_uint(g1);
         }
         tmem_st16(taddr + kOpSH + (k0 >> 1), hi);
         tmem_st16(taddr + kOpSL + (k0 >> 1), lo);
@@ -921,12 +936,14 @@ walk_umma_kernel(const __grid_constant__ CUtensorMap tm_wh, const __grid_constan
 #pragma unroll
         for (int j = 0; j < 16; j += 2) {
           const int i = ks * 16 + j;
-          const float n0 = u[part * 16 + j] - (__uint_as_float(dh[j]) + __uint_as_float(dl[j]));
-          const float n1 = u[part * 16 + j + 1] - (__uint_as_float(dh[j + 1]) + __uint_as_float(dl[j + 1]));
-          const float r0 = n0 * gates[i], r1 = n1 * gates[i + 1];
+          float z0, z1, n0, n1, r0, r1, e0, e1;
+          add2(z0, z1, __uint_as_float(dh[j]), __uint_as_float(dh[j + 1]), __uint_as_float(dl[j]), __uint_as_float(dl[j + 1]));
+          sub2(n0, n1, u[part * 16 + j], u[part * 16 + j + 1], z0, z1);
+          mul2(r0, r1, n0, n1, gates[i], gates[i + 1]);
           const uint32_t h = pack_bf16(r0, r1);
           nh[j >> 1] = h;
-          nl[j >> 1] = pack_bf16(r0 - bf16_lo(h), r1 - bf16_hi(h));
+          sub2(e0, e1, r0, r1, bf16_lo(h), bf16_hi(h));
+          nl[j >> 1] = pack_bf16(e0, e1);
           n16[j >> 1] = pack_bf16(n0, n1);
         }
         tmem_st8(taddr + kAccX + ks * 16, nh);
