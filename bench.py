@@ -270,7 +270,8 @@ def sequence_parallel_bench(args, workload):
         print(json.dumps(dict(
             metric=METRIC, value=workload.tokens / (ms * 1e-3), unit=UNIT, n_gpus=world, steps=args.steps,
             warmup=max(3, args.warmup), ms_per_step=ms, higher_is_better=True, scaling="strong", vs_baseline=None,
-            dtype="bf16 operands (state path as bf16 hi+lo pairs), f32 accumulate and state", data="synthetic",
+            dtype="bf16", dtype_detail="bf16 operands (state path as bf16 hi+lo pairs), f32 accumulate and state",
+            data="synthetic",
             config=dict(workload=f"{workload.name} B{workload.batch} T{workload.length} Hk{workload.key_heads} "
                                  f"Hv{workload.value_heads}", parallelism=f"sp{world}",
                         until_decayed=bool(args.until_decayed), l2="inputs exceed the 126 MB L2"),
@@ -424,7 +425,7 @@ def main():
     line = dict(
         metric=METRIC, value=workload.tokens * world / (ms_step * 1e-3), unit=UNIT, n_gpus=world,
         steps=args.steps, warmup=args.warmup, ms_per_step=ms_step, higher_is_better=True, scaling="weak",
-        vs_baseline=None, dtype="bf16 operands (state path as bf16 hi+lo pairs), f32 accumulate and state",
+        vs_baseline=None, dtype="bf16", dtype_detail="bf16 operands (state path as bf16 hi+lo pairs), f32 accumulate and state",
         data="synthetic", config=config_dict(workload, world, config_name),
         gpu_launches=args.steps * lib.actlize_la_sm100_launches_per_forward(config),
         kernels_ms=dict(prepare=ms_prepare, walk=ms_walk, forward=ms_step),
