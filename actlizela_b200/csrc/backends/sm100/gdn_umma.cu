@@ -102,11 +102,6 @@ GDN_F32X2(mul2, "mul")
 __device__ __forceinline__ float bf16_lo(uint32_t packed) { return __uint_as_float(packed << 16); }
 __device__ __forceinline__ float bf16_hi(uint32_t packed) { return __uint_as_float(packed & 0xffff0000u); }
 
-// byte offset of element (row, col) in a [64 rows][64 BF16] tile with 128-byte swizzle
-__device__ __forceinline__ int swizzled_offset(int row, int col) {
-  return row * 128 + ((((col >> 3) ^ (row & 7)) << 4) | ((col & 7) << 1));
-}
-
 // ================================================================================= prepare kernel
 // One CTA per (batch, value head, chunk) block, 256 threads, two CTAs per SM.  A warp owns the TMEM
 // lane quarter (warp & 3) and, of every accumulator it reads, the column half (warp >> 2).
@@ -743,7 +738,6 @@ constexpr int kMmaWarp = 0, kTmaWarp = 1, kChainWarp0 = 4, kChainWarps = 8, kOut
 constexpr int kWalkThreads = 512;
 constexpr int kWalkSmem = WalkLayout::kTotal + 1024;
 constexpr uint32_t kAccS = 0, kOpSH = 128, kOpSL = 192, kAccX = 256, kAccO = 384;   // ACC_O: two buffers of 64
-constexpr uint32_t kIdescN192 = idesc_bf16(128, 192, false, false);
 constexpr uint32_t kIdescN128 = idesc_bf16(128, 128, false, false);
 
 #ifdef GDN_SM100_PHASE_TIMING
