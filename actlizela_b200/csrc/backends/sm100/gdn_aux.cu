@@ -20,7 +20,9 @@ namespace {
 __device__ __forceinline__ float lo_bf16(uint32_t p) { return __uint_as_float(p << 16); }
 __device__ __forceinline__ float hi_bf16(uint32_t p) { return __uint_as_float(p & 0xffff0000u); }
 
-// 16 lanes per 128-wide head vector (8 BF16 = 16 bytes per lane), 16 vectors per 256-thread CTA.
+// 16 lanes per 128-wide head vector (8 BF16 = 16 bytes per lane); a 256-thread CTA covers 64 consecutive vectors in
+// four sweeps of 16 and issues the loads of all sweeps first (four 16-byte loads in flight per thread).
+constexpr int kPrepSweeps = 4;
 __global__ void __launch_bounds__(256)
 prepare_inputs_kernel(const __nv_bfloat16* __restrict__ mixed, long long mixed_stride,
                       const __nv_bfloat16* __restrict__ a, const __nv_bfloat16* __restrict__ b,
@@ -28,37 +30,49 @@ prepare_inputs_kernel(const __nv_bfloat16* __restrict__ mixed, long long mixed_s
                       __nv_bfloat16* __restrict__ q, __nv_bfloat16* __restrict__ k, __nv_bfloat16* __restrict__ v,
                       float* __restrict__ g, __nv_bfloat16* __restrict__ beta, long long tokens, int hk, int hv) {
   const int heads = 2 * hk + hv;
-  const long long slot = (long long)blockIdx.x * 16 + (threadIdx.x >> 4);
-  const bool live = slot < tokens * heads;    // idle groups redo the last vector and store nothing
-  const long long vec = live ? slot : tokens * heads - 1;
   const int lane = threadIdx.x & 15;
-  const long long token = vec / heads;
-  const int h = int(vec % heads);
-  const uint4 x = *reinterpret_cast<const uint4*>(mixed + token * mixed_stride + (long long)h * kDim + lane * 8);
-  if (h < 2 * hk) {
-    float f[8] = {lo_bf16(x.x), hi_bf16(x.x), lo_bf16(x.y), hi_bf16(x.y),
-                  lo_bf16(x.z), hi_bf16(x.z), lo_bf16(x.w), hi_bf16(x.w)};
-    float square = 0.f;
+  const long long first = (long long)blockIdx.x * (16 * kPrepSweeps) + (threadIdx.x >> 4);
+  const long long vectors = tokens * heads;
+  uint4 xs[kPrepSweeps];
 #pragma unroll
-    for (int i = 0; i < 8; ++i) square = fmaf(f[i], f[i], square);
+  for (int r = 0; r < kPrepSweeps; ++r) {
+    const long long slot = first + r * 16;
+    const long long vec = slot < vectors ? slot : vectors - 1;     // idle groups redo the last vector and store nothing
+    xs[r] = *reinterpret_cast<const uint4*>(mixed + (vec / heads) * mixed_stride + (vec % heads) * kDim + lane * 8);
+  }
 #pragma unroll
-    for (int d = 8; d; d >>= 1) square += __shfl_xor_sync(0xffffffffu, square, d, 16);
-    const float factor = rsqrtf(square + 1e-6f);
-    uint4 o;
-    o.x = pack_bf16(f[0] * factor, f[1] * factor);
-    o.y = pack_bf16(f[2] * factor, f[3] * factor);
-    o.z = pack_bf16(f[4] * factor, f[5] * factor);
-    o.w = pack_bf16(f[6] * factor, f[7] * factor);
-    __nv_bfloat16* dst = (h < hk ? q : k) + (token * hk + (h % hk)) * kDim + lane * 8;
-    if (live) *reinterpret_cast<uint4*>(dst) = o;
-  } else {
-    const int vh = h - 2 * hk;
-    if (live) *reinterpret_cast<uint4*>(v + (token * hv + vh) * kDim + lane * 8) = x;
-    if (live && lane == 0) {
-      const long long at = token * hv + vh;
-      const float z = __bfloat162float(a[at]) + dt_bias[vh];
-      g[at] = -expf(a_log[vh]) * (z > 20.f ? z : log1pf(expf(z)));
-      beta[at] = __float2bfloat16_rn(1.f / (1.f + expf(-__bfloat162float(b[at]))));
+  for (int r = 0; r < kPrepSweeps; ++r) {
+    const long long slot = first + r * 16;
+    const bool live = slot < vectors;
+    const long long vec = live ? slot : vectors - 1;
+    const long long token = vec / heads;
+    const int h = int(vec % heads);
+    const uint4 x = xs[r];
+    if (h < 2 * hk) {
+      float f[8] = {lo_bf16(x.x), hi_bf16(x.x), lo_bf16(x.y), hi_bf16(x.y),
+                    lo_bf16(x.z), hi_bf16(x.z), lo_bf16(x.w), hi_bf16(x.w)};
+      float square = 0.f;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) square = fmaf(f[i], f[i], square);
+#pragma unroll
+      for (int d = 8; d; d >>= 1) square += __shfl_xor_sync(0xffffffffu, square, d, 16);
+      const float factor = rsqrtf(square + 1e-6f);
+      uint4 o;
+      o.x = pack_bf16(f[0] * factor, f[1] * factor);
+      o.y = pack_bf16(f[2] * factor, f[3] * factor);
+      o.z = pack_bf16(f[4] * factor, f[5] * factor);
+      o.w = pack_bf16(f[6] * factor, f[7] * factor);
+      __nv_bfloat16* dst = (h < hk ? q : k) + (token * hk + (h % hk)) * kDim + lane * 8;
+      if (live) *reinterpret_cast<uint4*>(dst) = o;
+    } else {
+      const int vh = h - 2 * hk;
+      if (live) *reinterpret_cast<uint4*>(v + (token * hv + vh) * kDim + lane * 8) = x;
+      if (live && lane == 0) {
+        const long long at = token * hv + vh;
+        const float z = __bfloat162float(a[at]) + dt_bias[vh];
+        g[at] = -expf(a_log[vh]) * (z > 20.f ? z : log1pf(expf(z)));
+        beta[at] = __float2bfloat16_rn(1.f / (1.f + expf(-__bfloat162float(b[at]))));
+      }
     }
   }
 }
@@ -190,37 +204,50 @@ commit_step_kernel(const __nv_bfloat16* __restrict__ k, const void* __restrict__
   for (int r = 0; r < 64; ++r) column[r * kDim] = s[r];
 }
 
-// 16 lanes per 128-wide row (16 bytes per lane and tensor), 16 rows per 256-thread CTA.
+// 16 lanes per 128-wide row (16 bytes per lane and tensor); a 256-thread CTA covers 64 consecutive rows in four
+// sweeps of 16, and every thread issues the loads of all four sweeps before it touches the data, so that eight
+// 16-byte loads per thread are in flight (one row per thread group at a time left the memory system idle).
+constexpr int kNormSweeps = 4;
 __global__ void __launch_bounds__(256)
 rmsnorm_gated_kernel(const __nv_bfloat16* __restrict__ y, const __nv_bfloat16* __restrict__ z,
                      const __nv_bfloat16* __restrict__ weight, __nv_bfloat16* __restrict__ out, long long rows) {
-  const long long slot = (long long)blockIdx.x * 16 + (threadIdx.x >> 4);
-  const bool live = slot < rows;               // idle groups redo the last row and store nothing
-  const long long row = live ? slot : rows - 1;
   const int lane = threadIdx.x & 15;
-  const uint4 yy = *reinterpret_cast<const uint4*>(y + row * kDim + lane * 8);
-  const uint4 zz = *reinterpret_cast<const uint4*>(z + row * kDim + lane * 8);
+  const long long first = (long long)blockIdx.x * (16 * kNormSweeps) + (threadIdx.x >> 4);
+  uint4 yy[kNormSweeps], zz[kNormSweeps];
+#pragma unroll
+  for (int r = 0; r < kNormSweeps; ++r) {
+    const long long slot = first + r * 16;
+    const long long row = slot < rows ? slot : rows - 1;     // idle groups redo the last row and store nothing
+    yy[r] = *reinterpret_cast<const uint4*>(y + row * kDim + lane * 8);
+    zz[r] = *reinterpret_cast<const uint4*>(z + row * kDim + lane * 8);
+  }
   const uint4 ww = *reinterpret_cast<const uint4*>(weight + lane * 8);
-  const uint32_t yp[4] = {yy.x, yy.y, yy.z, yy.w}, zp[4] = {zz.x, zz.y, zz.z, zz.w}, wp[4] = {ww.x, ww.y, ww.z, ww.w};
-  float yf[8], square = 0.f;
+  const uint32_t wp[4] = {ww.x, ww.y, ww.z, ww.w};
 #pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    yf[2 * i] = lo_bf16(yp[i]);
-    yf[2 * i + 1] = hi_bf16(yp[i]);
-    square = fmaf(yf[2 * i], yf[2 * i], fmaf(yf[2 * i + 1], yf[2 * i + 1], square));
+  for (int r = 0; r < kNormSweeps; ++r) {
+    const long long slot = first + r * 16;
+    const uint32_t yp[4] = {yy[r].x, yy[r].y, yy[r].z, yy[r].w}, zp[4] = {zz[r].x, zz[r].y, zz[r].z, zz[r].w};
+    float yf[8], square = 0.f;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      yf[2 * i] = lo_bf16(yp[i]);
+      yf[2 * i + 1] = hi_bf16(yp[i]);
+      square = fmaf(yf[2 * i], yf[2 * i], fmaf(yf[2 * i + 1], yf[2 * i + 1], square));
+    }
+#pragma unroll
+    for (int d = 8; d; d >>= 1) square += __shfl_xor_sync(0xffffffffu, square, d, 16);
+    const float rstd = rsqrtf(square * (1.f / kDim) + 1e-6f);
+    uint32_t packed[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float z0 = lo_bf16(zp[i]), z1 = hi_bf16(zp[i]);
+      const float r0 = yf[2 * i] * rstd * lo_bf16(wp[i]) * (z0 / (1.f + expf(-z0)));
+      const float r1 = yf[2 * i + 1] * rstd * hi_bf16(wp[i]) * (z1 / (1.f + expf(-z1)));
+      packed[i] = pack_bf16(r0, r1);
+    }
+    if (slot < rows)
+      *reinterpret_cast<uint4*>(out + slot * kDim + lane * 8) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
   }
-#pragma unroll
-  for (int d = 8; d; d >>= 1) square += __shfl_xor_sync(0xffffffffu, square, d, 16);
-  const float rstd = rsqrtf(square * (1.f / kDim) + 1e-6f);
-  uint32_t packed[4];
-#pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    const float z0 = lo_bf16(zp[i]), z1 = hi_bf16(zp[i]);
-    const float r0 = yf[2 * i] * rstd * lo_bf16(wp[i]) * (z0 / (1.f + expf(-z0)));
-    const float r1 = yf[2 * i + 1] * rstd * hi_bf16(wp[i]) * (z1 / (1.f + expf(-z1)));
-    packed[i] = pack_bf16(r0, r1);
-  }
-  if (live) *reinterpret_cast<uint4*>(out + row * kDim + lane * 8) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
 }
 
 }  // namespace
@@ -237,8 +264,9 @@ extern "C" int actlize_la_sm100_prepare_inputs(
       (mixed_row_stride & 7) || (reinterpret_cast<uintptr_t>(mixed) & 15))
     return int(cudaErrorInvalidValue);
   const long long vectors = tokens * (2LL * hk + hv);
-  if ((vectors + 15) / 16 > INT_MAX) return int(cudaErrorInvalidValue);
-  prepare_inputs_kernel<<<(unsigned)((vectors + 15) / 16), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+  const long long ctas = (vectors + 16 * kPrepSweeps - 1) / (16 * kPrepSweeps);
+  if (ctas > INT_MAX) return int(cudaErrorInvalidValue);
+  prepare_inputs_kernel<<<(unsigned)ctas, 256, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const __nv_bfloat16*>(mixed), mixed_row_stride, static_cast<const __nv_bfloat16*>(a),
       static_cast<const __nv_bfloat16*>(b), a_log, dt_bias, static_cast<__nv_bfloat16*>(q),
       static_cast<__nv_bfloat16*>(k), static_cast<__nv_bfloat16*>(v), g, static_cast<__nv_bfloat16*>(beta), tokens, hk, hv);
@@ -282,11 +310,11 @@ extern "C" int actlize_la_sm100_commit_step(const void* k, const void* g, const 
 
 extern "C" int actlize_la_sm100_rmsnorm_gated(const void* y, const void* z, const void* weight, void* out,
                                               long long rows, void* stream) {
-  if (!y || !z || !weight || !out || rows <= 0 || (rows + 15) / 16 > INT_MAX) return int(cudaErrorInvalidValue);
+  if (!y || !z || !weight || !out || rows <= 0 || (rows + 63) / 64 > INT_MAX) return int(cudaErrorInvalidValue);
   if ((reinterpret_cast<uintptr_t>(y) | reinterpret_cast<uintptr_t>(z) | reinterpret_cast<uintptr_t>(weight) |
        reinterpret_cast<uintptr_t>(out)) & 15)
     return int(cudaErrorInvalidValue);
-  rmsnorm_gated_kernel<<<(unsigned)((rows + 15) / 16), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+  rmsnorm_gated_kernel<<<(unsigned)((rows + 16 * kNormSweeps - 1) / (16 * kNormSweeps)), 256, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const __nv_bfloat16*>(y), static_cast<const __nv_bfloat16*>(z),
       static_cast<const __nv_bfloat16*>(weight), static_cast<__nv_bfloat16*>(out), rows);
   return int(cudaGetLastError());

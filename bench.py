@@ -189,8 +189,9 @@ def aux_bench(args):
     else:
         rows = 65536 * hv
         y = torch.randn(rows, 128, generator=gen).to(torch.bfloat16).cuda()
+        z = torch.randn(rows, 128, generator=gen).to(torch.bfloat16).cuda()      # its own tensor: counted bytes are read
         w = torch.ones(128, dtype=torch.bfloat16, device="cuda")
-        call = lambda: rmsnorm_gated(y, y, w)
+        call = lambda: rmsnorm_gated(y, z, w)
         nbytes, units, unit = 3 * y.numel() * 2, rows // hv, "tokens/s"
         name = f"rmsnorm_gated rows{rows}"
     for _ in range(max(3, args.warmup)):
