@@ -39,6 +39,9 @@ EXPORTS = {
     "actlize_la_sm100_apply_transition": (_I, [_P] * 4 + [_I, _P]),
     "actlize_la_sm100_launches_per_forward": (_I, [_I]),
     "actlize_la_sm100_device_status": (_I, [_P, _I]),
+    "actlize_la_sm100_walk_plan_counts": (_I, [_P, _I]),
+    "actlize_la_sm100_last_failure": (_I, [_P]),
+    "actlize_la_sm100_selftest_walk_stall": (_I, [_P] * 7 + [_LL] + [_I] * 5 + [_P]),
     "actlize_la_sm100_selftest_wait_timeout": (_I, [_I, _P]),
     "actlize_la_sm100_prepare_inputs": (_I, [_P, _LL] + [_P] * 9 + [_LL, _I, _I, _P]),
     "actlize_la_sm100_decode_step": (_I, [_P] * 7 + [_I] * 4 + [_P]),
@@ -138,6 +141,30 @@ class NativeLibrary:
     def check(code):
         if code:
             raise RuntimeError(f"cuda_sm100 native call failed with CUDA error code {code}")
+
+    def last_failure(self, device):
+        """(code, block, wait site, chunk) of a kernel on ``device`` that gave up a bounded wait, or None.
+        Reads the host-visible record only: no synchronisation, so it reports launches that have already run."""
+        import torch
+        record = (C.c_int * 4)()
+        with torch.cuda.device(device):
+            self.check(self.lib.actlize_la_sm100_last_failure(record))
+        return tuple(record) if record[0] else None
+
+    def raise_on_failure(self, device, synchronize=False):
+        """Raise if a kernel on ``device`` gave up waiting (its outputs are incomplete); clears the record.
+        With ``synchronize`` the device is drained first, so every launch issued so far is covered."""
+        import torch
+        if synchronize:
+            torch.cuda.synchronize(device)
+        failure = self.last_failure(device)
+        if failure:
+            record = (C.c_int * 4)()
+            with torch.cuda.device(device):
+                self.check(self.lib.actlize_la_sm100_device_status(record, 1))
+            raise RuntimeError(
+                "a cuda_sm100 kernel gave up a bounded wait (code %d, block %d, wait site %d, chunk %d): the outputs "
+                "of that launch are incomplete and must be discarded" % failure)
 
 
 @lru_cache(maxsize=None)

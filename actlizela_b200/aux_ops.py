@@ -13,27 +13,47 @@ from __future__ import annotations
 from ._library import load_library
 
 
-def _bf16_cuda(x, name, last=None):
-    import torch
-    if x.dtype != torch.bfloat16 or x.device.type != "cuda" or not x.is_contiguous():
-        raise ValueError(f"{name} must be a contiguous BF16 CUDA tensor")
-    if last is not None and x.shape[-1] != last:
-        raise ValueError(f"{name} must have a last dimension of {last}")
+def _operands(*specs):
+    """Full check of every operand before a raw pointer of it reaches a kernel: shape and dtype first (so that the
+    messages are about the caller's mistake), then one common CUDA device, contiguity, 16-byte alignment and no
+    autograd.  ``specs`` are (name, tensor, expected shape, allowed dtypes)."""
+    anchor = None
+    for name, x, shape, dtypes in specs:
+        if tuple(x.shape) != tuple(shape):
+            raise ValueError(f"{name} must have shape {tuple(shape)}, not {tuple(x.shape)}")
+        if x.dtype not in dtypes:
+            raise ValueError(f"{name} must be of dtype {' or '.join(str(d) for d in dtypes)}, not {x.dtype}")
+    for name, x, _, _ in specs:
+        if x.device.type != "cuda":
+            raise ValueError(f"{name} must be a CUDA tensor")
+        anchor = anchor if anchor is not None else x.device
+        if x.device != anchor:
+            raise ValueError(f"{name} is on {x.device}, the other operands on {anchor}")
+        if not x.is_contiguous():
+            raise ValueError(f"{name} must be contiguous")
+        if x.data_ptr() % 16:
+            raise ValueError(f"{name} must be 16-byte aligned")
+        if x.requires_grad:
+            raise ValueError(f"{name} requires grad; these are forward-only operators")
+    return anchor
 
 
 def gdn_prepare_inputs(mixed, a, b, a_log, dt_bias, key_heads, value_heads):
     """mixed [N, (2Hk+Hv)*128] BF16, a,b [N,Hv] BF16, a_log, dt_bias [Hv] FP32 ->
     (q [N,Hk,128], k [N,Hk,128], v [N,Hv,128] BF16, g [N,Hv] FP32, beta [N,Hv] BF16)."""
     import torch
-    _bf16_cuda(a, "a", value_heads)
-    _bf16_cuda(b, "b", value_heads)
-    if mixed.dtype != torch.bfloat16 or mixed.device.type != "cuda" or mixed.ndim != 2 or mixed.stride(1) != 1:
-        raise ValueError("mixed must be a 2-D BF16 CUDA tensor with unit inner stride")
-    n, width = mixed.shape
-    if width != (2 * key_heads + value_heads) * 128 or value_heads % key_heads:
-        raise ValueError("mixed must hold [q heads | k heads | v heads] x 128 and Hv % Hk == 0")
-    if a_log.dtype != torch.float32 or dt_bias.dtype != torch.float32 or a_log.numel() != value_heads:
-        raise ValueError("a_log and dt_bias must be FP32 [Hv]")
+    bf16, fp32 = (torch.bfloat16,), (torch.float32,)
+    if type(key_heads) is not int or type(value_heads) is not int or key_heads < 1 or value_heads % key_heads:
+        raise ValueError("key_heads must be a positive integer that divides value_heads")
+    if mixed.ndim != 2 or mixed.shape[1] != (2 * key_heads + value_heads) * 128:
+        raise ValueError("mixed must be 2-D and hold [q heads | k heads | v heads] x 128 per row")
+    n = mixed.shape[0]
+    if mixed.dtype != torch.bfloat16 or mixed.stride(1) != 1 or mixed.stride(0) < mixed.shape[1] or mixed.stride(0) % 8:
+        raise ValueError("mixed must be BF16 with unit inner stride and a row stride that is a multiple of 8 elements")
+    _operands(("a", a, (n, value_heads), bf16), ("b", b, (n, value_heads), bf16),
+              ("a_log", a_log, (value_heads,), fp32), ("dt_bias", dt_bias, (value_heads,), fp32))
+    if mixed.device != a.device or mixed.data_ptr() % 16 or mixed.requires_grad:
+        raise ValueError("mixed must be on the operands' CUDA device, 16-byte aligned and without grad")
     lib = load_library()
     q = torch.empty(n, key_heads, 128, dtype=torch.bfloat16, device=mixed.device)
     k = torch.empty_like(q)
@@ -52,14 +72,16 @@ def gdn_decode_step(q, k, v, g, beta, state):
     """q,k [B,Hk,128], v [B,Hv,128] BF16, g [B,Hv] (BF16/FP32 natural-log decay), beta [B,Hv] BF16,
     state FP32 [B,Hv,128,128] updated IN PLACE.  Returns the BF16 output [B,Hv,128]."""
     import torch
-    for name, x in (("q", q), ("k", k), ("v", v), ("beta", beta)):
-        _bf16_cuda(x, name)
+    bf16, fp32 = (torch.bfloat16,), (torch.float32,)
+    if q.ndim != 3 or v.ndim != 3:
+        raise ValueError("q,k must be [B,Hk,128] and v [B,Hv,128]")
     b_, hk = q.shape[0], q.shape[1]
     hv = v.shape[1]
-    if tuple(state.shape) != (b_, hv, 128, 128) or state.dtype != torch.float32 or not state.is_contiguous():
-        raise ValueError("state must be contiguous FP32 [B,Hv,128,128] in K-by-V order")
-    if g.dtype not in (torch.bfloat16, torch.float32) or tuple(g.shape) != (b_, hv) or hv % hk:
-        raise ValueError("g must be BF16/FP32 [B,Hv] and Hv % Hk == 0")
+    if min(b_, hk, hv) < 1 or hv % hk:
+        raise ValueError("sizes must be positive and Hv % Hk == 0")
+    _operands(("q", q, (b_, hk, 128), bf16), ("k", k, (b_, hk, 128), bf16), ("v", v, (b_, hv, 128), bf16),
+              ("g", g, (b_, hv), (torch.bfloat16, torch.float32)), ("beta", beta, (b_, hv), bf16),
+              ("state", state, (b_, hv, 128, 128), fp32))
     lib = load_library()
     out = torch.empty_like(v)
     with torch.cuda.device(q.device):
@@ -82,18 +104,13 @@ def gdn_forward_projections(mixed, a, b, a_log, dt_bias, key_heads, value_heads,
     hk, hv = key_heads, value_heads
     if mixed.ndim != 3 or mixed.shape[2] != (2 * hk + hv) * 128 or hv % hk:
         raise ValueError("mixed must be [B,T,(2Hk+Hv)*128] with Hv % Hk == 0")
-    _bf16_cuda(mixed, "mixed")
-    _bf16_cuda(a, "a")
-    _bf16_cuda(b, "b")
     bsz, t = mixed.shape[0], mixed.shape[1]
-    if tuple(a.shape) != (bsz, t, hv) or tuple(b.shape) != (bsz, t, hv):
-        raise ValueError("a and b must be [B,T,Hv]")
-    for name, x in (("a_log", a_log), ("dt_bias", dt_bias)):
-        if x.dtype != torch.float32 or x.numel() != hv or x.device != mixed.device or not x.is_contiguous():
-            raise ValueError(f"{name} must be contiguous FP32 [Hv] on the inputs' device")
-    if initial_state is not None and (tuple(initial_state.shape) != (bsz, hv, 128, 128) or
-                                      initial_state.dtype != torch.float32 or not initial_state.is_contiguous()):
-        raise ValueError("initial_state must be contiguous FP32 [B,Hv,128,128]")
+    bf16, fp32 = (torch.bfloat16,), (torch.float32,)
+    specs = [("mixed", mixed, mixed.shape, bf16), ("a", a, (bsz, t, hv), bf16), ("b", b, (bsz, t, hv), bf16),
+             ("a_log", a_log, (hv,), fp32), ("dt_bias", dt_bias, (hv,), fp32)]
+    if initial_state is not None:
+        specs.append(("initial_state", initial_state, (bsz, hv, 128, 128), fp32))
+    _operands(*specs)
     owner = load_sm100()
     owner.library.configure(mixed.device)
     lib = owner.library.lib
@@ -114,16 +131,26 @@ def gdn_forward_projections(mixed, a, b, a_log, dt_bias, key_heads, value_heads,
     return out, final
 
 
-def _check_step_inputs(k, v, g, beta, state, width_axis):
+def _check_step_inputs(q, k, v, g, beta, state, delta=None, counts=None):
+    """Operands of the verify / commit pair; ``q``, ``v``, ``beta`` (verify) and ``delta``, ``counts`` (commit) are
+    checked when given."""
     import torch
+    bf16, fp32 = (torch.bfloat16,), (torch.float32,)
+    if k.ndim != 4 or g.ndim != 3:
+        raise ValueError("k must be [B,W,Hk,128] and g [B,W,Hv]")
     b_, w, hk = k.shape[0], k.shape[1], k.shape[2]
-    hv = v.shape[2] if v is not None else g.shape[2]
-    if tuple(state.shape) != (b_, hv, 128, 128) or state.dtype != torch.float32 or not state.is_contiguous():
-        raise ValueError("state must be contiguous FP32 [B,Hv,128,128] in K-by-V order")
-    if g.dtype not in (torch.bfloat16, torch.float32) or tuple(g.shape) != (b_, w, hv) or hv % hk or not g.is_contiguous():
-        raise ValueError("g must be contiguous BF16/FP32 [B,W,Hv] and Hv % Hk == 0")
+    hv = g.shape[2]
+    if min(b_, hk, hv) < 1 or hv % hk:
+        raise ValueError("sizes must be positive and Hv % Hk == 0")
     if not 1 <= w <= 64:
         raise ValueError("the step width must be 1..64 tokens")
+    specs = [("k", k, (b_, w, hk, 128), bf16), ("g", g, (b_, w, hv), (torch.bfloat16, torch.float32)),
+             ("state", state, (b_, hv, 128, 128), fp32)]
+    if q is not None:
+        specs += [("q", q, (b_, w, hk, 128), bf16), ("v", v, (b_, w, hv, 128), bf16), ("beta", beta, (b_, w, hv), bf16)]
+    if delta is not None:
+        specs += [("delta", delta, (b_, w, hv, 128), fp32), ("counts", counts, (b_,), (torch.int32,))]
+    _operands(*specs)
     return b_, w, hk, hv
 
 
@@ -133,9 +160,7 @@ def gdn_verify_step(q, k, v, g, beta, state):
     applies the accepted prefix (the reference's verify/commit pair, csrc/serving/gdn.cu:152-217,255-300,
     without its slot pool)."""
     import torch
-    for name, x in (("q", q), ("k", k), ("v", v), ("beta", beta)):
-        _bf16_cuda(x, name)
-    b_, w, hk, hv = _check_step_inputs(k, v, g, beta, state, 1)
+    b_, w, hk, hv = _check_step_inputs(q, k, v, g, beta, state)
     lib = load_library()
     out = torch.empty_like(v)
     delta = torch.empty(v.shape, dtype=torch.float32, device=v.device)
@@ -151,12 +176,7 @@ def gdn_commit_step(k, g, delta, counts, state):
     """Apply the first ``counts[b]`` (int32 device tensor [B], 0..W) recorded updates of a verify step to ``state``
     in place: S <- e^{g_t} S + k_t delta_t^T."""
     import torch
-    _bf16_cuda(k, "k")
-    b_, w, hk, hv = _check_step_inputs(k, None, g, None, state, 1)
-    if tuple(delta.shape) != (b_, w, hv, 128) or delta.dtype != torch.float32 or not delta.is_contiguous():
-        raise ValueError("delta must be contiguous FP32 [B,W,Hv,128]")
-    if counts.dtype != torch.int32 or tuple(counts.shape) != (b_,) or counts.device != state.device:
-        raise ValueError("counts must be an int32 device tensor [B]")
+    b_, w, hk, hv = _check_step_inputs(None, k, None, g, None, state, delta, counts)
     lib = load_library()
     with torch.cuda.device(k.device):
         lib.check(lib.lib.actlize_la_sm100_commit_step(
@@ -168,11 +188,10 @@ def gdn_commit_step(k, g, delta, counts, state):
 def rmsnorm_gated(y, z, weight):
     """y, z [..., 128] BF16, weight [128] BF16 -> BF16 tensor shaped like y."""
     import torch
-    _bf16_cuda(y, "y", 128)
-    _bf16_cuda(z, "z", 128)
-    _bf16_cuda(weight, "weight", 128)
-    if y.shape != z.shape or weight.numel() != 128:
-        raise ValueError("y and z must have the same shape and weight 128 entries")
+    if y.ndim < 1 or y.shape[-1] != 128:
+        raise ValueError("y must have a last dimension of 128")
+    bf16 = (torch.bfloat16,)
+    _operands(("y", y, y.shape, bf16), ("z", z, y.shape, bf16), ("weight", weight, (128,), bf16))
     lib = load_library()
     out = torch.empty_like(y)
     with torch.cuda.device(y.device):

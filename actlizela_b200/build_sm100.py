@@ -41,11 +41,12 @@ def render_policy_table(policy_path, out_path):
     data = json.loads(Path(policy_path).read_text())
     ids = data["configuration_ids"]
     rows = ",\n".join(
-        "  {%d, %d, %d, %d, %d, %d}" % (*row["shape"], ids[row["configuration"]], int(row.get("segments", 1)))
+        "  {%d, %d, %d, %d, %d, %d, %d}" % (*row["shape"], ids[row["configuration"]], int(row.get("segments", 1)),
+                                             int(row.get("parallel", 1)))
         for row in data["rows"])
     out_path.write_text(
         "// generated from sm100_policy.json (%s); do not edit\n"
-        "struct PolicyRow { int b, t, hk, hv, config, segments; };\n"
+        "struct PolicyRow { int b, t, hk, hv, config, segments, parallel; };\n"
         "constexpr int kPolicyDefault = %d;\n"
         "constexpr PolicyRow kPolicyRows[] = {\n%s\n};\n"
         % (data["id"], ids[data["default"]], rows))

@@ -31,14 +31,25 @@ bool geometry_ok(int b, int t, int hk, int hv) {
 // Bits 6 and 7 modify a walk-only call of the tcgen05 configuration (sequence-parallel scheme):
 // 0x40 = treat U as zero (state-transition pass), 0x80 = stop each (batch, value head) walk once the decay
 // accumulated since its start is below exp(-40) (no final state is written then).
+// Bits 16..19 hold the number of parallel sub-segments of the tcgen05 walk (0 or 1 = off, at most 8): every
+// (batch, value head) walk of a launch is cut into that many pieces walked by as many CTAs at the same time
+// (walk_umma_kernel); needs the tcgen05 prepare stage, which records the per-chunk contraction flag the split relies on.
 constexpr int kStageMask = 0x30, kPrepareOnly = 0x10, kWalkOnly = 0x20, kSegmentShift = 8, kMaxSegments = 16;
 constexpr int kWalkFlagMask = 0xc0, kHomogeneousBit = 0x40, kUntilDecayedBit = 0x80;
+constexpr int kParallelShift = 16, kMaxParallel = 8;
 bool config_ok(int config) {
-  const int segments = (config >> kSegmentShift) & 0xff;
-  if (config < 0 || (config & 0xf) > 4 || (config & ~(kStageMask | kWalkFlagMask | 0xf | (0xff << kSegmentShift))) != 0)
+  const int segments = (config >> kSegmentShift) & 0xff, parallel = (config >> kParallelShift) & 0xf;
+  if (config < 0 || (config & 0xf) > 4 ||
+      (config & ~(kStageMask | kWalkFlagMask | 0xf | (0xff << kSegmentShift) | (0xf << kParallelShift))) != 0)
     return false;
   if ((config & kWalkFlagMask) && ((config & 0xf) != 1 || (config & kStageMask) != kWalkOnly)) return false;
+  if (parallel > kMaxParallel || (parallel > 1 && ((config & 0xf) != 1 || (config & kWalkFlagMask)))) return false;
   return (config & kStageMask) != kStageMask && segments <= kMaxSegments;
+}
+// parallel sub-segments for a launch that walks `chunks` chunks per (batch, value head)
+int parallel_of(int config, int chunks) {
+  const int parallel = (config >> kParallelShift) & 0xf;
+  return parallel < 2 ? 1 : (parallel > chunks ? chunks : parallel);
 }
 int segments_of(int config, const Geometry& geo) {
   int segments = (config >> kSegmentShift) & 0xff;
@@ -133,10 +144,46 @@ extern "C" const char* actlize_la_sm100_numerical_contract(void) {
   return "wy-splitbf16-state-bf16-out-sm100-v1";
 }
 
+namespace gdn_sm100 {
+namespace {
+// Host-visible failure record, one page of this library's own static storage per device, pinned and mapped by
+// configure() (cudaHostRegister: nothing is allocated).  A kernel that gives up a bounded wait writes
+// (code, block, site, chunk) here as well as into its device word, so the host can notice without synchronising.
+constexpr int kMaxStatusDevices = 64;
+alignas(4096) int g_status_pages[kMaxStatusDevices][1024];
+bool g_status_mapped[kMaxStatusDevices] = {};
+
+int map_status_page() {
+  int device = -1;
+  cudaError_t e = cudaGetDevice(&device);
+  if (e != cudaSuccess) return int(e);
+  if (device < 0 || device >= kMaxStatusDevices) return int(cudaErrorInvalidDevice);
+  if (g_status_mapped[device]) return 0;
+  e = cudaHostRegister(g_status_pages[device], sizeof(g_status_pages[device]),
+                       cudaHostRegisterMapped | cudaHostRegisterPortable);
+  if (e != cudaSuccess) return int(e);
+  int* on_device = nullptr;
+  if ((e = cudaHostGetDevicePointer(reinterpret_cast<void**>(&on_device), g_status_pages[device], 0)) != cudaSuccess)
+    return int(e);
+  if (int rc = set_status_mirror_umma(on_device)) return rc;
+  if (int rc = set_status_mirror_chain(on_device)) return rc;
+  g_status_mapped[device] = true;
+  return 0;
+}
+volatile int* status_page_of_current_device() {
+  int device = -1;
+  if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= kMaxStatusDevices || !g_status_mapped[device])
+    return nullptr;
+  return g_status_pages[device];
+}
+}  // namespace
+}  // namespace gdn_sm100
+
 extern "C" int actlize_la_sm100_configure(void) {
   if (int rc = configure_simt()) return rc;
   if (int rc = configure_umma()) return rc;
   if (int rc = configure_chain()) return rc;
+  if (int rc = map_status_page()) return rc;
   return create_segment_streams();
 }
 
@@ -144,18 +191,24 @@ extern "C" int actlize_la_sm100_select(int b, int t, int hk, int hv, int gate_fp
   (void)gate_fp32;
   if (!geometry_ok(b, t, hk, hv)) return -1;
   for (const PolicyRow& row : kPolicyRows)
-    if (row.b == b && row.t == t && row.hk == hk && row.hv == hv) return row.config | (row.segments << kSegmentShift);
-  // no measured row: integer rule fitted to the measured ones (sm100_policy.py::default_segments is the same)
+    if (row.b == b && row.t == t && row.hk == hk && row.hv == hv)
+      return row.config | (row.segments << kSegmentShift) | (row.parallel << kParallelShift);
+  // no measured row: integer rules (sm100_policy.py::default_parallel / default_segments are the same).  Parallel
+  // sub-segments: as many as fill the 148 SMs with one walk CTA each, at least 8 chunks per sub-segment, at most 8.
+  // Sequence segments (prepare of a later segment next to the walk of an earlier one) only pay while the walk
+  // leaves SMs idle, i.e. when the walk is not split.
   const long long heads = (long long)b * hv, chunks = (t + kChunk - 1) / kChunk;
+  long long parallel = 148 / heads;
+  if (parallel > chunks / 8) parallel = chunks / 8;
+  if (parallel > kMaxParallel) parallel = kMaxParallel;
+  if (parallel < 1) parallel = 1;
   int segments = 1;
-  if (heads > 64) {
-    segments = 1;
-  } else {
+  if (heads <= 64 && parallel == 1) {
     int root = 0;
     while ((long long)(root + 1) * (root + 1) <= chunks / 8) ++root;
     segments = root < 1 ? 1 : (root > 8 ? 8 : root);
   }
-  return kPolicyDefault | (kPolicyDefault == 1 ? segments << kSegmentShift : 0);
+  return kPolicyDefault | (kPolicyDefault == 1 ? (segments << kSegmentShift) | (int(parallel) << kParallelShift) : 0);
 }
 
 extern "C" long long actlize_la_sm100_workspace_bytes(int b, int t, int hk, int hv, int config) {
@@ -177,7 +230,43 @@ extern "C" int actlize_la_sm100_selftest_wait_timeout(int tag, void* stream) {
 
 extern "C" int actlize_la_sm100_device_status(int* status4, int reset) {
   if (!status4) return int(cudaErrorInvalidValue);
-  return read_device_status(status4, reset);
+  volatile int* page = status_page_of_current_device();
+  if (!page) return read_device_status(status4, reset);        // configure() has not run on this device
+  cudaError_t e = cudaDeviceSynchronize();
+  if (e != cudaSuccess) return int(e);
+  for (int i = 0; i < 4; ++i) status4[i] = page[i];
+  if (reset) {
+    for (int i = 0; i < 4; ++i) page[i] = 0;
+    if (int rc = clear_device_status_umma()) return rc;
+    if (int rc = clear_device_status_chain()) return rc;
+  }
+  return 0;
+}
+
+extern "C" int actlize_la_sm100_last_failure(int* status4) {
+  if (!status4) return int(cudaErrorInvalidValue);
+  volatile int* page = status_page_of_current_device();
+  for (int i = 0; i < 4; ++i) status4[i] = page ? page[i] : 0;
+  return 0;
+}
+
+extern "C" int actlize_la_sm100_selftest_walk_stall(
+    const void* q, const void* k, const void* v, const void* g, const void* beta, void* output,
+    void* workspace, long long workspace_bytes_given, int b, int t, int hk, int hv, int gate_fp32, void* stream) {
+  if (!q || !k || !v || !g || !beta || !output || !workspace) return int(cudaErrorInvalidValue);
+  if (!geometry_ok(b, t, hk, hv) || t <= kChunk) return int(cudaErrorInvalidValue);     // at least two chunks
+  const Geometry geo{b, t, hk, hv};
+  if (workspace_bytes_given < workspace_bytes(geo) || (reinterpret_cast<uintptr_t>(workspace) & 255))
+    return int(cudaErrorInvalidValue);
+  const Inputs in{static_cast<const __nv_bfloat16*>(q), static_cast<const __nv_bfloat16*>(k),
+                  static_cast<const __nv_bfloat16*>(v), g, static_cast<const __nv_bfloat16*>(beta),
+                  nullptr, static_cast<__nv_bfloat16*>(output), nullptr, gate_fp32 ? 1 : 0};
+  return launch_walk_stall_selftest(in, geo, carve_workspace(workspace, geo), static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int actlize_la_sm100_walk_plan_counts(int* counts2, int reset) {
+  if (!counts2) return int(cudaErrorInvalidValue);
+  return read_walk_plan_counts(counts2, reset);
 }
 
 namespace {
@@ -226,6 +315,7 @@ int run_forward(const Inputs& in, Geometry geo, const Workspace& ws, int config,
     for (int i = 0; i < segments; ++i) {
       geo.chunk_begin = int((long long)chunks * i / segments);
       geo.chunk_count = int((long long)chunks * (i + 1) / segments) - geo.chunk_begin;
+      geo.parallel = parallel_of(config, geo.chunk_count);
       if (i == 0) {
         if (int rc = launch_prepare_tc(config, in, geo, ws, stream)) return rc;
         if ((e = cudaEventRecord(ss.start, stream)) != cudaSuccess) return int(e);
@@ -243,6 +333,7 @@ int run_forward(const Inputs& in, Geometry geo, const Workspace& ws, int config,
     if ((e = cudaEventRecord(ss.done, ss.walk)) != cudaSuccess) return int(e);
     return int(cudaStreamWaitEvent(stream, ss.done, 0));
   }
+  geo.parallel = parallel_of(config, geo.segment_chunks());
   if (!(config & kWalkOnly)) {
     if (int rc = in.mixed                  ? launch_prepare_fused(in, geo, ws, stream)
                  : is_chain(config)        ? launch_prepare_chain(in, geo, ws, stream)
@@ -442,6 +533,7 @@ extern "C" int actlize_la_sm100_forward_host(
       for (int i = 0; i < segments; ++i) {
         geo.chunk_begin = tapered_begin(chunks, i, segments);
         geo.chunk_count = tapered_begin(chunks, i + 1, segments) - geo.chunk_begin;
+        geo.parallel = parallel_of(config, geo.chunk_count);
         const long long t0 = (long long)geo.chunk_begin * kChunk;
         const long long rows = ((long long)(geo.chunk_begin + geo.chunk_count) * kChunk < t ?
                                 (long long)(geo.chunk_begin + geo.chunk_count) * kChunk : t) - t0;

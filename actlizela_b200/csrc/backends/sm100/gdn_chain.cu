@@ -520,6 +520,8 @@ walk_chain_kernel(const __grid_constant__ CUtensorMap tm_wh, const __grid_consta
 
 }  // namespace
 
+GDN_SM100_DEFINE_STATUS_HOOKS(chain)
+
 int configure_chain() {
   if (int rc = tensor_map_encoder().init()) return rc;
   return int(cudaFuncSetAttribute(walk_chain_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kChainSmem));

@@ -19,6 +19,9 @@ struct Geometry {
   int batch, sequence, key_heads, value_heads;
   // A launch may cover a contiguous range of chunks only (sequence segment); 0 chunks = the whole sequence.
   int chunk_begin = 0, chunk_count = 0;
+  // tcgen05 walk only: the launch's chunk range is cut into `parallel` sub-segments per (batch, value head), walked by
+  // as many CTAs at the same time (0 or 1 = one CTA walks the whole range); see walk_umma_kernel.
+  int parallel = 0;
   // Packed variable-length mode (tcgen05 kernels only): the tensors are [1, sequence = total tokens, H, ...],
   // `batch` is the number of sequences and `varlen` points at 2 (batch + 1) device integers: the token offsets
   // cu_seqlens[0..batch] followed by the chunk offsets chunk_prefix[0..batch] (every sequence starts a new chunk);
@@ -53,7 +56,8 @@ __device__ __forceinline__ int varlen_sequence_of(const int* chunk_prefix, int c
 //   qs          BF16 [64][128]  Q * exp(prefix) / sqrt(128)                       (token, key dim)
 //   p           BF16 [64][64]   tril(Q K^T * exp(prefix_i - prefix_j)) / sqrt(128)
 //   gates       FP32 [128]      [0,64): exp(prefix_last - prefix_i), 0 for padding rows;
-//                               [64]: exp(prefix_last); rest unused
+//                               [64]: exp(prefix_last); [65] (tcgen05 prepare only): non-zero when some token of the
+//                               chunk is not a contraction of the state (beta < 0 or beta |k|^2 > 2); rest unused
 //   g_hi, g_lo  BF16 [64][64]   only written by the chained configuration: G = W K_prev^T (token of this chunk,
 //                               token of the previous chunk), split G ~= hi + lo; in that configuration w_hi/w_lo
 //                               hold W scaled by the previous chunk's total decay (1 for the first chunk of a launch)
@@ -128,6 +132,7 @@ struct Inputs {
   __nv_bfloat16* k_norm = nullptr;
 };
 constexpr int kWalkHomogeneous = 1, kWalkUntilDecayed = 2;
+constexpr int kWalkSelftestStall = 4;     // the TMA producer stops after the first chunk (failure-detection self-test)
 constexpr float kDecayedLog2 = -40.f * 1.4426950408889634f;
 
 __device__ __forceinline__ float load_gate(const void* g, long long index, int gate_fp32) {
@@ -175,6 +180,13 @@ int launch_prepare_chain(const Inputs&, const Geometry&, const Workspace&, cudaS
 int launch_walk_chain(const Inputs&, const Geometry&, const Workspace&, cudaStream_t);
 int configure_chain();
 int read_device_status(int* host_out4, int reset);
+int read_walk_plan_counts(int* host_out2, int reset);
 int launch_wait_timeout_selftest(int tag, cudaStream_t);
+int launch_walk_stall_selftest(const Inputs&, const Geometry&, const Workspace&, cudaStream_t);
+// host-visible failure record and poll limit, per translation unit that holds tensor-core kernels
+int set_status_mirror_umma(int* device_pointer);
+int set_status_mirror_chain(int* device_pointer);
+int clear_device_status_umma();
+int clear_device_status_chain();
 
 }  // namespace gdn_sm100

@@ -76,6 +76,10 @@ TensorMapEncoder& tensor_map_encoder() {
 
 namespace {
 
+// Heads (batch x value head, summed over launches) that a parallel walk really split [0] / walked with one CTA
+// because a sub-segment does not decay or a token is not a contraction [1]; read by read_walk_plan_counts.
+__device__ int g_walk_plan_counts[2];
+
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr int kBox = 8192;            // one TMA box: 64 rows x 128 bytes
 constexpr uint32_t kIdescN64 = idesc_bf16(128, 64, false, false);      // A K-major (smem or TMEM), B K-major
@@ -325,6 +329,7 @@ prepare_umma_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
   const int quarter = warp & 3, chalf = warp >> 2;
   const int lrow = quarter * 32 + (tid & 31);          // accumulator row owned by this thread
   const uint32_t taddr = tmem + (uint32_t(quarter * 32) << 16);
+  bool not_contraction = false;
   if (ok) {
     const int i = lrow & 63, j0 = chalf * 32;
     const float pi = s_pl2[i];
@@ -353,6 +358,7 @@ prepare_umma_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
     } else {
       const float bi = s_beta[i];
       float* arow = sA + i * L::kLd + j0;
+      float kk = 0.f;                                    // k_i . k_i when the diagonal lies in this column half
 #pragma unroll
       for (int q4 = 0; q4 < 8; ++q4) {
         float a[4];
@@ -360,9 +366,12 @@ prepare_umma_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
         for (int e = 0; e < 4; ++e) {
           const int jj = q4 * 4 + e;
           a[e] = (j0 + jj < i) ? bi * __uint_as_float(d[jj]) * fast_exp2(pi - pj[jj]) : 0.f;
+          if (j0 + jj == i) kk = __uint_as_float(d[jj]);
         }
         *reinterpret_cast<float4*>(arow + q4 * 4) = make_float4(a[0], a[1], a[2], a[3]);
       }
+      // token i multiplies the state by exp(g_i) (I - beta_i k_i k_i^T): a contraction iff 0 <= beta_i |k_i|^2 <= 2
+      not_contraction = !(bi >= 0.f && bi * kk <= 2.f);
     }
     {
       // scaled query: row = tid/4, a quarter row (4 x 16 bytes of one TMA box row) per thread
@@ -387,7 +396,7 @@ prepare_umma_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
     for (int e = tid; e < 64 * L::kLd / 4; e += kPrepThreads)
       reinterpret_cast<float4*>(sT)[e] = make_float4(0.f, 0.f, 0.f, 0.f);
   }
-  __syncthreads();
+  const int chunk_not_contraction = __syncthreads_or(not_contraction);
   GDN_PSTAMP(3);
 
   // ---- phase 4: T = (I+A)^-1, blocked 16 -> 32 -> 64, all in FP32 on the CUDA cores
@@ -623,6 +632,7 @@ prepare_umma_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
     const float last = s_pl2[valid - 1];
     if (tid < kChunk) ws.gates[block * 128 + tid] = (tid < valid) ? fast_exp2(last - s_pl2[tid]) : 0.f;
     if (tid == kChunk) ws.gates[block * 128 + kChunk] = fast_exp2(last);
+    if (tid == kChunk + 1) ws.gates[block * 128 + kChunk + 1] = chunk_not_contraction ? 1.f : 0.f;
   }
   __syncthreads();
   if (kChained) {
@@ -752,6 +762,45 @@ constexpr uint32_t kIdescN128 = idesc_bf16(128, 128, false, false);
 #define GDN_OSTAMP(slot)
 #endif
 
+// First chunk boundary of a sub-segment at which the decay accumulated since the sub-segment's start is below
+// exp(-40): returns the number of leading chunks an incoming state still reaches (1..count), or -1 when the decay
+// never gets that far inside the sub-segment.  `not_contraction` collects word 65 of every chunk's gate vector.
+// Warp-collective; every caller with the same (first block, count) gets the same answer: two CTAs rely on that.
+__device__ __forceinline__ int decay_reach(const float* gates, long long first_block, int count, int lane,
+                                           bool& not_contraction) {
+  float total = 0.f;
+  int reach = -1;
+  bool flagged = false;
+  for (int c0 = 0; c0 < count; c0 += 32) {
+    const int c = c0 + lane;
+    float x = 0.f;
+    if (c < count) {
+      const float2 w = *reinterpret_cast<const float2*>(gates + (first_block + c) * 128 + kChunk);
+      x = log2f(w.x);
+      flagged |= w.y != 0.f;
+    }
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+      const float y = __shfl_up_sync(0xffffffffu, x, d);
+      if (lane >= d) x += y;
+    }
+    const unsigned below = __ballot_sync(0xffffffffu, c < count && total + x < kDecayedLog2);
+    if (below && reach < 0) reach = c0 + __ffs(below);
+    total += __shfl_sync(0xffffffffu, x, 31);
+  }
+  not_contraction |= __any_sync(0xffffffffu, flagged);
+  return reach;
+}
+
+// Parallel sub-segments (Geometry::parallel = P > 1): the launch's chunk range of every (batch, value head) is cut
+// into P sub-segments and the grid holds P CTAs per head.  CTA r walks sub-segment r from a ZERO state (r = 0 from
+// the true incoming state) and then carries on into the leading chunks of sub-segment r + 1, those that its state
+// still reaches with a weight above exp(-40), writing their output rows; CTA r + 1 computes the same number from the
+// same gate words and does not store those rows.  This is exact to exp(-40) of the state when every sub-segment
+// behind the first decays below exp(-40) within its own length and every token transition exp(g)(I - beta k k^T) is
+// a contraction (0 <= beta |k|^2 <= 2; the prepare kernel records violations).  A head for which that does not hold
+// is walked by its first CTA alone over the whole range, as without the split; its other CTAs leave at once.
+// The last sub-segment's CTA (or the single CTA) writes the outgoing state.
 __global__ void __launch_bounds__(kWalkThreads, 1)
 walk_umma_kernel(const __grid_constant__ CUtensorMap tm_wh, const __grid_constant__ CUtensorMap tm_wl,
                  const __grid_constant__ CUtensorMap tm_qs, const __grid_constant__ CUtensorMap tm_k,
@@ -774,11 +823,12 @@ walk_umma_kernel(const __grid_constant__ CUtensorMap tm_wh, const __grid_constan
   uint64_t* bar_stfree = bar_ops + 9;          // an older output store has finished reading its staging tile
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_ops + 12);
   volatile int* abort_word = reinterpret_cast<volatile int*>(tmem_slot + 1);
-  int* limit_slot = reinterpret_cast<int*>(tmem_slot + 2);
-  const AbortFlag abort{abort_word};
+  int* limit_slot = reinterpret_cast<int*>(tmem_slot + 2);      // [4]: chunks to walk, first chunk, unstored leading
+  const AbortFlag abort{abort_word};                            //      chunks, this CTA writes the outgoing state
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int bh = blockIdx.x;
+  const int parallel = geo.parallel > 1 ? geo.parallel : 1;
+  const int bh = blockIdx.x / parallel, sub = blockIdx.x % parallel;
   int b = bh / geo.value_heads;
   const int hv = bh % geo.value_heads;
   const int hk = hv / geo.group();
@@ -797,6 +847,7 @@ walk_umma_kernel(const __grid_constant__ CUtensorMap tm_wh, const __grid_constan
   }
   const float* state_in = geo.first_segment() ? in.initial : ws.carry;
   float* state_out = geo.last_segment() ? in.final_state : ws.carry;
+  if (sub > 0) state_in = nullptr;
 #ifdef GDN_SM100_PHASE_TIMING
   const long long t_begin = clock64();
 #endif
@@ -843,11 +894,40 @@ walk_umma_kernel(const __grid_constant__ CUtensorMap tm_wh, const __grid_constan
     }
     if (lane == 0) *limit_slot = stop;
   }
+  if (parallel > 1 && warp == kTmaWarp) {
+    // plan of this CTA (see the comment above the kernel); sub-segment r covers chunks [n r / P, n (r + 1) / P)
+    const int n = chunks;
+    bool serial = false;
+    int reach_mine = 0, reach_next = 0;
+    for (int r = 1; r < parallel; ++r) {
+      const int r0 = int((long long)n * r / parallel), r1 = int((long long)n * (r + 1) / parallel);
+      const int reach = decay_reach(ws.gates, block0 + r0, r1 - r0, lane, serial);
+      serial |= reach < 0;
+      if (r == sub) reach_mine = reach;
+      if (r == sub + 1) reach_next = reach;
+    }
+    if (lane == 0) {
+      if (sub == 0) atomicAdd(&g_walk_plan_counts[serial ? 1 : 0], 1);
+      const int c0 = int((long long)n * sub / parallel), c1 = int((long long)n * (sub + 1) / parallel);
+      limit_slot[0] = serial ? (sub == 0 ? n : 0) : c1 - c0 + (sub + 1 < parallel ? reach_next : 0);
+      limit_slot[1] = serial ? 0 : c0;
+      limit_slot[2] = (serial || sub == 0) ? 0 : reach_mine;
+      limit_slot[3] = serial ? sub == 0 : sub == parallel - 1;
+    }
+  }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = *tmem_slot;
   if (in.walk_flags & kWalkUntilDecayed) chunks = *limit_slot;
+  int unstored = 0;                          // leading chunks whose output rows the previous sub-segment's CTA writes
+  if (parallel > 1) {
+    chunks = limit_slot[0];
+    t_first += limit_slot[1] * kChunk;
+    block0 += limit_slot[1];
+    unstored = limit_slot[2];
+    if (!limit_slot[3]) state_out = nullptr;
+  }
 
   if (warp >= kChainWarp0 && warp < kChainWarp0 + kChainWarps) {
     // ------------------------------------------------------------------ state chain
@@ -992,6 +1072,8 @@ walk_umma_kernel(const __grid_constant__ CUtensorMap tm_wh, const __grid_constan
       __syncwarp();
       if (lane == 0) mbar_arrive(bar_ofree + (c & 1));
       GDN_OSTAMP(1);
+      if (c < unstored) continue;
+      const int cs = c - unstored;           // count of stored tiles: staging buffers and their barriers follow it
       if (geo.varlen && c == chunks - 1 && tail_valid < kChunk) {
         // packed mode, ragged end of a sequence: the rows behind it belong to the next sequence, so the tile
         // cannot leave through a clipping TMA store; this is the sequence's last chunk, nothing follows it
@@ -1004,10 +1086,10 @@ walk_umma_kernel(const __grid_constant__ CUtensorMap tm_wh, const __grid_constan
       }
       // stage the tile as two 128-byte-swizzled boxes [token][64 values] and hand it to a TMA store,
       // which also clips the rows of a tail chunk at the sequence end
-      uint8_t* stage = sm + L::kOut + (c & 1) * 2 * kBox + (v >> 6) * kBox + ((v & 7) << 1);
+      uint8_t* stage = sm + L::kOut + (cs & 1) * 2 * kBox + (v >> 6) * kBox + ((v & 7) << 1);
       const int chunk16 = (v & 63) >> 3;
       // the store that used this buffer two chunks ago has been read out (signalled one chunk ago)
-      if (c > 0) ok = mbar_wait(bar_stfree, (c - 1) & 1, abort, 21, c);
+      if (cs > 0) ok = mbar_wait(bar_stfree, (cs - 1) & 1, abort, 21, c);
       if (!ok) break;
 #pragma unroll
       for (int i = 0; i < 64; ++i)
@@ -1017,9 +1099,9 @@ walk_umma_kernel(const __grid_constant__ CUtensorMap tm_wh, const __grid_constan
       __syncwarp();
       if (lane == 0) mbar_arrive(bar_staged);
       if (tid == kOutWarp0 * 32) {
-        ok = mbar_wait(bar_staged, c & 1, abort, 22, c);
+        ok = mbar_wait(bar_staged, cs & 1, abort, 22, c);
         if (!ok) break;
-        const uint8_t* tile = sm + L::kOut + (c & 1) * 2 * kBox;
+        const uint8_t* tile = sm + L::kOut + (cs & 1) * 2 * kBox;
         tma_store_4d(&tm_out, tile, 0, hv, t_first + c * kChunk, b);
         tma_store_4d(&tm_out, tile + kBox, 64, hv, t_first + c * kChunk, b);
         tma_store_commit();
@@ -1038,6 +1120,7 @@ walk_umma_kernel(const __grid_constant__ CUtensorMap tm_wh, const __grid_constan
       prefetch_tensormap(&tm_k);
       prefetch_tensormap(&tm_p);
       for (int c = 0; c < chunks; ++c) {
+        if ((in.walk_flags & kWalkSelftestStall) && c > 0) break;       // failure-detection self-test only
         const int s = c % L::kStages;
         if (c >= L::kStages && !mbar_wait(empty + s, ((c / L::kStages) - 1) & 1, abort, 30, c)) break;
         uint8_t* st = sm + s * L::kStage;
@@ -1212,15 +1295,19 @@ int launch_walk_umma(const Inputs& in, const Geometry& geo, const Workspace& ws,
   if (int rc = enc.bf16_2d(&tm_qs, ws.qs, kDim, rows, kChunk)) return rc;
   if (int rc = enc.bf16_4d(&tm_k, in.k, kDim, geo.key_heads, geo.sequence, geo.varlen ? 1 : geo.batch, kChunk)) return rc;
   if (int rc = enc.bf16_2d(&tm_p, ws.p, kChunk, rows, kChunk)) return rc;
-  walk_umma_kernel<<<geo.batch * geo.value_heads, kWalkThreads, kWalkSmem, stream>>>(tm_wh, tm_wl, tm_qs, tm_k,
-                                                                                    tm_p, tm_out, in, geo, ws);
+  const int parallel = geo.parallel > 1 ? geo.parallel : 1;
+  if (parallel > 1 && (geo.varlen || in.walk_flags || parallel > geo.segment_chunks())) return int(cudaErrorInvalidValue);
+  if ((in.walk_flags & kWalkSelftestStall) && (in.walk_flags != kWalkSelftestStall || geo.varlen)) return int(cudaErrorInvalidValue);
+  walk_umma_kernel<<<geo.batch * geo.value_heads * parallel, kWalkThreads, kWalkSmem, stream>>>(
+      tm_wh, tm_wl, tm_qs, tm_k, tm_p, tm_out, in, geo, ws);
   return int(cudaGetLastError());
 }
 
 namespace {
-// One CTA waits, with a small poll limit, on an mbarrier that nothing ever completes.  The wait must
-// give up, record (code 1, block 0, site 99, chunk `tag`) in the status word and let the kernel end.
-__global__ void wait_timeout_selftest_kernel(int tag, uint32_t polls) {
+// One warp waits, through the bounded wait every kernel of this file uses, on an mbarrier that nothing ever
+// completes.  The wait must give up, record (code 1, block 0, site 99, chunk `tag`) in the status word and let
+// the kernel end.
+__global__ void wait_timeout_selftest_kernel(int tag) {
   __shared__ uint64_t bar;
   __shared__ int abort_word;
   if (threadIdx.x == 0) {
@@ -1230,16 +1317,48 @@ __global__ void wait_timeout_selftest_kernel(int tag, uint32_t polls) {
   }
   __syncthreads();
   const AbortFlag abort{&abort_word};
-  bool completed = false;
-  for (uint32_t spin = 0; spin < polls && !completed; ++spin) completed = mbar_try_wait(&bar, 0);
-  if (!completed && threadIdx.x == 0) abort.raise(1, 99, tag);
+  if (threadIdx.x == 0) mbar_wait(&bar, 0, abort, 99, tag);
   __syncthreads();
+}
+constexpr unsigned int kSelftestPolls = 1u << 12, kProductionPolls = 1u << 20;
+// the poll limit travels on the stream, in front of and behind the self-test launch (pageable source: staged
+// before the call returns)
+int set_spin_limit_on(cudaStream_t stream, unsigned int polls) {
+  return int(cudaMemcpyToSymbolAsync(g_spin_limit, &polls, sizeof(polls), 0, cudaMemcpyHostToDevice, stream));
 }
 }  // namespace
 
+GDN_SM100_DEFINE_STATUS_HOOKS(umma)
+
 int launch_wait_timeout_selftest(int tag, cudaStream_t stream) {
-  wait_timeout_selftest_kernel<<<1, 32, 0, stream>>>(tag, 1u << 12);
-  return int(cudaGetLastError());
+  if (int rc = set_spin_limit_on(stream, kSelftestPolls)) return rc;
+  wait_timeout_selftest_kernel<<<1, 32, 0, stream>>>(tag);
+  const int launched = int(cudaGetLastError());
+  const int restored = set_spin_limit_on(stream, kProductionPolls);
+  return launched ? launched : restored;
+}
+
+// The chunk walk with a producer that stops feeding it after the first chunk: every role of the real kernel runs
+// out of its bounded wait (or sees the CTA-wide flag), the CTA drains, frees its tensor memory and returns.
+int launch_walk_stall_selftest(const Inputs& in, const Geometry& geo, const Workspace& ws, cudaStream_t stream) {
+  if (int rc = set_spin_limit_on(stream, kSelftestPolls)) return rc;
+  Inputs stalled = in;
+  stalled.walk_flags = kWalkSelftestStall;
+  Geometry one = geo;
+  one.parallel = 0;
+  const int launched = launch_walk_umma(stalled, one, ws, stream);
+  const int restored = set_spin_limit_on(stream, kProductionPolls);
+  return launched ? launched : restored;
+}
+
+int read_walk_plan_counts(int* host_out2, int reset) {
+  cudaError_t e = cudaMemcpyFromSymbol(host_out2, g_walk_plan_counts, 2 * sizeof(int));
+  if (e != cudaSuccess) return int(e);
+  if (reset) {
+    const int zero[2] = {0, 0};
+    e = cudaMemcpyToSymbol(g_walk_plan_counts, zero, sizeof(zero));
+  }
+  return int(e);
 }
 
 int read_device_status(int* host_out4, int reset) {

@@ -16,10 +16,14 @@ namespace gdn_sm100 {
 // Status word of the translation unit that includes this header (the tensor-core kernels live in
 // one translation unit): [0] first failure code (0 = none), [1] block index, [2] wait site, [3] chunk.
 static __device__ int g_device_status[4];
+// Host-visible copy of the same record (pinned, mapped host memory; null until configure() has set it): written
+// once by the CTA that records a failure, so the host can notice a launch that gave up without synchronising.
+static __device__ int* g_status_mirror;
+// Poll limit of every bounded wait; the failure-detection self-test lowers it for one launch.
+static __device__ unsigned int g_spin_limit = 1u << 20;
 
 namespace ptx {
 
-constexpr uint32_t kSpinLimit = 1u << 20;
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
@@ -60,6 +64,14 @@ struct AbortFlag {
       g_device_status[1] = blockIdx.x;
       g_device_status[2] = site;
       g_device_status[3] = chunk;
+      volatile int* mirror = g_status_mirror;
+      if (mirror) {
+        mirror[1] = blockIdx.x;
+        mirror[2] = site;
+        mirror[3] = chunk;
+        __threadfence_system();
+        mirror[0] = code;
+      }
     }
   }
 };
@@ -72,7 +84,8 @@ struct AbortFlag {
 static __device__ __noinline__ bool mbar_wait_poll(uint32_t bar_addr, uint32_t parity, volatile int* flag, int site,
                                             int chunk) {
   const AbortFlag abort{flag};
-  for (uint32_t spin = 0; spin < kSpinLimit; ++spin) {
+  const uint32_t limit = g_spin_limit;
+  for (uint32_t spin = 0; spin < limit; ++spin) {
     uint32_t done;
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
@@ -276,5 +289,19 @@ struct TensorMapEncoder {
   int f32_2d(CUtensorMap* map, const void* base, uint64_t cols, uint64_t rows, uint32_t box_rows) const;
 };
 TensorMapEncoder& tensor_map_encoder();
+
+// Per translation unit (the status words above are file-local): point the kernels at the host-visible record,
+// clear the device record, set the poll limit.  Each returns a cudaError_t value.
+#define GDN_SM100_DEFINE_STATUS_HOOKS(suffix)                                                        \
+  int set_status_mirror_##suffix(int* device_pointer) {                                              \
+    return int(cudaMemcpyToSymbol(g_status_mirror, &device_pointer, sizeof(device_pointer)));        \
+  }                                                                                                  \
+  int clear_device_status_##suffix() {                                                               \
+    const int zero[4] = {0, 0, 0, 0};                                                                \
+    return int(cudaMemcpyToSymbol(g_device_status, zero, sizeof(zero)));                             \
+  }                                                                                                  \
+  int set_spin_limit_##suffix(unsigned int polls) {                                                  \
+    return int(cudaMemcpyToSymbol(g_spin_limit, &polls, sizeof(polls)));                             \
+  }
 
 }  // namespace gdn_sm100

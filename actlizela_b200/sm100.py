@@ -16,7 +16,11 @@ from .sm100_policy import policy, selection_for
 MATH_CONTRACT = "wy-splitbf16-state-bf16-out-sm100-v1"
 _DIAGNOSTIC_IDS = {"simt": 0, "umma": 1, "simt-prepare+umma-walk": 2, "umma-prepare+simt-walk": 3,
                    "umma-seg2": 1 | (2 << 8), "umma-seg4": 1 | (4 << 8), "umma-seg8": 1 | (8 << 8), "umma-seg16": 1 | (16 << 8),
-                   "chain": 4, "chain-seg2": 4 | (2 << 8), "chain-seg4": 4 | (4 << 8), "chain-seg8": 4 | (8 << 8)}
+                   "chain": 4, "chain-seg2": 4 | (2 << 8), "chain-seg4": 4 | (4 << 8), "chain-seg8": 4 | (8 << 8),
+                   # parallel sub-segments of the walk (bits 16..19), alone and with sequence segments
+                   "umma-par2": 1 | (2 << 16), "umma-par3": 1 | (3 << 16), "umma-par4": 1 | (4 << 16),
+                   "umma-par8": 1 | (8 << 16), "umma-seg2-par2": 1 | (2 << 8) | (2 << 16),
+                   "umma-seg2-par4": 1 | (2 << 8) | (4 << 16), "umma-seg4-par4": 1 | (4 << 8) | (4 << 16)}
 
 
 def configuration_id(name):
@@ -66,7 +70,6 @@ class Sm100Forward:
 
     def __init__(self, library):
         self.library = library
-        self._workspaces = {}
 
     def workspace_bytes(self, b, t, hk, hv, config):
         n = self.library.lib.actlize_la_sm100_workspace_bytes(b, t, hk, hv, config)
@@ -75,13 +78,23 @@ class Sm100Forward:
         return n
 
     def _workspace(self, device, nbytes):
+        """Scratch of one call, from PyTorch's stream-ordered caching allocator (as the reference allocates its
+        workspace per call, actlize_la/_gdn_ppu10.py:48-55): calls on different streams never share it, and in
+        steady state no cudaMalloc is reached.  A configuration with several sequence segments additionally
+        uses the library's per-device streams and events: only one such call may be in flight per device."""
         import torch
-        key = str(device)
-        held = self._workspaces.get(key)
-        if held is None or held.numel() < nbytes:
-            held = torch.empty(nbytes, dtype=torch.uint8, device=device)
-            self._workspaces[key] = held
-        return held
+        return torch.empty(nbytes, dtype=torch.uint8, device=device)
+
+    def check_device_status(self, device=None, synchronize=True):
+        """Raise RuntimeError if a kernel launched on ``device`` gave up a bounded wait.  Every wait inside the
+        kernels is bounded; a kernel that runs out records where, drains and returns, and its output rows and
+        final state are incomplete.  The forward itself never synchronises, so callers decide when to look: after
+        their own synchronisation point (``synchronize=False``) or here (``synchronize=True``).  Each forward
+        call also looks at the record first and raises for an earlier launch that failed."""
+        import torch
+        device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+        self.library.configure(device)
+        self.library.raise_on_failure(device, synchronize)
 
     def __call__(self, q, k, v, g, beta, initial_state=None, output_final_state=True, *,
                  configuration=None, mode="device", sm_count=None):
@@ -92,6 +105,7 @@ class Sm100Forward:
         else:
             config = configuration_id(configuration)
         self.library.configure(q.device)
+        self.library.raise_on_failure(q.device)        # an earlier launch that gave up: host-visible record, no sync
         out = torch.empty_like(v)
         final = (torch.empty((b, hv, 128, 128), dtype=torch.float32, device=q.device)
                  if output_final_state else None)

@@ -30,6 +30,8 @@ def policy():
         raise ValueError("duplicate or unknown SM100 policy row")
     if any(not 1 <= int(r.get("segments", 1)) <= 16 for r in rows):
         raise ValueError("SM100 policy row with an unsupported segment count")
+    if any(not 1 <= int(r.get("parallel", 1)) <= 8 for r in rows):
+        raise ValueError("SM100 policy row with an unsupported parallel sub-segment count")
     return data
 
 
@@ -43,20 +45,31 @@ class Selection:
     basis: str
     policy_id: str
     segments: int = 1     # sequence segments whose prepare overlaps the previous segment's walk
+    parallel: int = 1     # sub-segments of every (batch, value head) walk that are walked at the same time
 
     @property
     def configuration_id(self):
-        """Native configuration word: kernel family in the low bits, segment count in bits 8..15."""
-        return policy()["configuration_ids"][self.configuration] | (self.segments << 8)
+        """Native configuration word: kernel family in the low bits, segment count in bits 8..15, parallel
+        sub-segments of the walk in bits 16..19."""
+        family = policy()["configuration_ids"][self.configuration]
+        return family | (self.segments << 8) | ((self.parallel << 16) if family == 1 else 0)
+
+
+def default_parallel(batch, length, value_heads):
+    """Parallel sub-segments of the walk for a shape without a measured row: as many as give every one of the 148
+    SMs one walk CTA, at least 8 chunks per sub-segment, at most 8.  The native selector computes the same."""
+    heads, chunks = batch * value_heads, (length + 63) // 64
+    return max(1, min(8, 148 // heads, chunks // 8))
 
 
 def default_segments(batch, length, value_heads):
-    """Segment count for a shape without a measured row; integer rule fitted to the measured rows (the walk of a
-    segment occupies B*Hv SMs, the prepare of the next segment runs on the rest): up to 64 heads -> isqrt(chunks/8)
-    clamped to 1..8, more -> 1.  The native selector computes the same."""
+    """Segment count for a shape without a measured row.  Overlapping the prepare of a later segment with the walk
+    of an earlier one only pays while the walk leaves SMs idle, i.e. when it is not split into parallel
+    sub-segments: then up to 64 heads -> isqrt(chunks/8) clamped to 1..8, more -> 1.  The native selector computes
+    the same."""
     from math import isqrt
     heads, chunks = batch * value_heads, (length + 63) // 64
-    if heads > 64:
+    if heads > 64 or default_parallel(batch, length, value_heads) > 1:
         return 1
     return max(1, min(8, isqrt(chunks // 8)))
 
@@ -91,9 +104,9 @@ def select(shape, profile):
     for row in data["rows"]:
         if tuple(row["shape"]) == tuple(shape[:4]):
             return Selection(row["configuration"], "b200-measured-shape", data["id"],
-                             int(row.get("segments", 1)))
+                             int(row.get("segments", 1)), int(row.get("parallel", 1)))
     return Selection(data["default"], "unmeasured-shape-default", data["id"],
-                     default_segments(shape[0], shape[1], shape[3]))
+                     default_segments(shape[0], shape[1], shape[3]), default_parallel(shape[0], shape[1], shape[3]))
 
 
 def selection_for(q, v, *, mode="device", sm_count=None):

@@ -14,6 +14,13 @@ workspace of WY factors) is several times the 126 MB L2, so no L2 flush is neede
 steps.  `e2e` measures the same forward through the host-buffer entry of the C ABI with the
 host->device and device->host copies inside the timed region.  `--impl reference` times the CPU
 restatement of the reference's own FP32 path (oracle/) on the host cores instead.
+
+The same line carries, at N = 1, `per_config` (every named shape timed through the policy's configuration, with
+its fraction of the per-shape roofline) and, at N > 1, the two multi-GPU forms the path has: `shard_cfg2` (B8 T4096
+split by batch over the ranks, no collective, strong scaling) and `sp_cfg4` (T131072 split over the ranks, states
+handed on with NCCL send/recv, exact and decayed form), each with its efficiency against one GPU running the same
+shape and a `parity` object (key-head group 0 of the timed tensors against the CPU restatement, computed outside
+the timed regions).
 """
 from __future__ import annotations
 
@@ -91,8 +98,8 @@ class ClockSampler:
                     reasons=sorted(reasons), samples=len(sm))
 
 
-def cpu_reference_run(workload, steps, warmup, sample_note):
-    """Times the CPU restatement of the reference's FP32 path on the host cores."""
+def cpu_reference_run(workload, steps, warmup, sample_note, repeats=1):
+    """Times the CPU restatement of the reference's FP32 path on the host cores (`repeats` workloads per step)."""
     import torch
     from actlizela_b200.workloads import make_inputs
     from oracle import gdn_oracle as oracle
@@ -100,22 +107,29 @@ def cpu_reference_run(workload, steps, warmup, sample_note):
     usable = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
     torch.set_num_threads(max(1, usable))
     inputs = make_inputs(workload)
-    for _ in range(warmup):
-        oracle.chunk_forward_fp32(*inputs, output_final_state=True)
+    # the reference's own module when oracle/make_ref.py has placed it (kind "reference"), else its restatement
+    from oracle import make_ref
+    module = make_ref.load_ref()
+    if module is not None:
+        run, kind = (lambda: make_ref.reference_forward(module, *inputs, output_final_state=True)), "reference"
+    else:
+        run, kind = (lambda: oracle.chunk_forward_fp32(*inputs, output_final_state=True)), "port"
+    for _ in range(warmup * repeats):
+        run()
     start = time.perf_counter()
-    for _ in range(steps):
-        oracle.chunk_forward_fp32(*inputs, output_final_state=True)
+    for _ in range(steps * repeats):
+        run()
     elapsed = time.perf_counter() - start
-    value = workload.tokens * steps / elapsed
-    return dict(value=value, unit=UNIT, cores=torch.get_num_threads(), kind="port",
+    value = workload.tokens * steps * repeats / elapsed
+    return dict(value=value, unit=UNIT, cores=torch.get_num_threads(), kind=kind,
                 sample=sample_note, host_cpus=os.cpu_count(), ms_per_step=1e3 * elapsed / steps)
 
 
-def config_dict(workload, n_gpus, configuration):
+def config_dict(workload, n_gpus):
     return dict(workload=f"{workload.name} B{workload.batch} T{workload.length} Hk{workload.key_heads} "
                          f"Hv{workload.value_heads} D128 chunk64 gate={workload.gate_dtype}"
                          f"{' +initial' if workload.initial is not None else ''} per GPU",
-                configuration=configuration, sharding=f"batch x{n_gpus}, no collective",
+                sharding=f"batch x{n_gpus}, no collective",
                 l2="working set (inputs, outputs, WY workspace) exceeds the 126 MB L2; no flush between steps")
 
 
@@ -123,13 +137,15 @@ def reference_arm(args, workload):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    sample = "full per-GPU workload each step, all host threads"
-    base = cpu_reference_run(workload, args.steps, min(args.warmup, 1), sample)
+    # the native arm gives every GPU one workload per step (weak scaling); the host path gets the same N workloads
+    # per step, one after the other, so that both lines count equal work
+    sample = f"{args.gpus} x the full per-GPU workload each step (one per GPU of the native arm), all host threads"
+    base = cpu_reference_run(workload, args.steps, args.warmup, sample, repeats=args.gpus)
     line = dict(metric=METRIC, value=base["value"], unit=UNIT, n_gpus=args.gpus, steps=args.steps,
-                warmup=min(args.warmup, 1), ms_per_step=base["ms_per_step"], higher_is_better=True,
+                warmup=args.warmup, ms_per_step=base["ms_per_step"], higher_is_better=True,
                 scaling="weak", vs_baseline=None, dtype="f32", data="synthetic", impl="reference",
-                config=config_dict(workload, args.gpus, "cpu-oracle"),
-                cpu_baseline=dict(value=base["value"], unit=UNIT, cores=base["cores"], kind="port",
+                config=config_dict(workload, args.gpus), kernel_configuration=f"cpu-{base['kind']}",
+                cpu_baseline=dict(value=base["value"], unit=UNIT, cores=base["cores"], kind=base["kind"],
                                   sample=sample),
                 e2e=dict(value=base["value"], unit=UNIT, h2d_bytes_per_step=0, d2h_bytes_per_step=0))
     print(json.dumps(line), flush=True)
@@ -283,6 +299,218 @@ def sequence_parallel_bench(args, workload):
         dist.destroy_process_group()
 
 
+# --------------------------------------------------------------------------- helpers of the extra legs
+OUT_MAX_ABS, OUT_REL_F, STATE_REL_F = 2e-2, 1e-2, 1e-3       # the stated tolerances of the path
+
+
+def device_inputs(w, device, seed):
+    """Timing-only inputs with the workload's shapes and distributions, drawn on the device (the CPU generator of
+    workloads.make_inputs is kept for everything that is compared with the CPU restatement)."""
+    import torch
+    import torch.nn.functional as F
+    gen = torch.Generator(device=device).manual_seed(seed)
+    b, t, hk, hv = w.shape
+    normal = lambda *shape: torch.randn(*shape, generator=gen, device=device)
+    q = F.normalize(normal(b, t, hk, 128), dim=-1).to(torch.bfloat16)
+    k = F.normalize(normal(b, t, hk, 128), dim=-1).to(torch.bfloat16)
+    v = normal(b, t, hv, 128).to(torch.bfloat16)
+    g = (F.logsigmoid(normal(b, t, hv) + 2.0) if w.gate == "logsigmoid"
+         else -0.01 * torch.rand(b, t, hv, generator=gen, device=device))
+    g = g.to(torch.bfloat16 if w.gate_dtype == "bf16" else torch.float32)
+    beta = torch.sigmoid(normal(b, t, hv) + w.beta_shift).to(torch.bfloat16)
+    initial = None
+    if w.initial is not None:
+        initial = torch.zeros(b, hv, 128, 128, device=device) if w.initial == 0.0 else w.initial * normal(b, hv, 128, 128)
+    return [q, k, v, g, beta, initial]
+
+
+def plant_group(tensors, narrow, t0=0, t1=None):
+    """Overwrite key head 0 and its value heads in the device tensors with the CPU-generated `narrow` inputs
+    (token rows [t0, t1) of them): heads are independent, so that head group of the timed run can be checked
+    against the CPU restatement of the narrow workload."""
+    ratio = narrow[2].shape[2] // narrow[0].shape[2]
+    hk = narrow[0].shape[2]
+    for i, heads in ((0, hk), (1, hk), (2, hk * ratio), (3, hk * ratio), (4, hk * ratio)):
+        tensors[i][:, :, :heads] = narrow[i][:, t0:t1].to(tensors[i].device)
+    if tensors[5] is not None and narrow[5] is not None:
+        tensors[5][:, :hk * ratio] = narrow[5].to(tensors[5].device)
+
+
+def parity_metrics(out, want_out, state=None, want_state=None):
+    """Worst-case figures of one comparison with the CPU restatement, as plain floats."""
+    out, want_out = out.float().cpu(), want_out.float()
+    m = dict(out_max_abs=float((out - want_out).abs().max()),
+             out_rel_f=float((out - want_out).norm() / want_out.norm().clamp_min(1e-30)), state_rel_f=0.0)
+    if state is not None:
+        m["state_rel_f"] = float((state.cpu() - want_state).norm() / want_state.norm().clamp_min(1e-30))
+    return m
+
+
+def reduce_parity(m, device, world):
+    import torch
+    import torch.distributed as dist
+    x = torch.tensor([m["out_max_abs"], m["out_rel_f"], m["state_rel_f"]], device=device, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(x, op=dist.ReduceOp.MAX)
+    a, r, st = (float(v) for v in x.tolist())
+    return dict(out_max_abs=a, out_rel_f=r, state_rel_f=st, ok=bool(a <= OUT_MAX_ABS and r <= OUT_REL_F and st <= STATE_REL_F),
+                against="oracle.chunk_forward_fp32 on key-head group 0 of the timed tensors, max over ranks")
+
+
+def timed_loop(fn, steps, device, world, stream=None):
+    """K steps between two events on the launching stream, barrier + synchronise either side; per-step events give
+    the spread.  Returns (ms per step as total / K, max over ranks; dict of median / min / max over the K steps of
+    this rank's own event pairs)."""
+    import torch
+    import torch.distributed as dist
+    stream = stream or torch.cuda.current_stream()
+    marks = [torch.cuda.Event(enable_timing=True) for _ in range(steps + 1)]
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+        torch.cuda.synchronize()
+    marks[0].record(stream)
+    for i in range(steps):
+        fn()
+        marks[i + 1].record(stream)
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    total = torch.tensor([marks[0].elapsed_time(marks[-1])], device=device)
+    if world > 1:
+        dist.all_reduce(total, op=dist.ReduceOp.MAX)
+    each = sorted(marks[i].elapsed_time(marks[i + 1]) for i in range(steps))
+    return total.item() / steps, dict(median_ms=statistics.median(each), min_ms=each[0], max_ms=each[-1], samples=steps)
+
+
+def roofline_ms(w, peaks):
+    from actlizela_b200.workloads import algorithmic_bytes, algorithmic_flops
+    hbm_peak, tensor_peak, _ = peaks
+    return max(algorithmic_bytes(w) / (hbm_peak * 1e9), algorithmic_flops(w) / (tensor_peak * 1e12)) * 1e3
+
+
+def per_config_legs(device, skip, peaks, steps=5):
+    """Every named shape on one GPU through the policy's configuration: ms, tokens/s and the fraction of the
+    per-shape roofline (the slower of bytes / measured HBM bandwidth and FLOPs / measured BF16 peak)."""
+    import torch
+    from actlizela_b200 import gdn_forward
+    from actlizela_b200.sm100_policy import selection_for
+    from actlizela_b200.workloads import WORKLOADS
+    legs = {}
+    for name, w in WORKLOADS.items():
+        if name == skip:
+            continue
+        tensors = device_inputs(w, device, w.seed)
+        sel = selection_for(tensors[0], tensors[2])
+        call = lambda: gdn_forward(*tensors, output_final_state=True)
+        for _ in range(3):
+            call()
+        ms, spread = timed_loop(call, steps, device, 1)
+        legs[name] = dict(ms=ms, median_ms=spread["median_ms"], tokens_per_s=w.tokens / (ms * 1e-3),
+                          roofline_ms=roofline_ms(w, peaks), frac=roofline_ms(w, peaks) / ms,
+                          configuration=f"{sel.configuration} segments={sel.segments} parallel={sel.parallel}")
+        del tensors
+        torch.cuda.empty_cache()
+    return legs
+
+
+def shard_cfg2_leg(device, rank, world, steps, peaks):
+    """cfg2 (B8 T4096 Hk16 Hv32, BF16 gate) split by batch over the ranks, no collective: strong scaling against
+    one GPU running all eight batch rows."""
+    import torch
+    from actlizela_b200 import gdn_forward
+    from actlizela_b200.sharding import gdn_forward_sharded
+    from actlizela_b200.workloads import WORKLOADS, make_inputs
+    from oracle import gdn_oracle as oracle
+    w = WORKLOADS["cfg2"]
+    tensors = device_inputs(w, device, w.seed)                       # the same tensors on every rank
+    narrow = make_inputs(w.sliced(key_heads=1, value_heads=w.value_heads // w.key_heads))
+    plant_group(tensors, narrow)
+    whole = lambda: gdn_forward(*tensors, output_final_state=True)
+    mine = lambda: gdn_forward_sharded(*tensors, True, rank=rank, world_size=world)
+    for _ in range(3):
+        whole()
+        mine()
+    ms_one, _ = timed_loop(whole, steps, device, world)
+    ms_n, spread = timed_loop(mine, steps, device, world)
+    worst = dict(out_max_abs=0.0, out_rel_f=0.0, state_rel_f=0.0)
+    heads = narrow[2].shape[2]
+    for (b0, b1, v0, v1), out, final in mine():
+        if v0 != 0:
+            continue
+        want_out, want_state = oracle.chunk_forward_fp32(*[x[b0:b1] for x in narrow[:5]], narrow[5][b0:b1], True)
+        m = parity_metrics(out[:, :, :heads], want_out, final[:, :heads], want_state)
+        worst = {k: max(worst[k], m[k]) for k in worst}
+    return dict(workload="cfg2 B8 T4096 Hk16 Hv32 bf16 gate, zero initial state", sharding=f"batch rows over {world} ranks",
+                ms=ms_n, median_ms=spread["median_ms"], tokens_per_s=w.tokens / (ms_n * 1e-3), one_gpu_ms=ms_one,
+                efficiency=ms_one / (world * ms_n), roofline_frac=roofline_ms(w, peaks) / (world * ms_n),
+                scaling="strong", parity=reduce_parity(worst, device, world))
+
+
+def sp_cfg4_leg(device, rank, world, steps, peaks):
+    """cfg4 (B1 T131072 Hk16 Hv32) split over the ranks as contiguous token segments, states handed on with NCCL
+    send/recv: strong scaling against one GPU running the whole sequence; exact and decayed form."""
+    import torch
+    from actlizela_b200 import gdn_forward
+    from actlizela_b200.sequence_parallel import gdn_forward_sequence_parallel, segment_bounds
+    from actlizela_b200.workloads import WORKLOADS, make_inputs
+    from oracle import gdn_oracle as oracle
+    w = WORKLOADS["cfg4"]
+    t0, t1 = segment_bounds(w.length, world)[rank]
+    narrow = make_inputs(w.sliced(key_heads=1, value_heads=w.value_heads // w.key_heads))
+    heads = narrow[2].shape[2]
+    full = device_inputs(w, device, w.seed)
+    plant_group(full, narrow)
+    whole = lambda: gdn_forward(*full, output_final_state=True)
+    for _ in range(3):
+        whole()
+    ms_one, _ = timed_loop(whole, steps, device, world)
+    part = [x[:, t0:t1].contiguous() for x in full[:5]]
+    initial = full[5] if rank == 0 else None
+    del full
+    torch.cuda.empty_cache()
+    want_out, want_state = oracle.chunk_forward_fp32(*narrow, output_final_state=True)
+    result = dict(workload="cfg4 B1 T131072 Hk16 Hv32 fp32 gate, zero initial state",
+                  segments=f"{world} contiguous token segments, one per rank", one_gpu_ms=ms_one, scaling="strong")
+    for form, decayed in (("exact", False), ("decayed", True)):
+        call = lambda: gdn_forward_sequence_parallel(*part, initial, True, until_decayed=decayed)
+        for _ in range(3):
+            call()
+        ms, spread = timed_loop(call, steps, device, world)
+        out, final = call()
+        m = parity_metrics(out[:, :, :heads], want_out[:, t0:t1],
+                           final[:, :heads] if final is not None else None, want_state)
+        result[form] = dict(ms=ms, median_ms=spread["median_ms"], tokens_per_s=w.tokens / (ms * 1e-3),
+                            efficiency=ms_one / (world * ms), roofline_frac=roofline_ms(w, peaks) / (world * ms),
+                            parity=reduce_parity(m, device, world))
+    return result
+
+
+def copy_bound_ms(host, host_out, host_final, device, world, reps=5):
+    """The time the step's host->device and device->host bytes take as plain concurrent cudaMemcpyAsync calls, all
+    ranks at once (the floor of `e2e` on this box)."""
+    import torch
+    landing = [torch.empty_like(x, device=device) for x in host if x is not None]
+    src_out, src_final = torch.empty_like(host_out, device=device), torch.empty_like(host_final, device=device)
+    up, down = torch.cuda.Stream(device=device), torch.cuda.Stream(device=device)
+
+    def step():
+        up.wait_stream(torch.cuda.current_stream())
+        down.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(up):
+            for dst, src in zip(landing, [x for x in host if x is not None]):
+                dst.copy_(src, non_blocking=True)
+        with torch.cuda.stream(down):
+            host_out.copy_(src_out, non_blocking=True)
+            host_final.copy_(src_final, non_blocking=True)
+        torch.cuda.current_stream().wait_stream(up)
+        torch.cuda.current_stream().wait_stream(down)
+
+    step()
+    ms, _ = timed_loop(step, reps, device, world)
+    return ms
+
+
 def main():
     ap = argparse.ArgumentParser(description=__doc__)
     ap.add_argument("--gpus", type=int, default=1)
@@ -292,6 +520,8 @@ def main():
     ap.add_argument("--configuration", default=None, help="diagnostic override of the policy table")
     ap.add_argument("--impl", default="native", choices=("native", "reference"))
     ap.add_argument("--skip-cpu-baseline", action="store_true")
+    ap.add_argument("--skip-extra-legs", action="store_true",
+                    help="leave out per_config (N = 1) and shard_cfg2 / sp_cfg4 (N > 1)")
     ap.add_argument("--op", default="forward", choices=("forward", "decode", "prepare_inputs", "rmsnorm_gated", "varlen", "projections"),
                     help="forward is the headline metric; the others time a neighbouring memory-bound kernel")
     ap.add_argument("--parallelism", default="shard", choices=("shard", "sp"),
@@ -358,32 +588,17 @@ def main():
         if rc:
             raise RuntimeError(f"forward_prepared failed with CUDA error {rc}")
 
-    def sync_all():
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize()
-
     def timed(fn, steps):
-        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        sync_all()
-        start.record(stream)
-        for _ in range(steps):
-            fn()
-        stop.record(stream)
-        sync_all()
-        elapsed = torch.tensor([start.elapsed_time(stop)], device=device)
-        if world > 1:
-            dist.all_reduce(elapsed, op=dist.ReduceOp.MAX)
-        return elapsed.item() / steps          # ms per step, max over ranks
+        return timed_loop(fn, steps, device, world, stream)     # (ms per step, max over ranks; spread of the steps)
 
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()
     for _ in range(args.warmup):
         forward()
-    ms_step = timed(forward, args.steps)
-    ms_walk = timed(lambda: forward(0x20), args.steps)
-    ms_prepare = timed(lambda: forward(0x10), args.steps)
+    ms_step, spread = timed(forward, args.steps)
+    ms_walk, _ = timed(lambda: forward(0x20), args.steps)
+    ms_prepare, _ = timed(lambda: forward(0x10), args.steps)
     clocks = sampler.stop() if rank == 0 else None
     forward()
 
@@ -404,39 +619,62 @@ def main():
 
     e2e_steps = max(3, min(args.steps, 10))
     forward_host()
-    ms_e2e = timed(forward_host, e2e_steps)
+    ms_e2e, _ = timed(forward_host, e2e_steps)
     same = bool(torch.equal(host_out, out.cpu()))
     h2d = sum(x.numel() * x.element_size() for x in host if x is not None)
     d2h = host_out.numel() * 2 + host_final.numel() * 4
+    ms_copies = copy_bound_ms(host, host_out, host_final, device, world)
+    del arena
 
     status = (ctypes.c_int * 4)()
     lib.actlize_la_sm100_device_status(status, 0)
+    peaks = measured_peaks()
+    hbm_peak, tensor_peak, peak_source = peaks
+    extra = {}
+    if not args.skip_extra_legs:
+        del q, k, v, g, beta, initial, out, final
+        torch.cuda.empty_cache()
+        extra_steps = max(3, min(args.steps, 10))
+        if world == 1:
+            extra["per_config"] = per_config_legs(device, workload.name, peaks)
+        else:
+            extra["shard_cfg2"] = shard_cfg2_leg(device, rank, world, extra_steps, peaks)
+            extra["sp_cfg4"] = sp_cfg4_leg(device, rank, world, extra_steps, peaks)
     if rank != 0:
         if world > 1:
             dist.destroy_process_group()
         return
 
-    hbm_peak, tensor_peak, peak_source = measured_peaks()
     alg_bytes, alg_flops = algorithmic_bytes(shard), algorithmic_flops(shard)
-    achieved = alg_bytes / (ms_walk * 1e-3) / 1e9
-    # DRAM traffic of the walk kernel from the committed ncu capture (profiles/): 100.2 KB per
-    # (chunk, value head) block, scaled by the blocks of one whole-sequence launch
-    traffic = 100.2e3 * shard.batch * shard.value_heads * ((shard.length + 63) // 64) if config_name == "umma" else None
-    roofline_ms = max(alg_bytes / (hbm_peak * 1e9), alg_flops / (tensor_peak * 1e12)) * 1e3
+    # the roofline object describes the longer of the two kernels of a forward; both see the whole problem, so the
+    # algorithmic bytes of the path (each tensor once) are set against that kernel's own time
+    top, ms_top = ("prepare", ms_prepare) if ms_prepare > ms_walk else ("walk", ms_walk)
+    achieved = alg_bytes / (ms_top * 1e-3) / 1e9
+    # DRAM traffic per launch from the committed ncu captures of a smaller case (profiles/; caches flushed before the
+    # captured launch, so an upper bound), per (chunk, value head) block and scaled by the blocks of one launch
+    blocks = shard.batch * shard.value_heads * ((shard.length + 63) // 64)
+    traffic = 100.2e3 * blocks if (config_name == "umma" and top == "walk") else None
+    whole_ms = max(alg_bytes / (hbm_peak * 1e9), alg_flops / (tensor_peak * 1e12)) * 1e3
     line = dict(
         metric=METRIC, value=workload.tokens * world / (ms_step * 1e-3), unit=UNIT, n_gpus=world,
         steps=args.steps, warmup=args.warmup, ms_per_step=ms_step, higher_is_better=True, scaling="weak",
         vs_baseline=None, dtype="bf16", dtype_detail="bf16 operands (state path as bf16 hi+lo pairs), f32 accumulate and state",
-        data="synthetic", config=config_dict(workload, world, config_name),
+        data="synthetic", config=config_dict(workload, world),
+        kernel_configuration=dict(family=config_name, segments=(config >> 8) & 0xff, parallel=max(1, (config >> 16) & 0xf)),
         gpu_launches=args.steps * lib.actlize_la_sm100_launches_per_forward(config),
         kernels_ms=dict(prepare=ms_prepare, walk=ms_walk, forward=ms_step),
-        roofline=dict(bound="hbm", kernel="walk", achieved=achieved, peak=hbm_peak, unit="GB/s",
-                      frac=achieved / hbm_peak, traffic=traffic, peak_source=peak_source,
-                      algorithmic_bytes=alg_bytes, algorithmic_flops=alg_flops,
-                      whole_forward_frac=roofline_ms / ms_step),
+        step_spread=spread,
+        roofline=dict(bound="hbm", kernel=top, achieved=achieved, peak=hbm_peak, unit="GB/s",
+                      frac=achieved / hbm_peak, traffic=traffic,
+                      traffic_note=("cold-cache ncu capture of cfg0 scaled by blocks" if traffic else
+                                    "no capture of this kernel at this size; see profiles/"),
+                      peak_source=peak_source, algorithmic_bytes=alg_bytes, algorithmic_flops=alg_flops,
+                      whole_forward_frac=whole_ms / ms_step,
+                      tensor_frac=alg_flops / (ms_step * 1e-3) / (tensor_peak * 1e12)),
         e2e=dict(value=workload.tokens * world / (ms_e2e * 1e-3), unit=UNIT, h2d_bytes_per_step=h2d,
-                 d2h_bytes_per_step=d2h, ms_per_step=ms_e2e, output_equals_device_path=same),
-        clocks=clocks, device_status=list(status))
+                 d2h_bytes_per_step=d2h, ms_per_step=ms_e2e, output_equals_device_path=same,
+                 copy_bound_ms=ms_copies, over_copy_bound=ms_e2e / ms_copies),
+        clocks=clocks, device_status=list(status), **extra)
     if not args.skip_cpu_baseline:
         reps = 10
         line["cpu_baseline"] = {k2: v2 for k2, v2 in cpu_reference_run(

@@ -56,7 +56,7 @@ int actlize_la_sm100_abi_version(void);
  * Replaces actlize_la_ppu15_target_arch (csrc/backends/ppu15/launch.h:11). */
 int actlize_la_sm100_target_arch(void);
 
-/* Identity string of the numerical contract, e.g. "wy-tf32-state-bf16-out-sm100-v1".
+/* Identity string of the numerical contract, "wy-splitbf16-state-bf16-out-sm100-v1".
  * Counterpart of the pybind attribute math_contract checked by
  * actlize_la/gdn_sm90_interface.py:19-20. */
 const char* actlize_la_sm100_numerical_contract(void);
@@ -82,7 +82,12 @@ long long actlize_la_sm100_workspace_bytes(int batch, int sequence, int key_head
 /* Complete forward on caller-owned buffers: prepare kernel (per-chunk gate prefix, decay-masked
  * K.K^T, unit-lower-triangular inverse, WY factors) followed by the sequential chunk walk.
  * `config` is the value returned by actlize_la_sm100_select: kernel family in bits 0..3, number of
- * sequence segments in bits 8..15.  With more than one segment the prepare kernels and walks of the segments
+ * sequence segments in bits 8..15, number of parallel sub-segments of the walk in bits 16..19 (tcgen05 family only;
+ * 0 or 1 = off, at most 8).  With P parallel sub-segments P CTAs walk each (batch, value head) at the same time, every
+ * one from a zero state and on into the leading chunks of the next piece that its state still reaches; this is exact
+ * to exp(-40) of the state for heads whose pieces decay below exp(-40) within their own length and whose tokens
+ * satisfy 0 <= beta |k|^2 <= 2 (checked on the device from the gates and the prepare kernel's K K^T diagonal, no
+ * host read); any other head is walked by one CTA as without the split.  With more than one segment the prepare kernels and walks of the segments
  * behind the first run on two library-owned streams that are forked from and joined back into `stream` with
  * events (so the call stays asynchronous and capturable); those streams and events exist once per device,
  * therefore two segmented calls on the same device must not be in flight at the same time on different streams.
@@ -158,17 +163,44 @@ int actlize_la_sm100_rmsnorm_gated(const void* y, const void* z, const void* wei
                                    long long rows, void* stream);
 
 /* Diagnostic word written by a kernel whose bounded wait ran out (all waits on barriers are
- * bounded; a kernel that gives up drains, frees its tensor memory and returns): status4[0] = 0
- * when healthy else a failure code, [1] block index, [2] wait site, [3] chunk.  Synchronises the
- * device; `reset` != 0 clears the word.  Counterpart of the per-request `errors[]` status of the
- * reference's serving ABI (csrc/serving/abi.h:8-17). */
+ * bounded; a kernel that gives up drains, frees its tensor memory and returns; its output rows and
+ * final state are then incomplete): status4[0] = 0 when healthy else a failure code, [1] block index,
+ * [2] wait site, [3] chunk.  Synchronises the device; `reset` != 0 clears the word.  Counterpart of the
+ * per-request `errors[]` status of the reference's serving ABI (csrc/serving/abi.h:8-17). */
 int actlize_la_sm100_device_status(int* status4, int reset);
+
+/* The same record WITHOUT synchronising: the failing kernel also writes it to a page of pinned host
+ * memory that configure() maps into the device (cudaHostRegister of library-owned storage; nothing is
+ * allocated), and this call only reads that page.  A caller polls it after its own synchronisation, or
+ * before its next launch to learn about an earlier one; all zero when healthy or when configure() has not
+ * run on the current device.  Cleared by actlize_la_sm100_device_status(..., 1).  The forward entries
+ * stay fire-and-forget; checking this word is the caller's part of failing closed. */
+int actlize_la_sm100_last_failure(int* status4);
+
+/* Diagnostic counters of the parallel walk (config bits 16..19), summed over the launches since the last reset:
+ * counts2[0] = (batch, value head) walks that were split over several CTAs, counts2[1] = walks that one CTA did alone
+ * because a sub-segment does not decay below exp(-40) within its length or a token is not a contraction.
+ * Synchronises the device; `reset` != 0 clears the counters.  No counterpart in the reference (its kernels never
+ * split a head's walk over the sequence). */
+int actlize_la_sm100_walk_plan_counts(int* counts2, int reset);
 
 /* Failure-detection self-test: launches one small kernel whose bounded wait can never be satisfied
  * (an mbarrier nothing arrives on, a few thousand polls).  The kernel gives up, writes
  * (1, 0, 99, tag) to the status word read by actlize_la_sm100_device_status and ends normally: the
  * context stays usable.  No counterpart in the reference, whose kernels wait without a limit. */
 int actlize_la_sm100_selftest_wait_timeout(int tag, void* stream);
+
+/* Failure-detection self-test of the chunk walk itself: launches the tcgen05 walk over a workspace that an
+ * earlier forward_prepared call (configuration 1, one segment, same inputs) has filled, with a TMA producer
+ * that stops feeding it after the first chunk and with the poll limit of the bounded waits lowered for this
+ * launch (the limit travels on `stream` in front of and behind the kernel; run nothing else on the device
+ * meanwhile).  Every role of the real kernel runs out of its wait or sees the CTA-wide flag; the CTAs drain,
+ * free their tensor memory and return; the status record holds code 1.  `output` receives unspecified rows:
+ * pass a scratch buffer.  Needs at least two chunks (sequence > 64). */
+int actlize_la_sm100_selftest_walk_stall(
+    const void* q, const void* k, const void* v, const void* g, const void* beta, void* output,
+    void* workspace, long long workspace_bytes, int batch, int sequence, int key_heads, int value_heads,
+    int gate_fp32, void* stream);
 
 /* The forward on the raw projection outputs of the layer: the step before the path (Q/K L2-normalisation, gate
  * activation g = -exp(A_log) softplus(a + dt_bias), beta = sigmoid(b); csrc/serving/prefill.cu:45-70,

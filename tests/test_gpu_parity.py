@@ -177,6 +177,7 @@ def _oracle_by_head_group(cpu, key_heads_per_call=4):
 
 @pytest.mark.parametrize("name", ["cfg0", "headline", "cfg1", "cfg3"])
 def test_named_shapes_at_full_size(name, forward, native_library):
+    """Through the policy's configuration for the shape (cfg0, headline, cfg1: parallel sub-segments)."""
     w = WORKLOADS[name]
     cpu = make_inputs(w)
     want_out, want_state = _oracle_by_head_group(cpu)
@@ -187,16 +188,20 @@ def test_named_shapes_at_full_size(name, forward, native_library):
 
 
 def test_cfg2_batch_sharded_shape(forward):
-    """B8 T4096 BF16 gate: device result for every batch, CPU reference for two of them."""
+    """B8 T4096 BF16 gate at full size: every batch row against the CPU reference."""
     w = WORKLOADS["cfg2"]
     cpu = make_inputs(w)
     out, state = forward(*_to_device(cpu), True)
-    for b in (0, 7):
+    for b in range(w.batch):
         part = [x[b:b + 1] for x in cpu[:5]] + [cpu[5][b:b + 1]]
         want_out, want_state = _oracle_by_head_group(part)
         _check(out[b:b + 1], state[b:b + 1], want_out, want_state, ("cfg2", b))
-    # size-independent property: a batch element computed alone gives the same bits
-    solo_out, solo_state = forward(*[x[3:4].contiguous() for x in _to_device(cpu)], True)
+    # size-independent property: a batch element computed alone by the same kernel configuration gives the same
+    # bits (the policy would split the walk of a lone batch element, which agrees to exp(-40) of the state instead)
+    dev = _to_device(cpu)
+    whole_out, whole_state = forward(*dev, True, configuration="umma")
+    assert torch.equal(whole_out, out) and torch.equal(whole_state, state)      # cfg2's row is the unsplit walk
+    solo_out, solo_state = forward(*[x[3:4].contiguous() for x in dev], True, configuration="umma")
     assert torch.equal(solo_out, out[3:4]) and torch.equal(solo_state, state[3:4])
 
 
@@ -206,16 +211,111 @@ def test_long_sequence_segment_chaining(forward):
     w = WORKLOADS["cfg4"].sliced(key_heads=2, value_heads=4)
     cpu = make_inputs(w)
     dev = _to_device(cpu)
-    out, state = forward(*dev, True)
+    out, state = forward(*dev, True, configuration="umma")
     cut = 64 * 1000
     head = [x[:, :cut].contiguous() for x in dev[:5]]
     tail = [x[:, cut:].contiguous() for x in dev[:5]]
-    o1, s1 = forward(*head, dev[5], True)
-    o2, s2 = forward(*tail, s1, True)
+    o1, s1 = forward(*head, dev[5], True, configuration="umma")
+    o2, s2 = forward(*tail, s1, True, configuration="umma")
     assert torch.equal(torch.cat([o1, o2], 1), out) and torch.equal(s2, state)
+    # the policy's choice for this shape (the walk split into parallel sub-segments) agrees to exp(-40) of the state
+    split_out, split_state = forward(*dev, True)
+    assert oracle.max_abs(split_out.float(), out.float()) < 1e-5
+    assert oracle.rel_frobenius(split_state.cpu(), state.cpu()) < 1e-6
     want_out, want_state = oracle.chunk_forward_fp32(cpu[0][:, :, :1], cpu[1][:, :, :1], cpu[2][:, :, :2],
                                                      cpu[3][:, :, :2], cpu[4][:, :, :2], cpu[5][:, :2], True)
     _check(out[:, :, :2], state[:, :2], want_out, want_state, "cfg4-slice")
+
+
+def test_cfg4_at_full_size(forward, native_library):
+    """B1 T131072 Hk16 Hv32 through the policy's configuration: every head against the CPU reference (computed by
+    key-head groups to bound host memory)."""
+    w = WORKLOADS["cfg4"]
+    cpu = make_inputs(w)
+    out, state = forward(*_to_device(cpu), True)
+    torch.cuda.synchronize()
+    assert _status(native_library)[0] == 0
+    out, state = out.cpu(), state.cpu()
+    for h0 in range(0, w.key_heads, 2):
+        v0, v1 = 2 * h0, 2 * h0 + 4
+        part = (cpu[0][:, :, h0:h0 + 2], cpu[1][:, :, h0:h0 + 2], cpu[2][:, :, v0:v1], cpu[3][:, :, v0:v1],
+                cpu[4][:, :, v0:v1], cpu[5][:, v0:v1])
+        want_out, want_state = oracle.chunk_forward_fp32(*part, output_final_state=True)
+        _check(out[:, :, v0:v1], state[:, v0:v1], want_out, want_state, ("cfg4", h0))
+
+
+def _plan_counts(native_library, reset=True):
+    buf = (ctypes.c_int * 2)()
+    assert native_library.lib.actlize_la_sm100_walk_plan_counts(buf, int(reset)) == 0
+    return list(buf)
+
+
+@pytest.mark.parametrize("configuration", ["umma-par2", "umma-par3", "umma-par4", "umma-par8", "umma-seg2-par4"])
+def test_parallel_walk_matches_the_unsplit_walk(configuration, forward, native_library):
+    """Every (batch, value head) walk cut into sub-segments that start from a zero state at the same time: with the
+    benchmark gate each sub-segment forgets its incoming state within a few chunks, so the split walk agrees with
+    the unsplit one to exp(-40) of the state; both are checked against the CPU reference."""
+    w = WORKLOADS["cfg0"].sliced(batch=2, length=64 * 48 + 20, key_heads=2, value_heads=4, initial=0.1, seed=77)
+    cpu = make_inputs(w)
+    dev = _to_device(cpu)
+    want_out, want_state = oracle.chunk_forward_fp32(*cpu, output_final_state=True)
+    base_out, base_state = forward(*dev, True, configuration="umma")
+    _plan_counts(native_library)
+    out, state = forward(*dev, True, configuration=configuration)
+    torch.cuda.synchronize()
+    assert _status(native_library)[0] == 0
+    split, alone = _plan_counts(native_library)
+    launches = 2 if "seg2" in configuration else 1
+    assert split == launches * w.batch * w.value_heads and alone == 0, (split, alone)     # the split really ran
+    _check(out, state, want_out, want_state, configuration)
+    assert oracle.max_abs(out.float(), base_out.float()) < 1e-5
+    assert oracle.rel_frobenius(state.cpu(), base_state.cpu()) < 1e-6
+    again_out, again_state = forward(*dev, True, configuration=configuration)
+    assert torch.equal(again_out, out) and torch.equal(again_state, state)
+    out_only, none = forward(*dev, False, configuration=configuration)
+    assert none is None and torch.equal(out_only, out)
+
+
+@pytest.mark.parametrize("stress", ["no-decay", "long-keys", "negative-beta", "mixed-heads"])
+def test_parallel_walk_falls_back_per_head(stress, forward, native_library):
+    """Heads the split is not valid for, decided on the device: a sub-segment that does not decay below exp(-40), or
+    a token whose transition exp(g)(I - beta k k^T) is not a contraction (|k|^2 beta > 2, beta < 0).  Such a head
+    is walked by one CTA, bit for bit like the unsplit walk; the other heads of the same launch are still split."""
+    w = WORKLOADS["cfg0"].sliced(batch=1, length=64 * 32, key_heads=2, value_heads=4, initial=0.1, seed=78)
+    q, k, v, g, beta, init = make_inputs(w)
+    expect_alone = w.value_heads
+    if stress == "no-decay":
+        g = torch.zeros_like(g)
+    elif stress == "long-keys":
+        k = (k.float() * 2.5).to(torch.bfloat16)               # beta |k|^2 up to 6
+        q = (q.float() * 0.2).to(torch.bfloat16)
+        g = g * 4.0                                             # strong decay keeps the expanding steps bounded
+    elif stress == "negative-beta":
+        beta = beta.clone()
+        beta[0, 1500, 1] = -0.25                                # one token of one head
+        expect_alone = 1
+    else:
+        g = g.clone()
+        g[:, :, 2] = -0.001                                     # one slow head among fast ones
+        expect_alone = 1
+    cpu = (q, k, v, g.contiguous(), beta, init)
+    dev = _to_device(cpu)
+    base_out, base_state = forward(*dev, True, configuration="umma")
+    _plan_counts(native_library)
+    out, state = forward(*dev, True, configuration="umma-par4")
+    torch.cuda.synchronize()
+    assert _status(native_library)[0] == 0
+    split, alone = _plan_counts(native_library)
+    assert alone == expect_alone and split == w.value_heads - expect_alone, (split, alone)
+    if expect_alone == w.value_heads:
+        assert torch.equal(out, base_out) and torch.equal(state, base_state)
+    else:
+        lone = 1 if stress == "negative-beta" else 2
+        assert torch.equal(out[:, :, lone], base_out[:, :, lone]) and torch.equal(state[:, lone], base_state[:, lone])
+        assert oracle.max_abs(out.float(), base_out.float()) < 1e-5
+    want_out, want_state = oracle.wy_chunk_forward(*cpu)
+    if stress != "long-keys":       # (expanding transitions amplify rounding: that case is checked bit for bit above)
+        _check(out, state, want_out, want_state, stress)
 
 
 @pytest.mark.parametrize("config", [1, 1 | (4 << 8)], ids=["one-shot", "pipelined-4-segments"])
@@ -300,6 +400,39 @@ def test_bounded_wait_gives_up_and_reports(native_library, forward):
     assert torch.isfinite(out.float()).all()
 
 
+def test_stalled_walk_drains_and_the_next_call_reports_it(native_library, forward):
+    """The real chunk walk with a producer that stops after the first chunk (self-test entry): every role runs out
+    of its bounded wait, the CTAs drain and return, the failure is visible on the host without a synchronising
+    call, the next forward raises for it, and the one after that computes normally."""
+    lib = native_library.lib
+    w = WORKLOADS["cfg0"].sliced(length=64 * 3 + 9, key_heads=1, value_heads=2)
+    q, k, v, g, beta, _ = _to_device(make_inputs(w))
+    b, t, hk, hv = w.shape
+    native_library.configure(q.device)
+    nbytes = lib.actlize_la_sm100_workspace_bytes(b, t, hk, hv, 1)
+    ws = torch.empty(nbytes, dtype=torch.uint8, device="cuda")
+    out, final = torch.empty_like(v), torch.empty(b, hv, 128, 128, device="cuda")
+    stream = torch.cuda.current_stream().cuda_stream
+    assert lib.actlize_la_sm100_forward_prepared(
+        q.data_ptr(), k.data_ptr(), v.data_ptr(), g.data_ptr(), beta.data_ptr(), None, out.data_ptr(),
+        final.data_ptr(), ws.data_ptr(), nbytes, b, t, hk, hv, 1, 1, stream) == 0
+    torch.cuda.synchronize()
+    assert native_library.last_failure(q.device) is None
+    scratch = torch.empty_like(v)
+    assert lib.actlize_la_sm100_selftest_walk_stall(
+        q.data_ptr(), k.data_ptr(), v.data_ptr(), g.data_ptr(), beta.data_ptr(), scratch.data_ptr(),
+        ws.data_ptr(), nbytes, b, t, hk, hv, 1, stream) == 0
+    torch.cuda.synchronize()
+    failure = native_library.last_failure(q.device)            # plain host read
+    assert failure is not None and failure[0] == 1 and failure[3] >= 1, failure
+    with pytest.raises(RuntimeError, match="gave up a bounded wait"):
+        forward(q, k, v, g, beta, None, True)                  # raises before launching anything; clears the record
+    assert native_library.last_failure(q.device) is None
+    again_out, again_final = forward(q, k, v, g, beta, None, True, configuration="umma")
+    forward.check_device_status(q.device)
+    assert torch.equal(again_out, out) and torch.equal(again_final, final)
+
+
 def test_forward_is_graph_capturable(native_library):
     """forward_prepared (segmented: two streams joined by events) replays from a CUDA graph."""
     w = WORKLOADS["cfg0"].sliced(length=1024, key_heads=2, value_heads=4)
@@ -351,7 +484,7 @@ def test_random_geometries(seed, forward):
     _check(out, state, want_out, want_state, ("random", seed, w.shape))
 
 
-@pytest.mark.parametrize("configuration", ["umma", "chain", "chain-seg4"])
+@pytest.mark.parametrize("configuration", ["umma", "umma-par2", "chain", "chain-seg4"])
 @pytest.mark.parametrize("gate", ["none", "strong", "underflow", "mixed"])
 def test_extreme_gates(gate, configuration, forward, native_library):
     """Gate ranges beyond the benchmark distributions: no decay at all, a decay that empties the state within a

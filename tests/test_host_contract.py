@@ -172,7 +172,7 @@ def test_native_select_agrees_with_python_policy(native_library):
     lib = native_library.lib
     ids = sm100_policy.policy()["configuration_ids"]
     for row in sm100_policy.policy()["rows"]:
-        want = ids[row["configuration"]] | (row.get("segments", 1) << 8)
+        want = ids[row["configuration"]] | (row.get("segments", 1) << 8) | (row.get("parallel", 1) << 16)
         assert lib.actlize_la_sm100_select(*row["shape"], 1) == want
         profile_choice = sm100_policy.select((*row["shape"], 128, 128), B200)
         assert profile_choice.configuration_id == want
@@ -182,7 +182,12 @@ def test_native_select_agrees_with_python_policy(native_library):
         want = sm100_policy.select((*shape, 128, 128), B200)
         assert want.basis == "unmeasured-shape-default"
         assert lib.actlize_la_sm100_select(*shape, 0) == want.configuration_id, shape
-    assert sm100_policy.default_segments(1, 65536, 32) == 8 and sm100_policy.default_segments(1, 16384, 32) == 5
+    # the walk of up to 74 heads is split into parallel sub-segments (then one sequence segment); 75..148 heads
+    # leave SMs idle without room for a second CTA per head, so the prepare of later segments overlaps the walk
+    assert sm100_policy.default_parallel(1, 65536, 32) == 4 and sm100_policy.default_segments(1, 65536, 32) == 1
+    assert sm100_policy.default_parallel(1, 16384, 48) == 3 and sm100_policy.default_parallel(1, 1024, 16) == 2
+    assert sm100_policy.default_parallel(1, 16384, 100) == 1 and sm100_policy.default_segments(1, 16384, 64) == 1
+    assert sm100_policy.default_parallel(1, 1 << 20, 2) == 8 and sm100_policy.default_parallel(1, 511, 1) == 1
     assert sm100_policy.default_segments(3, 100, 4) == 1 and sm100_policy.default_segments(16, 8192, 32) == 1
     assert lib.actlize_la_sm100_select(1, 64, 3, 4, 0) < 0
     assert lib.actlize_la_sm100_select(0, 64, 1, 1, 0) < 0
@@ -266,3 +271,56 @@ def test_no_file_io_or_hashing_per_call(native_library):
             mock.patch.object(_library.Path, "is_file", side_effect=AssertionError("file system on the call path")):
         for _ in range(3):
             assert _library.load_library() is first
+
+
+def test_auxiliary_wrappers_reject_ill_formed_operands_before_any_launch():
+    """Every operand of the decode / verify / commit / input-preparation / gated-RMSNorm wrappers is checked for
+    shape, dtype, device, contiguity and alignment before a pointer reaches the library: CPU tensors only here,
+    so nothing can be launched (a well-formed CPU call fails on the device check)."""
+    from actlizela_b200 import aux_ops
+    bf16 = dict(dtype=torch.bfloat16)
+    b, w, hk, hv = 2, 3, 2, 4
+    q, k = torch.zeros(b, hk, 128, **bf16), torch.zeros(b, hk, 128, **bf16)
+    v, g, beta = torch.zeros(b, hv, 128, **bf16), torch.zeros(b, hv), torch.zeros(b, hv, **bf16)
+    state = torch.zeros(b, hv, 128, 128)
+    bad_decode = [
+        dict(k=torch.zeros(b, hk + 1, 128, **bf16)), dict(k=torch.zeros(b, hk, 64, **bf16)),
+        dict(v=torch.zeros(b + 1, hv, 128, **bf16)), dict(beta=torch.zeros(b, hv + 1, **bf16)),
+        dict(beta=torch.zeros(b, hv)), dict(g=torch.zeros(b, hv, dtype=torch.float64)),
+        dict(state=torch.zeros(b, hv, 128, 64)), dict(q=torch.zeros(b, 3, 128, **bf16), k=torch.zeros(b, 3, 128, **bf16)),
+    ]
+    for change in bad_decode:
+        args = {**dict(q=q, k=k, v=v, g=g, beta=beta, state=state), **change}
+        with pytest.raises(ValueError, match="shape|dtype|Hv % Hk"):
+            aux_ops.gdn_decode_step(**args)
+    with pytest.raises(ValueError, match="CUDA"):
+        aux_ops.gdn_decode_step(q, k, v, g, beta, state)
+
+    q4, k4 = torch.zeros(b, w, hk, 128, **bf16), torch.zeros(b, w, hk, 128, **bf16)
+    v4, g3, beta3 = torch.zeros(b, w, hv, 128, **bf16), torch.zeros(b, w, hv), torch.zeros(b, w, hv, **bf16)
+    for change in (dict(q=torch.zeros(b, w, hk, 64, **bf16)), dict(v=torch.zeros(b, w, hv + 1, 128, **bf16)),
+                   dict(beta=torch.zeros(b, w + 1, hv, **bf16)), dict(k=torch.zeros(b, 65, hk, 128, **bf16),
+                                                                     g=torch.zeros(b, 65, hv))):
+        args = {**dict(q=q4, k=k4, v=v4, g=g3, beta=beta3, state=state), **change}
+        with pytest.raises(ValueError, match="shape|width"):
+            aux_ops.gdn_verify_step(**args)
+    delta, counts = torch.zeros(b, w, hv, 128), torch.zeros(b, dtype=torch.int32)
+    for change in (dict(delta=torch.zeros(b, w, hv, 64)), dict(counts=torch.zeros(b + 1, dtype=torch.int32)),
+                   dict(counts=torch.zeros(b)), dict(g=torch.zeros(b, w, hv)[:, :, ::1].transpose(0, 1))):
+        args = {**dict(k=k4, g=g3, delta=delta, counts=counts, state=state), **change}
+        with pytest.raises(ValueError, match="shape|dtype"):
+            aux_ops.gdn_commit_step(**args)
+
+    n = 5
+    mixed = torch.zeros(n, (2 * hk + hv) * 128, **bf16)
+    a, a_log = torch.zeros(n, hv, **bf16), torch.zeros(hv)
+    for change in (dict(a=torch.zeros(n + 1, hv, **bf16)), dict(b=torch.zeros(n, hv)), dict(a_log=torch.zeros(hv + 1)),
+                   dict(dt_bias=torch.zeros(hv, dtype=torch.float64)), dict(mixed=torch.zeros(n, 100, **bf16))):
+        args = {**dict(mixed=mixed, a=a, b=a, a_log=a_log, dt_bias=a_log, key_heads=hk, value_heads=hv), **change}
+        with pytest.raises(ValueError):
+            aux_ops.gdn_prepare_inputs(**args)
+    y = torch.zeros(7, 128, **bf16)
+    for change in (dict(z=torch.zeros(6, 128, **bf16)), dict(weight=torch.zeros(64, **bf16)), dict(y=torch.zeros(7, 64, **bf16))):
+        args = {**dict(y=y, z=y, weight=torch.zeros(128, **bf16)), **change}
+        with pytest.raises(ValueError):
+            aux_ops.rmsnorm_gated(**args)

@@ -3,6 +3,7 @@
 Skipped where fewer than two GPUs are visible; the host logic of both paths is covered on CPU by
 tests/test_multi_rank_cpu.py.  No TMA multicast is used anywhere in this repository.
 """
+import socket
 import subprocess
 import sys
 from pathlib import Path
@@ -18,9 +19,12 @@ def test_sequence_parallel_and_sharded_on_two_gpus():
         pytest.skip("needs two GPUs")
     world = min(4, torch.cuda.device_count())
     worker = Path(__file__).with_name("multi_gpu_worker.py")
+    with socket.socket() as probe:              # a port that is free right now, instead of a fixed one
+        probe.bind(("127.0.0.1", 0))
+        port = probe.getsockname()[1]
     run = subprocess.run(
         [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}",
-         "--master-addr", "127.0.0.1", "--master-port", "29533", str(worker)],
+         "--master-addr", "127.0.0.1", "--master-port", str(port), str(worker)],
         capture_output=True, text=True, timeout=600)
     lines = [line for line in run.stdout.splitlines() if line.startswith(("OK", "FAIL"))]
     assert run.returncode == 0, run.stderr[-3000:]
