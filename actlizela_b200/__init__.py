@@ -27,6 +27,7 @@ _MODULES = {
     "gdn_verify_step": "aux_ops",
     "gdn_commit_step": "aux_ops",
     "rmsnorm_gated": "aux_ops",
+    "out_proj_gemm": "aux_ops",
 }
 
 

@@ -46,6 +46,7 @@ EXPORTS = {
     "actlize_la_sm100_prepare_inputs": (_I, [_P, _LL] + [_P] * 9 + [_LL, _I, _I, _P]),
     "actlize_la_sm100_decode_step": (_I, [_P] * 7 + [_I] * 4 + [_P]),
     "actlize_la_sm100_rmsnorm_gated": (_I, [_P] * 4 + [_LL, _P]),
+    "actlize_la_sm100_out_proj": (_I, [_P] * 3 + [_I] * 3 + [_P]),
     "actlize_la_sm100_verify_step": (_I, [_P] * 8 + [_I] * 5 + [_P]),
     "actlize_la_sm100_commit_step": (_I, [_P] * 5 + [_I] * 5 + [_P]),
     "actlize_la_sm100_forward_static_scratch": (_I, [_P] * 8 + [_I] * 6 + [_P]),

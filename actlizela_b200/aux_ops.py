@@ -6,7 +6,10 @@
   (reference: actlize_la/reference/gdn_chunk_ref.py:135-143; csrc/serving/gdn.cu:152).
 * ``rmsnorm_gated``: ``y * rsqrt(mean y^2 + 1e-6) * weight * silu(z)`` per 128-wide row
   (reference: actlize_la.rmsnorm_gated, docs/OUTPUT_GATE.md:7-15).
-All three are single memory-bound kernels launched on the caller's current stream.
+* ``out_proj_gemm``: ``A @ W^T`` with BF16 operands, the output projection behind ``rmsnorm_gated``
+  (reference: actlize_la.out_proj_gemm / out_proj_gemm_cutlass, docs/OUTPUT_GATE.md:17-24).
+The first three are single memory-bound kernels, the last one a tcgen05 GEMM; all are launched on the caller's
+current stream.
 """
 from __future__ import annotations
 
@@ -199,3 +202,24 @@ def rmsnorm_gated(y, z, weight):
             y.data_ptr(), z.data_ptr(), weight.data_ptr(), out.data_ptr(), y.numel() // 128,
             torch.cuda.current_stream().cuda_stream))
     return out
+
+
+def out_proj_gemm(a, w):
+    """C = A @ W^T: A [M,K] BF16 row-major, W [N,K] BF16 (Linear weight layout), FP32 accumulation, C [M,N] BF16.
+    K and N must be multiples of 8.  One tcgen05 kernel on the caller's current stream."""
+    import torch
+    if a.ndim != 2 or w.ndim != 2:
+        raise ValueError("A must be [M,K] and W [N,K]")
+    m, k = a.shape
+    n = w.shape[0]
+    if min(m, n, k) < 1 or k % 8 or n % 8:
+        raise ValueError("sizes must be positive and K, N multiples of 8")
+    bf16 = (torch.bfloat16,)
+    device = _operands(("A", a, (m, k), bf16), ("W", w, (n, k), bf16))
+    lib = load_library()
+    lib.configure(device)
+    c = torch.empty((m, n), dtype=torch.bfloat16, device=device)
+    with torch.cuda.device(device):
+        lib.check(lib.lib.actlize_la_sm100_out_proj(a.data_ptr(), w.data_ptr(), c.data_ptr(), m, n, k,
+                                                    torch.cuda.current_stream().cuda_stream))
+    return c

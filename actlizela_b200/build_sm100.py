@@ -27,7 +27,7 @@ PACKAGE = Path(__file__).resolve().parent
 ROOT = PACKAGE.parent
 SOURCE = PACKAGE / "csrc" / "backends" / "sm100"
 INCLUDE = ROOT / "include"
-UNITS = ("abi.cu", "gdn_simt.cu", "gdn_umma.cu", "gdn_chain.cu", "gdn_aux.cu", "static_scratch.cu")
+UNITS = ("abi.cu", "gdn_simt.cu", "gdn_umma.cu", "gdn_aux.cu", "out_proj.cu", "static_scratch.cu")
 ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
 FLAGS = ["-std=c++17", "-O3", "-lineinfo", "--expt-relaxed-constexpr", "-Xcompiler", "-fPIC",
          "-DNDEBUG", *ARCH_FLAGS]

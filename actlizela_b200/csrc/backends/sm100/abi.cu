@@ -18,7 +18,7 @@ bool geometry_ok(int b, int t, int hk, int hv) {
   if (hk > INT_MAX / kDim || hv > INT_MAX / kDim) return false;
   const long long chunks = (t + kChunk - 1) / kChunk;
   const long long heads = (long long)b * hv;
-  if (heads > INT_MAX / 4 || heads * chunks > INT_MAX / kChunk) return false;   // flattened grids, 32-bit TMA rows
+  if (heads > INT_MAX / 8 || heads * chunks > INT_MAX / kDim) return false;     // flattened grids, 32-bit TMA rows
   if ((long long)b * t * hv * kDim > (1LL << 40)) return false;
   return true;
 }
@@ -39,7 +39,7 @@ constexpr int kWalkFlagMask = 0xc0, kHomogeneousBit = 0x40, kUntilDecayedBit = 0
 constexpr int kParallelShift = 16, kMaxParallel = 8;
 bool config_ok(int config) {
   const int segments = (config >> kSegmentShift) & 0xff, parallel = (config >> kParallelShift) & 0xf;
-  if (config < 0 || (config & 0xf) > 4 ||
+  if (config < 0 || (config & 0xf) > 3 ||
       (config & ~(kStageMask | kWalkFlagMask | 0xf | (0xff << kSegmentShift) | (0xf << kParallelShift))) != 0)
     return false;
   if ((config & kWalkFlagMask) && ((config & 0xf) != 1 || (config & kStageMask) != kWalkOnly)) return false;
@@ -53,7 +53,7 @@ int parallel_of(int config, int chunks) {
 }
 int segments_of(int config, const Geometry& geo) {
   int segments = (config >> kSegmentShift) & 0xff;
-  if (((config & 0xf) != 1 && (config & 0xf) != 4) || (config & kStageMask) || segments < 2) return 1;
+  if ((config & 0xf) != 1 || (config & kStageMask) || segments < 2) return 1;
   const int chunks = geo.chunks();
   return segments > chunks ? chunks : segments;
 }
@@ -94,16 +94,13 @@ int create_segment_streams() {
 }
 // bit 0: prepare stage uses tcgen05 (1) or CUDA cores (0); configuration ids:
 // 0 = simt/simt, 1 = umma/umma, 2 = simt prepare + umma walk, 3 = umma prepare + simt walk
-// 4 = chained tensor-core pair (prepare also emits G and the decay-scaled W; see gdn_chain.cu)
-bool is_chain(int config) { return (config & 0xf) == 4; }
 bool prepare_is_umma(int config) { return (config & 0xf) == 1 || (config & 0xf) == 3; }
 bool walk_is_umma(int config) { return (config & 0xf) == 1 || (config & 0xf) == 2; }
-int launch_prepare_tc(int config, const Inputs& in, const Geometry& geo, const Workspace& ws, cudaStream_t stream) {
-  if (in.mixed) return launch_prepare_fused(in, geo, ws, stream);
-  return is_chain(config) ? launch_prepare_chain(in, geo, ws, stream) : launch_prepare_umma(in, geo, ws, stream);
+int launch_prepare_tc(int, const Inputs& in, const Geometry& geo, const Workspace& ws, cudaStream_t stream) {
+  return in.mixed ? launch_prepare_fused(in, geo, ws, stream) : launch_prepare_umma(in, geo, ws, stream);
 }
-int launch_walk_tc(int config, const Inputs& in, const Geometry& geo, const Workspace& ws, cudaStream_t stream) {
-  return is_chain(config) ? launch_walk_chain(in, geo, ws, stream) : launch_walk_umma(in, geo, ws, stream);
+int launch_walk_tc(int, const Inputs& in, const Geometry& geo, const Workspace& ws, cudaStream_t stream) {
+  return launch_walk_umma(in, geo, ws, stream);
 }
 
 __global__ void apply_transition_kernel(const float* __restrict__ m, const float* __restrict__ off,
@@ -113,6 +110,21 @@ __global__ void apply_transition_kernel(const float* __restrict__ m, const float
   __shared__ float tile_s[32][128];
   const long long base = (long long)blockIdx.x * kDim * kDim;
   const int col = threadIdx.x % kDim, rhalf = threadIdx.x / kDim;
+  {
+    // a transition matrix of exact zeros (a segment that forgets its incoming state) leaves out = b
+    bool nonzero = false;
+    const float4* m4 = reinterpret_cast<const float4*>(m + base);
+    for (int e = threadIdx.x; e < kDim * kDim / 4; e += blockDim.x) {
+      const float4 x = m4[e];
+      nonzero |= (x.x != 0.f) | (x.y != 0.f) | (x.z != 0.f) | (x.w != 0.f);
+    }
+    if (!__syncthreads_or(nonzero)) {
+      const float4* b4 = reinterpret_cast<const float4*>(off + base);
+      float4* o4 = reinterpret_cast<float4*>(s_out + base);
+      for (int e = threadIdx.x; e < kDim * kDim / 4; e += blockDim.x) o4[e] = b4[e];
+      return;
+    }
+  }
   float acc[64];
 #pragma unroll
   for (int r = 0; r < 64; ++r) acc[r] = off[base + (rhalf * 64 + r) * kDim + col];
@@ -166,7 +178,7 @@ int map_status_page() {
   if ((e = cudaHostGetDevicePointer(reinterpret_cast<void**>(&on_device), g_status_pages[device], 0)) != cudaSuccess)
     return int(e);
   if (int rc = set_status_mirror_umma(on_device)) return rc;
-  if (int rc = set_status_mirror_chain(on_device)) return rc;
+  if (int rc = set_status_mirror_gemm(on_device)) return rc;
   g_status_mapped[device] = true;
   return 0;
 }
@@ -182,7 +194,7 @@ volatile int* status_page_of_current_device() {
 extern "C" int actlize_la_sm100_configure(void) {
   if (int rc = configure_simt()) return rc;
   if (int rc = configure_umma()) return rc;
-  if (int rc = configure_chain()) return rc;
+  if (int rc = configure_out_proj()) return rc;
   if (int rc = map_status_page()) return rc;
   return create_segment_streams();
 }
@@ -214,14 +226,14 @@ extern "C" int actlize_la_sm100_select(int b, int t, int hk, int hv, int gate_fp
 extern "C" long long actlize_la_sm100_workspace_bytes(int b, int t, int hk, int hv, int config) {
   if (!geometry_ok(b, t, hk, hv) || !config_ok(config)) return -1;
   const Geometry geo{b, t, hk, hv};
-  return workspace_bytes(geo, segments_of(config, geo), is_chain(config));
+  return workspace_bytes(geo, segments_of(config, geo));
 }
 
 extern "C" int actlize_la_sm100_launches_per_forward(int config) {
   if (!config_ok(config)) return -1;
   if (config & kStageMask) return 1;
   const int segments = (config >> kSegmentShift) & 0xff;
-  return (((config & 0xf) == 1 || (config & 0xf) == 4) && segments > 1) ? 2 * segments : 2;
+  return ((config & 0xf) == 1 && segments > 1) ? 2 * segments : 2;
 }
 
 extern "C" int actlize_la_sm100_selftest_wait_timeout(int tag, void* stream) {
@@ -238,7 +250,7 @@ extern "C" int actlize_la_sm100_device_status(int* status4, int reset) {
   if (reset) {
     for (int i = 0; i < 4; ++i) page[i] = 0;
     if (int rc = clear_device_status_umma()) return rc;
-    if (int rc = clear_device_status_chain()) return rc;
+    if (int rc = clear_device_status_gemm()) return rc;
   }
   return 0;
 }
@@ -282,7 +294,7 @@ extern "C" int actlize_la_sm100_forward_prepared(
   if (!geometry_ok(b, t, hk, hv) || !config_ok(config)) return int(cudaErrorInvalidValue);
   Geometry geo{b, t, hk, hv};
   const int segments = segments_of(config, geo);
-  if (workspace_bytes_given < workspace_bytes(geo, segments, is_chain(config))) return int(cudaErrorInvalidValue);
+  if (workspace_bytes_given < workspace_bytes(geo, segments)) return int(cudaErrorInvalidValue);
   if ((reinterpret_cast<uintptr_t>(workspace) & 255) || (reinterpret_cast<uintptr_t>(q) & 15) ||
       (reinterpret_cast<uintptr_t>(k) & 15) || (reinterpret_cast<uintptr_t>(v) & 15) ||
       (reinterpret_cast<uintptr_t>(output) & 15))
@@ -294,7 +306,7 @@ extern "C" int actlize_la_sm100_forward_prepared(
                   static_cast<const __nv_bfloat16*>(v), g, static_cast<const __nv_bfloat16*>(beta),
                   initial, static_cast<__nv_bfloat16*>(output), final_state, gate_fp32 ? 1 : 0,
                   ((config & kHomogeneousBit) ? kWalkHomogeneous : 0) | ((config & kUntilDecayedBit) ? kWalkUntilDecayed : 0)};
-  const Workspace ws = carve_workspace(workspace, geo, is_chain(config));
+  const Workspace ws = carve_workspace(workspace, geo);
   return run_forward(in, geo, ws, config, segments, static_cast<cudaStream_t>(opaque_stream));
 }
 
@@ -336,15 +348,12 @@ int run_forward(const Inputs& in, Geometry geo, const Workspace& ws, int config,
   geo.parallel = parallel_of(config, geo.segment_chunks());
   if (!(config & kWalkOnly)) {
     if (int rc = in.mixed                  ? launch_prepare_fused(in, geo, ws, stream)
-                 : is_chain(config)        ? launch_prepare_chain(in, geo, ws, stream)
                  : prepare_is_umma(config) ? launch_prepare_umma(in, geo, ws, stream)
                                            : launch_prepare_simt(in, geo, ws, stream))
       return rc;
   }
   if (config & kPrepareOnly) return 0;
-  return is_chain(config)       ? launch_walk_chain(in, geo, ws, stream)
-         : walk_is_umma(config) ? launch_walk_umma(in, geo, ws, stream)
-                                : launch_walk_simt(in, geo, ws, stream);
+  return walk_is_umma(config) ? launch_walk_umma(in, geo, ws, stream) : launch_walk_simt(in, geo, ws, stream);
 }
 }  // namespace
 
@@ -399,7 +408,7 @@ extern "C" long long actlize_la_sm100_varlen_workspace_bytes(long long total_tok
   if (total_tokens <= 0 || total_tokens > INT_MAX || n_seqs <= 0 || !geometry_ok(1, int(total_tokens), hk, hv)) return -1;
   // every sequence starts a new chunk, so each may add one partly filled chunk to ceil(total / 64)
   const long long max_chunks = (total_tokens + kChunk - 1) / kChunk + n_seqs;
-  if (max_chunks * hv > INT_MAX / kChunk || (long long)n_seqs * hv > INT_MAX / 4) return -1;
+  if (max_chunks * hv > INT_MAX / kDim || (long long)n_seqs * hv > INT_MAX / 8) return -1;
   return varlen_table_bytes(n_seqs) + max_chunks * hv * kBlockBytes;
 }
 
@@ -471,7 +480,7 @@ Arena arena_layout(int b, int t, int hk, int hv, int gate_fp32, int has_initial,
   a.output = take(vv);
   a.final_state = has_final ? take(st) : -1;
   const Geometry geo{b, t, hk, hv};
-  a.workspace = take(workspace_bytes(geo, segments_of(config, geo), is_chain(config)));
+  a.workspace = take(workspace_bytes(geo, segments_of(config, geo)));
   a.total = off;
   return a;
 }
@@ -516,7 +525,7 @@ extern "C" int actlize_la_sm100_forward_host(
                       initial ? reinterpret_cast<const float*>(base + a.initial) : nullptr,
                       reinterpret_cast<__nv_bfloat16*>(base + a.output),
                       final_state ? reinterpret_cast<float*>(base + a.final_state) : nullptr, gate_fp32 ? 1 : 0};
-      const Workspace ws = carve_workspace(base + a.workspace, geo, is_chain(config));
+      const Workspace ws = carve_workspace(base + a.workspace, geo);
       const int chunks = geo.chunks();
       const long long gate_bytes = gate_fp32 ? 4 : 2;
       if ((e = cudaEventRecord(ss.start, stream)) != cudaSuccess) return int(e);

@@ -50,17 +50,17 @@ __device__ __forceinline__ int varlen_sequence_of(const int* chunk_prefix, int c
 }
 
 // Workspace: structure-of-arrays planes, one entry per (batch, value head, chunk) block,
-// block index = (b * Hv + hv) * chunks + c.  Per block:
-//   w_hi, w_lo  BF16 [64][128]  W = T (beta K Gamma), split W ~= hi + lo          (token, key dim)
-//   u           FP32 [64][128]  U = T (beta V)                                    (token, value dim)
-//   qs          BF16 [64][128]  Q * exp(prefix) / sqrt(128)                       (token, key dim)
+// block index = (b * Hv + hv) * chunks + c.  W and U are stored TRANSPOSED (dimension-major), which is the
+// orientation the tensor-core kernels produce and consume them in: the prepare kernel's accumulators hold
+// W^T / U^T with the key / value index on the tensor-memory lanes, and the walk reads W^T as an MN-major B
+// operand and U^T one value row per thread.  Per block:
+//   w_hi, w_lo  BF16 [128][64]  W^T, W = T (beta K Gamma), split W ~= hi + lo        (key dim, token)
+//   u           FP32 [128][64]  U^T, U = T (beta V)                                  (value dim, token)
+//   qs          BF16 [64][128]  Q * exp(prefix) / sqrt(128)                          (token, key dim)
 //   p           BF16 [64][64]   tril(Q K^T * exp(prefix_i - prefix_j)) / sqrt(128)
 //   gates       FP32 [128]      [0,64): exp(prefix_last - prefix_i), 0 for padding rows;
 //                               [64]: exp(prefix_last); [65] (tcgen05 prepare only): non-zero when some token of the
 //                               chunk is not a contraction of the state (beta < 0 or beta |k|^2 > 2); rest unused
-//   g_hi, g_lo  BF16 [64][64]   only written by the chained configuration: G = W K_prev^T (token of this chunk,
-//                               token of the previous chunk), split G ~= hi + lo; in that configuration w_hi/w_lo
-//                               hold W scaled by the previous chunk's total decay (1 for the first chunk of a launch)
 // plus, when the sequence is walked in segments, one FP32 [128][128] state per (batch, value head)
 // that carries the state from one segment's walk to the next (K-by-V order, like the public state).
 struct Workspace {
@@ -70,22 +70,22 @@ struct Workspace {
   __nv_bfloat16* qs;
   __nv_bfloat16* p;
   float* gates;
-  __nv_bfloat16* g_hi;
-  __nv_bfloat16* g_lo;
   float* carry;
 };
+// element (token, dim) of a transposed [128][64] plane of block `block`
+__host__ __device__ inline long long transposed_index(long long block, int token, int dim) {
+  return block * (kChunk * kDim) + (long long)dim * kChunk + token;
+}
 
 constexpr long long kBlockBytes =
     2LL * kChunk * kDim * 2 + kChunk * kDim * 4 + kChunk * kDim * 2 + kChunk * kChunk * 2 + 128 * 4;
-constexpr long long kChainBlockBytes = 2LL * kChunk * kChunk * 2;     // g_hi, g_lo: chained configuration only
 
-inline __host__ long long workspace_bytes(const Geometry& g, int segments = 1, bool chained = false) {
-  return g.blocks() * (kBlockBytes + (chained ? kChainBlockBytes : 0)) +
-         (segments > 1 ? (long long)g.batch * g.value_heads * kDim * kDim * 4 : 0);
+inline __host__ long long workspace_bytes(const Geometry& g, int segments = 1) {
+  return g.blocks() * kBlockBytes + (segments > 1 ? (long long)g.batch * g.value_heads * kDim * kDim * 4 : 0);
 }
 
 // Carve the planes out of one caller-owned allocation (256-byte aligned base required).
-inline __host__ Workspace carve_workspace(void* base, const Geometry& g, bool chained = false) {
+inline __host__ Workspace carve_workspace(void* base, const Geometry& g) {
   char* p = static_cast<char*>(base);
   const long long n = g.blocks();
   Workspace w;
@@ -95,11 +95,6 @@ inline __host__ Workspace carve_workspace(void* base, const Geometry& g, bool ch
   w.qs = reinterpret_cast<__nv_bfloat16*>(p);    p += n * kChunk * kDim * 2;
   w.p = reinterpret_cast<__nv_bfloat16*>(p);     p += n * kChunk * kChunk * 2;
   w.gates = reinterpret_cast<float*>(p);         p += n * 128 * 4;
-  w.g_hi = w.g_lo = nullptr;
-  if (chained) {
-    w.g_hi = reinterpret_cast<__nv_bfloat16*>(p);  p += n * kChunk * kChunk * 2;
-    w.g_lo = reinterpret_cast<__nv_bfloat16*>(p);  p += n * kChunk * kChunk * 2;
-  }
   w.carry = reinterpret_cast<float*>(p);         // only backed by memory when segments > 1
   return w;
 }
@@ -174,19 +169,16 @@ int launch_prepare_umma(const Inputs&, const Geometry&, const Workspace&, cudaSt
 int launch_prepare_fused(const Inputs&, const Geometry&, const Workspace&, cudaStream_t);   // Inputs::mixed etc. set
 int launch_walk_umma(const Inputs&, const Geometry&, const Workspace&, cudaStream_t);
 int configure_umma();
-// chained configuration: the prepare stage also emits G and the decay-scaled W, and the walk forms
-// W S of chunk c+1 from the state of chunk c-1's end plus G (N*rel) without waiting for the new state
-int launch_prepare_chain(const Inputs&, const Geometry&, const Workspace&, cudaStream_t);
-int launch_walk_chain(const Inputs&, const Geometry&, const Workspace&, cudaStream_t);
-int configure_chain();
 int read_device_status(int* host_out4, int reset);
 int read_walk_plan_counts(int* host_out2, int reset);
 int launch_wait_timeout_selftest(int tag, cudaStream_t);
 int launch_walk_stall_selftest(const Inputs&, const Geometry&, const Workspace&, cudaStream_t);
 // host-visible failure record and poll limit, per translation unit that holds tensor-core kernels
 int set_status_mirror_umma(int* device_pointer);
-int set_status_mirror_chain(int* device_pointer);
 int clear_device_status_umma();
-int clear_device_status_chain();
+int set_status_mirror_gemm(int* device_pointer);
+int clear_device_status_gemm();
+// out_proj GEMM of the step after the path (out_proj.cu)
+int configure_out_proj();
 
 }  // namespace gdn_sm100

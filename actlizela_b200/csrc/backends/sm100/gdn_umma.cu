@@ -107,43 +107,43 @@ __device__ __forceinline__ float bf16_lo(uint32_t packed) { return __uint_as_flo
 __device__ __forceinline__ float bf16_hi(uint32_t packed) { return __uint_as_float(packed & 0xffff0000u); }
 
 // ================================================================================= prepare kernel
-// One CTA per (batch, value head, chunk) block, 256 threads, two CTAs per SM.  A warp owns the TMEM
-// lane quarter (warp & 3) and, of every accumulator it reads, the column half (warp >> 2).
+// One CTA per (batch, value head, chunk) block, 256 threads, THREE CTAs per SM (at most 80 registers, 67 KB of
+// shared memory, 128 tensor-memory columns): the phases of a block are serial and latency bound, so the
+// throughput comes from the blocks in flight.  A warp owns the TMEM lane quarter (warp & 3) and, of every
+// accumulator it reads, the column half (warp >> 2).
 //   phase 1  TMA: Q, K chunk tiles (key head of the group) and V tile; gate prefix by two warps
 //   phase 2  D1[128x64] = [Q;K] K^T                                  (one tcgen05 product, 8 instructions)
 //   phase 3  rows 0..63  -> P = tril(QK^T * decay)/sqrt(128) -> BF16 -> workspace
-//            rows 64..127-> A = tril(beta_i KK^T * decay, -1) -> shared (FP32); scaled query rows -> workspace
-//   phase 4  T = (I+A)^-1 in FP32 on the CUDA cores, blocked: four 16x16 diagonal solves in registers, then
-//            T21 = -T22 (A21 T11) at block size 16 and 32 (the blocked scheme of the reference's
+//            rows 64..127-> A = tril(beta_i KK^T * decay, -1) -> shared (FP32); scaled query rows -> workspace;
+//            the diagonal k_i.k_i decides whether token i is a contraction (word 65 of the gate vector)
+//   phase 4  T = (I+A)^-1 in FP32 on the CUDA cores, IN PLACE, blocked: four 16x16 diagonal solves in registers,
+//            then T21 = -T22 (A21 T11) at block size 16 and 32 (the blocked scheme of the reference's
 //            tests/wy_cpu.py:21-41, with plain FP32 products instead of TF32x3)
-//            T diag(beta exp(p)) and T diag(beta) -> BF16 hi/lo K-major tiles in shared memory
-//   phase 5  W^T = K^T (T diag(beta exp p))^T,  U^T = V^T (T diag(beta))^T   (A = transposed K / V tiles)
-//   phase 6  accumulators -> W hi/lo BF16, U FP32 staged in shared memory, TMA stores; gate vector -> workspace
-// Chained variant (kChained): W is multiplied by the previous chunk's total decay (clamped below at 2^-100 so
-// that it can be divided out again; 1 for the first chunk of the launch) before it is split, and
-//   phase 7  G = W K_prev^T / scale from the staged [W_hi ; W_lo] tiles (one M = 128 product whose two lane
-//            halves are added through shared memory) -> BF16 hi/lo -> workspace
+//            T diag(beta exp(p)) and T diag(beta) -> BF16 hi/lo K-major tiles: the first pair over the dead Q
+//            boxes, the second over T itself (every thread holds its part of T in registers by then)
+//   phase 5  W^T = K^T (T diag(beta exp p))^T (into the columns D1 occupied),  U^T = V^T (T diag(beta))^T
+//            (A = transposed K / V tiles)
+//   phase 6  accumulators -> registers -> workspace.  The planes are stored transposed, [key or value dim][token]:
+//            a thread owns one row and writes its 32 tokens as contiguous 16-byte pieces; no staging, no transposition
 struct PrepLayout {
   static constexpr int kQ0 = 0, kK0 = kBox, kQ1 = 2 * kBox, kK1 = 3 * kBox;   // [Q;K] stacked, two K atoms
   static constexpr int kV0 = 4 * kBox, kV1 = 5 * kBox;
-  static constexpr int kLd = 68;                           // row pitch (floats) of the FP32 64x64 matrices
-  static constexpr int kA = 6 * kBox;                      // float [64][68]: A, row-major
-  static constexpr int kTwH = 6 * kBox, kTwL = 7 * kBox;   // written after A is dead
-  static constexpr int kTuH = 6 * kBox + 18 * 1024, kTuL = kTuH + kBox;
-  static constexpr int kT = kTuL + kBox;                   // float [64][68]: T, row-major
-  static constexpr int kX = kQ0;                           // block products, reuse the Q boxes after phase 3
+  static constexpr int kLd = 68;                           // row pitch (floats) of the FP32 64x64 matrix
+  static constexpr int kAT = 6 * kBox;                     // float [64][68]: A, then T in place
+  static constexpr int kTwH = kQ0, kTwL = kQ1;             // written after phase 4, when Q and the scratch are dead
+  static constexpr int kTuH = kAT, kTuL = kAT + kBox;      // written once T sits in registers
+  static constexpr int kX = kQ0;                           // block products of the inverse, on the dead Q box
   static constexpr int kLdX = 20, kLdX3 = 36;
-  static constexpr int kVec = kT + 64 * kLd * 4;           // float [4][64]: pl2, beta, beta*exp(p), exp(p)/sqrt(128)
-  static constexpr int kBars = kVec + 4 * 64 * 4;          // 2 mbarriers, tmem slot, abort flag, carry, 2 sums
+  static constexpr int kVec = kAT + 64 * kLd * 4;          // float [4][64]: pl2, beta, beta*exp(p), exp(p)/sqrt(128)
+  static constexpr int kBars = kVec + 4 * 64 * 4;          // 2 mbarriers, tmem slot, abort flag, carry
   static constexpr int kTotal = kBars + 64;
-  // chained variant: previous chunk's K tile (two boxes) lands on T once T is dead; the lane halves of the
-  // G product are added through a float [64][64] scratch on the dead T diag(beta) tiles
-  static constexpr int kKprev = kT, kGsum = kTuH;
-  static_assert(kKprev % 1024 == 0 && 2 * kBox <= 64 * kLd * 4, "previous K tile must fit on T, box aligned");
+  static_assert(2 * kBox <= 64 * kLd * 4 && kAT % 1024 == 0, "the U pair of T tiles must fit on T, box aligned");
+  static_assert(32 * kLdX3 * 4 <= kBox && 32 * kLdX * 4 <= kBox, "block-product scratch must fit in one Q box");
 };
 constexpr int kPrepThreads = 256;
 constexpr int kPrepSmem = PrepLayout::kTotal + 1024;
-constexpr int kPrepTmemCols = 256;   // D1 [0,64)  DW [64,128)  DU [128,192)  DG [192,256)
+constexpr int kPrepTmemCols = 128;   // D1 [0,64), later W^T;  U^T [64,128)
+static_assert(3 * (kPrepSmem + 1024) <= 227 * 1024, "three prepare CTAs must fit in one SM's shared memory");
 
 #ifdef GDN_SM100_PHASE_TIMING
 #define GDN_PSTAMP(slot) \
@@ -155,18 +155,15 @@ constexpr int kPrepTmemCols = 256;   // D1 [0,64)  DW [64,128)  DU [128,192)  DG
 // Fused variant (kFused): the tiles come from the packed projection rows (tm_q is a 2-D map over them, tm_k the 4-D
 // map of the normalised-key plane that the walk reads); Q and K rows are L2-normalised in shared memory with the
 // arithmetic of the separate input-preparation kernel (16 lanes per row), gate and beta are activated on load.
-template <bool kChained, bool kFused>
-__global__ void __launch_bounds__(kPrepThreads, 2)
+template <bool kFused>
+__global__ void __launch_bounds__(kPrepThreads, 3)
 prepare_umma_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
-                    const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_wh,
-                    const __grid_constant__ CUtensorMap tm_wl, const __grid_constant__ CUtensorMap tm_u,
-                    Inputs in, Geometry geo, Workspace ws) {
+                    const __grid_constant__ CUtensorMap tm_v, Inputs in, Geometry geo, Workspace ws) {
   // Indexing the declared array (no integer round trip) keeps these accesses in the shared state space.
   extern __shared__ __align__(1024) uint8_t raw_smem[];
   uint8_t* sm = raw_smem + ((1024u - (smem_u32(raw_smem) & 1023u)) & 1023u);
   using L = PrepLayout;
-  float* sA = reinterpret_cast<float*>(sm + L::kA);
-  float* sT = reinterpret_cast<float*>(sm + L::kT);
+  float* sAT = reinterpret_cast<float*>(sm + L::kAT);
   float* sX = reinterpret_cast<float*>(sm + L::kX);
   float* s_pl2 = reinterpret_cast<float*>(sm + L::kVec);
   float* s_beta = s_pl2 + 64;
@@ -247,17 +244,6 @@ prepare_umma_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
       beta = __bfloat162float(in.beta[gi]);
     }
   }
-  if (kChained && warp >= 2 && warp < 4) {
-    // total log-decay of the previous chunk (always a full chunk), summed by warps 2 and 3
-    float prev = 0.f;
-    if (chunk > geo.chunk_begin) {
-      const long long gi = ((long long)b * geo.sequence + t0 - kChunk + (tid - 64)) * geo.value_heads + hv;
-      prev = load_gate(in.g, gi, in.gate_fp32);
-    }
-#pragma unroll
-    for (int d = 16; d > 0; d >>= 1) prev += __shfl_xor_sync(0xffffffffu, prev, d);
-    if ((tid & 31) == 0) carry[warp - 1] = prev;
-  }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
@@ -331,79 +317,80 @@ prepare_umma_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
   const uint32_t taddr = tmem + (uint32_t(quarter * 32) << 16);
   bool not_contraction = false;
   if (ok) {
-    const int i = lrow & 63, j0 = chalf * 32;
-    const float pi = s_pl2[i];
-    uint32_t d[32];
-    tmem_ld32(taddr + j0, d);
-    float pj[32];
-#pragma unroll
-    for (int q4 = 0; q4 < 8; ++q4) {
-      const float4 t = *reinterpret_cast<const float4*>(s_pl2 + j0 + q4 * 4);
-      pj[q4 * 4] = t.x; pj[q4 * 4 + 1] = t.y; pj[q4 * 4 + 2] = t.z; pj[q4 * 4 + 3] = t.w;
-    }
+    const int i = lrow & 63;
+    const float pi = s_pl2[i], bi = s_beta[i];
+    uint32_t d[2][16];
+    tmem_ld16(taddr + chalf * 32, d[0]);
+    tmem_ld16(taddr + chalf * 32 + 16, d[1]);
     tmem_wait_ld();
-    if (lrow < 64) {
-      uint32_t packed[16];
+    float kk = 0.f;                                      // k_i . k_i when the diagonal lies in this column half
 #pragma unroll
-      for (int jj = 0; jj < 32; jj += 2) {
-        const int j = j0 + jj;
-        const float a0 = (j <= i) ? __uint_as_float(d[jj]) * fast_exp2(pi - pj[jj]) * kScale : 0.f;
-        const float a1 = (j + 1 <= i) ? __uint_as_float(d[jj + 1]) * fast_exp2(pi - pj[jj + 1]) * kScale : 0.f;
-        packed[jj >> 1] = pack_bf16(a0, a1);
+    for (int piece = 0; piece < 2; ++piece) {
+      const int j0 = chalf * 32 + piece * 16;
+      float pj[16];
+#pragma unroll
+      for (int q4 = 0; q4 < 4; ++q4) {
+        const float4 t = *reinterpret_cast<const float4*>(s_pl2 + j0 + q4 * 4);
+        pj[q4 * 4] = t.x; pj[q4 * 4 + 1] = t.y; pj[q4 * 4 + 2] = t.z; pj[q4 * 4 + 3] = t.w;
       }
-      uint4* dst = reinterpret_cast<uint4*>(ws.p + (block * kChunk + i) * kChunk + j0);
+      if (lrow < 64) {
+        uint32_t packed[8];
 #pragma unroll
-      for (int q4 = 0; q4 < 4; ++q4)
-        dst[q4] = make_uint4(packed[q4 * 4], packed[q4 * 4 + 1], packed[q4 * 4 + 2], packed[q4 * 4 + 3]);
-    } else {
-      const float bi = s_beta[i];
-      float* arow = sA + i * L::kLd + j0;
-      float kk = 0.f;                                    // k_i . k_i when the diagonal lies in this column half
-#pragma unroll
-      for (int q4 = 0; q4 < 8; ++q4) {
-        float a[4];
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const int jj = q4 * 4 + e;
-          a[e] = (j0 + jj < i) ? bi * __uint_as_float(d[jj]) * fast_exp2(pi - pj[jj]) : 0.f;
-          if (j0 + jj == i) kk = __uint_as_float(d[jj]);
+        for (int jj = 0; jj < 16; jj += 2) {
+          const int j = j0 + jj;
+          const float a0 = (j <= i) ? __uint_as_float(d[piece][jj]) * fast_exp2(pi - pj[jj]) * kScale : 0.f;
+          const float a1 = (j + 1 <= i) ? __uint_as_float(d[piece][jj + 1]) * fast_exp2(pi - pj[jj + 1]) * kScale : 0.f;
+          packed[jj >> 1] = pack_bf16(a0, a1);
         }
-        *reinterpret_cast<float4*>(arow + q4 * 4) = make_float4(a[0], a[1], a[2], a[3]);
+        uint4* dst = reinterpret_cast<uint4*>(ws.p + (block * kChunk + i) * kChunk + j0);
+        dst[0] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+        dst[1] = make_uint4(packed[4], packed[5], packed[6], packed[7]);
+      } else {
+        float* arow = sAT + i * L::kLd + j0;
+#pragma unroll
+        for (int q4 = 0; q4 < 4; ++q4) {
+          float a[4];
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const int jj = q4 * 4 + e;
+            a[e] = (j0 + jj < i) ? bi * __uint_as_float(d[piece][jj]) * fast_exp2(pi - pj[jj]) : 0.f;
+            if (j0 + jj == i) kk = __uint_as_float(d[piece][jj]);
+          }
+          *reinterpret_cast<float4*>(arow + q4 * 4) = make_float4(a[0], a[1], a[2], a[3]);
+        }
       }
-      // token i multiplies the state by exp(g_i) (I - beta_i k_i k_i^T): a contraction iff 0 <= beta_i |k_i|^2 <= 2
-      not_contraction = !(bi >= 0.f && bi * kk <= 2.f);
     }
+    tc_fence_before();      // D1's columns are overwritten by the W^T product once every thread has passed the barriers
+    // token i multiplies the state by exp(g_i) (I - beta_i k_i k_i^T): a contraction iff 0 <= beta_i |k_i|^2 <= 2
+    if (lrow >= 64) not_contraction = !(bi >= 0.f && bi * kk <= 2.f);
     {
       // scaled query: row = tid/4, a quarter row (4 x 16 bytes of one TMA box row) per thread
       const int row = tid >> 2, half = (tid >> 1) & 1, sub = tid & 1;
       const float qs = s_qscale[row];
       const uint8_t* src = sm + (half ? L::kQ1 : L::kQ0) + row * 128;
       __nv_bfloat16* dst = ws.qs + (block * kChunk + row) * kDim + half * 64 + sub * 32;
-      uint4 v[4];
-#pragma unroll
-      for (int cc = 0; cc < 4; ++cc)
-        v[cc] = *reinterpret_cast<const uint4*>(src + (((sub * 4 + cc) ^ (row & 7)) << 4));
 #pragma unroll
       for (int cc = 0; cc < 4; ++cc) {
+        const uint4 v = *reinterpret_cast<const uint4*>(src + (((sub * 4 + cc) ^ (row & 7)) << 4));
         uint4 o;
-        o.x = pack_bf16(bf16_lo(v[cc].x) * qs, bf16_hi(v[cc].x) * qs);
-        o.y = pack_bf16(bf16_lo(v[cc].y) * qs, bf16_hi(v[cc].y) * qs);
-        o.z = pack_bf16(bf16_lo(v[cc].z) * qs, bf16_hi(v[cc].z) * qs);
-        o.w = pack_bf16(bf16_lo(v[cc].w) * qs, bf16_hi(v[cc].w) * qs);
+        o.x = pack_bf16(bf16_lo(v.x) * qs, bf16_hi(v.x) * qs);
+        o.y = pack_bf16(bf16_lo(v.y) * qs, bf16_hi(v.y) * qs);
+        o.z = pack_bf16(bf16_lo(v.z) * qs, bf16_hi(v.z) * qs);
+        o.w = pack_bf16(bf16_lo(v.w) * qs, bf16_hi(v.w) * qs);
         *reinterpret_cast<uint4*>(dst + cc * 8) = o;
       }
     }
-    for (int e = tid; e < 64 * L::kLd / 4; e += kPrepThreads)
-      reinterpret_cast<float4*>(sT)[e] = make_float4(0.f, 0.f, 0.f, 0.f);
   }
   const int chunk_not_contraction = __syncthreads_or(not_contraction);
+  ok = __syncthreads_and(ok);                  // uniform from here on: the warp-level barrier below needs that
   GDN_PSTAMP(3);
 
-  // ---- phase 4: T = (I+A)^-1, blocked 16 -> 32 -> 64, all in FP32 on the CUDA cores
-  // level 1: the four 16x16 diagonal blocks, one column per thread (left-looking, in registers)
+  // ---- phase 4: T = (I+A)^-1 in place, blocked 16 -> 32 -> 64, all in FP32 on the CUDA cores
+  // level 1: the four 16x16 diagonal blocks, one column per thread (left-looking, in registers); the 16 threads
+  // of a block sit in one warp and overwrite the block only after all of them have read it
   if (ok && tid < 64) {
     const int blk = tid >> 4, c = tid & 15;
-    const float* a0 = sA + (blk * 16) * L::kLd + blk * 16;
+    float* a0 = sAT + (blk * 16) * L::kLd + blk * 16;
     float x[16];
     float4 cur[4], nxt[4] = {};
 #pragma unroll
@@ -425,13 +412,13 @@ prepare_umma_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
 #pragma unroll
       for (int q = 0; q < 4; ++q) cur[q] = nxt[q];
     }
-    float* t0 = sT + (blk * 16) * L::kLd + blk * 16 + c;
+    __syncwarp();
 #pragma unroll
-    for (int i = 0; i < 16; ++i) t0[i * L::kLd] = x[i];
+    for (int i = 0; i < 16; ++i) a0[i * L::kLd + c] = x[i];
   }
   __syncthreads();
   GDN_PSTAMP(7);
-  // level 2: inside each 32x32 diagonal block, T21 = -T22 (A21 T11) with 16x16 blocks;
+  // level 2: inside each 32x32 diagonal block, T21 = -T22 (A21 T11) with 16x16 blocks, written where A21 was;
   // thread -> (block, row i, column pair)
   {
     const int big = tid >> 7, i = (tid & 127) >> 3, cg = tid & 7;
@@ -439,40 +426,36 @@ prepare_umma_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
     float a[16];
     float2 acc = make_float2(0.f, 0.f);
     if (ok) {
-      const float* arow = sA + (o + 16 + i) * L::kLd + o;
-      float2 t[16];
+      const float* arow = sAT + (o + 16 + i) * L::kLd + o;
 #pragma unroll
       for (int q4 = 0; q4 < 4; ++q4) {
         const float4 v = *reinterpret_cast<const float4*>(arow + q4 * 4);
         a[q4 * 4] = v.x; a[q4 * 4 + 1] = v.y; a[q4 * 4 + 2] = v.z; a[q4 * 4 + 3] = v.w;
       }
 #pragma unroll
-      for (int k = 0; k < 16; ++k) t[k] = *reinterpret_cast<const float2*>(sT + (o + k) * L::kLd + o + cg * 2);
-#pragma unroll
       for (int k = 0; k < 16; ++k) {
-        acc.x = fmaf(a[k], t[k].x, acc.x);
-        acc.y = fmaf(a[k], t[k].y, acc.y);
+        const float2 t = *reinterpret_cast<const float2*>(sAT + (o + k) * L::kLd + o + cg * 2);
+        acc.x = fmaf(a[k], t.x, acc.x);
+        acc.y = fmaf(a[k], t.y, acc.y);
       }
       *reinterpret_cast<float2*>(sX + (big * 16 + i) * L::kLdX + cg * 2) = acc;
     }
     __syncthreads();
     if (ok) {
-      const float* trow = sT + (o + 16 + i) * L::kLd + o + 16;
-      float2 t[16];
+      const float* trow = sAT + (o + 16 + i) * L::kLd + o + 16;
 #pragma unroll
       for (int q4 = 0; q4 < 4; ++q4) {
         const float4 v = *reinterpret_cast<const float4*>(trow + q4 * 4);
         a[q4 * 4] = v.x; a[q4 * 4 + 1] = v.y; a[q4 * 4 + 2] = v.z; a[q4 * 4 + 3] = v.w;
       }
-#pragma unroll
-      for (int k = 0; k < 16; ++k) t[k] = *reinterpret_cast<const float2*>(sX + (big * 16 + k) * L::kLdX + cg * 2);
       acc = make_float2(0.f, 0.f);
 #pragma unroll
       for (int k = 0; k < 16; ++k) {
-        acc.x = fmaf(a[k], t[k].x, acc.x);
-        acc.y = fmaf(a[k], t[k].y, acc.y);
+        const float2 t = *reinterpret_cast<const float2*>(sX + (big * 16 + k) * L::kLdX + cg * 2);
+        acc.x = fmaf(a[k], t.x, acc.x);
+        acc.y = fmaf(a[k], t.y, acc.y);
       }
-      *reinterpret_cast<float2*>(sT + (o + 16 + i) * L::kLd + o + cg * 2) = make_float2(-acc.x, -acc.y);
+      *reinterpret_cast<float2*>(sAT + (o + 16 + i) * L::kLd + o + cg * 2) = make_float2(-acc.x, -acc.y);
     }
   }
   __syncthreads();
@@ -480,110 +463,103 @@ prepare_umma_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
   // level 3: T21 = -T22 (A21 T11) with 32x32 blocks; thread -> row i, four columns
   {
     const int i = tid >> 3, cg = tid & 7;
-    float a[32];
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
     if (ok) {
-      const float* arow = sA + (32 + i) * L::kLd;
-#pragma unroll
-      for (int q4 = 0; q4 < 8; ++q4) {
-        const float4 v = *reinterpret_cast<const float4*>(arow + q4 * 4);
-        a[q4 * 4] = v.x; a[q4 * 4 + 1] = v.y; a[q4 * 4 + 2] = v.z; a[q4 * 4 + 3] = v.w;
-      }
+      const float* arow = sAT + (32 + i) * L::kLd;
 #pragma unroll
       for (int k0 = 0; k0 < 32; k0 += 8) {
-        float4 t[8];
-#pragma unroll
-        for (int k = 0; k < 8; ++k) t[k] = *reinterpret_cast<const float4*>(sT + (k0 + k) * L::kLd + cg * 4);
+        const float4 a0 = *reinterpret_cast<const float4*>(arow + k0), a1 = *reinterpret_cast<const float4*>(arow + k0 + 4);
+        const float a[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
 #pragma unroll
         for (int k = 0; k < 8; ++k) {
-          acc.x = fmaf(a[k0 + k], t[k].x, acc.x); acc.y = fmaf(a[k0 + k], t[k].y, acc.y);
-          acc.z = fmaf(a[k0 + k], t[k].z, acc.z); acc.w = fmaf(a[k0 + k], t[k].w, acc.w);
+          const float4 t = *reinterpret_cast<const float4*>(sAT + (k0 + k) * L::kLd + cg * 4);
+          acc.x = fmaf(a[k], t.x, acc.x); acc.y = fmaf(a[k], t.y, acc.y);
+          acc.z = fmaf(a[k], t.z, acc.z); acc.w = fmaf(a[k], t.w, acc.w);
         }
       }
       *reinterpret_cast<float4*>(sX + i * L::kLdX3 + cg * 4) = acc;
     }
     __syncthreads();
     if (ok) {
-      const float* trow = sT + (32 + i) * L::kLd + 32;
-#pragma unroll
-      for (int q4 = 0; q4 < 8; ++q4) {
-        const float4 v = *reinterpret_cast<const float4*>(trow + q4 * 4);
-        a[q4 * 4] = v.x; a[q4 * 4 + 1] = v.y; a[q4 * 4 + 2] = v.z; a[q4 * 4 + 3] = v.w;
-      }
+      const float* trow = sAT + (32 + i) * L::kLd + 32;
       acc = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
       for (int k0 = 0; k0 < 32; k0 += 8) {
-        float4 t[8];
-#pragma unroll
-        for (int k = 0; k < 8; ++k) t[k] = *reinterpret_cast<const float4*>(sX + (k0 + k) * L::kLdX3 + cg * 4);
+        const float4 a0 = *reinterpret_cast<const float4*>(trow + k0), a1 = *reinterpret_cast<const float4*>(trow + k0 + 4);
+        const float a[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
 #pragma unroll
         for (int k = 0; k < 8; ++k) {
-          acc.x = fmaf(a[k0 + k], t[k].x, acc.x); acc.y = fmaf(a[k0 + k], t[k].y, acc.y);
-          acc.z = fmaf(a[k0 + k], t[k].z, acc.z); acc.w = fmaf(a[k0 + k], t[k].w, acc.w);
+          const float4 t = *reinterpret_cast<const float4*>(sX + (k0 + k) * L::kLdX3 + cg * 4);
+          acc.x = fmaf(a[k], t.x, acc.x); acc.y = fmaf(a[k], t.y, acc.y);
+          acc.z = fmaf(a[k], t.z, acc.z); acc.w = fmaf(a[k], t.w, acc.w);
         }
       }
-      *reinterpret_cast<float4*>(sT + (32 + i) * L::kLd + cg * 4) = make_float4(-acc.x, -acc.y, -acc.z, -acc.w);
+      *reinterpret_cast<float4*>(sAT + (32 + i) * L::kLd + cg * 4) = make_float4(-acc.x, -acc.y, -acc.z, -acc.w);
     }
   }
   __syncthreads();
   GDN_PSTAMP(9);
-  // T diag(beta exp p) and T diag(beta) as BF16 hi/lo K-major tiles (these overwrite the A matrix);
-  // thread -> row i, sixteen columns
-  if (ok) {
+  // T diag(beta exp p) and T diag(beta) as BF16 hi/lo K-major tiles; thread -> row i, sixteen columns.
+  // The W pair goes to the Q boxes at once; the U pair overwrites T, so it waits until every thread has read its part.
+  {
     const int i = tid >> 2, c0 = (tid & 3) * 16;
-    float t[16], cw[16], cu[16];
+    uint32_t uh[8], ul[8];
+    if (ok) {
 #pragma unroll
-    for (int q4 = 0; q4 < 4; ++q4) {
-      const float4 tv = *reinterpret_cast<const float4*>(sT + i * L::kLd + c0 + q4 * 4);
-      const float4 wv = *reinterpret_cast<const float4*>(s_coefw + c0 + q4 * 4);
-      const float4 uv = *reinterpret_cast<const float4*>(s_beta + c0 + q4 * 4);
-      t[q4 * 4] = tv.x; t[q4 * 4 + 1] = tv.y; t[q4 * 4 + 2] = tv.z; t[q4 * 4 + 3] = tv.w;
-      cw[q4 * 4] = wv.x; cw[q4 * 4 + 1] = wv.y; cw[q4 * 4 + 2] = wv.z; cw[q4 * 4 + 3] = wv.w;
-      cu[q4 * 4] = uv.x; cu[q4 * 4 + 1] = uv.y; cu[q4 * 4 + 2] = uv.z; cu[q4 * 4 + 3] = uv.w;
-    }
+      for (int g8 = 0; g8 < 2; ++g8) {
+        const int c = c0 + g8 * 8;
+        float t[8], cw[8], cu[8];
 #pragma unroll
-    for (int g8 = 0; g8 < 2; ++g8) {
-      uint32_t wh[4], wl[4], uh[4], ul[4];
+        for (int q4 = 0; q4 < 2; ++q4) {
+          const float4 tv = *reinterpret_cast<const float4*>(sAT + i * L::kLd + c + q4 * 4);
+          const float4 wv = *reinterpret_cast<const float4*>(s_coefw + c + q4 * 4);
+          const float4 uv = *reinterpret_cast<const float4*>(s_beta + c + q4 * 4);
+          t[q4 * 4] = tv.x; t[q4 * 4 + 1] = tv.y; t[q4 * 4 + 2] = tv.z; t[q4 * 4 + 3] = tv.w;
+          cw[q4 * 4] = wv.x; cw[q4 * 4 + 1] = wv.y; cw[q4 * 4 + 2] = wv.z; cw[q4 * 4 + 3] = wv.w;
+          cu[q4 * 4] = uv.x; cu[q4 * 4 + 1] = uv.y; cu[q4 * 4 + 2] = uv.z; cu[q4 * 4 + 3] = uv.w;
+        }
+        uint32_t wh[4], wl[4];
 #pragma unroll
-      for (int e = 0; e < 8; e += 2) {
-        const int x = g8 * 8 + e;
-        const float w0 = t[x] * cw[x], w1 = t[x + 1] * cw[x + 1];
-        const float u0 = t[x] * cu[x], u1 = t[x + 1] * cu[x + 1];
-        const uint32_t hw = pack_bf16(w0, w1), hu = pack_bf16(u0, u1);
-        wh[e >> 1] = hw;
-        wl[e >> 1] = pack_bf16(w0 - bf16_lo(hw), w1 - bf16_hi(hw));
-        uh[e >> 1] = hu;
-        ul[e >> 1] = pack_bf16(u0 - bf16_lo(hu), u1 - bf16_hi(hu));
+        for (int e = 0; e < 8; e += 2) {
+          const float w0 = t[e] * cw[e], w1 = t[e + 1] * cw[e + 1];
+          const float u0 = t[e] * cu[e], u1 = t[e + 1] * cu[e + 1];
+          const uint32_t hw = pack_bf16(w0, w1), hu = pack_bf16(u0, u1);
+          wh[e >> 1] = hw;
+          wl[e >> 1] = pack_bf16(w0 - bf16_lo(hw), w1 - bf16_hi(hw));
+          uh[g8 * 4 + (e >> 1)] = hu;
+          ul[g8 * 4 + (e >> 1)] = pack_bf16(u0 - bf16_lo(hu), u1 - bf16_hi(hu));
+        }
+        const int off = i * 128 + (((c >> 3) ^ (i & 7)) << 4);
+        *reinterpret_cast<uint4*>(sm + L::kTwH + off) = make_uint4(wh[0], wh[1], wh[2], wh[3]);
+        *reinterpret_cast<uint4*>(sm + L::kTwL + off) = make_uint4(wl[0], wl[1], wl[2], wl[3]);
       }
-      const int c = c0 + g8 * 8;
-      const int off = i * 128 + (((c >> 3) ^ (i & 7)) << 4);
-      *reinterpret_cast<uint4*>(sm + L::kTwH + off) = make_uint4(wh[0], wh[1], wh[2], wh[3]);
-      *reinterpret_cast<uint4*>(sm + L::kTwL + off) = make_uint4(wl[0], wl[1], wl[2], wl[3]);
-      *reinterpret_cast<uint4*>(sm + L::kTuH + off) = make_uint4(uh[0], uh[1], uh[2], uh[3]);
-      *reinterpret_cast<uint4*>(sm + L::kTuL + off) = make_uint4(ul[0], ul[1], ul[2], ul[3]);
     }
-    fence_proxy_async_smem();
+    __syncthreads();
+    if (ok) {
+#pragma unroll
+      for (int g8 = 0; g8 < 2; ++g8) {
+        const int c = c0 + g8 * 8;
+        const int off = i * 128 + (((c >> 3) ^ (i & 7)) << 4);
+        *reinterpret_cast<uint4*>(sm + L::kTuH + off) = make_uint4(uh[g8 * 4], uh[g8 * 4 + 1], uh[g8 * 4 + 2], uh[g8 * 4 + 3]);
+        *reinterpret_cast<uint4*>(sm + L::kTuL + off) = make_uint4(ul[g8 * 4], ul[g8 * 4 + 1], ul[g8 * 4 + 2], ul[g8 * 4 + 3]);
+      }
+      fence_proxy_async_smem();
+    }
   }
   __syncthreads();
   GDN_PSTAMP(4);
 
-  // ---- phase 5: W^T and U^T
+  // ---- phase 5: W^T (into D1's columns, which every thread has read) and U^T
   if (tid == 0 && ok) {
     tc_fence_after();
     const uint32_t base = smem_u32(sm);
-    if (kChained) {
-      // T is dead: fetch the previous chunk's K tile onto it (rows before the sequence start read as zero)
-      mbar_arrive_expect_tx(bar_tma, 2 * kBox);
-      tma_load_4d(sm + L::kKprev, &tm_k, bar_tma, 0, hk, t0 - kChunk, b);
-      tma_load_4d(sm + L::kKprev + kBox, &tm_k, bar_tma, 64, hk, t0 - kChunk, b);
-    }
 #pragma unroll
     for (int part = 0; part < 2; ++part) {
 #pragma unroll
       for (int ks = 0; ks < 4; ++ks) {
         const uint64_t a = smem_desc(base + L::kK0 + ks * 2048, L::kK1 - L::kK0, 1024);
         const uint64_t bb = smem_desc(base + (part ? L::kTwL : L::kTwH) + ks * 32, 16, 1024);
-        mma_ss(tmem + 64, a, bb, kIdescN64AT, (part | ks) != 0);
+        mma_ss(tmem + 0, a, bb, kIdescN64AT, (part | ks) != 0);
       }
     }
 #pragma unroll
@@ -592,117 +568,53 @@ prepare_umma_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
       for (int ks = 0; ks < 4; ++ks) {
         const uint64_t a = smem_desc(base + L::kV0 + ks * 2048, L::kV1 - L::kV0, 1024);
         const uint64_t bb = smem_desc(base + (part ? L::kTuL : L::kTuH) + ks * 32, 16, 1024);
-        mma_ss(tmem + 128, a, bb, kIdescN64AT, (part | ks) != 0);
+        mma_ss(tmem + 64, a, bb, kIdescN64AT, (part | ks) != 0);
       }
     }
-    if (kFused) tma_store_wait_read();      // the key tile's store has left shared memory before staging reuses it
     mma_commit(bar_mma);
   }
-  ok = ok && mbar_wait(bar_mma, 1, abort, 3, chunk);
-  tc_fence_after();
-  GDN_PSTAMP(5);
-
-  // ---- phase 6: W (hi/lo) and U leave through shared memory and TMA stores; every input tile is dead
-  // by now, so the staging boxes reuse their space: per 64-wide key atom [W hi | W lo] (0, 8K | 16K, 24K),
-  // U [32K,64K).
-  float w_scale = 1.f;
-  if (kChained && chunk > geo.chunk_begin) w_scale = fmaxf(exp2f((carry[1] + carry[2]) * kLog2e), 0x1p-100f);
+  // the gate vector does not depend on the products: write it while they run
   if (ok) {
-    const int tk0 = chalf * 32;
-    uint32_t dw[32], du[32];
-    tmem_ld32(taddr + 64 + tk0, dw);
-    tmem_ld32(taddr + 128 + tk0, du);
-    tmem_wait_ld();
-    // lrow is the key (W) / value (U) index; W boxes are 128-byte swizzled [token][64 BF16], U boxes dense
-    // [token][32 FP32]
-    uint8_t* wbox = sm + (lrow >> 6) * 2 * kBox + ((lrow & 7) << 1);
-    const int wchunk = (lrow & 63) >> 3;
-    float* ubox = reinterpret_cast<float*>(sm + 4 * kBox + (lrow >> 5) * kBox) + (lrow & 31);
-#pragma unroll
-    for (int jj = 0; jj < 32; ++jj) {
-      const int tok = tk0 + jj;
-      __nv_bfloat16 hi, lo;
-      split_bf16(__uint_as_float(dw[jj]) * w_scale, hi, lo);
-      const int off = tok * 128 + ((wchunk ^ (tok & 7)) << 4);
-      *reinterpret_cast<__nv_bfloat16*>(wbox + off) = hi;
-      *reinterpret_cast<__nv_bfloat16*>(wbox + kBox + off) = lo;
-      ubox[tok * 32] = __uint_as_float(du[jj]);
-    }
-    fence_proxy_async_smem();
     const float last = s_pl2[valid - 1];
     if (tid < kChunk) ws.gates[block * 128 + tid] = (tid < valid) ? fast_exp2(last - s_pl2[tid]) : 0.f;
     if (tid == kChunk) ws.gates[block * 128 + kChunk] = fast_exp2(last);
     if (tid == kChunk + 1) ws.gates[block * 128 + kChunk + 1] = chunk_not_contraction ? 1.f : 0.f;
   }
-  __syncthreads();
-  if (kChained) {
-    // ---- phase 7: G = (W_hi + W_lo) K_prev^T: A = the staged [W_hi ; W_lo] rows (M = 128), B = previous K tile
-    if (ok) ok = mbar_wait(bar_tma, 1, abort, 4, chunk);
-    if (tid == 0 && ok) {
-      tc_fence_after();
-      const uint32_t base = smem_u32(sm);
+  ok = ok && mbar_wait(bar_mma, 1, abort, 3, chunk);
+  tc_fence_after();
+  GDN_PSTAMP(5);
+
+  // ---- phase 6: W (hi/lo) and U leave for the transposed workspace planes: lrow is the key (W) / value (U)
+  // index, the thread's 32 tokens are contiguous in its row
+  if (ok) {
 #pragma unroll
-      for (int ks = 0; ks < 8; ++ks) {
-        const uint32_t a = base + (ks >> 2) * 2 * kBox + (ks & 3) * 32;
-        const uint32_t bb = base + L::kKprev + (ks >> 2) * kBox + (ks & 3) * 32;
-        mma_ss(tmem + 192, smem_desc(a, 16, 1024), smem_desc(bb, 16, 1024), kIdescN64, ks > 0);
-      }
-      mma_commit(bar_mma);
-    }
-  }
-  if (tid == 0 && ok) {
-    const int row = int(block * kChunk);
-    tma_store_2d(&tm_wh, sm, 0, row);
-    tma_store_2d(&tm_wh, sm + 2 * kBox, 64, row);
-    tma_store_2d(&tm_wl, sm + kBox, 0, row);
-    tma_store_2d(&tm_wl, sm + 3 * kBox, 64, row);
-#pragma unroll
-    for (int part = 0; part < 4; ++part) tma_store_2d(&tm_u, sm + (4 + part) * kBox, part * 32, row);
-    tma_store_commit();
-  }
-  if (kChained) {
-    ok = ok && mbar_wait(bar_mma, 0, abort, 5, chunk);
-    tc_fence_after();
-    // lanes 64..127 hold the W_lo part of row (lane - 64): hand it to the thread of the W_hi row through a
-    // float [64][64] scratch (16-byte slots XOR-swizzled by the row so that a warp's stores spread over banks)
-    float* gsum = reinterpret_cast<float*>(sm + L::kGsum);
-    const int grow = lrow & 63, slot0 = chalf * 8;
-    uint32_t dg[32];
-    if (ok) {
-      tmem_ld32(taddr + 192 + chalf * 32, dg);
+    for (int piece = 0; piece < 2; ++piece) {
+      const int tk0 = chalf * 32 + piece * 16;
+      uint32_t dw[16], du[16];
+      tmem_ld16(taddr + tk0, dw);
+      tmem_ld16(taddr + 64 + tk0, du);
       tmem_wait_ld();
-      if (lrow >= 64) {
+      uint32_t hi[8], lo[8];
 #pragma unroll
-        for (int q4 = 0; q4 < 8; ++q4)
-          *reinterpret_cast<uint4*>(gsum + grow * 64 + (((slot0 + q4) ^ (grow & 15)) << 2)) =
-              make_uint4(dg[q4 * 4], dg[q4 * 4 + 1], dg[q4 * 4 + 2], dg[q4 * 4 + 3]);
+      for (int jj = 0; jj < 16; jj += 2) {
+        const float w0 = __uint_as_float(dw[jj]), w1 = __uint_as_float(dw[jj + 1]);
+        const uint32_t h = pack_bf16(w0, w1);
+        hi[jj >> 1] = h;
+        lo[jj >> 1] = pack_bf16(w0 - bf16_lo(h), w1 - bf16_hi(h));
       }
-    }
-    __syncthreads();
-    if (ok && lrow < 64) {
-      const float inv = 1.f / w_scale;
-      uint32_t gh[16], gl[16];
+      const long long at = transposed_index(block, tk0, lrow);
+      uint4* dh = reinterpret_cast<uint4*>(ws.w_hi + at);
+      uint4* dl = reinterpret_cast<uint4*>(ws.w_lo + at);
+      dh[0] = make_uint4(hi[0], hi[1], hi[2], hi[3]);
+      dh[1] = make_uint4(hi[4], hi[5], hi[6], hi[7]);
+      dl[0] = make_uint4(lo[0], lo[1], lo[2], lo[3]);
+      dl[1] = make_uint4(lo[4], lo[5], lo[6], lo[7]);
+      uint4* dst_u = reinterpret_cast<uint4*>(ws.u + at);
 #pragma unroll
-      for (int q4 = 0; q4 < 8; ++q4) {
-        const float4 o = *reinterpret_cast<const float4*>(gsum + grow * 64 + (((slot0 + q4) ^ (grow & 15)) << 2));
-        const float g0 = (__uint_as_float(dg[q4 * 4]) + o.x) * inv, g1 = (__uint_as_float(dg[q4 * 4 + 1]) + o.y) * inv;
-        const float g2 = (__uint_as_float(dg[q4 * 4 + 2]) + o.z) * inv, g3 = (__uint_as_float(dg[q4 * 4 + 3]) + o.w) * inv;
-        const uint32_t h0 = pack_bf16(g0, g1), h1 = pack_bf16(g2, g3);
-        gh[q4 * 2] = h0;
-        gh[q4 * 2 + 1] = h1;
-        gl[q4 * 2] = pack_bf16(g0 - bf16_lo(h0), g1 - bf16_hi(h0));
-        gl[q4 * 2 + 1] = pack_bf16(g2 - bf16_lo(h1), g3 - bf16_hi(h1));
-      }
-      uint4* dh = reinterpret_cast<uint4*>(ws.g_hi + (block * kChunk + grow) * kChunk + chalf * 32);
-      uint4* dl = reinterpret_cast<uint4*>(ws.g_lo + (block * kChunk + grow) * kChunk + chalf * 32);
-#pragma unroll
-      for (int q4 = 0; q4 < 4; ++q4) {
-        dh[q4] = make_uint4(gh[q4 * 4], gh[q4 * 4 + 1], gh[q4 * 4 + 2], gh[q4 * 4 + 3]);
-        dl[q4] = make_uint4(gl[q4 * 4], gl[q4 * 4 + 1], gl[q4 * 4 + 2], gl[q4 * 4 + 3]);
-      }
+      for (int q4 = 0; q4 < 4; ++q4) dst_u[q4] = make_uint4(du[q4 * 4], du[q4 * 4 + 1], du[q4 * 4 + 2], du[q4 * 4 + 3]);
     }
   }
-  if (tid == 0 && ok) tma_store_wait_read();
+  if (kFused && tid == 0) tma_store_wait_read();    // the key tile's store has left shared memory
   GDN_PSTAMP(6);
   if (!ok) {
     for (int i = 0; i < 20; ++i) __nanosleep(100000);   // let copies in flight land before the CTA leaves
@@ -732,9 +644,10 @@ prepare_umma_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
 //        starts on the first half of the K range while the second half is still being written.
 //        warps 12-15 output epilogue; warps 2-3 idle.
 struct WalkLayout {
-  // B operand of the wide product: per 64-wide K atom the rows [W_hi | W_lo | Qs] (3 boxes, contiguous)
-  static constexpr int kB0 = 0, kB1 = 3 * kBox;
-  static constexpr int kWH = 0, kWL = kBox, kQS = 2 * kBox;     // box offsets inside an atom
+  // one ring stage: W^T hi and lo tiles [128 key lines][64 tokens] (MN-major B operand of the wide product, the
+  // lo tile one 16 KB tile behind the hi tile), Qs as two K-major boxes, K as two boxes, P, the gate vector
+  static constexpr int kWH = 0, kWL = 2 * kBox;
+  static constexpr int kQS0 = 4 * kBox, kQS1 = 5 * kBox;
   static constexpr int kK = 6 * kBox, kP = 8 * kBox;
   static constexpr int kGates = 9 * kBox;
   static constexpr int kStage = 9 * kBox + 1024;
@@ -748,7 +661,7 @@ constexpr int kMmaWarp = 0, kTmaWarp = 1, kChainWarp0 = 4, kChainWarps = 8, kOut
 constexpr int kWalkThreads = 512;
 constexpr int kWalkSmem = WalkLayout::kTotal + 1024;
 constexpr uint32_t kAccS = 0, kOpSH = 128, kOpSL = 192, kAccX = 256, kAccO = 384;   // ACC_O: two buffers of 64
-constexpr uint32_t kIdescN128 = idesc_bf16(128, 128, false, false);
+constexpr uint32_t kIdescN64BT = idesc_bf16(128, 64, false, true);     // B MN-major, N = 64
 
 #ifdef GDN_SM100_PHASE_TIMING
 #define GDN_STAMP(slot)                                                                        \
@@ -894,6 +807,13 @@ walk_umma_kernel(const __grid_constant__ CUtensorMap tm_wh, const __grid_constan
     }
     if (lane == 0) *limit_slot = stop;
   }
+  if ((in.walk_flags & kWalkHomogeneous) && warp == kTmaWarp) {
+    // transition pass: a range that decays below exp(-40) (all tokens contractions) has a transition matrix
+    // below exp(-40) in norm; it is returned as exact zeros without walking
+    bool flagged = false;
+    const int reach = decay_reach(ws.gates, block0, chunks, lane, flagged);
+    if (lane == 0) limit_slot[1] = (reach >= 0 && !flagged) ? 1 : 0;
+  }
   if (parallel > 1 && warp == kTmaWarp) {
     // plan of this CTA (see the comment above the kernel); sub-segment r covers chunks [n r / P, n (r + 1) / P)
     const int n = chunks;
@@ -920,6 +840,10 @@ walk_umma_kernel(const __grid_constant__ CUtensorMap tm_wh, const __grid_constan
   tc_fence_after();
   const uint32_t tmem = *tmem_slot;
   if (in.walk_flags & kWalkUntilDecayed) chunks = *limit_slot;
+  if ((in.walk_flags & kWalkHomogeneous) && limit_slot[1]) {
+    chunks = 0;
+    state_in = nullptr;           // zeros go into tensor memory and straight out as the transition matrix
+  }
   int unstored = 0;                          // leading chunks whose output rows the previous sub-segment's CTA writes
   if (parallel > 1) {
     chunks = limit_slot[0];
@@ -950,9 +874,10 @@ walk_umma_kernel(const __grid_constant__ CUtensorMap tm_wh, const __grid_constan
     for (int c = 0; c < chunks && ok; ++c) {
       const int s = c % L::kStages;
       const float* gates = reinterpret_cast<const float*>(sm + s * L::kStage + L::kGates);
-      const float* urow = ws.u + ((block0 + c) * kChunk + half * 32) * kDim + v;
-      if (c + 1 < chunks)      // pull the next chunk's U rows of this warp towards L2
-        asm volatile("prefetch.global.L2 [%0];" ::"l"(urow + kChunk * kDim + lane * kDim - lane));
+      // U^T plane: this thread's value row, its 32 tokens contiguous (128 bytes)
+      const float* urow = ws.u + ((block0 + c) * kDim + v) * kChunk + half * 32;
+      if (c + 1 < chunks)      // pull the next chunk's row towards L2
+        asm volatile("prefetch.global.L2 [%0];" ::"l"(urow + kChunk * kDim));
 
       if (c > 0) ok = mbar_wait(bar_s, (c - 1) & 1, abort, 10, c);
       ok = ok && mbar_wait(full + s, (c / L::kStages) & 1, abort, 11, c);
@@ -994,7 +919,11 @@ walk_umma_kernel(const __grid_constant__ CUtensorMap tm_wh, const __grid_constan
 
       float u[32];
 #pragma unroll
-      for (int i = 0; i < 32; ++i) u[i] = (in.walk_flags & kWalkHomogeneous) ? 0.f : __ldg(urow + i * kDim);
+      for (int i4 = 0; i4 < 8; ++i4) {
+        const float4 x = (in.walk_flags & kWalkHomogeneous) ? make_float4(0.f, 0.f, 0.f, 0.f)
+                                                            : __ldg(reinterpret_cast<const float4*>(urow) + i4);
+        u[i4 * 4] = x.x; u[i4 * 4 + 1] = x.y; u[i4 * 4 + 2] = x.z; u[i4 * 4 + 3] = x.w;
+      }
 
       ok = mbar_wait(bar_ws, c & 1, abort, 12, c);
       if (!ok) break;
@@ -1127,12 +1056,10 @@ walk_umma_kernel(const __grid_constant__ CUtensorMap tm_wh, const __grid_constan
         const int row = int((block0 + c) * kChunk);
         mbar_arrive_expect_tx(full + s, L::kTxBytes);
         bulk_load(st + L::kGates, ws.gates + (block0 + c) * 128, 512, full + s);
-        tma_load_2d(st + L::kB0 + L::kWH, &tm_wh, full + s, 0, row);
-        tma_load_2d(st + L::kB1 + L::kWH, &tm_wh, full + s, 64, row);
-        tma_load_2d(st + L::kB0 + L::kWL, &tm_wl, full + s, 0, row);
-        tma_load_2d(st + L::kB1 + L::kWL, &tm_wl, full + s, 64, row);
-        tma_load_2d(st + L::kB0 + L::kQS, &tm_qs, full + s, 0, row);
-        tma_load_2d(st + L::kB1 + L::kQS, &tm_qs, full + s, 64, row);
+        tma_load_2d(st + L::kWH, &tm_wh, full + s, 0, 2 * row);       // transposed planes: 128 rows per block
+        tma_load_2d(st + L::kWL, &tm_wl, full + s, 0, 2 * row);
+        tma_load_2d(st + L::kQS0, &tm_qs, full + s, 0, row);
+        tma_load_2d(st + L::kQS1, &tm_qs, full + s, 64, row);
         tma_load_4d(st + L::kK, &tm_k, full + s, 0, hk, t_first + c * kChunk, b);
         tma_load_4d(st + L::kK + kBox, &tm_k, full + s, 64, hk, t_first + c * kChunk, b);
         tma_load_2d(st + L::kP, &tm_p, full + s, 0, row);
@@ -1151,39 +1078,40 @@ walk_umma_kernel(const __grid_constant__ CUtensorMap tm_wh, const __grid_constan
       bool ok = true;
       // Descriptors of ring stage 0; stage 1 is a constant further on (the start-address field counts 16-byte units).
       static_assert(L::kStages == 2 && L::kStage % 16 == 0, "descriptor arithmetic below assumes a two-stage ring");
-      const uint64_t dB0 = smem_desc(st0 + L::kB0, 16, 1024), dB1 = smem_desc(st0 + L::kB1, 16, 1024);
+      const uint64_t dW = smem_desc(st0 + L::kWH, L::kWL - L::kWH, 1024);      // MN-major: 64-token groups hi | lo
+      const uint64_t dQ0 = smem_desc(st0 + L::kQS0, 16, 1024), dQ1 = smem_desc(st0 + L::kQS1, 16, 1024);
       const uint64_t dK = smem_desc(st0 + L::kK, kBox, 1024), dP = smem_desc(st0 + L::kP, 16, 1024);
       for (int c = 0; c < chunks && ok; ++c) {
         const uint64_t stage = uint64_t((c & 1) * (L::kStage >> 4));
-        const uint64_t b0 = dB0 + stage, b1 = dB1 + stage, kd = dK + stage, pd = dP + stage;
+        const uint64_t wd = dW + stage, q0 = dQ0 + stage, q1 = dQ1 + stage, kd = dK + stage, pd = dP + stage;
         const uint32_t acc_o = tm + kAccO + (c & 1) * 64;
-        // St [W_hi ; W_lo]^T with St ~ SH + SL (the SL pass only against W_hi, into its own accumulator).  K steps
-        // {0,1,4,5} of the split become available first, {2,3,6,7} second.  The chain waits for this product only;
-        // the state part of the output, St Qs^T, reads the same operands and is issued behind the commit, so that
-        // it runs while the chain warps form N.
+        // St [W_hi | W_lo] with St ~ SH + SL (the SL pass only against W_hi, added to the first half).  The B
+        // operand is the transposed W tile: key index on the 128-byte lines (K), tokens contiguous (N); one K
+        // step of 16 keys is 2048 bytes.  K steps {0,1,4,5} of the split become available first, {2,3,6,7}
+        // second.  The chain waits for this product only; the state part of the output, St Qs^T, reads the same
+        // operands and is issued behind the commit, so that it runs while the chain warps form N.
         ok = mbar_wait(bar_ops, c & 1, abort, 41, c);
         tc_fence_after();
 #pragma unroll
         for (int q = 0; q < 4; ++q) {
           const int ks = (q >> 1) * 4 + (q & 1);
-          const uint64_t bdesc = ((ks >> 2) ? b1 : b0) + uint64_t((ks & 3) * 2);     // +32 bytes per K step
-          mma_ts(tm + kAccX, tm + kOpSH + ks * 8, bdesc, kIdescN128, q != 0);
-          mma_ts(tm + kAccX, tm + kOpSL + ks * 8, bdesc, kIdescN64, 1);
+          const uint64_t bdesc = wd + uint64_t(ks * 128);
+          mma_ts(tm + kAccX, tm + kOpSH + ks * 8, bdesc, kIdescN128BT, q != 0);
+          mma_ts(tm + kAccX, tm + kOpSL + ks * 8, bdesc, kIdescN64BT, 1);
         }
         ok &= mbar_wait(bar_ops + 1, c & 1, abort, 41, c);
         tc_fence_after();
 #pragma unroll
         for (int q = 0; q < 4; ++q) {
           const int ks = (q >> 1) * 4 + 2 + (q & 1);
-          const uint64_t bdesc = ((ks >> 2) ? b1 : b0) + uint64_t((ks & 3) * 2);
-          mma_ts(tm + kAccX, tm + kOpSH + ks * 8, bdesc, kIdescN128, 1);
-          mma_ts(tm + kAccX, tm + kOpSL + ks * 8, bdesc, kIdescN64, 1);
+          const uint64_t bdesc = wd + uint64_t(ks * 128);
+          mma_ts(tm + kAccX, tm + kOpSH + ks * 8, bdesc, kIdescN128BT, 1);
+          mma_ts(tm + kAccX, tm + kOpSL + ks * 8, bdesc, kIdescN64BT, 1);
         }
         mma_commit(bar_ws);
 #pragma unroll
         for (int ks = 0; ks < 8; ++ks)
-          mma_ts(acc_o, tm + kOpSH + ks * 8, ((ks >> 2) ? b1 : b0) + uint64_t((ks & 3) * 2 + (L::kQS >> 4)),
-                 kIdescN64, ks != 0);
+          mma_ts(acc_o, tm + kOpSH + ks * 8, ((ks >> 2) ? q1 : q0) + uint64_t((ks & 3) * 2), kIdescN64, ks != 0);
         // St += (N*rel)^T K (accumulator already holds gamma * St); token groups {0,2} first, {1,3} second
         ok &= mbar_wait(bar_opn, c & 1, abort, 43, c);
         tc_fence_after();
@@ -1230,26 +1158,21 @@ walk_umma_kernel(const __grid_constant__ CUtensorMap tm_wh, const __grid_constan
 // ======================================================================================= launchers
 int configure_umma() {
   if (int rc = tensor_map_encoder().init()) return rc;
-  cudaError_t e = cudaFuncSetAttribute(prepare_umma_kernel<false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                       kPrepSmem);
+  cudaError_t e = cudaFuncSetAttribute(prepare_umma_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kPrepSmem);
   if (e != cudaSuccess) return int(e);
-  e = cudaFuncSetAttribute(prepare_umma_kernel<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kPrepSmem);
-  if (e != cudaSuccess) return int(e);
-  e = cudaFuncSetAttribute(prepare_umma_kernel<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kPrepSmem);
+  e = cudaFuncSetAttribute(prepare_umma_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kPrepSmem);
   if (e != cudaSuccess) return int(e);
   e = cudaFuncSetAttribute(walk_umma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kWalkSmem);
   return int(e);
 }
 
-namespace {
-int launch_prepare_tc(const Inputs& in, const Geometry& geo, const Workspace& ws, cudaStream_t stream, bool chained) {
+int launch_prepare_umma(const Inputs& in, const Geometry& geo, const Workspace& ws, cudaStream_t stream) {
   TensorMapEncoder& enc = tensor_map_encoder();
   if (int rc = enc.init()) return rc;
-  CUtensorMap tm_q, tm_k, tm_v, tm_wh, tm_wl, tm_u;
-  const uint64_t rows = uint64_t(geo.blocks()) * kChunk;
+  CUtensorMap tm_q, tm_k, tm_v;
   const bool fused = in.mixed != nullptr;
   if (fused) {
-    if (chained || geo.varlen) return int(cudaErrorInvalidValue);
+    if (geo.varlen) return int(cudaErrorInvalidValue);
     // one 2-D map over the packed projection rows; the 4-D map of the normalised-key plane is the store target
     if (int rc = enc.bf16_2d(&tm_q, in.mixed, uint64_t(in.mixed_stride), uint64_t(geo.batch) * geo.sequence, kChunk)) return rc;
     if (int rc = enc.bf16_4d(&tm_k, in.k_norm, kDim, geo.key_heads, geo.sequence, geo.batch, kChunk)) return rc;
@@ -1259,29 +1182,16 @@ int launch_prepare_tc(const Inputs& in, const Geometry& geo, const Workspace& ws
     if (int rc = enc.bf16_4d(&tm_k, in.k, kDim, geo.key_heads, geo.sequence, geo.varlen ? 1 : geo.batch, kChunk)) return rc;
     if (int rc = enc.bf16_4d(&tm_v, in.v, kDim, geo.value_heads, geo.sequence, geo.varlen ? 1 : geo.batch, kChunk)) return rc;
   }
-  if (int rc = enc.bf16_2d(&tm_wh, ws.w_hi, kDim, rows, kChunk)) return rc;
-  if (int rc = enc.bf16_2d(&tm_wl, ws.w_lo, kDim, rows, kChunk)) return rc;
-  if (int rc = enc.f32_2d(&tm_u, ws.u, kDim, rows, kChunk)) return rc;
   const unsigned grid = (unsigned)((geo.varlen ? 1LL : (long long)geo.batch) * geo.value_heads * geo.segment_chunks());
   if (fused)
-    prepare_umma_kernel<false, true><<<grid, kPrepThreads, kPrepSmem, stream>>>(tm_q, tm_k, tm_v, tm_wh, tm_wl, tm_u, in, geo, ws);
-  else if (chained)
-    prepare_umma_kernel<true, false><<<grid, kPrepThreads, kPrepSmem, stream>>>(tm_q, tm_k, tm_v, tm_wh, tm_wl, tm_u, in, geo, ws);
+    prepare_umma_kernel<true><<<grid, kPrepThreads, kPrepSmem, stream>>>(tm_q, tm_k, tm_v, in, geo, ws);
   else
-    prepare_umma_kernel<false, false><<<grid, kPrepThreads, kPrepSmem, stream>>>(tm_q, tm_k, tm_v, tm_wh, tm_wl, tm_u, in, geo, ws);
+    prepare_umma_kernel<false><<<grid, kPrepThreads, kPrepSmem, stream>>>(tm_q, tm_k, tm_v, in, geo, ws);
   return int(cudaGetLastError());
-}
-}  // namespace
-
-int launch_prepare_umma(const Inputs& in, const Geometry& geo, const Workspace& ws, cudaStream_t stream) {
-  return launch_prepare_tc(in, geo, ws, stream, false);
-}
-int launch_prepare_chain(const Inputs& in, const Geometry& geo, const Workspace& ws, cudaStream_t stream) {
-  return launch_prepare_tc(in, geo, ws, stream, true);
 }
 int launch_prepare_fused(const Inputs& in, const Geometry& geo, const Workspace& ws, cudaStream_t stream) {
   if (!in.mixed || !in.act_a || !in.act_b || !in.a_log || !in.dt_bias || !in.k_norm) return int(cudaErrorInvalidValue);
-  return launch_prepare_tc(in, geo, ws, stream, false);
+  return launch_prepare_umma(in, geo, ws, stream);
 }
 
 int launch_walk_umma(const Inputs& in, const Geometry& geo, const Workspace& ws, cudaStream_t stream) {
@@ -1290,8 +1200,9 @@ int launch_walk_umma(const Inputs& in, const Geometry& geo, const Workspace& ws,
   const uint64_t rows = uint64_t(geo.blocks()) * kChunk;
   CUtensorMap tm_wh, tm_wl, tm_qs, tm_k, tm_p, tm_out;
   if (int rc = enc.bf16_4d(&tm_out, in.output, kDim, geo.value_heads, geo.sequence, geo.varlen ? 1 : geo.batch, kChunk)) return rc;
-  if (int rc = enc.bf16_2d(&tm_wh, ws.w_hi, kDim, rows, kChunk)) return rc;
-  if (int rc = enc.bf16_2d(&tm_wl, ws.w_lo, kDim, rows, kChunk)) return rc;
+  // W^T planes: [blocks * 128 key rows][64 tokens], one 128-row box per block
+  if (int rc = enc.bf16_2d(&tm_wh, ws.w_hi, kChunk, 2 * rows, kDim)) return rc;
+  if (int rc = enc.bf16_2d(&tm_wl, ws.w_lo, kChunk, 2 * rows, kDim)) return rc;
   if (int rc = enc.bf16_2d(&tm_qs, ws.qs, kDim, rows, kChunk)) return rc;
   if (int rc = enc.bf16_4d(&tm_k, in.k, kDim, geo.key_heads, geo.sequence, geo.varlen ? 1 : geo.batch, kChunk)) return rc;
   if (int rc = enc.bf16_2d(&tm_p, ws.p, kChunk, rows, kChunk)) return rc;

@@ -43,14 +43,22 @@ constexpr int kMaxDevices = 64;
 std::mutex g_setup_mutex;
 void* g_scratch_address[kMaxDevices] = {};
 
-// One-time set-up for the current device; returns a cudaError_t value.
-int scratch_for_current_device(void** address) {
+// One-time set-up for the current device; returns a cudaError_t value.  The set-up cannot run while `stream` is
+// being captured (it configures kernels and looks up a symbol address): a first call made inside a capture is
+// refused with cudaErrorStreamCaptureUnsupported instead of breaking the capture.
+int scratch_for_current_device(void** address, cudaStream_t stream) {
   int device = -1;
   cudaError_t e = cudaGetDevice(&device);
   if (e != cudaSuccess) return int(e);
   if (device < 0 || device >= kMaxDevices) return int(cudaErrorInvalidDevice);
   std::lock_guard<std::mutex> lock(g_setup_mutex);
   if (!g_scratch_address[device]) {
+    cudaStreamCaptureStatus capturing = cudaStreamCaptureStatusNone;
+    if (cudaStreamIsCapturing(stream, &capturing) != cudaSuccess || capturing != cudaStreamCaptureStatusNone) {
+      std::fprintf(stderr, "actlize_la_sm100_forward_static_scratch: the first call on a device sets the library up and "
+                           "must be made before stream capture begins\n");
+      return int(cudaErrorStreamCaptureUnsupported);
+    }
     if (int rc = actlize_la_sm100_configure()) return rc;
     void* ptr = nullptr;
     e = cudaGetSymbolAddress(&ptr, g_static_scratch);
@@ -81,8 +89,9 @@ extern "C" int actlize_la_sm100_forward_static_scratch(
     return ACTLIZE_LA_SM100_ERROR_SCRATCH_TOO_SMALL;
   }
   void* scratch = nullptr;
-  if (int rc = scratch_for_current_device(&scratch)) return rc;
-  // the built-in array has no room for the carry state of a segmented walk: always one segment here
+  if (int rc = scratch_for_current_device(&scratch, static_cast<cudaStream_t>(stream))) return rc;
+  // the built-in array has no room for the carry state of a segmented walk: always one sequence segment here
+  // (kernel family, stage and walk bits and the parallel sub-segment count pass through)
   return actlize_la_sm100_forward_prepared(q, k, v, g, beta, initial, output, final_state, scratch,
-                                           kStaticBytes, b, t, hk, hv, gate_fp32, config & 0xff, stream);
+                                           kStaticBytes, b, t, hk, hv, gate_fp32, config & ~0xff00, stream);
 }

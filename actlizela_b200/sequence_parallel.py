@@ -6,11 +6,19 @@ the reference itself has no multi-device path).  Because the recurrence treats e
 column independently, ``b`` is the final state of the segment run from a zero state and
 ``M`` is the final state of the same recurrence run with ``v = 0`` from the identity.
 
-Scheme (exact for any decay):
-  1. every rank but the first and the last computes (M_r, b_r) of its own segment, in parallel;
-  2. the incoming states are chained rank to rank, ``S_in(r+1) = M_r S_in(r) + b_r``, with one
-     point-to-point message of B*Hv FP32 128x128 blocks per hop (NCCL send/recv on GPUs);
-  3. every rank runs the ordinary forward on its segment from its true incoming state.
+Scheme (exact for any decay, no host read anywhere):
+  1. every rank behind the first prepares its segment once and walks it from a zero state (outputs and ``b_r``)
+     and, next to that, from the identity with ``v = 0`` (``M_r``; the kernel returns exact zeros at once for a
+     segment whose decay falls below exp(-40), which is decided on the device from the gate sums);
+  2. one grouped exchange of point-to-point messages: every rank sends its pair ``(M_r, b_r)`` to every LATER
+     rank (rank 0 sends its true outgoing state as ``b_0``) and receives the pairs of every EARLIER rank; the
+     exclusive scan ``S_in(r) = M_{r-1} S_in(r-1) + b_{r-1}`` is then folded locally.  All messages of the job
+     are in flight at the same time (NCCL send/recv over NVLink on GPUs), so the exchange costs one message
+     latency instead of a chain of dependent hops;
+  3. every rank rewrites the leading chunks of its output that its incoming state still reaches (the walk stops,
+     per batch and value head, at the first chunk boundary where the decay since the segment start is below
+     exp(-40); a head that never gets there is rewritten to the end); the last rank forms the final state
+     ``M_r S_in + b_r``.
 Segment boundaries must be multiples of the chunk size (64) so that chunking, and therefore
 rounding, is the same as in the unsplit run.
 """
@@ -22,6 +30,8 @@ import torch
 def segment_bounds(length, world_size, chunk=64):
     """Token range of each rank: whole chunks, as even as possible."""
     chunks = (length + chunk - 1) // chunk
+    if world_size < 1 or chunks < world_size:
+        raise ValueError(f"{length} tokens are {chunks} chunks of {chunk}: too few for {world_size} ranks")
     bounds = []
     for rank in range(world_size):
         c0, c1 = rank * chunks // world_size, (rank + 1) * chunks // world_size
@@ -45,30 +55,46 @@ def native_apply_transition(m, b, s):
     return out
 
 
-_DECAYED = -40.0      # natural log: below this a segment's transition matrix is treated as zero
-
-
 def _neighbour(group, rank):
     import torch.distributed as dist
     return dist.get_global_rank(group, rank) if group else rank
 
 
+def _check_segments(t, rank, world, group, segment_lengths, device):
+    """Every rank raises the same error, before any state message is posted: a bad segment must not leave its
+    neighbours waiting in a receive.  With ``segment_lengths`` (the token count of every rank, known to all) the
+    check is local; without it the lengths are gathered first, which costs one small collective and a host read."""
+    import torch.distributed as dist
+    if segment_lengths is None:
+        mine = torch.tensor([t], dtype=torch.int64, device=device)
+        gathered = [torch.empty_like(mine) for _ in range(world)]
+        dist.all_gather(gathered, mine, group=group)
+        segment_lengths = [int(x.item()) for x in gathered]
+    segment_lengths = [int(x) for x in segment_lengths]
+    if len(segment_lengths) != world or segment_lengths[rank] != t:
+        raise ValueError("segment_lengths must list the token count of every rank, this rank's included")
+    if any(n < 1 for n in segment_lengths):
+        raise ValueError("every rank needs at least one token (fewer chunks than ranks?)")
+    if any(n % 64 for n in segment_lengths[:-1]):
+        raise ValueError("every segment but the last must be a multiple of 64 tokens")
+
+
 def gdn_forward_sequence_parallel(q, k, v, g, beta, initial_state=None, output_final_state=True, *,
                                   group=None, forward_fn=None, apply_transition=None, segment_fn=None,
-                                  until_decayed=False, **forward_options):
+                                  until_decayed=False, segment_lengths=None, **forward_options):
     """Forward over a sequence split across the ranks of ``group``.
 
     Every rank passes ITS OWN contiguous segment (q,k [B,Tr,Hk,128] ...), segments in rank
     order, every segment except the last a multiple of 64 tokens.  ``initial_state`` is read on
     rank 0 only.  Returns (output of the local segment, final state on the LAST rank or None).
+    ``segment_lengths`` (token count of every rank) lets the arguments be checked without communication.
 
     On CUDA tensors the ranks behind the first prepare their segment once and walk it several times
-    (``Sm100Forward.prepare_segment``): offset and transition pass next to each other, then, once the incoming
-    state has arrived, the final pass.  ``until_decayed=True`` replaces that final pass by a walk over the leading
-    chunks only, those the incoming state still reaches with a weight above exp(-40) (valid when every chunk
-    transition is a contraction, which holds for L2-normalised keys and beta in [0, 1]); the remaining rows keep
-    the zero-state outputs and the final state comes from ``M S_in + b``.  ``forward_fn`` (any complete forward)
-    selects the generic three-pass form instead; ``segment_fn`` substitutes the prepared-segment factory.
+    (``Sm100Forward.prepare_segment``), see the module text.  ``until_decayed=True`` is the caller's statement
+    that every segment forgets its incoming state (decay below exp(-40) within the segment, every token a
+    contraction: L2-normalised keys, beta in [0, 1]); the transition pass is then skipped and only ``b_{r-1}``
+    travels, from each rank to the next.  ``forward_fn`` (any complete forward) selects the generic three-pass
+    form on complete forwards instead; ``segment_fn`` substitutes the prepared-segment factory.
     """
     import torch.distributed as dist
     rank, world = dist.get_rank(group), dist.get_world_size(group)
@@ -81,65 +107,73 @@ def gdn_forward_sequence_parallel(q, k, v, g, beta, initial_state=None, output_f
         apply_transition = native_apply_transition if q.is_cuda else _torch_apply_transition
     if world == 1:
         return forward_fn(q, k, v, g, beta, initial_state, output_final_state, **forward_options)
-    if rank < world - 1 and t % 64:
-        raise ValueError("every segment but the last must be a multiple of 64 tokens")
+    _check_segments(t, rank, world, group, segment_lengths, q.device)
+    if staged and forward_options:
+        raise ValueError("forward options apply to the generic form (forward_fn) only")
     state_shape = (b, hv, d, d)
     last = rank == world - 1
+    new_state = lambda: torch.empty(state_shape, dtype=torch.float32, device=q.device)
+    later = [_neighbour(group, r) for r in range(rank + 1, world)]
+
+    def exchange(offset, transition):
+        """Post this rank's pair to every later rank and collect the pairs of every earlier rank, all at once.
+        Returns the incoming state of this rank (None on rank 0)."""
+        ops, received = [], []
+        for r in range(rank):
+            pair = (new_state() if r > 0 else None, new_state())       # rank 0 sends its outgoing state only
+            received.append(pair)
+            source = _neighbour(group, r)
+            if pair[0] is not None:
+                ops.append(dist.P2POp(dist.irecv, pair[0], source, group))
+            ops.append(dist.P2POp(dist.irecv, pair[1], source, group))
+        for target in later:
+            if transition is not None:
+                ops.append(dist.P2POp(dist.isend, transition, target, group))
+            ops.append(dist.P2POp(dist.isend, offset, target, group))
+        for work in (dist.batch_isend_irecv(ops) if ops else []):
+            work.wait()
+        if not received:
+            return None
+        state = received[0][1]
+        for m, off in received[1:]:
+            state = apply_transition(m, off, state)
+        return state
 
     if rank == 0:
-        # the first segment starts from the caller's state; its final state is the next rank's incoming state
+        # the first segment starts from the caller's state; its true outgoing state plays the part of b_0
         out, final = forward_fn(q, k, v, g, beta, initial_state, True, **forward_options)
-        dist.send(final, dst=_neighbour(group, 1), group=group)
+        if until_decayed:
+            dist.send(final, dst=later[0], group=group)
+        else:
+            exchange(final, None)
         return out, None
 
     if staged:
-        if forward_options:
-            raise ValueError("forward options apply to the generic form (forward_fn) only")
         if segment_fn is None:
             from .sm100 import load_sm100
             segment_fn = load_sm100().prepare_segment
         segment = segment_fn(q, k, v, g, beta)
-        incoming = torch.empty(state_shape, dtype=torch.float32, device=q.device)
-        source, target = _neighbour(group, rank - 1), (None if last else _neighbour(group, rank + 1))
-        # the whole segment's decay, per batch and value head: one small reduction and one host read
-        if until_decayed and bool((g.float().sum(dim=1).max() < _DECAYED).item()):
-            # M_r is below exp(-40): the outgoing state is b_r whatever comes in, so it leaves at once and all
-            # hand-offs of the job overlap; the incoming state only reaches the leading chunks of the output
+        if until_decayed:
+            # the caller vouches that M_r is below exp(-40): b_r leaves at once, whatever comes in
             offset = segment.offset_pipelined()
-            ops = [dist.P2POp(dist.irecv, incoming, source, group)]
+            incoming = new_state()
+            ops = [dist.P2POp(dist.irecv, incoming, _neighbour(group, rank - 1), group)]
             if not last:
-                ops.append(dist.P2POp(dist.isend, offset, target, group))
+                ops.append(dist.P2POp(dist.isend, offset, later[0], group))
             for work in dist.batch_isend_irecv(ops):
                 work.wait()
             out = segment.finish_decayed(incoming)
             return out, (offset if (last and output_final_state) else None)
-        offset = transition = None
-        if not last or until_decayed:
-            offset, transition = segment.offset_and_transition(
-                need_transition=not last or bool(output_final_state))
-        else:
-            segment.prepare()
-        dist.recv(incoming, src=source, group=group)
-        if not last:
-            outgoing = apply_transition(transition, offset, incoming)
-            dist.send(outgoing, dst=target, group=group)
-        if until_decayed:
-            out = segment.finish_decayed(incoming)
-            final = apply_transition(transition, offset, incoming) if (last and output_final_state) else None
-        else:
-            out, final = segment.finish(incoming, bool(last and output_final_state))
-        return out, (final if (last and output_final_state) else None)
+        offset, transition = segment.offset_and_transition(need_transition=True)
+        incoming = exchange(offset, transition)
+        out = segment.finish_decayed(incoming)
+        final = apply_transition(transition, offset, incoming) if (last and output_final_state) else None
+        return out, final
 
-    transition = offset = None
-    if not last:
-        # (M_r, b_r): two state-only passes over the local segment
-        _, offset = forward_fn(q, k, v, g, beta, None, True, **forward_options)
-        eye = torch.eye(d, dtype=torch.float32, device=q.device).expand(state_shape).contiguous()
-        _, transition = forward_fn(q, k, torch.zeros_like(v), g, beta, eye, True, **forward_options)
-    incoming = torch.empty(state_shape, dtype=torch.float32, device=q.device)
-    dist.recv(incoming, src=_neighbour(group, rank - 1), group=group)
-    if not last:
-        outgoing = apply_transition(transition, offset, incoming)
-        dist.send(outgoing, dst=_neighbour(group, rank + 1), group=group)
+    # generic form on complete forwards: (M_r, b_r) by two state-only passes, the same exchange, a third pass
+    _, offset = forward_fn(q, k, v, g, beta, None, True, **forward_options)
+    eye = torch.eye(d, dtype=torch.float32, device=q.device).expand(state_shape).contiguous()
+    _, transition = forward_fn(q, k, torch.zeros_like(v), g, beta, eye, True, **forward_options)
+    incoming = exchange(offset, transition)
     out, final = forward_fn(q, k, v, g, beta, incoming, bool(output_final_state and last), **forward_options)
     return out, (final if (output_final_state and last) else None)

@@ -16,7 +16,6 @@ from .sm100_policy import policy, selection_for
 MATH_CONTRACT = "wy-splitbf16-state-bf16-out-sm100-v1"
 _DIAGNOSTIC_IDS = {"simt": 0, "umma": 1, "simt-prepare+umma-walk": 2, "umma-prepare+simt-walk": 3,
                    "umma-seg2": 1 | (2 << 8), "umma-seg4": 1 | (4 << 8), "umma-seg8": 1 | (8 << 8), "umma-seg16": 1 | (16 << 8),
-                   "chain": 4, "chain-seg2": 4 | (2 << 8), "chain-seg4": 4 | (4 << 8), "chain-seg8": 4 | (8 << 8),
                    # parallel sub-segments of the walk (bits 16..19), alone and with sequence segments
                    "umma-par2": 1 | (2 << 16), "umma-par3": 1 | (3 << 16), "umma-par4": 1 | (4 << 16),
                    "umma-par8": 1 | (8 << 16), "umma-seg2-par2": 1 | (2 << 8) | (2 << 16),
@@ -176,7 +175,10 @@ class PreparedSegment:
         self.owner, self.tensors = owner, (q, k, v, g, beta)
         b, t, hk, hv = self.dims
         owner.library.configure(q.device)
-        self.pipelined_config = selection_for(q, v).configuration_id       # the policy's segmented form
+        selection = selection_for(q, v)
+        self.pipelined_config = selection.configuration_id                 # the policy's complete forward
+        # the walk alone, split into the policy's parallel sub-segments (offset pass from a zero state)
+        self.split_walk = self._CONFIG | self._WALK | ((selection.parallel << 16) if selection.parallel > 1 else 0)
         self.nbytes = max(owner.workspace_bytes(b, t, hk, hv, self._CONFIG),
                           owner.workspace_bytes(b, t, hk, hv, self.pipelined_config))
         self.workspace = torch.empty(self.nbytes, dtype=torch.uint8, device=q.device)
@@ -209,7 +211,9 @@ class PreparedSegment:
 
     def offset_and_transition(self, need_transition=True):
         """(b_r, M_r) of ``S_out = M_r S_in + b_r``; the zero-state outputs stay in ``self.output``.
-        One prepare launch, then the two walks next to each other on two streams (a walk occupies B*Hv SMs)."""
+        One prepare launch, then the two walks next to each other on two streams: the offset walk split into the
+        policy's parallel sub-segments, the transition walk one CTA per (batch, value head), which returns exact
+        zeros at once for a head whose segment decays below exp(-40)."""
         import torch
         self._launch(self._CONFIG | self._PREPARE, None, self.output, None)
         offset, transition = self._state(), None
@@ -225,7 +229,7 @@ class PreparedSegment:
                 self._launch(self._CONFIG | self._WALK | self._HOMOGENEOUS, eye, scratch, transition)
                 for x in (eye, transition, scratch):
                     x.record_stream(self._side)
-        self._launch(self._CONFIG | self._WALK, None, self.output, offset)
+        self._launch(self.split_walk, None, self.output, offset)
         if need_transition:
             torch.cuda.current_stream().wait_stream(self._side)
         return offset, transition

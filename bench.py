@@ -18,7 +18,7 @@ restatement of the reference's own FP32 path (oracle/) on the host cores instead
 The same line carries, at N = 1, `per_config` (every named shape timed through the policy's configuration, with
 its fraction of the per-shape roofline) and, at N > 1, the two multi-GPU forms the path has: `shard_cfg2` (B8 T4096
 split by batch over the ranks, no collective, strong scaling) and `sp_cfg4` (T131072 split over the ranks, states
-handed on with NCCL send/recv, exact and decayed form), each with its efficiency against one GPU running the same
+handed on with NCCL send/recv; the exact form and the one where the caller vouches for the decay), each with its efficiency against one GPU running the same
 shape and a `parity` object (key-head group 0 of the timed tensors against the CPU restatement, computed outside
 the timed regions).
 """
@@ -187,6 +187,34 @@ def aux_bench(args):
         nbytes = mixed.numel() * 2 + 2 * a.numel() * 2 + t * hv * 256 + hv * 65536
         units, unit = t, "tokens/s"
         name = f"forward on projections B1 T{t} Hk{hk} Hv{hv}"
+    elif args.op == "out_proj":
+        # the output projection behind the gated RMSNorm at the reference's production shape
+        from actlizela_b200 import out_proj_gemm
+        m, kk, n = 8192, 4096, 2560
+        a = torch.randn(m, kk, generator=gen).to(torch.bfloat16).cuda()
+        w = torch.randn(n, kk, generator=gen).to(torch.bfloat16).cuda()
+        call = lambda: out_proj_gemm(a, w)
+        flops = 2.0 * m * n * kk
+        for _ in range(max(3, args.warmup)):
+            call()
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        start.record()
+        for _ in range(args.steps):
+            call()
+        stop.record()
+        torch.cuda.synchronize()
+        ms = start.elapsed_time(stop) / args.steps
+        _, tensor_peak, source = measured_peaks()
+        achieved = flops / (ms * 1e-3) / 1e12
+        print(json.dumps(dict(metric="out_proj tokens/s", value=m / (ms * 1e-3), unit="tokens/s", n_gpus=1,
+                              steps=args.steps, warmup=max(3, args.warmup), ms_per_step=ms, higher_is_better=True,
+                              data="synthetic", dtype="bf16", gpu_launches=args.steps,
+                              config=dict(workload=f"out_proj M{m} K{kk} N{n}", l2="operands exceed no cache: compute bound"),
+                              roofline=dict(bound="tensor", achieved=achieved, peak=tensor_peak, unit="TFLOP/s",
+                                            frac=achieved / tensor_peak, traffic=None, peak_source=source,
+                                            algorithmic_flops=flops))), flush=True)
+        return
     elif args.op == "varlen":
         # 64 packed prefill requests with seeded ragged lengths (mean 256 tokens); per token and value head the same
         # algorithmic bytes as the fixed-shape forward
@@ -245,7 +273,9 @@ def sequence_parallel_bench(args, workload):
     device = torch.device("cuda", local)
     if world > 1:
         dist.init_process_group("nccl", device_id=device)
-    t0, t1 = segment_bounds(workload.length, world)[rank]
+    bounds = segment_bounds(workload.length, world)
+    lengths = [b1 - b0 for b0, b1 in bounds]
+    t0, t1 = bounds[rank]
     # the rank's own segment, drawn from the workload's distributions with a per-rank seed (synthetic data: only
     # the first rank gets the workload's initial state)
     part = workload.sliced(length=t1 - t0, seed=workload.seed + 7919 * rank,
@@ -255,7 +285,8 @@ def sequence_parallel_bench(args, workload):
     def step():
         if world == 1:
             return gdn_forward(q, k, v, g, beta, initial, True)
-        return gdn_forward_sequence_parallel(q, k, v, g, beta, initial, True, until_decayed=args.until_decayed)
+        return gdn_forward_sequence_parallel(q, k, v, g, beta, initial, True, until_decayed=args.until_decayed,
+                                             segment_lengths=lengths)
 
     def sync_all():
         torch.cuda.synchronize()
@@ -449,14 +480,16 @@ def shard_cfg2_leg(device, rank, world, steps, peaks):
 
 def sp_cfg4_leg(device, rank, world, steps, peaks):
     """cfg4 (B1 T131072 Hk16 Hv32) split over the ranks as contiguous token segments, states handed on with NCCL
-    send/recv: strong scaling against one GPU running the whole sequence; exact and decayed form."""
+    send/recv: strong scaling against one GPU running the whole sequence; the exact form and the vouched one."""
     import torch
     from actlizela_b200 import gdn_forward
     from actlizela_b200.sequence_parallel import gdn_forward_sequence_parallel, segment_bounds
     from actlizela_b200.workloads import WORKLOADS, make_inputs
     from oracle import gdn_oracle as oracle
     w = WORKLOADS["cfg4"]
-    t0, t1 = segment_bounds(w.length, world)[rank]
+    bounds = segment_bounds(w.length, world)
+    lengths = [b1 - b0 for b0, b1 in bounds]
+    t0, t1 = bounds[rank]
     narrow = make_inputs(w.sliced(key_heads=1, value_heads=w.value_heads // w.key_heads))
     heads = narrow[2].shape[2]
     full = device_inputs(w, device, w.seed)
@@ -472,8 +505,11 @@ def sp_cfg4_leg(device, rank, world, steps, peaks):
     want_out, want_state = oracle.chunk_forward_fp32(*narrow, output_final_state=True)
     result = dict(workload="cfg4 B1 T131072 Hk16 Hv32 fp32 gate, zero initial state",
                   segments=f"{world} contiguous token segments, one per rank", one_gpu_ms=ms_one, scaling="strong")
-    for form, decayed in (("exact", False), ("decayed", True)):
-        call = lambda: gdn_forward_sequence_parallel(*part, initial, True, until_decayed=decayed)
+    # "exact": decided on the device per (batch, value head), valid for any gate; "vouched": the caller states that
+    # every segment forgets its incoming state, so no transition pass runs and only b travels to the next rank
+    for form, decayed in (("exact", False), ("vouched", True)):
+        call = lambda: gdn_forward_sequence_parallel(*part, initial, True, until_decayed=decayed,
+                                                     segment_lengths=lengths)
         for _ in range(3):
             call()
         ms, spread = timed_loop(call, steps, device, world)
@@ -522,7 +558,7 @@ def main():
     ap.add_argument("--skip-cpu-baseline", action="store_true")
     ap.add_argument("--skip-extra-legs", action="store_true",
                     help="leave out per_config (N = 1) and shard_cfg2 / sp_cfg4 (N > 1)")
-    ap.add_argument("--op", default="forward", choices=("forward", "decode", "prepare_inputs", "rmsnorm_gated", "varlen", "projections"),
+    ap.add_argument("--op", default="forward", choices=("forward", "decode", "prepare_inputs", "rmsnorm_gated", "varlen", "projections", "out_proj"),
                     help="forward is the headline metric; the others time a neighbouring memory-bound kernel")
     ap.add_argument("--parallelism", default="shard", choices=("shard", "sp"),
                     help="shard: every rank one per-GPU workload (weak scaling, the headline form); sp: one sequence "

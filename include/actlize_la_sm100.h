@@ -38,13 +38,11 @@ extern "C" {
  * (per-kernel timing; the walk-only form needs a workspace filled by an earlier call). */
 #define ACTLIZE_LA_SM100_STAGE_PREPARE_ONLY 0x10
 #define ACTLIZE_LA_SM100_STAGE_WALK_ONLY 0x20
-/* id 4: chained tensor-core pair (the prepare stage also emits G = W K_prev^T; experimental, not in the table).
- * Two modifiers of a walk-only call of configuration 1, used by the sequence-parallel scheme (several walks over
+/* Two modifiers of a walk-only call of configuration 1, used by the sequence-parallel scheme (several walks over
  * one prepared workspace): WALK_HOMOGENEOUS treats U as zero, which with the identity as initial state yields the
  * state-transition matrix of the segment; WALK_UNTIL_DECAYED stops every (batch, value head) walk at the first chunk
  * boundary where the decay accumulated since the segment start is below exp(-40), leaving later output rows
  * untouched (final_state must be NULL). */
-#define ACTLIZE_LA_SM100_CONFIG_CHAIN 4
 #define ACTLIZE_LA_SM100_WALK_HOMOGENEOUS 0x40
 #define ACTLIZE_LA_SM100_WALK_UNTIL_DECAYED 0x80
 
@@ -161,6 +159,14 @@ int actlize_la_sm100_commit_step(const void* k, const void* g, const float* delt
  * Replaces rmsnorm_gated (csrc/output_gate/output_gate.cu:4-5,73-92). */
 int actlize_la_sm100_rmsnorm_gated(const void* y, const void* z, const void* weight, void* out,
                                    long long rows, void* stream);
+
+/* Step after, second half: the output projection C[M,N] = A[M,K] W[N,K]^T with BF16 operands, FP32 accumulation and
+ * a BF16 result; A row-major, W in the Linear layout [N][K], C row-major; K and N multiples of 8, all pointers
+ * 16-byte aligned.  One tcgen05 kernel (128 x 128 tiles, TMA-fed, accumulator in tensor memory); call
+ * actlize_la_sm100_configure once per device first.
+ * Replaces out_proj_gemm / out_proj_gemm_cutlass (csrc/output_gate/output_gate.cu, output_gate_cutlass.cu;
+ * docs/OUTPUT_GATE.md:17-24). */
+int actlize_la_sm100_out_proj(const void* a, const void* w, void* c, int m, int n, int k, void* stream);
 
 /* Diagnostic word written by a kernel whose bounded wait ran out (all waits on barriers are
  * bounded; a kernel that gives up drains, frees its tensor memory and returns; its output rows and

@@ -211,3 +211,39 @@ def test_forward_on_projections_equals_prepare_then_forward(shape):
         assert torch.equal(state, want_state)
     out_only, none = gdn_forward_projections(mixed, a, b, a_log, dt_bias, hk, hv, None, False)
     assert none is None and torch.equal(out_only, out)
+
+
+@pytest.mark.parametrize("m,k,n", [(512, 4096, 2560), (2048, 4096, 2560), (37, 4096, 2560), (100, 128, 64),
+                                   (129, 72, 136), (8192, 4096, 2560)])
+def test_out_proj_gemm_matches_fp32_matmul(m, k, n):
+    """The reference's shapes (tests/test_output_gate.py:31-40) plus ragged tiles in every dimension; the
+    comparison is the reference's own (FP32 matmul of the BF16 operands, rounded to BF16, 1 % of the largest
+    entry) and a tighter one that only allows the final BF16 rounding and FP32 summation order."""
+    from actlizela_b200 import out_proj_gemm
+    gen = torch.Generator().manual_seed(m + k + n)
+    a = torch.randn(m, k, generator=gen).to(torch.bfloat16).cuda()
+    w = torch.randn(n, k, generator=gen).to(torch.bfloat16).cuda()
+    want = a.float() @ w.float().t()                                   # plain PyTorch FP32 reference of the same op
+    got = out_proj_gemm(a, w)
+    torch.cuda.synchronize()
+    assert got.shape == (m, n) and got.dtype == torch.bfloat16
+    rel = (got.float() - want.to(torch.bfloat16).float()).abs().max().item() / want.abs().max().item()
+    assert rel < 1e-2, rel
+    # BF16 rounding of the result (2^-8 relative) plus FP32 accumulation noise
+    assert ((got.float() - want).abs() <= 2 ** -7 * want.abs() + 1e-3 * k ** 0.5).all()
+
+
+def test_rmsnorm_gated_then_out_proj_shape_chain():
+    """[T*32,128] -> gated RMSNorm -> reshape [T,4096] -> out_proj [T,2560] (tests/test_output_gate.py:55-65)."""
+    from actlizela_b200 import out_proj_gemm, rmsnorm_gated
+    gen = torch.Generator().manual_seed(3)
+    t = 64
+    y = torch.randn(t * 32, 128, generator=gen).to(torch.bfloat16).cuda()
+    z = torch.randn(t * 32, 128, generator=gen).to(torch.bfloat16).cuda()
+    weight = torch.randn(128, generator=gen).to(torch.bfloat16).cuda()
+    w = (torch.randn(2560, 4096, generator=gen) / 64).to(torch.bfloat16).cuda()
+    gated = rmsnorm_gated(y, z, weight).reshape(t, 32 * 128)
+    out = out_proj_gemm(gated, w)
+    want = gated.float() @ w.float().t()
+    assert out.shape == (t, 2560)
+    assert oracle.rel_frobenius(out.float().cpu(), want.cpu()) < 5e-3

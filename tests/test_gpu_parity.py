@@ -19,7 +19,7 @@ from tests.cases import ALL_CASES, build_case
 pytestmark = pytest.mark.gpu
 
 OUT_MAX_ABS, OUT_REL_F, STATE_REL_F = 2e-2, 1e-2, 1e-3
-CONFIGS = ["simt", "umma", "chain"]
+CONFIGS = ["simt", "umma"]
 
 
 @pytest.fixture(scope="module")
@@ -100,6 +100,9 @@ def _workspace_planes(native_library, inputs, config):
     for name, size, dtype in sizes:
         planes[name] = ws[off:off + size].view(dtype).clone()
         off += size
+    # W and U are stored per block as [dimension][token]; back to [token][dimension] for the comparison
+    for name in ("w_hi", "w_lo", "u"):
+        planes[name] = planes[name].view(n, 128, 64).transpose(1, 2).contiguous()
     planes["w"] = planes["w_hi"].float() + planes["w_lo"].float()
     planes["gates"] = planes["gates"].view(n, 128)[:, :65].contiguous()
     return planes, out, final
@@ -368,25 +371,6 @@ def test_segmented_walk_equals_the_single_launch_bitwise(configuration, forward,
     assert _status(native_library)[0] == 0
 
 
-@pytest.mark.parametrize("configuration", ["chain-seg2", "chain-seg4", "chain-seg8"])
-def test_segmented_chained_walk(configuration, forward, native_library):
-    """The chained walk starts every launch from the plain W S product, so a segmented run differs from the
-    single launch by rounding only; both stay inside the criterion against the oracle."""
-    w = WORKLOADS["cfg3"].sliced(batch=2, length=1000, key_heads=2, value_heads=8)     # 16 chunks, tail of 40
-    cpu = make_inputs(w)
-    dev = _to_device(cpu)
-    want_out, want_state = oracle.wy_chunk_forward(*cpu)
-    out, state = forward(*dev, True, configuration="chain")
-    seg_out, seg_state = forward(*dev, True, configuration=configuration)
-    again_out, again_state = forward(*dev, True, configuration=configuration)
-    torch.cuda.synchronize()
-    assert _status(native_library)[0] == 0
-    assert torch.equal(seg_out, again_out) and torch.equal(seg_state, again_state)
-    _check(out, state, want_out, want_state, "chain")
-    _check(seg_out, seg_state, want_out, want_state, configuration)
-    assert oracle.rel_frobenius(seg_state.cpu(), state.cpu()) < 1e-4
-
-
 def test_bounded_wait_gives_up_and_reports(native_library, forward):
     """A wait that can never be satisfied runs out, leaves a status record, and the context stays usable."""
     lib = native_library.lib
@@ -484,12 +468,11 @@ def test_random_geometries(seed, forward):
     _check(out, state, want_out, want_state, ("random", seed, w.shape))
 
 
-@pytest.mark.parametrize("configuration", ["umma", "umma-par2", "chain", "chain-seg4"])
+@pytest.mark.parametrize("configuration", ["umma", "umma-par2", "simt"])
 @pytest.mark.parametrize("gate", ["none", "strong", "underflow", "mixed"])
 def test_extreme_gates(gate, configuration, forward, native_library):
     """Gate ranges beyond the benchmark distributions: no decay at all, a decay that empties the state within a
-    chunk, one whose chunk product underflows FP32 (the chained configuration divides a clamped decay out of G),
-    and a mixture of these per head."""
+    chunk, one whose chunk product underflows FP32, and a mixture of these per head."""
     w = WORKLOADS["cfg3"].sliced(batch=1, length=520, key_heads=2, value_heads=4, initial=0.1, seed=4242)
     q, k, v, g, beta, init = make_inputs(w)
     gen = torch.Generator().manual_seed(99)

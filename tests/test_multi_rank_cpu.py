@@ -77,11 +77,15 @@ def test_shard_plan_covers_every_unit_exactly_once():
 
 
 def test_segment_bounds_are_chunk_aligned():
-    for length, world in [(131072, 8), (3000, 4), (65, 2), (64, 2), (1, 3)]:
+    for length, world in [(131072, 8), (3000, 4), (65, 2), (129, 3), (64, 1)]:
         bounds = segment_bounds(length, world)
         assert bounds[0][0] == 0 and bounds[-1][1] == length
+        assert all(b1 > b0 for b0, b1 in bounds)                      # nobody is left without tokens
         for (a0, a1), (b0, _) in zip(bounds, bounds[1:]):
             assert a1 == b0 and a1 % 64 == 0 or a1 == length
+    for length, world in [(64, 2), (1, 3), (128, 3)]:                 # fewer chunks than ranks
+        with pytest.raises(ValueError, match="too few"):
+            segment_bounds(length, world)
 
 
 def _free_port():
@@ -114,22 +118,34 @@ def _worker(rank, world, port, mode, result_queue):
             result_queue.put((rank, worst))
         else:
             if mode.startswith("sp-decayed"):
-                # strong decay: the incoming state is gone within the first chunks of a segment; the weaker variant
-                # does not empty a whole segment, so the transition matrix is still exchanged
+                # strong decay: the incoming state is gone within the first chunks of a segment, which is what a
+                # caller of until_decayed=True vouches for; the weaker variant does not empty a whole segment and
+                # goes through the exact form, whose final pass still stops where a head has decayed
                 g = g * (25.0 if mode == "sp-decayed" else 4.0)
                 want_out, want_state = _oracle_forward(q, k, v, g, beta, init)
-            t0, t1 = segment_bounds(q.shape[1], world)[rank]
+            bounds = segment_bounds(q.shape[1], world)
+            lengths = [b1 - b0 for b0, b1 in bounds] if mode != "sp-staged" else None     # None: gathered first
+            t0, t1 = bounds[rank]
             part = [x[:, t0:t1].contiguous() for x in (q, k, v, g, beta)]
             if mode == "sp":
                 out, final = gdn_forward_sequence_parallel(
-                    *part, init if rank == 0 else None, True, forward_fn=_oracle_forward)
+                    *part, init if rank == 0 else None, True, forward_fn=_oracle_forward, segment_lengths=lengths)
             else:
                 # the staged form: prepared segment walked several times; rank 0 still runs a complete forward
                 import actlizela_b200.gdn_interface as interface
                 interface.gdn_forward = _oracle_forward
                 out, final = gdn_forward_sequence_parallel(
                     *part, init if rank == 0 else None, True, segment_fn=_OracleSegment,
-                    until_decayed=mode.startswith("sp-decayed"))
+                    until_decayed=(mode == "sp-decayed"), segment_lengths=lengths)
+            if mode == "sp" and world == 3:
+                # a segment that is not a multiple of 64 tokens is refused on every rank alike, before any message
+                try:
+                    gdn_forward_sequence_parallel(*part, None, True, forward_fn=_oracle_forward,
+                                                  segment_lengths=[64, 63, q.shape[1] - 127])
+                except ValueError:
+                    pass
+                else:
+                    raise AssertionError("bad segment lengths were accepted")
             worst = oracle.max_abs(out, want_out[:, t0:t1])
             if rank == world - 1:
                 worst = max(worst, oracle.rel_frobenius(final, want_state))
@@ -141,7 +157,7 @@ def _worker(rank, world, port, mode, result_queue):
 
 
 @pytest.mark.parametrize("mode,world", [("shard", 2), ("sp", 2), ("sp", 3), ("sp-staged", 2), ("sp-staged", 3),
-                                        ("sp-decayed", 3), ("sp-decayed-partly", 3)])
+                                        ("sp-staged", 4), ("sp-decayed", 3), ("sp-decayed-partly", 3)])
 def test_two_rank_paths_match_the_unsplit_run(mode, world):
     ctx = mp.get_context("spawn")
     queue = ctx.Queue()
