@@ -54,6 +54,7 @@ EXPORTS = {
     "actlize_la_sm100_forward_projections": (_I, [_P, _LL] + [_P] * 8 + [_LL] + [_I] * 5 + [_P]),
     "actlize_la_sm100_varlen_workspace_bytes": (_LL, [_LL, _I, _I, _I]),
     "actlize_la_sm100_forward_varlen": (_I, [_P] * 9 + [_LL, _P] + [_I] * 4 + [_P]),
+    "actlize_la_sm100_forward_varlen_device": (_I, [_P] * 9 + [_LL, _P, _I, _LL] + [_I] * 3 + [_P]),
 }
 
 

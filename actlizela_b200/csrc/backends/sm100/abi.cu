@@ -103,6 +103,23 @@ int launch_walk_tc(int, const Inputs& in, const Geometry& geo, const Workspace& 
   return launch_walk_umma(in, geo, ws, stream);
 }
 
+// Offsets table of the packed mode from DEVICE offsets: cu_seqlens[0..n] (forced into 0 <= ... <= total and
+// non-decreasing, so that no later index can leave the tensors) followed by the chunk prefix.
+__global__ void varlen_table_kernel(const int* __restrict__ cu_seqlens, int n_seqs, int total, int* __restrict__ table) {
+  if (threadIdx.x != 0 || blockIdx.x != 0) return;
+  int chunks = 0, previous = 0;
+  table[0] = 0;
+  table[n_seqs + 1] = 0;
+  for (int i = 1; i <= n_seqs; ++i) {
+    int at = cu_seqlens[i];
+    at = at < previous ? previous : (at > total ? total : at);
+    chunks += (at - previous + kChunk - 1) / kChunk;
+    table[i] = at;
+    table[n_seqs + 1 + i] = chunks;
+    previous = at;
+  }
+}
+
 __global__ void apply_transition_kernel(const float* __restrict__ m, const float* __restrict__ off,
                                         const float* __restrict__ s_in, float* __restrict__ s_out) {
   // one CTA per 128x128 block: out = M @ S + b, 256 threads, each 64 outputs
@@ -443,6 +460,35 @@ extern "C" int actlize_la_sm100_forward_varlen(
   Geometry geo{n_seqs, total, hk, hv};
   geo.varlen = static_cast<const int*>(workspace);
   geo.total_chunks = chunks;
+  const Inputs in{static_cast<const __nv_bfloat16*>(q), static_cast<const __nv_bfloat16*>(k),
+                  static_cast<const __nv_bfloat16*>(v), g, static_cast<const __nv_bfloat16*>(beta),
+                  initial_states, static_cast<__nv_bfloat16*>(output), final_states, gate_fp32 ? 1 : 0};
+  const Workspace ws = carve_workspace(static_cast<char*>(workspace) + varlen_table_bytes(n_seqs), geo);
+  if (int rc = launch_prepare_umma(in, geo, ws, stream)) return rc;
+  return launch_walk_umma(in, geo, ws, stream);
+}
+
+extern "C" int actlize_la_sm100_forward_varlen_device(
+    const void* q, const void* k, const void* v, const void* g, const void* beta,
+    const float* initial_states, void* output, float* final_states,
+    void* workspace, long long workspace_bytes_given,
+    const int* cu_seqlens_device, int n_seqs, long long total_tokens, int hk, int hv, int gate_fp32,
+    void* opaque_stream) {
+  if (!q || !k || !v || !g || !beta || !output || !workspace || !cu_seqlens_device) return int(cudaErrorInvalidValue);
+  const long long need = actlize_la_sm100_varlen_workspace_bytes(total_tokens, n_seqs, hk, hv);
+  if (need < 0 || workspace_bytes_given < need) return int(cudaErrorInvalidValue);
+  if ((reinterpret_cast<uintptr_t>(workspace) & 255) || (reinterpret_cast<uintptr_t>(q) & 15) ||
+      (reinterpret_cast<uintptr_t>(k) & 15) || (reinterpret_cast<uintptr_t>(v) & 15) ||
+      (reinterpret_cast<uintptr_t>(output) & 15))
+    return int(cudaErrorInvalidValue);
+  cudaStream_t stream = static_cast<cudaStream_t>(opaque_stream);
+  varlen_table_kernel<<<1, 32, 0, stream>>>(cu_seqlens_device, n_seqs, int(total_tokens), static_cast<int*>(workspace));
+  if (cudaError_t e = cudaGetLastError()) return int(e);
+  Geometry geo{n_seqs, int(total_tokens), hk, hv};
+  geo.varlen = static_cast<const int*>(workspace);
+  // the host does not know the lengths: the grids and the workspace indexing use the upper bound (every sequence
+  // may add one partly filled chunk); prepare blocks behind the real chunk count leave at once
+  geo.total_chunks = int((total_tokens + kChunk - 1) / kChunk + n_seqs);
   const Inputs in{static_cast<const __nv_bfloat16*>(q), static_cast<const __nv_bfloat16*>(k),
                   static_cast<const __nv_bfloat16*>(v), g, static_cast<const __nv_bfloat16*>(beta),
                   initial_states, static_cast<__nv_bfloat16*>(output), final_states, gate_fp32 ? 1 : 0};

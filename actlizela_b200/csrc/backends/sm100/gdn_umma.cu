@@ -189,6 +189,7 @@ prepare_umma_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
     // next sequence and are neutralised by beta = 0 / zero gate weights exactly like zero-filled padding rows
     const int gchunk = chunk;
     const int* prefix = geo.varlen + geo.batch + 1;
+    if (gchunk >= prefix[geo.batch]) return;     // grid sized by an upper bound of the chunk count (device offsets)
     const int seq = varlen_sequence_of(prefix, geo.batch, gchunk);
     chunk = gchunk - prefix[seq];
     t0 = geo.varlen[seq] + chunk * kChunk;

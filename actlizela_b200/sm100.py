@@ -129,12 +129,22 @@ class Sm100Forward:
         import ctypes
         import torch
         b, total, hk, hv = _validate(q, k, v, g, beta, None)
-        bounds = [int(x) for x in cu_seqlens]
-        n = len(bounds) - 1
-        if b != 1 or n < 1 or bounds[0] != 0 or bounds[-1] != total:
-            raise ValueError("varlen expects batch 1 and cu_seqlens running from 0 to the token count")
-        if any(b1 < b0 for b0, b1 in zip(bounds, bounds[1:])):
-            raise ValueError("cu_seqlens must be non-decreasing")
+        on_device = isinstance(cu_seqlens, torch.Tensor) and cu_seqlens.is_cuda
+        if on_device:
+            # offsets that live on the device are handed over as they are: no host read, capturable
+            if (cu_seqlens.dtype != torch.int32 or cu_seqlens.ndim != 1 or cu_seqlens.numel() < 2
+                    or cu_seqlens.device != q.device or not cu_seqlens.is_contiguous()):
+                raise ValueError("device cu_seqlens must be a contiguous int32 vector [N+1] on the inputs' device")
+            n, bounds = cu_seqlens.numel() - 1, None
+            if b != 1:
+                raise ValueError("varlen expects batch 1")
+        else:
+            bounds = [int(x) for x in cu_seqlens]
+            n = len(bounds) - 1
+            if b != 1 or n < 1 or bounds[0] != 0 or bounds[-1] != total:
+                raise ValueError("varlen expects batch 1 and cu_seqlens running from 0 to the token count")
+            if any(b1 < b0 for b0, b1 in zip(bounds, bounds[1:])):
+                raise ValueError("cu_seqlens must be non-decreasing")
         if initial_states is not None:
             if (tuple(initial_states.shape) != (n, hv, 128, 128) or initial_states.dtype != torch.float32
                     or initial_states.device != q.device or not initial_states.is_contiguous()):
@@ -148,6 +158,15 @@ class Sm100Forward:
         if nbytes < 0:
             raise ValueError("geometry exceeds the native grid limits")
         workspace = self._workspace(q.device, nbytes)
+        if on_device:
+            with torch.cuda.device(q.device):
+                self.library.check(lib.actlize_la_sm100_forward_varlen_device(
+                    q.data_ptr(), k.data_ptr(), v.data_ptr(), g.data_ptr(), beta.data_ptr(),
+                    initial_states.data_ptr() if initial_states is not None else None,
+                    out.data_ptr(), final.data_ptr() if final is not None else None,
+                    workspace.data_ptr(), nbytes, cu_seqlens.data_ptr(), n, total, hk, hv,
+                    int(g.dtype == torch.float32), torch.cuda.current_stream().cuda_stream))
+            return out, final
         offsets = (ctypes.c_int * (n + 1))(*bounds)
         with torch.cuda.device(q.device):
             stream = torch.cuda.current_stream().cuda_stream

@@ -2,7 +2,8 @@
 
 The reference's serving prefill pads every request into a fixed ``[R, W]`` batch before its forward
 (csrc/serving/prefill.cu:196-255).  Here the sequences stay packed: ``q,k,v,g,beta`` are
-``[1, total_tokens, H, ...]`` and ``cu_seqlens`` (host integers, length N+1) marks the boundaries.
+``[1, total_tokens, H, ...]`` and ``cu_seqlens`` (host integers, or an int32 device tensor, length N+1) marks
+the boundaries.
 The default path is the native entry ``actlize_la_sm100_forward_varlen``: one prepare and one walk launch
 for all sequences, every sequence chunked from its own start.  ``per_sequence=True`` instead hands each
 sequence (a contiguous slice) to the fixed-shape forward, two launches per sequence; both produce the same
@@ -18,6 +19,12 @@ def gdn_forward_varlen(q, k, v, g, beta, cu_seqlens, initial_states=None, output
     ``initial_states`` is FP32 ``[N,Hv,128,128]`` or None; sequences of length 0 keep their state.
     """
     import torch
+    if isinstance(cu_seqlens, torch.Tensor) and cu_seqlens.is_cuda and not per_sequence and forward_fn is None:
+        # int32 offsets in device memory go to the native entry untouched (no host read; capturable)
+        if forward_options:
+            raise ValueError("forward options apply to the per-sequence path only")
+        from .sm100 import load_sm100
+        return load_sm100().varlen(q, k, v, g, beta, cu_seqlens, initial_states, output_final_state)
     bounds = [int(x) for x in cu_seqlens]
     if q.shape[0] != 1 or len(bounds) < 2 or bounds[0] != 0 or bounds[-1] != q.shape[1]:
         raise ValueError("varlen expects batch 1 and cu_seqlens running from 0 to the token count")

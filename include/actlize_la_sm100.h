@@ -241,6 +241,19 @@ int actlize_la_sm100_forward_varlen(
     void* workspace, long long workspace_bytes,
     const int* cu_seqlens_host, int n_seqs, int hk, int hv, int gate_fp32, void* stream);
 
+/* The packed forward with the offsets on the DEVICE: cu_seqlens_device[0..n_seqs] are int32 in device memory, as a
+ * serving scheduler produces them; nothing is read on the host, nothing is allocated, and the call consists of kernel
+ * launches only (a one-thread kernel builds the offsets table, then the two tcgen05 kernels), so it can be captured
+ * in a CUDA graph.  `total_tokens` is the token dimension of the tensors.  Offsets are forced into
+ * 0 <= ... <= total_tokens and made non-decreasing on the device; tokens behind the last offset are not written.
+ * Grids and workspace are sized for the upper bound ceil(total/64) + n_seqs chunks
+ * (actlize_la_sm100_varlen_workspace_bytes already returns that). */
+int actlize_la_sm100_forward_varlen_device(
+    const void* q, const void* k, const void* v, const void* g, const void* beta,
+    const float* initial_states, void* output, float* final_states,
+    void* workspace, long long workspace_bytes,
+    const int* cu_seqlens_device, int n_seqs, long long total_tokens, int hk, int hv, int gate_fp32, void* stream);
+
 /* The same forward for callers that cannot allocate device memory (no counterpart in the
  * reference): the workspace is a fixed array inside the library instead of a caller buffer.
  * Meant for plugins inside a host framework that owns all allocations, or loops where a

@@ -122,6 +122,10 @@ def test_native_varlen_equals_the_per_sequence_forward_bitwise(lengths):
         assert torch.equal(finals, ref_finals)
         out_only, none = gdn_forward_varlen(q, k, v, g, beta, bounds, initial, False)
         assert none is None and torch.equal(out_only, out)
+        # the same offsets as an int32 device tensor: nothing is read on the host, the grids cover an upper bound
+        on_device = torch.tensor(bounds, dtype=torch.int32, device="cuda")
+        dev_out, dev_finals = gdn_forward_varlen(q, k, v, g, beta, on_device, initial, True)
+        assert torch.equal(dev_out, out) and torch.equal(dev_finals, finals)
 
 
 def test_native_varlen_rejects_bad_offsets(native_library):
