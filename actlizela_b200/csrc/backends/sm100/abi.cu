@@ -510,6 +510,16 @@ int tapered_begin(int chunks, int i, int segments) {
   return begin;
 }
 
+// Sequence segments of the host-buffer entry: the configuration's own count when it has one; otherwise the entry
+// picks a pipeline depth itself, because its segments exist to overlap the PCIe transfers with the computation,
+// whatever the device-resident forward prefers (tcgen05 family only: the other kernels cannot start mid-sequence).
+int host_segments_of(int config, const Geometry& geo) {
+  const int segments = segments_of(config, geo);
+  if (segments > 1 || (config & 0xf) != 1 || (config & (kStageMask | kWalkFlagMask))) return segments;
+  const int chunks = geo.chunks();
+  return chunks >= 32 ? 4 : (chunks >= 8 ? 2 : 1);
+}
+
 struct Arena {
   long long q, k, v, g, beta, initial, output, final_state, workspace, total;
 };
@@ -526,7 +536,7 @@ Arena arena_layout(int b, int t, int hk, int hv, int gate_fp32, int has_initial,
   a.output = take(vv);
   a.final_state = has_final ? take(st) : -1;
   const Geometry geo{b, t, hk, hv};
-  a.workspace = take(workspace_bytes(geo, segments_of(config, geo)));
+  a.workspace = take(workspace_bytes(geo, host_segments_of(config, geo)));
   a.total = off;
   return a;
 }
@@ -555,7 +565,7 @@ extern "C" int actlize_la_sm100_forward_host(
   cudaError_t e;
   {
     Geometry geo{b, t, hk, hv};
-    const int segments = segments_of(config, geo);
+    const int segments = host_segments_of(config, geo);
     if (segments > 1) {
       // Pipelined form: the sequence is cut into the same chunk-aligned segments as the computation.
       // Inputs of segment i+1 travel host -> device on one copy stream while segment i is prepared and

@@ -102,7 +102,9 @@ int actlize_la_sm100_forward_prepared(
  * memory management: copies the host tensors to the device, runs forward_prepared and copies
  * output / final state back, all on `stream`, then synchronises that stream.
  * `device_arena` is caller-owned device memory of at least
- * actlize_la_sm100_host_arena_bytes(...) bytes.  Follows the pack -> forward_prepared ->
+ * actlize_la_sm100_host_arena_bytes(...) bytes.  The sequence is cut into segments (the configuration's count, or
+ * four / two of the entry's own choice for the tcgen05 family when the configuration names one) whose transfers in
+ * both directions overlap the computation of their neighbours on library-owned copy streams.  Follows the pack -> forward_prepared ->
  * scatter shape of the reference's prefill adapter (csrc/serving/prefill.cu:196-255). */
 long long actlize_la_sm100_host_arena_bytes(int batch, int sequence, int key_heads, int value_heads,
                                             int gate_fp32, int has_initial, int has_final,
