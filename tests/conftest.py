@@ -32,10 +32,19 @@ def golden():
 
 @pytest.fixture(scope="session")
 def native_library():
-    """The built native library (builds it in-tree if the shared object is absent)."""
+    """The built native library; rebuilt in-tree when it is absent or older than the sources it records."""
     from actlizela_b200 import _library
+    from actlizela_b200.build_sm100 import build, sha
     path = _library.NATIVE_DIRECTORY / _library.LIBRARY_NAME
-    if not path.is_file():
-        from actlizela_b200.build_sm100 import build
+    receipt = _library.NATIVE_DIRECTORY / "build.json"
+    stale = not path.is_file() or not receipt.is_file()
+    if not stale:
+        # a binary older than the sources must not be what the tests exercise: compare the receipt's source hashes
+        recorded = json.loads(receipt.read_text()).get("source_sha256", {})
+        stale = not recorded or any(not (ROOT / name).is_file() or sha(ROOT / name) != digest
+                                    for name, digest in recorded.items())
+        sources = (ROOT / "actlizela_b200" / "csrc" / "backends" / "sm100").iterdir()
+        stale = stale or any(str(p.relative_to(ROOT)) not in recorded for p in sources if p.suffix in (".cu", ".cuh", ".h"))
+    if stale:
         build(quiet=True)
     return _library.load_library()
