@@ -60,15 +60,20 @@ class ClockSampler:
     def __init__(self, index):
         self.index, self.rows, self.process = index, [], None
 
-    def start(self):
+    def start(self, wait_s=5.0):
+        """Starts the sampling loop and waits for its first row, so that short timed regions are covered."""
         try:
             self.process = subprocess.Popen(
                 ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.QUERY}",
-                 "--format=csv,noheader,nounits", "-lms", "20"],
+                 "--format=csv,noheader,nounits", "-lms", "10"],
                 stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             threading.Thread(target=self._read, daemon=True).start()
         except OSError:
             self.process = None
+            return
+        deadline = time.perf_counter() + wait_s
+        while not self.rows and time.perf_counter() < deadline:
+            time.sleep(0.01)
 
     def _read(self):
         for line in self.process.stdout:
@@ -635,7 +640,6 @@ def main():
     ms_step, spread = timed(forward, args.steps)
     ms_walk, _ = timed(lambda: forward(0x20), args.steps)
     ms_prepare, _ = timed(lambda: forward(0x10), args.steps)
-    clocks = sampler.stop() if rank == 0 else None
     forward()
 
     # end to end through the host-buffer entry: pinned host tensors in, output + state back
@@ -659,6 +663,7 @@ def main():
     same = bool(torch.equal(host_out, out.cpu()))
     h2d = sum(x.numel() * x.element_size() for x in host if x is not None)
     d2h = host_out.numel() * 2 + host_final.numel() * 4
+    clocks = sampler.stop() if rank == 0 else None       # sampled over the device-timed loops and the end-to-end loop
     ms_copies = copy_bound_ms(host, host_out, host_final, device, world)
     del arena
 
