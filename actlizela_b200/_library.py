@@ -37,6 +37,7 @@ EXPORTS = {
     "actlize_la_sm100_host_arena_bytes": (_LL, [_I] * 8),
     "actlize_la_sm100_forward_host": (_I, [_P] * 9 + [_LL] + [_I] * 6 + [_P]),
     "actlize_la_sm100_apply_transition": (_I, [_P] * 4 + [_I, _P]),
+    "actlize_la_sm100_fold_transitions": (_I, [_P, _I] + [_P] * 4 + [_I, _P]),
     "actlize_la_sm100_launches_per_forward": (_I, [_I]),
     "actlize_la_sm100_device_status": (_I, [_P, _I]),
     "actlize_la_sm100_walk_plan_counts": (_I, [_P, _I]),

@@ -120,13 +120,12 @@ __global__ void varlen_table_kernel(const int* __restrict__ cu_seqlens, int n_se
   }
 }
 
-__global__ void apply_transition_kernel(const float* __restrict__ m, const float* __restrict__ off,
-                                        const float* __restrict__ s_in, float* __restrict__ s_out) {
-  // one CTA per 128x128 block: out = M @ S + b, 256 threads, each 64 outputs
-  __shared__ float tile_m[32][129];
-  __shared__ float tile_s[32][128];
-  const long long base = (long long)blockIdx.x * kDim * kDim;
+// One affine step of a 128x128 state block, out = M @ S + b, by the 256 threads of a CTA (each 64 outputs).
+// `s_in` and `s_out` may be the same block: every read of s_in is finished before the first write.
+__device__ void affine_step(const float* m, const float* off, const float* s_in, float* s_out,
+                            float (*tile_m)[129], float (*tile_s)[128]) {
   const int col = threadIdx.x % kDim, rhalf = threadIdx.x / kDim;
+  const long long base = 0;
   {
     // a transition matrix of exact zeros (a segment that forgets its incoming state) leaves out = b
     bool nonzero = false;
@@ -158,8 +157,43 @@ __global__ void apply_transition_kernel(const float* __restrict__ m, const float
       for (int r = 0; r < 64; ++r) acc[r] = fmaf(tile_m[kk][rhalf * 64 + r], sv, acc[r]);
     }
   }
+  __syncthreads();
 #pragma unroll
   for (int r = 0; r < 64; ++r) s_out[base + (rhalf * 64 + r) * kDim + col] = acc[r];
+}
+
+__global__ void apply_transition_kernel(const float* __restrict__ m, const float* __restrict__ off,
+                                        const float* __restrict__ s_in, float* __restrict__ s_out) {
+  __shared__ float tile_m[32][129];
+  __shared__ float tile_s[32][128];
+  const long long base = (long long)blockIdx.x * kDim * kDim;
+  affine_step(m + base, off + base, s_in + base, s_out + base, tile_m, tile_s);
+}
+
+// Exclusive scan of a rank's incoming state in one launch: `pairs` holds the (M_j, b_j) of the n earlier ranks as
+// [n][2][blocks][128][128] (M_0 is unused: rank 0 contributes its true outgoing state as b_0);
+// incoming = fold_j (M_j * incoming + b_j); optionally outgoing = my_m * incoming + my_b.  One CTA per block.
+__global__ void fold_transitions_kernel(const float* __restrict__ pairs, int n, int blocks,
+                                        float* __restrict__ incoming, float* __restrict__ outgoing,
+                                        const float* __restrict__ my_m, const float* __restrict__ my_b) {
+  __shared__ float tile_m[32][129];
+  __shared__ float tile_s[32][128];
+  const long long block = kDim * kDim, base = (long long)blockIdx.x * block;
+  float* state = incoming + base;
+  {
+    const float4* b0 = reinterpret_cast<const float4*>(pairs + (1LL * blocks) * block + base);
+    float4* dst = reinterpret_cast<float4*>(state);
+    for (int e = threadIdx.x; e < kDim * kDim / 4; e += blockDim.x) dst[e] = b0[e];
+  }
+  for (int j = 1; j < n; ++j) {
+    __syncthreads();                 // the state written by the previous step is visible to the whole CTA
+    affine_step(pairs + (2LL * j * blocks) * block + base, pairs + ((2LL * j + 1) * blocks) * block + base, state, state,
+                tile_m, tile_s);
+  }
+  if (outgoing) {
+    __syncthreads();
+    affine_step(my_m + base, my_b + base, state, outgoing + base, tile_m, tile_s);
+  }
 }
 
 }  // namespace
@@ -652,6 +686,16 @@ extern "C" int actlize_la_sm100_forward_host(
   if (final_state) GDN_COPY(final_state, base + a.final_state, st, cudaMemcpyDeviceToHost);
 #undef GDN_COPY
   return int(cudaStreamSynchronize(stream));
+}
+
+extern "C" int actlize_la_sm100_fold_transitions(const float* pairs, int n_pairs, const float* my_transition,
+                                                 const float* my_offset, float* incoming, float* outgoing,
+                                                 int blocks, void* opaque_stream) {
+  if (!pairs || !incoming || n_pairs <= 0 || blocks <= 0) return int(cudaErrorInvalidValue);
+  if (outgoing && (!my_transition || !my_offset || outgoing == incoming)) return int(cudaErrorInvalidValue);
+  fold_transitions_kernel<<<blocks, 256, 0, static_cast<cudaStream_t>(opaque_stream)>>>(
+      pairs, n_pairs, blocks, incoming, outgoing, my_transition, my_offset);
+  return int(cudaGetLastError());
 }
 
 extern "C" int actlize_la_sm100_apply_transition(const float* transition, const float* offset,

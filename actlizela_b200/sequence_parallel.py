@@ -12,7 +12,7 @@ Scheme (exact for any decay, no host read anywhere):
      segment whose decay falls below exp(-40), which is decided on the device from the gate sums);
   2. one grouped exchange of point-to-point messages: every rank sends its pair ``(M_r, b_r)`` to every LATER
      rank (rank 0 sends its true outgoing state as ``b_0``) and receives the pairs of every EARLIER rank; the
-     exclusive scan ``S_in(r) = M_{r-1} S_in(r-1) + b_{r-1}`` is then folded locally.  All messages of the job
+     exclusive scan ``S_in(r) = M_{r-1} S_in(r-1) + b_{r-1}`` is then folded locally, in one kernel launch.  All messages of the job
      are in flight at the same time (NCCL send/recv over NVLink on GPUs), so the exchange costs one message
      latency instead of a chain of dependent hops;
   3. every rank rewrites the leading chunks of its output that its incoming state still reaches (the walk stops,
@@ -53,6 +53,30 @@ def native_apply_transition(m, b, s):
             m.data_ptr(), b.data_ptr(), s.data_ptr(), out.data_ptr(),
             s.shape[0] * s.shape[1], torch.cuda.current_stream().cuda_stream))
     return out
+
+
+def native_fold_transitions(pairs, transition, offset, want_outgoing):
+    """Incoming state of a rank from the pairs of all earlier ranks, and optionally its outgoing state
+    ``M_r S_in + b_r``, in ONE launch (``actlize_la_sm100_fold_transitions``).  ``pairs`` is
+    [n, 2, B, Hv, 128, 128] with (M_j, b_j) of rank j at [j]; M_0 is not read."""
+    from ._library import load_library
+    lib = load_library()
+    incoming = torch.empty_like(pairs[0, 1])
+    outgoing = torch.empty_like(incoming) if want_outgoing else None
+    with torch.cuda.device(pairs.device):
+        lib.check(lib.lib.actlize_la_sm100_fold_transitions(
+            pairs.data_ptr(), pairs.shape[0], transition.data_ptr() if want_outgoing else None,
+            offset.data_ptr() if want_outgoing else None, incoming.data_ptr(),
+            outgoing.data_ptr() if want_outgoing else None, pairs.shape[2] * pairs.shape[3],
+            torch.cuda.current_stream().cuda_stream))
+    return incoming, outgoing
+
+
+def _torch_fold_transitions(pairs, transition, offset, want_outgoing):
+    state = pairs[0, 1]
+    for j in range(1, pairs.shape[0]):
+        state = _torch_apply_transition(pairs[j, 0], pairs[j, 1], state)
+    return state, (_torch_apply_transition(transition, offset, state) if want_outgoing else None)
 
 
 def _neighbour(group, rank):
@@ -115,29 +139,32 @@ def gdn_forward_sequence_parallel(q, k, v, g, beta, initial_state=None, output_f
     new_state = lambda: torch.empty(state_shape, dtype=torch.float32, device=q.device)
     later = [_neighbour(group, r) for r in range(rank + 1, world)]
 
-    def exchange(offset, transition):
+    fold = native_fold_transitions if (q.is_cuda and apply_transition is native_apply_transition) else None
+
+    def exchange(offset, transition, want_outgoing=False):
         """Post this rank's pair to every later rank and collect the pairs of every earlier rank, all at once.
-        Returns the incoming state of this rank (None on rank 0)."""
-        ops, received = [], []
+        Returns (incoming state of this rank, its outgoing state if asked for); (None, None) on rank 0."""
+        ops = []
+        pairs = torch.empty((rank, 2) + state_shape, dtype=torch.float32, device=q.device) if rank else None
         for r in range(rank):
-            pair = (new_state() if r > 0 else None, new_state())       # rank 0 sends its outgoing state only
-            received.append(pair)
             source = _neighbour(group, r)
-            if pair[0] is not None:
-                ops.append(dist.P2POp(dist.irecv, pair[0], source, group))
-            ops.append(dist.P2POp(dist.irecv, pair[1], source, group))
+            if r > 0:                                      # rank 0 sends its outgoing state only
+                ops.append(dist.P2POp(dist.irecv, pairs[r, 0], source, group))
+            ops.append(dist.P2POp(dist.irecv, pairs[r, 1], source, group))
         for target in later:
             if transition is not None:
                 ops.append(dist.P2POp(dist.isend, transition, target, group))
             ops.append(dist.P2POp(dist.isend, offset, target, group))
         for work in (dist.batch_isend_irecv(ops) if ops else []):
             work.wait()
-        if not received:
-            return None
-        state = received[0][1]
-        for m, off in received[1:]:
-            state = apply_transition(m, off, state)
-        return state
+        if pairs is None:
+            return None, None
+        if fold is not None:
+            return fold(pairs, transition, offset, want_outgoing)
+        state = pairs[0, 1]
+        for j in range(1, rank):
+            state = apply_transition(pairs[j, 0], pairs[j, 1], state)
+        return state, (apply_transition(transition, offset, state) if want_outgoing else None)
 
     if rank == 0:
         # the first segment starts from the caller's state; its true outgoing state plays the part of b_0
@@ -165,15 +192,14 @@ def gdn_forward_sequence_parallel(q, k, v, g, beta, initial_state=None, output_f
             out = segment.finish_decayed(incoming)
             return out, (offset if (last and output_final_state) else None)
         offset, transition = segment.offset_and_transition(need_transition=True)
-        incoming = exchange(offset, transition)
+        incoming, final = exchange(offset, transition, want_outgoing=bool(last and output_final_state))
         out = segment.finish_decayed(incoming)
-        final = apply_transition(transition, offset, incoming) if (last and output_final_state) else None
         return out, final
 
     # generic form on complete forwards: (M_r, b_r) by two state-only passes, the same exchange, a third pass
     _, offset = forward_fn(q, k, v, g, beta, None, True, **forward_options)
     eye = torch.eye(d, dtype=torch.float32, device=q.device).expand(state_shape).contiguous()
     _, transition = forward_fn(q, k, torch.zeros_like(v), g, beta, eye, True, **forward_options)
-    incoming = exchange(offset, transition)
+    incoming, _ = exchange(offset, transition)
     out, final = forward_fn(q, k, v, g, beta, incoming, bool(output_final_state and last), **forward_options)
     return out, (final if (output_final_state and last) else None)

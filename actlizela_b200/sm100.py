@@ -84,6 +84,30 @@ class Sm100Forward:
         import torch
         return torch.empty(nbytes, dtype=torch.uint8, device=device)
 
+    def _side_stream(self, device):
+        """One extra stream per device for the transition pass that runs next to the offset pass."""
+        import torch
+        streams = self.__dict__.setdefault("_side_streams", {})
+        key = str(device)
+        if key not in streams:
+            streams[key] = torch.cuda.Stream(device=device)
+        return streams[key]
+
+    def _transition_operands(self, like):
+        """Identity states [B,Hv,128,128] and a throw-away output buffer for transition passes, kept per device and
+        shape (read-only, respectively garbage by definition, so sharing them between calls is harmless)."""
+        import torch
+        cache = self.__dict__.setdefault("_transition_cache", {})
+        b, _, hv, _ = like.shape
+        key = (str(like.device), tuple(like.shape))
+        held = cache.get(key)
+        if held is None:
+            eye = torch.eye(128, dtype=torch.float32, device=like.device).expand(b, hv, 128, 128).contiguous()
+            held = cache[key] = (eye, torch.empty_like(like))
+            if len(cache) > 8:
+                cache.pop(next(iter(cache)))
+        return held
+
     def check_device_status(self, device=None, synchronize=True):
         """Raise RuntimeError if a kernel launched on ``device`` gave up a bounded wait.  Every wait inside the
         kernels is bounded; a kernel that runs out records where, drains and returns, and its output rows and
@@ -240,14 +264,13 @@ class PreparedSegment:
             b, _, _, hv = self.dims
             current = torch.cuda.current_stream()
             if self._side is None:
-                self._side = torch.cuda.Stream(device=self.output.device)
+                self._side = self.owner._side_stream(self.output.device)
             self._side.wait_stream(current)
+            eye, scratch = self.owner._transition_operands(self.output)
             with torch.cuda.stream(self._side):
-                eye = torch.eye(128, dtype=torch.float32, device=self.output.device).expand(b, hv, 128, 128).contiguous()
-                transition, scratch = self._state(), torch.empty_like(self.output)
+                transition = self._state()
                 self._launch(self._CONFIG | self._WALK | self._HOMOGENEOUS, eye, scratch, transition)
-                for x in (eye, transition, scratch):
-                    x.record_stream(self._side)
+                transition.record_stream(self._side)
         self._launch(self.split_walk, None, self.output, offset)
         if need_transition:
             torch.cuda.current_stream().wait_stream(self._side)

@@ -124,6 +124,15 @@ int actlize_la_sm100_apply_transition(const float* transition, const float* offs
                                       const float* state_in, float* state_out,
                                       int blocks, void* stream);
 
+/* The exclusive scan of a rank's incoming state in one launch: `pairs` is FP32 [n_pairs][2][blocks][128][128] with the
+ * (transition, offset) of earlier rank j at [j] (the transition of pair 0 is not read: the first rank contributes
+ * its true outgoing state as offset 0); incoming = fold over j of (transition_j @ incoming + offset_j).  When
+ * `outgoing` is not NULL it receives my_transition @ incoming + my_offset.  A transition block of exact zeros (a
+ * segment that forgets its incoming state) costs a scan of the block instead of a product. */
+int actlize_la_sm100_fold_transitions(const float* pairs, int n_pairs, const float* my_transition,
+                                      const float* my_offset, float* incoming, float* outgoing,
+                                      int blocks, void* stream);
+
 /* ---- the steps either side of the forward (memory-bound, one streaming kernel each) ---- */
 
 /* Step before: from a fused projection row [q heads | k heads | v heads] x 128 BF16 per token

@@ -356,6 +356,25 @@ def test_apply_transition_kernel(native_library):
     assert oracle.rel_frobenius(got.cpu(), want.cpu()) < 1e-6
 
 
+def test_fold_transitions_kernel(native_library):
+    """The exclusive scan of a rank's incoming state in one launch, against the same fold in FP64; pairs whose
+    transition is exactly zero (a segment that forgets its incoming state) take the short cut."""
+    from actlizela_b200.sequence_parallel import native_fold_transitions
+    gen = torch.Generator().manual_seed(6)
+    pairs = (0.2 * torch.randn(5, 2, 2, 3, 128, 128, generator=gen)).cuda()
+    pairs[2, 0] = 0                                   # rank 2 forgets what comes in
+    pairs[4, 0, 1, 2] = 0                             # ... rank 4 only for one head
+    mine_m, mine_b = (0.2 * torch.randn(2, 3, 128, 128, generator=gen)).cuda(), torch.randn(2, 3, 128, 128, generator=gen).cuda()
+    incoming, outgoing = native_fold_transitions(pairs, mine_m, mine_b, True)
+    only_in, none = native_fold_transitions(pairs[:1].contiguous(), mine_m, mine_b, False)
+    want = pairs[0, 1].double()
+    for j in range(1, 5):
+        want = pairs[j, 0].double() @ want + pairs[j, 1].double()
+    assert oracle.rel_frobenius(incoming.cpu(), want.cpu()) < 1e-6
+    assert oracle.rel_frobenius(outgoing.cpu(), (mine_m.double() @ want + mine_b.double()).cpu()) < 1e-6
+    assert none is None and torch.equal(only_in, pairs[0, 1])
+
+
 @pytest.mark.parametrize("configuration", ["umma-seg2", "umma-seg4", "umma-seg8"])
 def test_segmented_walk_equals_the_single_launch_bitwise(configuration, forward, native_library):
     """Prepare of later segments overlaps the walk of earlier ones; the arithmetic is unchanged."""
