@@ -50,12 +50,12 @@ __device__ __forceinline__ int varlen_sequence_of(const int* chunk_prefix, int c
 }
 
 // Workspace: structure-of-arrays planes, one entry per (batch, value head, chunk) block,
-// block index = (b * Hv + hv) * chunks + c.  W and U are stored TRANSPOSED (dimension-major), which is the
-// orientation the tensor-core kernels produce and consume them in: the prepare kernel's accumulators hold
-// W^T / U^T with the key / value index on the tensor-memory lanes, and the walk reads W^T as an MN-major B
-// operand and U^T one value row per thread.  Per block:
+// block index = (b * Hv + hv) * chunks + c.  W is stored TRANSPOSED (key-dimension-major), the orientation the
+// tensor-core kernels produce and consume it in: the prepare kernel's accumulator holds W^T with the key index on the
+// tensor-memory lanes, and the walk reads W^T as an MN-major B operand.  U is token-major: the walk's chain warps
+// read it one value per lane.  Per block:
 //   w_hi, w_lo  BF16 [128][64]  W^T, W = T (beta K Gamma), split W ~= hi + lo        (key dim, token)
-//   u           FP32 [128][64]  U^T, U = T (beta V)                                  (value dim, token)
+//   u           FP32 [64][128]  U = T (beta V)                                       (token, value dim)
 //   qs          BF16 [64][128]  Q * exp(prefix) / sqrt(128)                          (token, key dim)
 //   p           BF16 [64][64]   tril(Q K^T * exp(prefix_i - prefix_j)) / sqrt(128)
 //   gates       FP32 [128]      [0,64): exp(prefix_last - prefix_i), 0 for padding rows;
@@ -72,7 +72,7 @@ struct Workspace {
   float* gates;
   float* carry;
 };
-// element (token, dim) of a transposed [128][64] plane of block `block`
+// element (token, dim) of a transposed [128][64] plane (w_hi, w_lo) of block `block`
 __host__ __device__ inline long long transposed_index(long long block, int token, int dim) {
   return block * (kChunk * kDim) + (long long)dim * kChunk + token;
 }

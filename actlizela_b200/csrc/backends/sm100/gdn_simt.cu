@@ -139,7 +139,7 @@ prepare_simt_kernel(Inputs in, Geometry geo, Workspace ws) {
       const int i = half * (kChunk / 2) + r;
       float acc = 0.f;
       for (int c = 0; c <= i; ++c) acc = fmaf(sT[i * (kChunk + 1) + c] * sbeta[c], sX[c * kPad + d], acc);
-      ws.u[transposed_index(block, i, d)] = acc;
+      ws.u[block * kChunk * kDim + i * kDim + d] = acc;
     }
   }
   if (tid < kChunk) ws.gates[block * 128 + tid] = (tid < valid) ? expf(sp[valid - 1] - sp[tid]) : 0.f;
@@ -196,7 +196,7 @@ walk_simt_kernel(Inputs in, Geometry geo, Workspace ws) {
     for (int e = tid; e < kChunk * kChunk; e += kWalkThreads)
       sP[(e / kChunk) * (kChunk + 1) + e % kChunk] = __bfloat162float(ws.p[block * kChunk * kChunk + e]);
     for (int e = tid; e < kChunk * kVt; e += kWalkThreads)
-      sU[e] = ws.u[transposed_index(block, e / kVt, v0 + e % kVt)];
+      sU[e] = ws.u[block * kChunk * kDim + (e / kVt) * kDim + v0 + e % kVt];
     if (tid < 128) sG[tid] = ws.gates[block * 128 + tid];
     __syncthreads();
 

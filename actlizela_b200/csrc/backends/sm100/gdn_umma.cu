@@ -123,8 +123,9 @@ __device__ __forceinline__ float bf16_hi(uint32_t packed) { return __uint_as_flo
 //            boxes, the second over T itself (every thread holds its part of T in registers by then)
 //   phase 5  W^T = K^T (T diag(beta exp p))^T (into the columns D1 occupied),  U^T = V^T (T diag(beta))^T
 //            (A = transposed K / V tiles)
-//   phase 6  accumulators -> registers -> workspace.  The planes are stored transposed, [key or value dim][token]:
-//            a thread owns one row and writes its 32 tokens as contiguous 16-byte pieces; no staging, no transposition
+//   phase 6  accumulators -> registers -> workspace.  W is stored transposed, [key dim][token]: a thread owns one
+//            row and stages its 32 tokens as 16-byte pieces in swizzled tiles that leave through TMA stores; U is
+//            token-major and leaves straight from registers (a warp writes 128 contiguous bytes per token)
 struct PrepLayout {
   static constexpr int kQ0 = 0, kK0 = kBox, kQ1 = 2 * kBox, kK1 = 3 * kBox;   // [Q;K] stacked, two K atoms
   static constexpr int kV0 = 4 * kBox, kV1 = 5 * kBox;
@@ -133,6 +134,7 @@ struct PrepLayout {
   static constexpr int kTwH = kQ0, kTwL = kQ1;             // written after phase 4, when Q and the scratch are dead
   static constexpr int kTuH = kAT, kTuL = kAT + kBox;      // written once T sits in registers
   static constexpr int kX = kQ0;                           // block products of the inverse, on the dead Q box
+  static constexpr int kStageWH = 0, kStageWL = 2 * kBox;  // phase 6: W^T hi / lo tiles [128][64] over the Q/K boxes
   static constexpr int kLdX = 20, kLdX3 = 36;
   static constexpr int kVec = kAT + 64 * kLd * 4;          // float [4][64]: pl2, beta, beta*exp(p), exp(p)/sqrt(128)
   static constexpr int kBars = kVec + 4 * 64 * 4;          // 2 mbarriers, tmem slot, abort flag, carry
@@ -158,7 +160,8 @@ static_assert(3 * (kPrepSmem + 1024) <= 227 * 1024, "three prepare CTAs must fit
 template <bool kFused>
 __global__ void __launch_bounds__(kPrepThreads, 3)
 prepare_umma_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
-                    const __grid_constant__ CUtensorMap tm_v, Inputs in, Geometry geo, Workspace ws) {
+                    const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_wh,
+                    const __grid_constant__ CUtensorMap tm_wl, Inputs in, Geometry geo, Workspace ws) {
   // Indexing the declared array (no integer round trip) keeps these accesses in the shared state space.
   extern __shared__ __align__(1024) uint8_t raw_smem[];
   uint8_t* sm = raw_smem + ((1024u - (smem_u32(raw_smem) & 1023u)) & 1023u);
@@ -365,20 +368,21 @@ prepare_umma_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
     // token i multiplies the state by exp(g_i) (I - beta_i k_i k_i^T): a contraction iff 0 <= beta_i |k_i|^2 <= 2
     if (lrow >= 64) not_contraction = !(bi >= 0.f && bi * kk <= 2.f);
     {
-      // scaled query: row = tid/4, a quarter row (4 x 16 bytes of one TMA box row) per thread
-      const int row = tid >> 2, half = (tid >> 1) & 1, sub = tid & 1;
-      const float qs = s_qscale[row];
-      const uint8_t* src = sm + (half ? L::kQ1 : L::kQ0) + row * 128;
-      __nv_bfloat16* dst = ws.qs + (block * kChunk + row) * kDim + half * 64 + sub * 32;
+      // scaled query: sixteen lanes cover one 256-byte row (lane -> 16-byte piece), so a warp instruction writes two
+      // whole rows, 512 contiguous bytes; four passes of 16 rows
+      const int piece = tid & 15;
+      const uint8_t* box = sm + (piece < 8 ? L::kQ0 : L::kQ1);
 #pragma unroll
-      for (int cc = 0; cc < 4; ++cc) {
-        const uint4 v = *reinterpret_cast<const uint4*>(src + (((sub * 4 + cc) ^ (row & 7)) << 4));
+      for (int pass = 0; pass < 4; ++pass) {
+        const int row = pass * 16 + (tid >> 4);
+        const float qs = s_qscale[row];
+        const uint4 v = *reinterpret_cast<const uint4*>(box + row * 128 + (((piece & 7) ^ (row & 7)) << 4));
         uint4 o;
         o.x = pack_bf16(bf16_lo(v.x) * qs, bf16_hi(v.x) * qs);
         o.y = pack_bf16(bf16_lo(v.y) * qs, bf16_hi(v.y) * qs);
         o.z = pack_bf16(bf16_lo(v.z) * qs, bf16_hi(v.z) * qs);
         o.w = pack_bf16(bf16_lo(v.w) * qs, bf16_hi(v.w) * qs);
-        *reinterpret_cast<uint4*>(dst + cc * 8) = o;
+        *reinterpret_cast<uint4*>(ws.qs + (block * kChunk + row) * kDim + piece * 8) = o;
       }
     }
   }
@@ -572,6 +576,7 @@ prepare_umma_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
         mma_ss(tmem + 64, a, bb, kIdescN64AT, (part | ks) != 0);
       }
     }
+    if (kFused) tma_store_wait_read();      // the key tile's store has left shared memory before phase 6 reuses it
     mma_commit(bar_mma);
   }
   // the gate vector does not depend on the products: write it while they run
@@ -585,9 +590,16 @@ prepare_umma_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
   tc_fence_after();
   GDN_PSTAMP(5);
 
-  // ---- phase 6: W (hi/lo) and U leave for the transposed workspace planes: lrow is the key (W) / value (U)
-  // index, the thread's 32 tokens are contiguous in its row
+  // ---- phase 6: W (hi/lo) and U leave for the workspace; lrow is the key (W) / value (U) index.
+  // W^T: the thread's 32 tokens are contiguous in its row; they are staged as 16-byte pieces in two
+  // 128-byte-swizzled tiles [128 keys][64 tokens] on the dead input boxes and leave through two TMA stores
+  // (16-byte stores from registers to global would touch 32 lines per warp instruction).
+  // U: token-major [64][128] FP32, what the walk's chain warps read one value per lane: a warp's 32 lanes write
+  // 128 contiguous bytes per token straight from registers.
   if (ok) {
+    uint8_t* stage_hi = sm + L::kStageWH + lrow * 128;
+    uint8_t* stage_lo = sm + L::kStageWL + lrow * 128;
+    float* dst_u = ws.u + block * (kChunk * kDim) + lrow;
 #pragma unroll
     for (int piece = 0; piece < 2; ++piece) {
       const int tk0 = chalf * 32 + piece * 16;
@@ -603,19 +615,25 @@ prepare_umma_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
         hi[jj >> 1] = h;
         lo[jj >> 1] = pack_bf16(w0 - bf16_lo(h), w1 - bf16_hi(h));
       }
-      const long long at = transposed_index(block, tk0, lrow);
-      uint4* dh = reinterpret_cast<uint4*>(ws.w_hi + at);
-      uint4* dl = reinterpret_cast<uint4*>(ws.w_lo + at);
-      dh[0] = make_uint4(hi[0], hi[1], hi[2], hi[3]);
-      dh[1] = make_uint4(hi[4], hi[5], hi[6], hi[7]);
-      dl[0] = make_uint4(lo[0], lo[1], lo[2], lo[3]);
-      dl[1] = make_uint4(lo[4], lo[5], lo[6], lo[7]);
-      uint4* dst_u = reinterpret_cast<uint4*>(ws.u + at);
 #pragma unroll
-      for (int q4 = 0; q4 < 4; ++q4) dst_u[q4] = make_uint4(du[q4 * 4], du[q4 * 4 + 1], du[q4 * 4 + 2], du[q4 * 4 + 3]);
+      for (int h8 = 0; h8 < 2; ++h8) {          // eight tokens = one 16-byte slot of the swizzled row
+        const int slot = (((tk0 >> 3) + h8) ^ (lrow & 7)) << 4;
+        *reinterpret_cast<uint4*>(stage_hi + slot) = make_uint4(hi[h8 * 4], hi[h8 * 4 + 1], hi[h8 * 4 + 2], hi[h8 * 4 + 3]);
+        *reinterpret_cast<uint4*>(stage_lo + slot) = make_uint4(lo[h8 * 4], lo[h8 * 4 + 1], lo[h8 * 4 + 2], lo[h8 * 4 + 3]);
+      }
+#pragma unroll
+      for (int jj = 0; jj < 16; ++jj) dst_u[(tk0 + jj) * kDim] = __uint_as_float(du[jj]);
     }
+    fence_proxy_async_smem();
   }
-  if (kFused && tid == 0) tma_store_wait_read();    // the key tile's store has left shared memory
+  __syncthreads();
+  if (tid == 0 && ok) {
+    const int row = int(block * kDim);
+    tma_store_2d(&tm_wh, sm + L::kStageWH, 0, row);
+    tma_store_2d(&tm_wl, sm + L::kStageWL, 0, row);
+    tma_store_commit();
+    tma_store_wait_read();
+  }
   GDN_PSTAMP(6);
   if (!ok) {
     for (int i = 0; i < 20; ++i) __nanosleep(100000);   // let copies in flight land before the CTA leaves
@@ -875,10 +893,10 @@ walk_umma_kernel(const __grid_constant__ CUtensorMap tm_wh, const __grid_constan
     for (int c = 0; c < chunks && ok; ++c) {
       const int s = c % L::kStages;
       const float* gates = reinterpret_cast<const float*>(sm + s * L::kStage + L::kGates);
-      // U^T plane: this thread's value row, its 32 tokens contiguous (128 bytes)
-      const float* urow = ws.u + ((block0 + c) * kDim + v) * kChunk + half * 32;
-      if (c + 1 < chunks)      // pull the next chunk's row towards L2
-        asm volatile("prefetch.global.L2 [%0];" ::"l"(urow + kChunk * kDim));
+      // U plane, token-major: the 32 lanes of the warp read 128 contiguous bytes per token
+      const float* urow = ws.u + ((block0 + c) * kChunk + half * 32) * kDim + v;
+      if (c + 1 < chunks)      // pull the next chunk's U rows of this warp towards L2
+        asm volatile("prefetch.global.L2 [%0];" ::"l"(urow + kChunk * kDim + lane * kDim - lane));
 
       if (c > 0) ok = mbar_wait(bar_s, (c - 1) & 1, abort, 10, c);
       ok = ok && mbar_wait(full + s, (c / L::kStages) & 1, abort, 11, c);
@@ -920,11 +938,7 @@ walk_umma_kernel(const __grid_constant__ CUtensorMap tm_wh, const __grid_constan
 
       float u[32];
 #pragma unroll
-      for (int i4 = 0; i4 < 8; ++i4) {
-        const float4 x = (in.walk_flags & kWalkHomogeneous) ? make_float4(0.f, 0.f, 0.f, 0.f)
-                                                            : __ldg(reinterpret_cast<const float4*>(urow) + i4);
-        u[i4 * 4] = x.x; u[i4 * 4 + 1] = x.y; u[i4 * 4 + 2] = x.z; u[i4 * 4 + 3] = x.w;
-      }
+      for (int i = 0; i < 32; ++i) u[i] = (in.walk_flags & kWalkHomogeneous) ? 0.f : __ldg(urow + i * kDim);
 
       ok = mbar_wait(bar_ws, c & 1, abort, 12, c);
       if (!ok) break;
@@ -1183,11 +1197,16 @@ int launch_prepare_umma(const Inputs& in, const Geometry& geo, const Workspace& 
     if (int rc = enc.bf16_4d(&tm_k, in.k, kDim, geo.key_heads, geo.sequence, geo.varlen ? 1 : geo.batch, kChunk)) return rc;
     if (int rc = enc.bf16_4d(&tm_v, in.v, kDim, geo.value_heads, geo.sequence, geo.varlen ? 1 : geo.batch, kChunk)) return rc;
   }
+  // W^T planes: [blocks * 128 key rows][64 tokens], one 128-row box per block (the walk loads the same boxes)
+  CUtensorMap tm_wh, tm_wl;
+  const uint64_t plane_rows = uint64_t(geo.blocks()) * kDim;
+  if (int rc = enc.bf16_2d(&tm_wh, ws.w_hi, kChunk, plane_rows, kDim)) return rc;
+  if (int rc = enc.bf16_2d(&tm_wl, ws.w_lo, kChunk, plane_rows, kDim)) return rc;
   const unsigned grid = (unsigned)((geo.varlen ? 1LL : (long long)geo.batch) * geo.value_heads * geo.segment_chunks());
   if (fused)
-    prepare_umma_kernel<true><<<grid, kPrepThreads, kPrepSmem, stream>>>(tm_q, tm_k, tm_v, in, geo, ws);
+    prepare_umma_kernel<true><<<grid, kPrepThreads, kPrepSmem, stream>>>(tm_q, tm_k, tm_v, tm_wh, tm_wl, in, geo, ws);
   else
-    prepare_umma_kernel<false><<<grid, kPrepThreads, kPrepSmem, stream>>>(tm_q, tm_k, tm_v, in, geo, ws);
+    prepare_umma_kernel<false><<<grid, kPrepThreads, kPrepSmem, stream>>>(tm_q, tm_k, tm_v, tm_wh, tm_wl, in, geo, ws);
   return int(cudaGetLastError());
 }
 int launch_prepare_fused(const Inputs& in, const Geometry& geo, const Workspace& ws, cudaStream_t stream) {

@@ -100,8 +100,8 @@ def _workspace_planes(native_library, inputs, config):
     for name, size, dtype in sizes:
         planes[name] = ws[off:off + size].view(dtype).clone()
         off += size
-    # W and U are stored per block as [dimension][token]; back to [token][dimension] for the comparison
-    for name in ("w_hi", "w_lo", "u"):
+    # W is stored per block as [key dimension][token]; back to [token][dimension] for the comparison
+    for name in ("w_hi", "w_lo"):
         planes[name] = planes[name].view(n, 128, 64).transpose(1, 2).contiguous()
     planes["w"] = planes["w_hi"].float() + planes["w_lo"].float()
     planes["gates"] = planes["gates"].view(n, 128)[:, :65].contiguous()
