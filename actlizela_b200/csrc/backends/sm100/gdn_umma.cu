@@ -103,6 +103,43 @@ GDN_F32X2(add2, "add")
 GDN_F32X2(sub2, "sub")
 GDN_F32X2(mul2, "mul")
 #undef GDN_F32X2
+// d += a b for one m16n8k8 tile with FP32-grade accuracy from TF32 tensor-core products: a ~ ah + al, b ~ bh + bl
+// (both parts TF32), d += ah bh + ah bl + al bh (the 3xTF32 scheme the reference uses for these merges,
+// tests/wy_cpu.py:10-18).  Fragment layout of mma.m16n8k8: g = lane / 4, t = lane % 4;
+// a = {A[g][t], A[g+8][t], A[g][t+4], A[g+8][t+4]}, b = {B[t][g], B[t+4][g]}, d = {D[g][2t], D[g][2t+1], D[g+8][2t], D[g+8][2t+1]}.
+__device__ __forceinline__ void mma_tf32x3(float (&d)[4], const float (&a)[4], const float (&b)[2]) {
+  uint32_t ah[4], al[4], bh[2], bl[2];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(ah[i]) : "f"(a[i]));
+    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(al[i]) : "f"(a[i] - __uint_as_float(ah[i])));
+  }
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(bh[i]) : "f"(b[i]));
+    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(bl[i]) : "f"(b[i] - __uint_as_float(bh[i])));
+  }
+#define GDN_MMA_TF32(A, B)                                                                              \
+  asm volatile("mma.sync.aligned.m16n8k8.row.col.f32.tf32.tf32.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, " \
+               "{%8, %9}, {%0, %1, %2, %3};"                                                             \
+               : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])                                          \
+               : "r"(A[0]), "r"(A[1]), "r"(A[2]), "r"(A[3]), "r"(B[0]), "r"(B[1]))
+  GDN_MMA_TF32(al, bh);
+  GDN_MMA_TF32(ah, bl);
+  GDN_MMA_TF32(ah, bh);
+#undef GDN_MMA_TF32
+}
+// One m16n8 tile of D = A B over k in [0, kdim): A row-major with pitch lda (rows a_row0 + {g, g+8}), B row-major with
+// pitch ldb (column b_col0 + g); both in shared memory.
+__device__ __forceinline__ void tile_product_tf32x3(float (&d)[4], const float* a, int lda, const float* b, int ldb,
+                                                    int kdim, int g, int t) {
+#pragma unroll
+  for (int k0 = 0; k0 < kdim; k0 += 8) {
+    const float av[4] = {a[g * lda + k0 + t], a[(g + 8) * lda + k0 + t], a[g * lda + k0 + t + 4], a[(g + 8) * lda + k0 + t + 4]};
+    const float bv[2] = {b[(k0 + t) * ldb + g], b[(k0 + t + 4) * ldb + g]};
+    mma_tf32x3(d, av, bv);
+  }
+}
 __device__ __forceinline__ float bf16_lo(uint32_t packed) { return __uint_as_float(packed << 16); }
 __device__ __forceinline__ float bf16_hi(uint32_t packed) { return __uint_as_float(packed & 0xffff0000u); }
 
@@ -116,9 +153,9 @@ __device__ __forceinline__ float bf16_hi(uint32_t packed) { return __uint_as_flo
 //   phase 3  rows 0..63  -> P = tril(QK^T * decay)/sqrt(128) -> BF16 -> workspace
 //            rows 64..127-> A = tril(beta_i KK^T * decay, -1) -> shared (FP32); scaled query rows -> workspace;
 //            the diagonal k_i.k_i decides whether token i is a contraction (word 65 of the gate vector)
-//   phase 4  T = (I+A)^-1 in FP32 on the CUDA cores, IN PLACE, blocked: four 16x16 diagonal solves in registers,
-//            then T21 = -T22 (A21 T11) at block size 16 and 32 (the blocked scheme of the reference's
-//            tests/wy_cpu.py:21-41, with plain FP32 products instead of TF32x3)
+//   phase 4  T = (I+A)^-1 IN PLACE, blocked: four 16x16 diagonal solves in FP32 registers, then
+//            T21 = -T22 (A21 T11) at block size 16 and 32 as 3xTF32 mma.sync tiles (the blocked scheme and the
+//            TF32x3 merges of the reference's tests/wy_cpu.py:10-41)
 //            T diag(beta exp(p)) and T diag(beta) -> BF16 hi/lo K-major tiles: the first pair over the dead Q
 //            boxes, the second over T itself (every thread holds its part of T in registers by then)
 //   phase 5  W^T = K^T (T diag(beta exp p))^T (into the columns D1 occupied),  U^T = V^T (T diag(beta))^T
@@ -423,91 +460,54 @@ prepare_umma_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
   }
   __syncthreads();
   GDN_PSTAMP(7);
-  // level 2: inside each 32x32 diagonal block, T21 = -T22 (A21 T11) with 16x16 blocks, written where A21 was;
-  // thread -> (block, row i, column pair)
+  // level 2: inside each 32x32 diagonal block, T21 = -T22 (A21 T11) with 16x16 blocks, written where A21 was.
+  // Levels 2 and 3 are small dense products: they run on the tensor cores as m16n8k8 TF32 tiles with the 3xTF32
+  // split (FP32-grade accuracy), one tile per warp, operands read from shared memory one word per lane; as FP32 FMAs
+  // with vector loads they made up more than half of the kernel's shared-memory traffic, which is what bounds it.
   {
-    const int big = tid >> 7, i = (tid & 127) >> 3, cg = tid & 7;
-    const int o = big * 32;
-    float a[16];
-    float2 acc = make_float2(0.f, 0.f);
-    if (ok) {
-      const float* arow = sAT + (o + 16 + i) * L::kLd + o;
-#pragma unroll
-      for (int q4 = 0; q4 < 4; ++q4) {
-        const float4 v = *reinterpret_cast<const float4*>(arow + q4 * 4);
-        a[q4 * 4] = v.x; a[q4 * 4 + 1] = v.y; a[q4 * 4 + 2] = v.z; a[q4 * 4 + 3] = v.w;
-      }
-#pragma unroll
-      for (int k = 0; k < 16; ++k) {
-        const float2 t = *reinterpret_cast<const float2*>(sAT + (o + k) * L::kLd + o + cg * 2);
-        acc.x = fmaf(a[k], t.x, acc.x);
-        acc.y = fmaf(a[k], t.y, acc.y);
-      }
-      *reinterpret_cast<float2*>(sX + (big * 16 + i) * L::kLdX + cg * 2) = acc;
+    const int lane = tid & 31, g = lane >> 2, t = lane & 3;
+    const int big = warp >> 1, nt = warp & 1, o = big * 32;        // warps 0..3: (diagonal block, 8-column tile)
+    float c[4] = {0.f, 0.f, 0.f, 0.f};
+    if (ok && warp < 4) {
+      tile_product_tf32x3(c, sAT + (o + 16) * L::kLd + o, L::kLd, sAT + o * L::kLd + o + nt * 8, L::kLd, 16, g, t);
+      *reinterpret_cast<float2*>(sX + (big * 16 + g) * L::kLdX + nt * 8 + 2 * t) = make_float2(c[0], c[1]);
+      *reinterpret_cast<float2*>(sX + (big * 16 + g + 8) * L::kLdX + nt * 8 + 2 * t) = make_float2(c[2], c[3]);
     }
     __syncthreads();
-    if (ok) {
-      const float* trow = sAT + (o + 16 + i) * L::kLd + o + 16;
-#pragma unroll
-      for (int q4 = 0; q4 < 4; ++q4) {
-        const float4 v = *reinterpret_cast<const float4*>(trow + q4 * 4);
-        a[q4 * 4] = v.x; a[q4 * 4 + 1] = v.y; a[q4 * 4 + 2] = v.z; a[q4 * 4 + 3] = v.w;
-      }
-      acc = make_float2(0.f, 0.f);
-#pragma unroll
-      for (int k = 0; k < 16; ++k) {
-        const float2 t = *reinterpret_cast<const float2*>(sX + (big * 16 + k) * L::kLdX + cg * 2);
-        acc.x = fmaf(a[k], t.x, acc.x);
-        acc.y = fmaf(a[k], t.y, acc.y);
-      }
-      *reinterpret_cast<float2*>(sAT + (o + 16 + i) * L::kLd + o + cg * 2) = make_float2(-acc.x, -acc.y);
+    if (ok && warp < 4) {
+      c[0] = c[1] = c[2] = c[3] = 0.f;
+      tile_product_tf32x3(c, sAT + (o + 16) * L::kLd + o + 16, L::kLd, sX + big * 16 * L::kLdX + nt * 8, L::kLdX, 16, g, t);
+      *reinterpret_cast<float2*>(sAT + (o + 16 + g) * L::kLd + o + nt * 8 + 2 * t) = make_float2(-c[0], -c[1]);
+      *reinterpret_cast<float2*>(sAT + (o + 16 + g + 8) * L::kLd + o + nt * 8 + 2 * t) = make_float2(-c[2], -c[3]);
     }
   }
   __syncthreads();
   GDN_PSTAMP(8);
-  // level 3: T21 = -T22 (A21 T11) with 32x32 blocks; thread -> row i, four columns
+  // level 3: T21 = -T22 (A21 T11) with 32x32 blocks: eight tiles, one per warp
   {
-    const int i = tid >> 3, cg = tid & 7;
-    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    const int lane = tid & 31, g = lane >> 2, t = lane & 3;
+    const int mt = warp >> 2, nt = warp & 3;
+    float c[4] = {0.f, 0.f, 0.f, 0.f};
     if (ok) {
-      const float* arow = sAT + (32 + i) * L::kLd;
-#pragma unroll
-      for (int k0 = 0; k0 < 32; k0 += 8) {
-        const float4 a0 = *reinterpret_cast<const float4*>(arow + k0), a1 = *reinterpret_cast<const float4*>(arow + k0 + 4);
-        const float a[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
-#pragma unroll
-        for (int k = 0; k < 8; ++k) {
-          const float4 t = *reinterpret_cast<const float4*>(sAT + (k0 + k) * L::kLd + cg * 4);
-          acc.x = fmaf(a[k], t.x, acc.x); acc.y = fmaf(a[k], t.y, acc.y);
-          acc.z = fmaf(a[k], t.z, acc.z); acc.w = fmaf(a[k], t.w, acc.w);
-        }
-      }
-      *reinterpret_cast<float4*>(sX + i * L::kLdX3 + cg * 4) = acc;
+      tile_product_tf32x3(c, sAT + (32 + mt * 16) * L::kLd, L::kLd, sAT + nt * 8, L::kLd, 32, g, t);
+      *reinterpret_cast<float2*>(sX + (mt * 16 + g) * L::kLdX3 + nt * 8 + 2 * t) = make_float2(c[0], c[1]);
+      *reinterpret_cast<float2*>(sX + (mt * 16 + g + 8) * L::kLdX3 + nt * 8 + 2 * t) = make_float2(c[2], c[3]);
     }
     __syncthreads();
     if (ok) {
-      const float* trow = sAT + (32 + i) * L::kLd + 32;
-      acc = make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll
-      for (int k0 = 0; k0 < 32; k0 += 8) {
-        const float4 a0 = *reinterpret_cast<const float4*>(trow + k0), a1 = *reinterpret_cast<const float4*>(trow + k0 + 4);
-        const float a[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
-#pragma unroll
-        for (int k = 0; k < 8; ++k) {
-          const float4 t = *reinterpret_cast<const float4*>(sX + (k0 + k) * L::kLdX3 + cg * 4);
-          acc.x = fmaf(a[k], t.x, acc.x); acc.y = fmaf(a[k], t.y, acc.y);
-          acc.z = fmaf(a[k], t.z, acc.z); acc.w = fmaf(a[k], t.w, acc.w);
-        }
-      }
-      *reinterpret_cast<float4*>(sAT + (32 + i) * L::kLd + cg * 4) = make_float4(-acc.x, -acc.y, -acc.z, -acc.w);
+      c[0] = c[1] = c[2] = c[3] = 0.f;
+      tile_product_tf32x3(c, sAT + (32 + mt * 16) * L::kLd + 32, L::kLd, sX + nt * 8, L::kLdX3, 32, g, t);
+      *reinterpret_cast<float2*>(sAT + (32 + mt * 16 + g) * L::kLd + nt * 8 + 2 * t) = make_float2(-c[0], -c[1]);
+      *reinterpret_cast<float2*>(sAT + (32 + mt * 16 + g + 8) * L::kLd + nt * 8 + 2 * t) = make_float2(-c[2], -c[3]);
     }
   }
   __syncthreads();
   GDN_PSTAMP(9);
-  // T diag(beta exp p) and T diag(beta) as BF16 hi/lo K-major tiles; thread -> row i, sixteen columns.
+  // T diag(beta exp p) and T diag(beta) as BF16 hi/lo K-major tiles; thread -> row i, sixteen columns (conflict-free:
+  // the row pitch of 68 words spreads eight consecutive rows over all banks, the tile rows are swizzled).
   // The W pair goes to the Q boxes at once; the U pair overwrites T, so it waits until every thread has read its part.
   {
-    const int i = tid >> 2, c0 = (tid & 3) * 16;
+    const int i = tid & 63, c0 = (tid >> 6) * 16;      // a warp's lanes: consecutive rows, the same columns
     uint32_t uh[8], ul[8];
     if (ok) {
 #pragma unroll
