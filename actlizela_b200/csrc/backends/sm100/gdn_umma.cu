@@ -108,16 +108,20 @@ GDN_F32X2(mul2, "mul")
 // tests/wy_cpu.py:10-18).  Fragment layout of mma.m16n8k8: g = lane / 4, t = lane % 4;
 // a = {A[g][t], A[g+8][t], A[g][t+4], A[g+8][t+4]}, b = {B[t][g], B[t+4][g]}, d = {D[g][2t], D[g][2t+1], D[g+8][2t], D[g+8][2t+1]}.
 __device__ __forceinline__ void mma_tf32x3(float (&d)[4], const float (&a)[4], const float (&b)[2]) {
+  // The high part is the operand with its 13 low mantissa bits cleared (a TF32 value), the low part the exact FP32
+  // remainder, of which the tensor core reads the leading TF32 bits: about 2^-20 relative in all, below the
+  // 16 significant bits the inverse is later stored with.  Logic and add instructions: the conversion unit, the
+  // kernel's busiest pipe, stays free for the BF16 packing.
   uint32_t ah[4], al[4], bh[2], bl[2];
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
-    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(ah[i]) : "f"(a[i]));
-    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(al[i]) : "f"(a[i] - __uint_as_float(ah[i])));
+    ah[i] = __float_as_uint(a[i]) & 0xffffe000u;
+    al[i] = __float_as_uint(a[i] - __uint_as_float(ah[i]));
   }
 #pragma unroll
   for (int i = 0; i < 2; ++i) {
-    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(bh[i]) : "f"(b[i]));
-    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(bl[i]) : "f"(b[i] - __uint_as_float(bh[i])));
+    bh[i] = __float_as_uint(b[i]) & 0xffffe000u;
+    bl[i] = __float_as_uint(b[i] - __uint_as_float(bh[i]));
   }
 #define GDN_MMA_TF32(A, B)                                                                              \
   asm volatile("mma.sync.aligned.m16n8k8.row.col.f32.tf32.tf32.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, " \
@@ -368,6 +372,18 @@ prepare_umma_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
 #pragma unroll
     for (int piece = 0; piece < 2; ++piece) {
       const int j0 = chalf * 32 + piece * 16;
+      if (j0 > (i | 31)) {
+        // the whole piece lies above the diagonal for every row of this warp (rows (i & ~31) .. (i | 31)): zeros
+        if (lrow < 64) {
+          uint4* dst = reinterpret_cast<uint4*>(ws.p + (block * kChunk + i) * kChunk + j0);
+          dst[0] = dst[1] = make_uint4(0u, 0u, 0u, 0u);
+        } else {
+#pragma unroll
+          for (int q4 = 0; q4 < 4; ++q4)
+            *reinterpret_cast<float4*>(sAT + i * L::kLd + j0 + q4 * 4) = make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+        continue;
+      }
       float pj[16];
 #pragma unroll
       for (int q4 = 0; q4 < 4; ++q4) {
