@@ -223,7 +223,22 @@ prepare_umma_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
   const int tid = threadIdx.x, warp = tid >> 5;
   const int chunks = geo.chunks(), seg_chunks = geo.segment_chunks();
   int chunk = geo.chunk_begin + blockIdx.x % seg_chunks;      // chunk index inside its sequence
-  const int bh = blockIdx.x / seg_chunks;
+  int bh = blockIdx.x / seg_chunks;
+  if (!geo.varlen) {
+    // Block order = reverse of the order in which the walk consumes the blocks: the walk's CTAs (one per
+    // (batch, head) and parallel sub-segment) all start at the first chunk of their sub-segment, so the blocks
+    // prepared LAST are the leading chunks of every sub-segment of every head, and the walk finds them in L2.
+    // The grid covers heads x sub-segments x longest sub-segment; a slot behind a shorter sub-segment's end is empty.
+    const int parallel = geo.parallel > 1 ? geo.parallel : 1;
+    const int longest = (seg_chunks + parallel - 1) / parallel;
+    const int units = geo.batch * geo.value_heads * parallel;
+    const int offset = longest - 1 - int(blockIdx.x) / units, unit = int(blockIdx.x) % units;
+    const int sub = unit % parallel;
+    const int sub_begin = int((long long)seg_chunks * sub / parallel), sub_end = int((long long)seg_chunks * (sub + 1) / parallel);
+    if (sub_begin + offset >= sub_end) return;
+    bh = unit / parallel;
+    chunk = geo.chunk_begin + sub_begin + offset;
+  }
   const int b = bh / geo.value_heads, hv = bh % geo.value_heads;     // packed mode: bh = hv, b = 0
   const int hk = hv / geo.group();
   int t0 = chunk * kChunk, t_end = geo.sequence;
@@ -1218,7 +1233,10 @@ int launch_prepare_umma(const Inputs& in, const Geometry& geo, const Workspace& 
   const uint64_t plane_rows = uint64_t(geo.blocks()) * kDim;
   if (int rc = enc.bf16_2d(&tm_wh, ws.w_hi, kChunk, plane_rows, kDim)) return rc;
   if (int rc = enc.bf16_2d(&tm_wl, ws.w_lo, kChunk, plane_rows, kDim)) return rc;
-  const unsigned grid = (unsigned)((geo.varlen ? 1LL : (long long)geo.batch) * geo.value_heads * geo.segment_chunks());
+  const int parallel = geo.parallel > 1 ? geo.parallel : 1;
+  const unsigned grid = geo.varlen
+      ? (unsigned)((long long)geo.value_heads * geo.segment_chunks())
+      : (unsigned)((long long)geo.batch * geo.value_heads * parallel * ((geo.segment_chunks() + parallel - 1) / parallel));
   if (fused)
     prepare_umma_kernel<true><<<grid, kPrepThreads, kPrepSmem, stream>>>(tm_q, tm_k, tm_v, tm_wh, tm_wl, in, geo, ws);
   else
