@@ -413,8 +413,8 @@ extern "C" long long actlize_la_sm100_projections_workspace_bytes(int b, int t, 
   if (!geometry_ok(b, t, hk, hv) || !config_ok(config) || (config & 0xf) != 1 || (config & (kStageMask | kWalkFlagMask)))
     return -1;
   const Geometry geo{b, t, hk, hv};
-  // the ordinary workspace plus the normalised keys [B][T][Hk][128] BF16
-  return ((workspace_bytes(geo, segments_of(config, geo)) + 255) & ~255LL) + (long long)b * t * hk * kDim * 2;
+  // the ordinary workspace plus the normalised keys and queries, each [B][T][Hk][128] BF16
+  return ((workspace_bytes(geo, segments_of(config, geo)) + 255) & ~255LL) + 2 * (((long long)b * t * hk * kDim * 2 + 255) & ~255LL);
 }
 
 extern "C" int actlize_la_sm100_forward_projections(
@@ -433,9 +433,11 @@ extern "C" int actlize_la_sm100_forward_projections(
   const int segments = segments_of(config, geo);
   const Workspace ws = carve_workspace(workspace, geo);
   Inputs in{};
-  in.k_norm = reinterpret_cast<__nv_bfloat16*>(static_cast<char*>(workspace) +
-                                               ((workspace_bytes(geo, segments) + 255) & ~255LL));
+  char* planes = static_cast<char*>(workspace) + ((workspace_bytes(geo, segments) + 255) & ~255LL);
+  in.k_norm = reinterpret_cast<__nv_bfloat16*>(planes);
+  in.q_norm = reinterpret_cast<__nv_bfloat16*>(planes + (((long long)b * t * hk * kDim * 2 + 255) & ~255LL));
   in.k = in.k_norm;                 // what the walk reads
+  in.q = in.q_norm;
   in.initial = initial;
   in.output = static_cast<__nv_bfloat16*>(output);
   in.final_state = final_state;

@@ -56,18 +56,18 @@ __device__ __forceinline__ int varlen_sequence_of(const int* chunk_prefix, int c
 // read it one value per lane.  Per block:
 //   w_hi, w_lo  BF16 [128][64]  W^T, W = T (beta K Gamma), split W ~= hi + lo        (key dim, token)
 //   u           FP32 [64][128]  U = T (beta V)                                       (token, value dim)
-//   qs          BF16 [64][128]  Q * exp(prefix) / sqrt(128)                          (token, key dim)
 //   p           BF16 [64][64]   tril(Q K^T * exp(prefix_i - prefix_j)) / sqrt(128)
-//   gates       FP32 [128]      [0,64): exp(prefix_last - prefix_i), 0 for padding rows;
+//   gates       FP32 [192]      [0,64): exp(prefix_last - prefix_i), 0 for padding rows;
 //                               [64]: exp(prefix_last); [65] (tcgen05 prepare only): non-zero when some token of the
-//                               chunk is not a contraction of the state (beta < 0 or beta |k|^2 > 2); rest unused
+//                               chunk is not a contraction of the state (beta < 0 or beta |k|^2 > 2);
+//                               [128,192): exp(prefix_i) / sqrt(128), the scale the walk applies to the rows of its
+//                               Q tile (the scaled queries are not stored: the walk reads q itself); rest unused
 // plus, when the sequence is walked in segments, one FP32 [128][128] state per (batch, value head)
 // that carries the state from one segment's walk to the next (K-by-V order, like the public state).
 struct Workspace {
   __nv_bfloat16* w_hi;
   __nv_bfloat16* w_lo;
   float* u;
-  __nv_bfloat16* qs;
   __nv_bfloat16* p;
   float* gates;
   float* carry;
@@ -77,8 +77,8 @@ __host__ __device__ inline long long transposed_index(long long block, int token
   return block * (kChunk * kDim) + (long long)dim * kChunk + token;
 }
 
-constexpr long long kBlockBytes =
-    2LL * kChunk * kDim * 2 + kChunk * kDim * 4 + kChunk * kDim * 2 + kChunk * kChunk * 2 + 128 * 4;
+constexpr int kGateWords = 192, kGateQueryScale = 128;     // words per gate vector; first word of the query scales
+constexpr long long kBlockBytes = 2LL * kChunk * kDim * 2 + kChunk * kDim * 4 + kChunk * kChunk * 2 + kGateWords * 4;
 
 inline __host__ long long workspace_bytes(const Geometry& g, int segments = 1) {
   return g.blocks() * kBlockBytes + (segments > 1 ? (long long)g.batch * g.value_heads * kDim * kDim * 4 : 0);
@@ -92,9 +92,8 @@ inline __host__ Workspace carve_workspace(void* base, const Geometry& g) {
   w.w_hi = reinterpret_cast<__nv_bfloat16*>(p);  p += n * kChunk * kDim * 2;
   w.w_lo = reinterpret_cast<__nv_bfloat16*>(p);  p += n * kChunk * kDim * 2;
   w.u = reinterpret_cast<float*>(p);             p += n * kChunk * kDim * 4;
-  w.qs = reinterpret_cast<__nv_bfloat16*>(p);    p += n * kChunk * kDim * 2;
   w.p = reinterpret_cast<__nv_bfloat16*>(p);     p += n * kChunk * kChunk * 2;
-  w.gates = reinterpret_cast<float*>(p);         p += n * 128 * 4;
+  w.gates = reinterpret_cast<float*>(p);         p += n * kGateWords * 4;
   w.carry = reinterpret_cast<float*>(p);         // only backed by memory when segments > 1
   return w;
 }
@@ -125,6 +124,7 @@ struct Inputs {
   const float* a_log = nullptr;
   const float* dt_bias = nullptr;
   __nv_bfloat16* k_norm = nullptr;
+  __nv_bfloat16* q_norm = nullptr;      // likewise the normalised queries [B][T][Hk][128] (the walk gets it as its `q`)
 };
 constexpr int kWalkHomogeneous = 1, kWalkUntilDecayed = 2;
 constexpr int kWalkSelftestStall = 4;     // the TMA producer stops after the first chunk (failure-detection self-test)

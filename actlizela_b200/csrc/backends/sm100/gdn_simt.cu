@@ -3,7 +3,7 @@
 // It exists as an independent device-side cross-check of the tensor-core kernels: the same
 // workspace layout is produced and consumed, so either stage can be exchanged with its
 // tcgen05 counterpart when a numerical difference has to be located.  All contractions are
-// plain FP32 FMAs; only the quantities the workspace stores in BF16 (P, scaled Q) or as a
+// plain FP32 FMAs; only the quantities the tensor-core path rounds to BF16 (P, scaled Q) or to a
 // BF16 hi+lo pair (W) are rounded.
 //
 // Math (per 64-token chunk, value head h, key head h / (Hv/Hk)); p = inclusive prefix of g:
@@ -83,11 +83,6 @@ prepare_simt_kernel(Inputs in, Geometry geo, Workspace ws) {
     sT[i * (kChunk + 1) + j] = (j < i) ? sbeta[i] * kk * decay : 0.f;
     ws.p[block * kChunk * kChunk + e] = __float2bfloat16_rn(qk * decay * kScale);
   }
-  // scaled query: Q * exp(p) / sqrt(128)
-  for (int e = tid; e < kChunk * kDim; e += kPrepareThreads) {
-    const int i = e / kDim, d = e % kDim;
-    ws.qs[block * kChunk * kDim + e] = __float2bfloat16_rn(sX[i * kPad + d] * sexp[i] * kScale);
-  }
   __syncthreads();
 
   // T = (I + A)^-1 by forward substitution, one column per thread, in place
@@ -142,8 +137,9 @@ prepare_simt_kernel(Inputs in, Geometry geo, Workspace ws) {
       ws.u[block * kChunk * kDim + i * kDim + d] = acc;
     }
   }
-  if (tid < kChunk) ws.gates[block * 128 + tid] = (tid < valid) ? expf(sp[valid - 1] - sp[tid]) : 0.f;
-  if (tid == kChunk) ws.gates[block * 128 + kChunk] = expf(sp[valid - 1]);
+  if (tid < kChunk) ws.gates[block * kGateWords + tid] = (tid < valid) ? expf(sp[valid - 1] - sp[tid]) : 0.f;
+  if (tid == kChunk) ws.gates[block * kGateWords + kChunk] = expf(sp[valid - 1]);
+  if (tid < kChunk) ws.gates[block * kGateWords + kGateQueryScale + tid] = sexp[tid] * kScale;   // query scale
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -187,17 +183,21 @@ walk_simt_kernel(Inputs in, Geometry geo, Workspace ws) {
       const long long off = block * kChunk * kDim + e;
       sW[i * kPad + d] = __bfloat162float(ws.w_hi[transposed_index(block, i, d)]) +
                          __bfloat162float(ws.w_lo[transposed_index(block, i, d)]);
-      sQ[i * kPad + d] = __bfloat162float(ws.qs[off]);
-      float kv = 0.f;
-      if (i < valid)
-        kv = __bfloat162float(in.k[(((long long)b * geo.sequence + t0 + i) * geo.key_heads + hk) * kDim + d]);
+      float kv = 0.f, qv = 0.f;
+      if (i < valid) {
+        const long long at = (((long long)b * geo.sequence + t0 + i) * geo.key_heads + hk) * kDim + d;
+        kv = __bfloat162float(in.k[at]);
+        // the scaled query as the tensor-core walk forms it: one BF16 rounding of q * exp(p) / sqrt(128)
+        qv = __bfloat162float(__float2bfloat16_rn(__bfloat162float(in.q[at]) * ws.gates[block * kGateWords + kGateQueryScale + i]));
+      }
+      sQ[i * kPad + d] = qv;
       sK[i * kPad + d] = kv;
     }
     for (int e = tid; e < kChunk * kChunk; e += kWalkThreads)
       sP[(e / kChunk) * (kChunk + 1) + e % kChunk] = __bfloat162float(ws.p[block * kChunk * kChunk + e]);
     for (int e = tid; e < kChunk * kVt; e += kWalkThreads)
       sU[e] = ws.u[block * kChunk * kDim + (e / kVt) * kDim + v0 + e % kVt];
-    if (tid < 128) sG[tid] = ws.gates[block * 128 + tid];
+    if (tid < 128) sG[tid] = ws.gates[block * kGateWords + tid];
     __syncthreads();
 
     // N = U - W S

@@ -155,7 +155,7 @@ __device__ __forceinline__ float bf16_hi(uint32_t packed) { return __uint_as_flo
 //   phase 1  TMA: Q, K chunk tiles (key head of the group) and V tile; gate prefix by two warps
 //   phase 2  D1[128x64] = [Q;K] K^T                                  (one tcgen05 product, 8 instructions)
 //   phase 3  rows 0..63  -> P = tril(QK^T * decay)/sqrt(128) -> BF16 -> workspace
-//            rows 64..127-> A = tril(beta_i KK^T * decay, -1) -> shared (FP32); scaled query rows -> workspace;
+//            rows 64..127-> A = tril(beta_i KK^T * decay, -1) -> shared (FP32);
 //            the diagonal k_i.k_i decides whether token i is a contraction (word 65 of the gate vector)
 //   phase 4  T = (I+A)^-1 IN PLACE, blocked: four 16x16 diagonal solves in FP32 registers, then
 //            T21 = -T22 (A21 T11) at block size 16 and 32 as 3xTF32 mma.sync tiles (the blocked scheme and the
@@ -190,7 +190,7 @@ static_assert(3 * (kPrepSmem + 1024) <= 227 * 1024, "three prepare CTAs must fit
 
 #ifdef GDN_SM100_PHASE_TIMING
 #define GDN_PSTAMP(slot) \
-  if (tid == 0) ws.gates[block * 128 + 80 + (slot)] = float((clock64() - t_begin) & 0xffffff)
+  if (tid == 0) ws.gates[block * kGateWords + 80 + (slot)] = float((clock64() - t_begin) & 0xffffff)
 #else
 #define GDN_PSTAMP(slot)
 #endif
@@ -348,10 +348,13 @@ prepare_umma_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
       fence_proxy_async_smem();
     }
     __syncthreads();
-    // the walk reads the normalised keys: one CTA per key-head group stores the tile (rows behind T are clipped)
+    // the walk reads the normalised queries and keys: one CTA per key-head group stores the tiles (rows behind T
+    // are clipped); tm_v doubles as the map of the normalised-query plane in this variant
     if (tid == 0 && ok && hv % geo.group() == 0) {
       tma_store_4d(&tm_k, sm + L::kK0, 0, hk, t0, b);
       tma_store_4d(&tm_k, sm + L::kK1, 64, hk, t0, b);
+      tma_store_4d(&tm_v, sm + L::kQ0, 0, hk, t0, b);
+      tma_store_4d(&tm_v, sm + L::kQ1, 64, hk, t0, b);
       tma_store_commit();
     }
   }
@@ -435,25 +438,9 @@ prepare_umma_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
     tc_fence_before();      // D1's columns are overwritten by the W^T product once every thread has passed the barriers
     // token i multiplies the state by exp(g_i) (I - beta_i k_i k_i^T): a contraction iff 0 <= beta_i |k_i|^2 <= 2
     if (lrow >= 64) not_contraction = !(bi >= 0.f && bi * kk <= 2.f);
-    {
-      // scaled query: sixteen lanes cover one 256-byte row (lane -> 16-byte piece), so a warp instruction writes two
-      // whole rows, 512 contiguous bytes; four passes of 16 rows
-      const int piece = tid & 15;
-      const uint8_t* box = sm + (piece < 8 ? L::kQ0 : L::kQ1);
-#pragma unroll
-      for (int pass = 0; pass < 4; ++pass) {
-        const int row = pass * 16 + (tid >> 4);
-        const float qs = s_qscale[row];
-        const uint4 v = *reinterpret_cast<const uint4*>(box + row * 128 + (((piece & 7) ^ (row & 7)) << 4));
-        uint4 o;
-        o.x = pack_bf16(bf16_lo(v.x) * qs, bf16_hi(v.x) * qs);
-        o.y = pack_bf16(bf16_lo(v.y) * qs, bf16_hi(v.y) * qs);
-        o.z = pack_bf16(bf16_lo(v.z) * qs, bf16_hi(v.z) * qs);
-        o.w = pack_bf16(bf16_lo(v.w) * qs, bf16_hi(v.w) * qs);
-        *reinterpret_cast<uint4*>(ws.qs + (block * kChunk + row) * kDim + piece * 8) = o;
-      }
-    }
   }
+  if (kFused && tid == 0) tma_store_wait_read();     // the Q and K tiles' stores have left shared memory: the
+                                                     // inverse's scratch and the T tiles reuse the Q boxes from here on
   const int chunk_not_contraction = __syncthreads_or(not_contraction);
   ok = __syncthreads_and(ok);                  // uniform from here on: the warp-level barrier below needs that
   GDN_PSTAMP(3);
@@ -607,15 +594,15 @@ prepare_umma_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
         mma_ss(tmem + 64, a, bb, kIdescN64AT, (part | ks) != 0);
       }
     }
-    if (kFused) tma_store_wait_read();      // the key tile's store has left shared memory before phase 6 reuses it
     mma_commit(bar_mma);
   }
   // the gate vector does not depend on the products: write it while they run
   if (ok) {
     const float last = s_pl2[valid - 1];
-    if (tid < kChunk) ws.gates[block * 128 + tid] = (tid < valid) ? fast_exp2(last - s_pl2[tid]) : 0.f;
-    if (tid == kChunk) ws.gates[block * 128 + kChunk] = fast_exp2(last);
-    if (tid == kChunk + 1) ws.gates[block * 128 + kChunk + 1] = chunk_not_contraction ? 1.f : 0.f;
+    if (tid < kChunk) ws.gates[block * kGateWords + tid] = (tid < valid) ? fast_exp2(last - s_pl2[tid]) : 0.f;
+    if (tid == kChunk) ws.gates[block * kGateWords + kChunk] = fast_exp2(last);
+    if (tid == kChunk + 1) ws.gates[block * kGateWords + kChunk + 1] = chunk_not_contraction ? 1.f : 0.f;
+    if (tid >= 128 && tid < 128 + kChunk) ws.gates[block * kGateWords + kGateQueryScale + tid - 128] = s_qscale[tid - 128];
   }
   ok = ok && mbar_wait(bar_mma, 1, abort, 3, chunk);
   tc_fence_after();
@@ -692,22 +679,25 @@ prepare_umma_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
 //        warps 4-11 state chain: a warp owns the 32 TMEM lanes of quarter (warp & 3) and, of every tile it
 //        touches, one column half.  Both chain steps are signalled in two halves so that the MMA issuer
 //        starts on the first half of the K range while the second half is still being written.
-//        warps 12-15 output epilogue; warps 2-3 idle.
+//        warps 2-3 query scaling: the Q tile of a ring stage becomes Qs = Q exp(p) / sqrt(128) in place (one BF16
+//        rounding, a row's scale from the gate vector) before the issuer reads it for the state part of the output;
+//        warps 12-15 output epilogue.
 struct WalkLayout {
   // one ring stage: W^T hi and lo tiles [128 key lines][64 tokens] (MN-major B operand of the wide product, the
-  // lo tile one 16 KB tile behind the hi tile), Qs as two K-major boxes, K as two boxes, P, the gate vector
+  // lo tile one 16 KB tile behind the hi tile), Q as two K-major boxes (scaled in place to Qs by the scaling
+  // warps), K as two boxes, P, the gate vector (768 bytes)
   static constexpr int kWH = 0, kWL = 2 * kBox;
   static constexpr int kQS0 = 4 * kBox, kQS1 = 5 * kBox;
   static constexpr int kK = 6 * kBox, kP = 8 * kBox;
   static constexpr int kGates = 9 * kBox;
   static constexpr int kStage = 9 * kBox + 1024;
   static constexpr int kStages = 2;
-  static constexpr int kTxBytes = 9 * kBox + 512;
+  static constexpr int kTxBytes = 9 * kBox + kGateWords * 4;
   static constexpr int kOut = kStages * kStage;           // two staging tiles [64 tokens][128 values] BF16
   static constexpr int kBars = kOut + 4 * kBox;
   static constexpr int kTotal = kBars + 256;
 };
-constexpr int kMmaWarp = 0, kTmaWarp = 1, kChainWarp0 = 4, kChainWarps = 8, kOutWarp0 = 12;
+constexpr int kMmaWarp = 0, kTmaWarp = 1, kScaleWarp0 = 2, kScaleWarps = 2, kChainWarp0 = 4, kChainWarps = 8, kOutWarp0 = 12;
 constexpr int kWalkThreads = 512;
 constexpr int kWalkSmem = WalkLayout::kTotal + 1024;
 constexpr uint32_t kAccS = 0, kOpSH = 128, kOpSL = 192, kAccX = 256, kAccO = 384;   // ACC_O: two buffers of 64
@@ -715,10 +705,10 @@ constexpr uint32_t kIdescN64BT = idesc_bf16(128, 64, false, true);     // B MN-m
 
 #ifdef GDN_SM100_PHASE_TIMING
 #define GDN_STAMP(slot)                                                                        \
-  if (tid == kChainWarp0 * 32) ws.gates[(block0 + c) * 128 + 96 + (slot)] = float((clock64() - t_begin) & 0xffffff)
-#define GDN_MSTAMP(slot) ws.gates[(block0 + c) * 128 + 104 + (slot)] = float((clock64() - t_begin) & 0xffffff)
+  if (tid == kChainWarp0 * 32) ws.gates[(block0 + c) * kGateWords + 96 + (slot)] = float((clock64() - t_begin) & 0xffffff)
+#define GDN_MSTAMP(slot) ws.gates[(block0 + c) * kGateWords + 104 + (slot)] = float((clock64() - t_begin) & 0xffffff)
 #define GDN_OSTAMP(slot)                                                                       \
-  if (tid == kOutWarp0 * 32) ws.gates[(block0 + c) * 128 + 112 + (slot)] = float((clock64() - t_begin) & 0xffffff)
+  if (tid == kOutWarp0 * 32) ws.gates[(block0 + c) * kGateWords + 112 + (slot)] = float((clock64() - t_begin) & 0xffffff)
 #else
 #define GDN_STAMP(slot)
 #define GDN_MSTAMP(slot)
@@ -738,7 +728,7 @@ __device__ __forceinline__ int decay_reach(const float* gates, long long first_b
     const int c = c0 + lane;
     float x = 0.f;
     if (c < count) {
-      const float2 w = *reinterpret_cast<const float2*>(gates + (first_block + c) * 128 + kChunk);
+      const float2 w = *reinterpret_cast<const float2*>(gates + (first_block + c) * kGateWords + kChunk);
       x = log2f(w.x);
       flagged |= w.y != 0.f;
     }
@@ -766,7 +756,7 @@ __device__ __forceinline__ int decay_reach(const float* gates, long long first_b
 // The last sub-segment's CTA (or the single CTA) writes the outgoing state.
 __global__ void __launch_bounds__(kWalkThreads, 1)
 walk_umma_kernel(const __grid_constant__ CUtensorMap tm_wh, const __grid_constant__ CUtensorMap tm_wl,
-                 const __grid_constant__ CUtensorMap tm_qs, const __grid_constant__ CUtensorMap tm_k,
+                 const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                  const __grid_constant__ CUtensorMap tm_p, const __grid_constant__ CUtensorMap tm_out,
                  Inputs in, Geometry geo, Workspace ws) {
   // Indexing the declared array (no integer round trip) keeps these accesses in the shared state space.
@@ -784,7 +774,8 @@ walk_umma_kernel(const __grid_constant__ CUtensorMap tm_wh, const __grid_constan
   uint64_t* bar_ofree = bar_ops + 10;          // [2] output accumulator (c & 1) drained (one arrival per output warp)
   uint64_t* bar_staged = bar_ops + 8;          // output tile staged in shared memory (one arrival per output warp)
   uint64_t* bar_stfree = bar_ops + 9;          // an older output store has finished reading its staging tile
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_ops + 12);
+  uint64_t* bar_qs = bar_ops + 12;             // [2] the ring stage's Q tile has been scaled (one arrival per scaling warp)
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_ops + 14);
   volatile int* abort_word = reinterpret_cast<volatile int*>(tmem_slot + 1);
   int* limit_slot = reinterpret_cast<int*>(tmem_slot + 2);      // [4]: chunks to walk, first chunk, unstored leading
   const AbortFlag abort{abort_word};                            //      chunks, this CTA writes the outgoing state
@@ -831,6 +822,8 @@ walk_umma_kernel(const __grid_constant__ CUtensorMap tm_wh, const __grid_constan
     mbar_init(bar_ofree + 1, 4);
     mbar_init(bar_staged, 4);
     mbar_init(bar_stfree, 1);
+    mbar_init(bar_qs, kScaleWarps);
+    mbar_init(bar_qs + 1, kScaleWarps);
     *abort_word = 0;
     fence_barrier_init();
   }
@@ -845,7 +838,7 @@ walk_umma_kernel(const __grid_constant__ CUtensorMap tm_wh, const __grid_constan
     int stop = chunks;
     for (int c0 = 0; c0 < chunks && stop == chunks; c0 += 32) {
       const int c = c0 + lane;
-      float x = c < chunks ? log2f(ws.gates[(block0 + c) * 128 + kChunk]) : 0.f;
+      float x = c < chunks ? log2f(ws.gates[(block0 + c) * kGateWords + kChunk]) : 0.f;
 #pragma unroll
       for (int d = 1; d < 32; d <<= 1) {
         const float y = __shfl_up_sync(0xffffffffu, x, d);
@@ -1086,12 +1079,41 @@ walk_umma_kernel(const __grid_constant__ CUtensorMap tm_wh, const __grid_constan
       GDN_OSTAMP(2);
     }
     if (tid == kOutWarp0 * 32) tma_store_wait_all();
+  } else if (warp >= kScaleWarp0 && warp < kScaleWarp0 + kScaleWarps) {
+    // ------------------------------------------------------------------ query scaling
+    // 64 threads turn the 64 x 128 Q tile of a ring stage into Qs in place: 16 pieces of 16 bytes per thread; a
+    // row's 16 pieces lie in two swizzled boxes (columns 0..63 and 64..127)
+    const int t64 = tid - kScaleWarp0 * 32;
+    bool ok = true;
+    for (int c = 0; c < chunks && ok; ++c) {
+      const int s = c % L::kStages;
+      ok = mbar_wait(full + s, (c / L::kStages) & 1, abort, 50, c);
+      if (!ok) break;
+      uint8_t* st = sm + s * L::kStage;
+      const float* scale = reinterpret_cast<const float*>(st + L::kGates) + kGateQueryScale;
+#pragma unroll 4
+      for (int it = 0; it < 16; ++it) {
+        const int piece = it * 64 + t64, row = piece >> 4, col16 = piece & 15;
+        uint4* at = reinterpret_cast<uint4*>(st + (col16 < 8 ? L::kQS0 : L::kQS1) + row * 128 + (((col16 & 7) ^ (row & 7)) << 4));
+        const float f = scale[row];
+        const uint4 v = *at;
+        uint4 o;
+        o.x = pack_bf16(bf16_lo(v.x) * f, bf16_hi(v.x) * f);
+        o.y = pack_bf16(bf16_lo(v.y) * f, bf16_hi(v.y) * f);
+        o.z = pack_bf16(bf16_lo(v.z) * f, bf16_hi(v.z) * f);
+        o.w = pack_bf16(bf16_lo(v.w) * f, bf16_hi(v.w) * f);
+        *at = o;
+      }
+      fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar_qs + s);
+    }
   } else if (warp == kTmaWarp) {
     // ------------------------------------------------------------------ TMA producer
     if (lane == 0) {
       prefetch_tensormap(&tm_wh);
       prefetch_tensormap(&tm_wl);
-      prefetch_tensormap(&tm_qs);
+      prefetch_tensormap(&tm_q);
       prefetch_tensormap(&tm_k);
       prefetch_tensormap(&tm_p);
       for (int c = 0; c < chunks; ++c) {
@@ -1101,11 +1123,11 @@ walk_umma_kernel(const __grid_constant__ CUtensorMap tm_wh, const __grid_constan
         uint8_t* st = sm + s * L::kStage;
         const int row = int((block0 + c) * kChunk);
         mbar_arrive_expect_tx(full + s, L::kTxBytes);
-        bulk_load(st + L::kGates, ws.gates + (block0 + c) * 128, 512, full + s);
+        bulk_load(st + L::kGates, ws.gates + (block0 + c) * kGateWords, kGateWords * 4, full + s);
         tma_load_2d(st + L::kWH, &tm_wh, full + s, 0, 2 * row);       // transposed planes: 128 rows per block
         tma_load_2d(st + L::kWL, &tm_wl, full + s, 0, 2 * row);
-        tma_load_2d(st + L::kQS0, &tm_qs, full + s, 0, row);
-        tma_load_2d(st + L::kQS1, &tm_qs, full + s, 64, row);
+        tma_load_4d(st + L::kQS0, &tm_q, full + s, 0, hk, t_first + c * kChunk, b);
+        tma_load_4d(st + L::kQS1, &tm_q, full + s, 64, hk, t_first + c * kChunk, b);
         tma_load_4d(st + L::kK, &tm_k, full + s, 0, hk, t_first + c * kChunk, b);
         tma_load_4d(st + L::kK + kBox, &tm_k, full + s, 64, hk, t_first + c * kChunk, b);
         tma_load_2d(st + L::kP, &tm_p, full + s, 0, row);
@@ -1155,6 +1177,8 @@ walk_umma_kernel(const __grid_constant__ CUtensorMap tm_wh, const __grid_constan
           mma_ts(tm + kAccX, tm + kOpSL + ks * 8, bdesc, kIdescN64BT, 1);
         }
         mma_commit(bar_ws);
+        ok &= mbar_wait(bar_qs + (c & 1), (c >> 1) & 1, abort, 44, c);     // scaled long ago: the tile landed a chunk ahead
+        tc_fence_after();
 #pragma unroll
         for (int ks = 0; ks < 8; ++ks)
           mma_ts(acc_o, tm + kOpSH + ks * 8, ((ks >> 2) ? q1 : q0) + uint64_t((ks & 3) * 2), kIdescN64, ks != 0);
@@ -1222,7 +1246,7 @@ int launch_prepare_umma(const Inputs& in, const Geometry& geo, const Workspace& 
     // one 2-D map over the packed projection rows; the 4-D map of the normalised-key plane is the store target
     if (int rc = enc.bf16_2d(&tm_q, in.mixed, uint64_t(in.mixed_stride), uint64_t(geo.batch) * geo.sequence, kChunk)) return rc;
     if (int rc = enc.bf16_4d(&tm_k, in.k_norm, kDim, geo.key_heads, geo.sequence, geo.batch, kChunk)) return rc;
-    tm_v = tm_q;
+    if (int rc = enc.bf16_4d(&tm_v, in.q_norm, kDim, geo.key_heads, geo.sequence, geo.batch, kChunk)) return rc;
   } else {
     if (int rc = enc.bf16_4d(&tm_q, in.q, kDim, geo.key_heads, geo.sequence, geo.varlen ? 1 : geo.batch, kChunk)) return rc;
     if (int rc = enc.bf16_4d(&tm_k, in.k, kDim, geo.key_heads, geo.sequence, geo.varlen ? 1 : geo.batch, kChunk)) return rc;
@@ -1244,7 +1268,8 @@ int launch_prepare_umma(const Inputs& in, const Geometry& geo, const Workspace& 
   return int(cudaGetLastError());
 }
 int launch_prepare_fused(const Inputs& in, const Geometry& geo, const Workspace& ws, cudaStream_t stream) {
-  if (!in.mixed || !in.act_a || !in.act_b || !in.a_log || !in.dt_bias || !in.k_norm) return int(cudaErrorInvalidValue);
+  if (!in.mixed || !in.act_a || !in.act_b || !in.a_log || !in.dt_bias || !in.k_norm || !in.q_norm)
+    return int(cudaErrorInvalidValue);
   return launch_prepare_umma(in, geo, ws, stream);
 }
 
@@ -1252,19 +1277,19 @@ int launch_walk_umma(const Inputs& in, const Geometry& geo, const Workspace& ws,
   TensorMapEncoder& enc = tensor_map_encoder();
   if (int rc = enc.init()) return rc;
   const uint64_t rows = uint64_t(geo.blocks()) * kChunk;
-  CUtensorMap tm_wh, tm_wl, tm_qs, tm_k, tm_p, tm_out;
+  CUtensorMap tm_wh, tm_wl, tm_q, tm_k, tm_p, tm_out;
   if (int rc = enc.bf16_4d(&tm_out, in.output, kDim, geo.value_heads, geo.sequence, geo.varlen ? 1 : geo.batch, kChunk)) return rc;
   // W^T planes: [blocks * 128 key rows][64 tokens], one 128-row box per block
   if (int rc = enc.bf16_2d(&tm_wh, ws.w_hi, kChunk, 2 * rows, kDim)) return rc;
   if (int rc = enc.bf16_2d(&tm_wl, ws.w_lo, kChunk, 2 * rows, kDim)) return rc;
-  if (int rc = enc.bf16_2d(&tm_qs, ws.qs, kDim, rows, kChunk)) return rc;
+  if (int rc = enc.bf16_4d(&tm_q, in.q, kDim, geo.key_heads, geo.sequence, geo.varlen ? 1 : geo.batch, kChunk)) return rc;
   if (int rc = enc.bf16_4d(&tm_k, in.k, kDim, geo.key_heads, geo.sequence, geo.varlen ? 1 : geo.batch, kChunk)) return rc;
   if (int rc = enc.bf16_2d(&tm_p, ws.p, kChunk, rows, kChunk)) return rc;
   const int parallel = geo.parallel > 1 ? geo.parallel : 1;
   if (parallel > 1 && (geo.varlen || in.walk_flags || parallel > geo.segment_chunks())) return int(cudaErrorInvalidValue);
   if ((in.walk_flags & kWalkSelftestStall) && (in.walk_flags != kWalkSelftestStall || geo.varlen)) return int(cudaErrorInvalidValue);
   walk_umma_kernel<<<geo.batch * geo.value_heads * parallel, kWalkThreads, kWalkSmem, stream>>>(
-      tm_wh, tm_wl, tm_qs, tm_k, tm_p, tm_out, in, geo, ws);
+      tm_wh, tm_wl, tm_q, tm_k, tm_p, tm_out, in, geo, ws);
   return int(cudaGetLastError());
 }
 

@@ -14,7 +14,7 @@
 //     (batch, value head, 64-token chunk): B * Hv * ceil(T / 64) must not exceed it.  A larger
 //     geometry is refused with ACTLIZE_LA_SM100_ERROR_SCRATCH_TOO_SMALL and a one-line message on
 //     stderr; nothing is launched.  Every GPU on which the library is loaded keeps the array
-//     (about 5.5 MiB) until the process exits.
+//     (about 4.6 MiB) until the process exits.
 //   * The first call on a device performs a one-time set-up on that device (kernel attributes and
 //     the look-up of the array's device address).  Make that first call before any stream capture.
 //   * All calls share the one array and it keeps the previous call's contents.  Nothing in it has to

@@ -694,7 +694,7 @@ def main():
     # DRAM traffic per launch from the committed ncu captures of a smaller case (profiles/; caches flushed before the
     # captured launch, so an upper bound), per (chunk, value head) block and scaled by the blocks of one launch
     blocks = shard.batch * shard.value_heads * ((shard.length + 63) // 64)
-    traffic = 100.2e3 * blocks if (config_name == "umma" and top == "walk") else None
+    traffic = {"walk": 135.7e3, "prepare": 66.3e3}[top] * blocks if config_name == "umma" else None
     whole_ms = max(alg_bytes / (hbm_peak * 1e9), alg_flops / (tensor_peak * 1e12)) * 1e3
     line = dict(
         metric=METRIC, value=workload.tokens * world / (ms_step * 1e-3), unit=UNIT, n_gpus=world,
@@ -707,8 +707,9 @@ def main():
         step_spread=spread,
         roofline=dict(bound="hbm", kernel=top, achieved=achieved, peak=hbm_peak, unit="GB/s",
                       frac=achieved / hbm_peak, traffic=traffic,
-                      traffic_note=("cold-cache ncu capture of cfg0 scaled by blocks" if traffic else
-                                    "no capture of this kernel at this size; see profiles/"),
+                      traffic_note=("dram bytes read + written of one launch in the ncu capture of cfg0 (caches flushed "
+                                    "before the launch; workspace lines still dirty in L2 at its end are not in it), "
+                                    "per block, scaled by the blocks of this launch" if traffic else None),
                       peak_source=peak_source, algorithmic_bytes=alg_bytes, algorithmic_flops=alg_flops,
                       whole_forward_frac=whole_ms / ms_step,
                       tensor_frac=alg_flops / (ms_step * 1e-3) / (tensor_peak * 1e12)),

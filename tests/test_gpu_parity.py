@@ -94,8 +94,8 @@ def _workspace_planes(native_library, inputs, config):
     torch.cuda.synchronize()
     n = b * hv * ((t + 63) // 64)
     sizes = [("w_hi", n * 64 * 128 * 2, torch.bfloat16), ("w_lo", n * 64 * 128 * 2, torch.bfloat16),
-             ("u", n * 64 * 128 * 4, torch.float32), ("qs", n * 64 * 128 * 2, torch.bfloat16),
-             ("p", n * 64 * 64 * 2, torch.bfloat16), ("gates", n * 128 * 4, torch.float32)]
+             ("u", n * 64 * 128 * 4, torch.float32),
+             ("p", n * 64 * 64 * 2, torch.bfloat16), ("gates", n * 192 * 4, torch.float32)]
     planes, off = {}, 0
     for name, size, dtype in sizes:
         planes[name] = ws[off:off + size].view(dtype).clone()
@@ -104,7 +104,8 @@ def _workspace_planes(native_library, inputs, config):
     for name in ("w_hi", "w_lo"):
         planes[name] = planes[name].view(n, 128, 64).transpose(1, 2).contiguous()
     planes["w"] = planes["w_hi"].float() + planes["w_lo"].float()
-    planes["gates"] = planes["gates"].view(n, 128)[:, :65].contiguous()
+    planes["qscale"] = planes["gates"].view(n, 192)[:, 128:].contiguous()       # exp(prefix_i) / sqrt(128)
+    planes["gates"] = planes["gates"].view(n, 192)[:, :65].contiguous()
     return planes, out, final
 
 
@@ -128,6 +129,11 @@ def test_prepare_intermediates_match_the_oracle(name, native_library, forward):
         last = prefix.gather(-1, valid_last[..., None])
         gam = planes["gates"][:, 64].view(*prefix.shape[:3]).cpu()
         assert oracle.rel_frobenius(gam, last[..., 0].exp()) < 1e-5, (name, config, "gamma")
+        # the per-token query scale the walk applies (rows behind a tail are padding: compare the valid ones)
+        qscale = planes["qscale"].view(*prefix.shape).cpu()
+        want_scale = prefix.exp() / 128 ** 0.5
+        valid = torch.arange(64)[None, None, None, :] <= valid_last[..., None]
+        assert oracle.rel_frobenius(qscale[valid], want_scale[valid]) < 1e-5, (name, config, "query scale")
 
 
 def test_output_only_equals_full_and_replay_is_bit_stable(forward):

@@ -197,7 +197,7 @@ def test_native_argument_rejection_without_a_device(native_library):
     lib = native_library.lib
     invalid = 1   # cudaErrorInvalidValue
     n = lib.actlize_la_sm100_workspace_bytes(1, 8192, 16, 32, 1)
-    assert n == 32 * 128 * (16384 * 2 + 32768 + 16384 + 8192 + 512)
+    assert n == 32 * 128 * (16384 * 2 + 32768 + 8192 + 768)       # W^T hi/lo, U, P, gate vector per block
     # a segmented walk carries one FP32 128x128 state per (batch, value head) between segments
     assert lib.actlize_la_sm100_workspace_bytes(1, 8192, 16, 32, 1 | (4 << 8)) == n + 32 * 65536
     assert lib.actlize_la_sm100_launches_per_forward(1 | (4 << 8)) == 8
