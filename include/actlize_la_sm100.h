@@ -226,7 +226,7 @@ int actlize_la_sm100_selftest_walk_stall(
  * [Hk q vectors | Hk k vectors | Hv v vectors] x 128, `a` and `b` are BF16 [B*T][Hv], `a_log`, `dt_bias` FP32 [Hv].
  * Same results, bit for bit, as prepare_inputs followed by forward_prepared with an FP32 gate.  `config` as returned
  * by actlize_la_sm100_select (tcgen05 configuration, segments allowed, no stage bits); the workspace
- * (actlize_la_sm100_projections_workspace_bytes) also holds the normalised keys for the walk.  Rows behind a batch
+ * (actlize_la_sm100_projections_workspace_bytes) also holds the normalised queries and keys for the walk.  Rows behind a batch
  * element's end inside its last chunk are the next element's tokens and meet exact zeros: inputs must be finite. */
 long long actlize_la_sm100_projections_workspace_bytes(int b, int t, int hk, int hv, int config);
 int actlize_la_sm100_forward_projections(
