@@ -724,22 +724,29 @@ __device__ __forceinline__ int decay_reach(const float* gates, long long first_b
   float total = 0.f;
   int reach = -1;
   bool flagged = false;
-  for (int c0 = 0; c0 < count; c0 += 32) {
-    const int c = c0 + lane;
-    float x = 0.f;
-    if (c < count) {
-      const float2 w = *reinterpret_cast<const float2*>(gates + (first_block + c) * kGateWords + kChunk);
-      x = log2f(w.x);
-      flagged |= w.y != 0.f;
+  for (int c0 = 0; c0 < count; c0 += 128) {
+    // four independent loads in flight per lane, then four scan steps of 32 chunks
+    float2 w[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const int c = c0 + u * 32 + lane;
+      w[u] = c < count ? *reinterpret_cast<const float2*>(gates + (first_block + c) * kGateWords + kChunk)
+                       : make_float2(1.f, 0.f);
     }
 #pragma unroll
-    for (int d = 1; d < 32; d <<= 1) {
-      const float y = __shfl_up_sync(0xffffffffu, x, d);
-      if (lane >= d) x += y;
+    for (int u = 0; u < 4; ++u) {
+      const int c = c0 + u * 32 + lane;
+      float x = c < count ? log2f(w[u].x) : 0.f;
+      flagged |= w[u].y != 0.f;
+#pragma unroll
+      for (int d = 1; d < 32; d <<= 1) {
+        const float y = __shfl_up_sync(0xffffffffu, x, d);
+        if (lane >= d) x += y;
+      }
+      const unsigned below = __ballot_sync(0xffffffffu, c < count && total + x < kDecayedLog2);
+      if (below && reach < 0) reach = c0 + u * 32 + __ffs(below);
+      total += __shfl_sync(0xffffffffu, x, 31);
     }
-    const unsigned below = __ballot_sync(0xffffffffu, c < count && total + x < kDecayedLog2);
-    if (below && reach < 0) reach = c0 + __ffs(below);
-    total += __shfl_sync(0xffffffffu, x, 31);
   }
   not_contraction |= __any_sync(0xffffffffu, flagged);
   return reach;
@@ -777,8 +784,8 @@ walk_umma_kernel(const __grid_constant__ CUtensorMap tm_wh, const __grid_constan
   uint64_t* bar_qs = bar_ops + 12;             // [2] the ring stage's Q tile has been scaled (one arrival per scaling warp)
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_ops + 14);
   volatile int* abort_word = reinterpret_cast<volatile int*>(tmem_slot + 1);
-  int* limit_slot = reinterpret_cast<int*>(tmem_slot + 2);      // [4]: chunks to walk, first chunk, unstored leading
-  const AbortFlag abort{abort_word};                            //      chunks, this CTA writes the outgoing state
+  int* limit_slot = reinterpret_cast<int*>(tmem_slot + 2);      // [4]: [0] chunks of a cut-short walk, [1] transition is zero
+  const AbortFlag abort{abort_word};
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int parallel = geo.parallel > 1 ? geo.parallel : 1;
@@ -857,26 +864,14 @@ walk_umma_kernel(const __grid_constant__ CUtensorMap tm_wh, const __grid_constan
     const int reach = decay_reach(ws.gates, block0, chunks, lane, flagged);
     if (lane == 0) limit_slot[1] = (reach >= 0 && !flagged) ? 1 : 0;
   }
-  if (parallel > 1 && warp == kTmaWarp) {
-    // plan of this CTA (see the comment above the kernel); sub-segment r covers chunks [n r / P, n (r + 1) / P)
+  int* reach_slot = limit_slot + 4;             // [8] per sub-segment: chunks an incoming state reaches, -1 = invalid
+  if (parallel > 1 && warp >= 1 && warp < parallel) {
+    // plan (see the comment above the kernel): warp r scans sub-segment r, chunks [n r / P, n (r + 1) / P)
     const int n = chunks;
-    bool serial = false;
-    int reach_mine = 0, reach_next = 0;
-    for (int r = 1; r < parallel; ++r) {
-      const int r0 = int((long long)n * r / parallel), r1 = int((long long)n * (r + 1) / parallel);
-      const int reach = decay_reach(ws.gates, block0 + r0, r1 - r0, lane, serial);
-      serial |= reach < 0;
-      if (r == sub) reach_mine = reach;
-      if (r == sub + 1) reach_next = reach;
-    }
-    if (lane == 0) {
-      if (sub == 0) atomicAdd(&g_walk_plan_counts[serial ? 1 : 0], 1);
-      const int c0 = int((long long)n * sub / parallel), c1 = int((long long)n * (sub + 1) / parallel);
-      limit_slot[0] = serial ? (sub == 0 ? n : 0) : c1 - c0 + (sub + 1 < parallel ? reach_next : 0);
-      limit_slot[1] = serial ? 0 : c0;
-      limit_slot[2] = (serial || sub == 0) ? 0 : reach_mine;
-      limit_slot[3] = serial ? sub == 0 : sub == parallel - 1;
-    }
+    const int r0 = int((long long)n * warp / parallel), r1 = int((long long)n * (warp + 1) / parallel);
+    bool flagged = false;
+    const int reach = decay_reach(ws.gates, block0 + r0, r1 - r0, lane, flagged);
+    if (lane == 0) reach_slot[warp] = flagged ? -1 : reach;
   }
   tc_fence_before();
   __syncthreads();
@@ -889,11 +884,21 @@ walk_umma_kernel(const __grid_constant__ CUtensorMap tm_wh, const __grid_constan
   }
   int unstored = 0;                          // leading chunks whose output rows the previous sub-segment's CTA writes
   if (parallel > 1) {
-    chunks = limit_slot[0];
-    t_first += limit_slot[1] * kChunk;
-    block0 += limit_slot[1];
-    unstored = limit_slot[2];
-    if (!limit_slot[3]) state_out = nullptr;
+    const int n = chunks;
+    bool serial = false;
+    for (int r = 1; r < parallel; ++r) serial |= reach_slot[r] < 0;
+    if (tid == 0 && sub == 0) atomicAdd(&g_walk_plan_counts[serial ? 1 : 0], 1);
+    if (serial) {
+      chunks = sub == 0 ? n : 0;             // the head's first CTA walks the whole range alone
+      if (sub != 0) state_out = nullptr;
+    } else {
+      const int c0 = int((long long)n * sub / parallel), c1 = int((long long)n * (sub + 1) / parallel);
+      chunks = c1 - c0 + (sub + 1 < parallel ? reach_slot[sub + 1] : 0);
+      t_first += c0 * kChunk;
+      block0 += c0;
+      unstored = sub == 0 ? 0 : reach_slot[sub];
+      if (sub != parallel - 1) state_out = nullptr;
+    }
   }
 
   if (warp >= kChainWarp0 && warp < kChainWarp0 + kChainWarps) {
