@@ -7,7 +7,8 @@
 //   (W S)^T = St W^T     (Q S)^T = St Q^T     (P N)^T = N^T P^T     St += (N*rel)^T K
 // all have M = 128 value rows, and St / N^T are consumed as A operands straight from tensor memory.
 //
-// Precision.  All MMAs are kind::f16 with BF16 operands and FP32 accumulation.  Quantities on the
+// Precision.  All tcgen05 MMAs are kind::f16 with BF16 operands and FP32 accumulation (the small block products
+// of the triangular inverse run as 3xTF32 mma.sync tiles, see the prepare kernel).  Quantities on the
 // path to the final state are carried as BF16 pairs x ~= hi + lo (16 significant bits):
 // the triangular inverse T (scaled by beta, exp(prefix)), W, the state operand of W S and N*rel.
 // K, V, Q are exact BF16 inputs.  U is never rounded (FP32 from accumulator to register).
@@ -373,7 +374,7 @@ prepare_umma_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
   tc_fence_after();
   GDN_PSTAMP(2);
 
-  // ---- phase 3: masks and decays on D1, scaled query rows
+  // ---- phase 3: masks and decays on D1
   // warp -> TMEM lane quarter (warp & 3) and column half (warp >> 2) of the 64 columns
   const int quarter = warp & 3, chalf = warp >> 2;
   const int lrow = quarter * 32 + (tid & 31);          // accumulator row owned by this thread
@@ -663,7 +664,8 @@ prepare_umma_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
 #undef GDN_PSTAMP
 
 // ==================================================================================== walk kernel
-// One CTA per (batch, value head), 512 threads, one CTA per SM.  Tensor memory (512 columns):
+// One CTA per (batch, value head), or per (batch, value head, parallel sub-segment): see the comment above the
+// kernel; 512 threads, one CTA per SM.  Tensor memory (512 columns):
 //   ACC_S [  0,128)  St FP32 accumulator (pre-scaled by the chunk decay before the update MMA)
 //   OP_SH [128,192)  St BF16 hi, packed pairs      OP_SL [192,256)  St BF16 lo
 //   ACC_X [256,384)  S_hi^T [W_hi ; W_lo]^T, with S_lo^T W_hi^T added to the first half:
