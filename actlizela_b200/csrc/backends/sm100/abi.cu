@@ -31,17 +31,22 @@ bool geometry_ok(int b, int t, int hk, int hv) {
 // Bits 6 and 7 modify a walk-only call of the tcgen05 configuration (sequence-parallel scheme):
 // 0x40 = treat U as zero (state-transition pass), 0x80 = stop each (batch, value head) walk once the decay
 // accumulated since its start is below exp(-40) (no final state is written then).
+// Bit 20 (0x100000) makes a walk-only call of the tcgen05 configuration the OFFSET pass of that scheme: per (batch,
+// value head) only the shortest suffix of the sequence whose decay is below exp(-40) is walked, from a zero state,
+// no output row is written, and `final_state` receives the state the sequence ends in from a zero (or, to exp(-40),
+// any) incoming state; a head without such a suffix is walked whole.
 // Bits 16..19 hold the number of parallel sub-segments of the tcgen05 walk (0 or 1 = off, at most 8): every
 // (batch, value head) walk of a launch is cut into that many pieces walked by as many CTAs at the same time
 // (walk_umma_kernel); needs the tcgen05 prepare stage, which records the per-chunk contraction flag the split relies on.
 constexpr int kStageMask = 0x30, kPrepareOnly = 0x10, kWalkOnly = 0x20, kSegmentShift = 8, kMaxSegments = 16;
 constexpr int kWalkFlagMask = 0xc0, kHomogeneousBit = 0x40, kUntilDecayedBit = 0x80;
-constexpr int kParallelShift = 16, kMaxParallel = 8;
+constexpr int kParallelShift = 16, kMaxParallel = 8, kOffsetTailBit = 0x100000;
 bool config_ok(int config) {
   const int segments = (config >> kSegmentShift) & 0xff, parallel = (config >> kParallelShift) & 0xf;
   if (config < 0 || (config & 0xf) > 3 ||
-      (config & ~(kStageMask | kWalkFlagMask | 0xf | (0xff << kSegmentShift) | (0xf << kParallelShift))) != 0)
+      (config & ~(kStageMask | kWalkFlagMask | 0xf | (0xff << kSegmentShift) | (0xf << kParallelShift) | kOffsetTailBit)) != 0)
     return false;
+  if ((config & kOffsetTailBit) && (config & ~kOffsetTailBit) != (1 | kWalkOnly)) return false;
   if ((config & kWalkFlagMask) && ((config & 0xf) != 1 || (config & kStageMask) != kWalkOnly)) return false;
   if (parallel > kMaxParallel || (parallel > 1 && ((config & 0xf) != 1 || (config & kWalkFlagMask)))) return false;
   return (config & kStageMask) != kStageMask && segments <= kMaxSegments;
@@ -353,10 +358,12 @@ extern "C" int actlize_la_sm100_forward_prepared(
   if (output == workspace || (void*)final_state == workspace || (void*)final_state == output)
     return int(cudaErrorInvalidValue);
   if ((config & kUntilDecayedBit) && final_state) return int(cudaErrorInvalidValue);   // a cut-short walk has no final state
+  if ((config & kOffsetTailBit) && !final_state) return int(cudaErrorInvalidValue);    // the offset pass writes nothing else
   const Inputs in{static_cast<const __nv_bfloat16*>(q), static_cast<const __nv_bfloat16*>(k),
                   static_cast<const __nv_bfloat16*>(v), g, static_cast<const __nv_bfloat16*>(beta),
                   initial, static_cast<__nv_bfloat16*>(output), final_state, gate_fp32 ? 1 : 0,
-                  ((config & kHomogeneousBit) ? kWalkHomogeneous : 0) | ((config & kUntilDecayedBit) ? kWalkUntilDecayed : 0)};
+                  ((config & kHomogeneousBit) ? kWalkHomogeneous : 0) | ((config & kUntilDecayedBit) ? kWalkUntilDecayed : 0) |
+                      ((config & kOffsetTailBit) ? kWalkTail : 0)};
   const Workspace ws = carve_workspace(workspace, geo);
   return run_forward(in, geo, ws, config, segments, static_cast<cudaStream_t>(opaque_stream));
 }

@@ -127,6 +127,7 @@ struct Inputs {
   __nv_bfloat16* q_norm = nullptr;      // likewise the normalised queries [B][T][Hk][128] (the walk gets it as its `q`)
 };
 constexpr int kWalkHomogeneous = 1, kWalkUntilDecayed = 2;
+constexpr int kWalkTail = 8;              // offset pass: walk, from zero, only the suffix that decides the outgoing state
 constexpr int kWalkSelftestStall = 4;     // the TMA producer stops after the first chunk (failure-detection self-test)
 constexpr float kDecayedLog2 = -40.f * 1.4426950408889634f;
 

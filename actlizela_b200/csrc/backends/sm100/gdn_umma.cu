@@ -754,6 +754,37 @@ __device__ __forceinline__ int decay_reach(const float* gates, long long first_b
   return reach;
 }
 
+// Shortest suffix of a chunk range whose accumulated decay is below exp(-40) and whose tokens are all contractions:
+// returns its length in chunks (1..count), or -1 when there is none.  A walk of that suffix from a zero state ends
+// in the state the whole range ends in from ANY incoming state, to exp(-40) of that state.  Warp-collective.
+__device__ __forceinline__ int decay_suffix(const float* gates, long long first_block, int count, int lane) {
+  float total = 0.f;
+  bool flagged = false;
+  for (int done = 0; done < count; done += 32) {
+    const int back = done + lane;                         // chunks behind the range's last one
+    const float2 w = back < count
+        ? *reinterpret_cast<const float2*>(gates + (first_block + count - 1 - back) * kGateWords + kChunk)
+        : make_float2(1.f, 0.f);
+    float x = back < count ? log2f(w.x) : 0.f;
+    flagged |= w.y != 0.f;
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+      const float y = __shfl_up_sync(0xffffffffu, x, d);
+      if (lane >= d) x += y;
+    }
+    const unsigned below = __ballot_sync(0xffffffffu, back < count && total + x < kDecayedLog2);
+    if (below) {
+      // flags of chunks in front of the suffix (higher lanes) do not matter
+      const int length = __ffs(below);
+      const unsigned bad = __ballot_sync(0xffffffffu, flagged) & (0xffffffffu >> (32 - length));
+      return bad ? -1 : done + length;
+    }
+    if (__any_sync(0xffffffffu, flagged)) return -1;      // (so `flagged` only ever holds this step's chunks)
+    total += __shfl_sync(0xffffffffu, x, 31);
+  }
+  return -1;
+}
+
 // Parallel sub-segments (Geometry::parallel = P > 1): the launch's chunk range of every (batch, value head) is cut
 // into P sub-segments and the grid holds P CTAs per head.  CTA r walks sub-segment r from a ZERO state (r = 0 from
 // the true incoming state) and then carries on into the leading chunks of sub-segment r + 1, those that its state
@@ -786,7 +817,7 @@ walk_umma_kernel(const __grid_constant__ CUtensorMap tm_wh, const __grid_constan
   uint64_t* bar_qs = bar_ops + 12;             // [2] the ring stage's Q tile has been scaled (one arrival per scaling warp)
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_ops + 14);
   volatile int* abort_word = reinterpret_cast<volatile int*>(tmem_slot + 1);
-  int* limit_slot = reinterpret_cast<int*>(tmem_slot + 2);      // [4]: [0] chunks of a cut-short walk, [1] transition is zero
+  int* limit_slot = reinterpret_cast<int*>(tmem_slot + 2);      // [4]: [0] chunks of a cut-short walk, [1] transition is zero, [2] suffix of the offset pass
   const AbortFlag abort{abort_word};
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -866,6 +897,10 @@ walk_umma_kernel(const __grid_constant__ CUtensorMap tm_wh, const __grid_constan
     const int reach = decay_reach(ws.gates, block0, chunks, lane, flagged);
     if (lane == 0) limit_slot[1] = (reach >= 0 && !flagged) ? 1 : 0;
   }
+  if ((in.walk_flags & kWalkTail) && warp == kTmaWarp) {
+    const int keep = decay_suffix(ws.gates, block0, chunks, lane);
+    if (lane == 0) limit_slot[2] = keep > 0 ? keep : chunks;        // no such suffix: the whole range from zero
+  }
   int* reach_slot = limit_slot + 4;             // [8] per sub-segment: chunks an incoming state reaches, -1 = invalid
   if (parallel > 1 && warp >= 1 && warp < parallel) {
     // plan (see the comment above the kernel): warp r scans sub-segment r, chunks [n r / P, n (r + 1) / P)
@@ -885,6 +920,14 @@ walk_umma_kernel(const __grid_constant__ CUtensorMap tm_wh, const __grid_constan
     state_in = nullptr;           // zeros go into tensor memory and straight out as the transition matrix
   }
   int unstored = 0;                          // leading chunks whose output rows the previous sub-segment's CTA writes
+  if (in.walk_flags & kWalkTail) {
+    // offset pass: only the suffix that determines the outgoing state, from zero, no output rows
+    const int keep = limit_slot[2];
+    t_first += (chunks - keep) * kChunk;
+    block0 += chunks - keep;
+    chunks = unstored = keep;
+    state_in = nullptr;
+  }
   if (parallel > 1) {
     const int n = chunks;
     bool serial = false;
@@ -1295,6 +1338,9 @@ int launch_walk_umma(const Inputs& in, const Geometry& geo, const Workspace& ws,
   const int parallel = geo.parallel > 1 ? geo.parallel : 1;
   if (parallel > 1 && (geo.varlen || in.walk_flags || parallel > geo.segment_chunks())) return int(cudaErrorInvalidValue);
   if ((in.walk_flags & kWalkSelftestStall) && (in.walk_flags != kWalkSelftestStall || geo.varlen)) return int(cudaErrorInvalidValue);
+  if ((in.walk_flags & kWalkTail) &&
+      (in.walk_flags != kWalkTail || geo.varlen || !geo.first_segment() || !geo.last_segment() || !in.final_state))
+    return int(cudaErrorInvalidValue);
   walk_umma_kernel<<<geo.batch * geo.value_heads * parallel, kWalkThreads, kWalkSmem, stream>>>(
       tm_wh, tm_wl, tm_q, tm_k, tm_p, tm_out, in, geo, ws);
   return int(cudaGetLastError());

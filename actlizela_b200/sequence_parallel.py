@@ -7,14 +7,18 @@ column independently, ``b`` is the final state of the segment run from a zero st
 ``M`` is the final state of the same recurrence run with ``v = 0`` from the identity.
 
 Scheme (exact for any decay, no host read anywhere):
-  1. every rank behind the first prepares its segment once and walks it from a zero state (outputs and ``b_r``)
-     and, next to that, from the identity with ``v = 0`` (``M_r``; the kernel returns exact zeros at once for a
-     segment whose decay falls below exp(-40), which is decided on the device from the gate sums);
-  2. one grouped exchange of point-to-point messages: every rank sends its pair ``(M_r, b_r)`` to every LATER
-     rank (rank 0 sends its true outgoing state as ``b_0``) and receives the pairs of every EARLIER rank; the
-     exclusive scan ``S_in(r) = M_{r-1} S_in(r-1) + b_{r-1}`` is then folded locally, in one kernel launch.  All messages of the job
-     are in flight at the same time (NCCL send/recv over NVLink on GPUs), so the exchange costs one message
-     latency instead of a chain of dependent hops;
+  1. every rank prepares its segment once.  Two short passes on a side stream give the pair early: ``b_r`` from a
+     zero-state walk of only the suffix of the segment that decides the outgoing state (the chunks since the decay
+     fell below exp(-40), counted from the segment's end; the whole segment when there is no such suffix), and
+     ``M_r`` from the identity with ``v = 0`` (exact zeros at once for a segment that decays below exp(-40)); both
+     decisions are made on the device from the gate sums.  Meanwhile the main stream walks the segment's output
+     rows from a zero state (rank 0: from the caller's state);
+  2. next to that walk, one grouped exchange of point-to-point messages: every rank sends its pair ``(M_r, b_r)``
+     to every LATER rank (rank 0 sends its true outgoing state as ``b_0``) and receives the pairs of every EARLIER
+     rank; the exclusive scan ``S_in(r) = M_{r-1} S_in(r-1) + b_{r-1}`` is then folded locally, in one kernel
+     launch.  All messages of the job are in flight at the same time (NCCL send/recv over NVLink on GPUs), so the
+     exchange costs one message latency instead of a chain of dependent hops, and that latency hides behind the
+     output walk;
   3. every rank rewrites the leading chunks of its output that its incoming state still reaches (the walk stops,
      per batch and value head, at the first chunk boundary where the decay since the segment start is below
      exp(-40); a head that never gets there is rewritten to the end); the last rank forms the final state
@@ -113,7 +117,7 @@ def gdn_forward_sequence_parallel(q, k, v, g, beta, initial_state=None, output_f
     rank 0 only.  Returns (output of the local segment, final state on the LAST rank or None).
     ``segment_lengths`` (token count of every rank) lets the arguments be checked without communication.
 
-    On CUDA tensors the ranks behind the first prepare their segment once and walk it several times
+    On CUDA tensors every rank prepares its segment once and walks it several times
     (``Sm100Forward.prepare_segment``), see the module text.  ``until_decayed=True`` is the caller's statement
     that every segment forgets its incoming state (decay below exp(-40) within the segment, every token a
     contraction: L2-normalised keys, beta in [0, 1]); the transition pass is then skipped and only ``b_{r-1}``
@@ -166,35 +170,41 @@ def gdn_forward_sequence_parallel(q, k, v, g, beta, initial_state=None, output_f
             state = apply_transition(pairs[j, 0], pairs[j, 1], state)
         return state, (apply_transition(transition, offset, state) if want_outgoing else None)
 
-    if rank == 0:
-        # the first segment starts from the caller's state; its true outgoing state plays the part of b_0
-        out, final = forward_fn(q, k, v, g, beta, initial_state, True, **forward_options)
-        if until_decayed:
-            dist.send(final, dst=later[0], group=group)
-        else:
-            exchange(final, None)
-        return out, None
-
     if staged:
         if segment_fn is None:
             from .sm100 import load_sm100
             segment_fn = load_sm100().prepare_segment
         segment = segment_fn(q, k, v, g, beta)
-        if until_decayed:
-            # the caller vouches that M_r is below exp(-40): b_r leaves at once, whatever comes in
-            offset = segment.offset_pipelined()
-            incoming = new_state()
-            ops = [dist.P2POp(dist.irecv, incoming, _neighbour(group, rank - 1), group)]
-            if not last:
-                ops.append(dist.P2POp(dist.isend, offset, later[0], group))
-            for work in dist.batch_isend_irecv(ops):
-                work.wait()
-            out = segment.finish_decayed(incoming)
-            return out, (offset if (last and output_final_state) else None)
-        offset, transition = segment.offset_and_transition(need_transition=True)
-        incoming, final = exchange(offset, transition, want_outgoing=bool(last and output_final_state))
-        out = segment.finish_decayed(incoming)
-        return out, final
+        # the pair leaves early (short passes on a side stream), so the exchange runs next to the long output walk
+        offset, transition = segment.early_pair(need_transition=not until_decayed)
+        segment.walk_outputs(initial_state if rank == 0 else None)
+        incoming = final = None
+        with segment.side():
+            if rank == 0 and transition is not None and initial_state is not None:
+                offset = apply_transition(transition, offset, initial_state)     # true outgoing state of rank 0
+            if until_decayed:
+                # the caller vouches that M_r is below exp(-40): b_r is the outgoing state, whatever comes in
+                ops = []
+                if rank:
+                    incoming = new_state()
+                    ops.append(dist.P2POp(dist.irecv, incoming, _neighbour(group, rank - 1), group))
+                if not last:
+                    ops.append(dist.P2POp(dist.isend, offset, later[0], group))
+                for work in dist.batch_isend_irecv(ops):
+                    work.wait()
+                final = offset
+            else:
+                incoming, final = exchange(offset, None if rank == 0 else transition,
+                                           want_outgoing=bool(rank and last and output_final_state))
+        segment.join(incoming, final)
+        out = segment.finish_decayed(incoming) if rank else segment.output
+        return out, (final if (last and output_final_state) else None)
+
+    if rank == 0:
+        # the first segment starts from the caller's state; its true outgoing state plays the part of b_0
+        out, final = forward_fn(q, k, v, g, beta, initial_state, True, **forward_options)
+        exchange(final, None)
+        return out, None
 
     # generic form on complete forwards: (M_r, b_r) by two state-only passes, the same exchange, a third pass
     _, offset = forward_fn(q, k, v, g, beta, None, True, **forward_options)

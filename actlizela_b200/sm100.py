@@ -85,12 +85,13 @@ class Sm100Forward:
         return torch.empty(nbytes, dtype=torch.uint8, device=device)
 
     def _side_stream(self, device):
-        """One extra stream per device for the transition pass that runs next to the offset pass."""
+        """One extra, high-priority stream per device for the short passes (and the state exchange) that run next
+        to the long output walk: their CTAs get the next free SMs ahead of the walk's."""
         import torch
         streams = self.__dict__.setdefault("_side_streams", {})
         key = str(device)
         if key not in streams:
-            streams[key] = torch.cuda.Stream(device=device)
+            streams[key] = torch.cuda.Stream(device=device, priority=-1)
         return streams[key]
 
     def _transition_operands(self, like):
@@ -206,11 +207,11 @@ class PreparedSegment:
     """The WY factors of one token segment in a workspace of its own, and the walks over them.
 
     Used by the sequence-parallel scheme: the factors do not depend on the recurrent state, so the offset pass
-    (zero state), the transition pass (identity state, U treated as zero) and the final pass (true incoming state)
-    share the prepare work.  Built on stage-restricted calls of ``actlize_la_sm100_forward_prepared`` (tcgen05
+    (zero state, only the deciding suffix), the transition pass (identity state, U treated as zero), the output walk
+    and the correction pass (true incoming state) share the prepare work.  Built on stage-restricted calls of ``actlize_la_sm100_forward_prepared`` (tcgen05
     configuration); nothing is launched before the first method call.
     """
-    _CONFIG, _PREPARE, _WALK, _HOMOGENEOUS, _UNTIL_DECAYED = 1, 0x10, 0x20, 0x40, 0x80
+    _CONFIG, _PREPARE, _WALK, _HOMOGENEOUS, _UNTIL_DECAYED, _OFFSET_TAIL = 1, 0x10, 0x20, 0x40, 0x80, 0x100000
 
     def __init__(self, owner, q, k, v, g, beta):
         import torch
@@ -219,11 +220,9 @@ class PreparedSegment:
         b, t, hk, hv = self.dims
         owner.library.configure(q.device)
         selection = selection_for(q, v)
-        self.pipelined_config = selection.configuration_id                 # the policy's complete forward
-        # the walk alone, split into the policy's parallel sub-segments (offset pass from a zero state)
+        # the walk alone, split into the policy's parallel sub-segments
         self.split_walk = self._CONFIG | self._WALK | ((selection.parallel << 16) if selection.parallel > 1 else 0)
-        self.nbytes = max(owner.workspace_bytes(b, t, hk, hv, self._CONFIG),
-                          owner.workspace_bytes(b, t, hk, hv, self.pipelined_config))
+        self.nbytes = owner.workspace_bytes(b, t, hk, hv, self._CONFIG)
         self.workspace = torch.empty(self.nbytes, dtype=torch.uint8, device=q.device)
         self.output = torch.empty_like(v)
         self._side = None
@@ -244,37 +243,49 @@ class PreparedSegment:
         b, _, _, hv = self.dims
         return torch.empty((b, hv, 128, 128), dtype=torch.float32, device=self.output.device)
 
-    def offset_pipelined(self):
-        """b_r (final state from a zero state) through the complete, segmented forward: prepare of later
-        segments next to the walk of earlier ones.  Leaves the zero-state outputs in ``self.output`` and the
-        factors of the whole segment in the workspace."""
-        offset = self._state()
-        self._launch(self.pipelined_config, None, self.output, offset)
-        return offset
-
-    def offset_and_transition(self, need_transition=True):
-        """(b_r, M_r) of ``S_out = M_r S_in + b_r``; the zero-state outputs stay in ``self.output``.
-        One prepare launch, then the two walks next to each other on two streams: the offset walk split into the
-        policy's parallel sub-segments, the transition walk one CTA per (batch, value head), which returns exact
-        zeros at once for a head whose segment decays below exp(-40)."""
+    def early_pair(self, need_transition=True):
+        """(b_r, M_r) of ``S_out = M_r S_in + b_r``, produced EARLY: one prepare launch on the current stream, then,
+        on a high-priority side stream, the offset pass (per head only the suffix of the segment that decides the
+        outgoing state, from zero: a few chunks when the gate decays) and the transition pass (exact zeros at
+        once for a head whose segment decays below exp(-40)).  The caller launches the long output walk on the
+        current stream next (``walk_outputs``) and can exchange the pair inside ``side()`` while that walk runs;
+        ``join()`` orders the current stream behind the side stream."""
         import torch
         self._launch(self._CONFIG | self._PREPARE, None, self.output, None)
-        offset, transition = self._state(), None
-        if need_transition:
-            b, _, _, hv = self.dims
-            current = torch.cuda.current_stream()
-            if self._side is None:
-                self._side = self.owner._side_stream(self.output.device)
-            self._side.wait_stream(current)
-            eye, scratch = self.owner._transition_operands(self.output)
-            with torch.cuda.stream(self._side):
-                transition = self._state()
+        offset = self._state()
+        transition = self._state() if need_transition else None
+        current = torch.cuda.current_stream()
+        if self._side is None:
+            self._side = self.owner._side_stream(self.output.device)
+        self._side.wait_stream(current)
+        eye, scratch = self.owner._transition_operands(self.output)
+        with torch.cuda.stream(self._side):
+            self._launch(self._CONFIG | self._WALK | self._OFFSET_TAIL, None, scratch, offset)
+            offset.record_stream(self._side)
+            if need_transition:
                 self._launch(self._CONFIG | self._WALK | self._HOMOGENEOUS, eye, scratch, transition)
                 transition.record_stream(self._side)
-        self._launch(self.split_walk, None, self.output, offset)
-        if need_transition:
-            torch.cuda.current_stream().wait_stream(self._side)
         return offset, transition
+
+    def walk_outputs(self, initial=None):
+        """The output rows of the segment walked from ``initial`` (zero when None) over the prepared factors, split
+        into the policy's parallel sub-segments; no final state (``early_pair`` has the outgoing state)."""
+        self._launch(self.split_walk, initial, self.output, None)
+        return self.output
+
+    def side(self):
+        """Context manager: work issued inside runs on the side stream, behind the passes of ``early_pair``."""
+        import torch
+        return torch.cuda.stream(self._side)
+
+    def join(self, *tensors):
+        """The current stream waits for the side stream; ``tensors`` made there may then be used on it."""
+        import torch
+        current = torch.cuda.current_stream()
+        current.wait_stream(self._side)
+        for x in tensors:
+            if x is not None:
+                x.record_stream(current)
 
     def prepare(self):
         """Only the factors (for a rank that has nothing else to do before its incoming state arrives)."""

@@ -45,6 +45,13 @@ extern "C" {
  * untouched (final_state must be NULL). */
 #define ACTLIZE_LA_SM100_WALK_HOMOGENEOUS 0x40
 #define ACTLIZE_LA_SM100_WALK_UNTIL_DECAYED 0x80
+/* A third walk-only form of configuration 1, on its own (no other modifier, no sub-segments): the OFFSET pass.  Per
+ * (batch, value head) only the shortest suffix of the sequence whose accumulated decay is below exp(-40) (all of its
+ * tokens contractions) is walked, from a zero state; no output row is written (`output` must still be a valid
+ * buffer) and `final_state` (required) receives the state the sequence ends in from a zero incoming state, which to
+ * exp(-40) is what it ends in from any.  A head without such a suffix is walked whole: then the result is bit-equal
+ * to the ordinary zero-state walk.  It gives a sequence-parallel rank its outgoing state after a few chunks of work. */
+#define ACTLIZE_LA_SM100_WALK_OFFSET_SUFFIX 0x100000
 
 /* ABI version of this library; the loader refuses a mismatch.
  * Counterpart: ala_abi_version in csrc/serving/abi.h:67-82. */

@@ -520,35 +520,53 @@ def test_extreme_gates(gate, configuration, forward, native_library):
 
 
 def test_prepared_segment_walks(forward, native_library):
-    """Several walks over one prepared workspace (the building block of the sequence-parallel scheme): the offset
-    pass, the transition pass (identity state, U treated as zero) against the oracle's M, the final pass bit-equal
-    to the ordinary forward, and the walk that stops once the incoming state has decayed."""
+    """Several walks over one prepared workspace (the building block of the sequence-parallel scheme): the early
+    pair (offset pass over the deciding suffix; transition pass with identity state and U treated as zero, against
+    the oracle's M), the output walk, the final pass bit-equal to the ordinary forward, and the walk that stops
+    once the incoming state has decayed."""
     w = WORKLOADS["cfg0"].sliced(batch=2, length=64 * 12 + 20, key_heads=2, value_heads=4, initial=0.1)
     cpu = make_inputs(w)
     dev = _to_device(cpu)
     q, k, v, g, beta, init = dev
     segment = forward.prepare_segment(q, k, v, g, beta)
-    offset, transition = segment.offset_and_transition()
-    zero_out = segment.output.clone()
+    offset, transition = segment.early_pair()
+    zero_out = segment.walk_outputs(None).clone()
+    segment.join()
     want_zero_out, want_offset = forward(q, k, v, g, beta, None, True, configuration="umma")
-    assert torch.equal(zero_out, want_zero_out) and torch.equal(offset, want_offset)
+    assert torch.equal(zero_out, want_zero_out)
+    # the suffix walk leaves out what has decayed below exp(-40): equal to FP32 rounding, not bit for bit
+    assert oracle.rel_frobenius(offset.cpu(), want_offset.cpu()) < 1e-6
     want_m = oracle.segment_transition(cpu[1], cpu[3], cpu[4])
     assert oracle.rel_frobenius(transition.cpu(), want_m) < 1e-3
     # S_out = M S_in + b reproduces the forward's final state
     want_out, want_state = forward(q, k, v, g, beta, init, True, configuration="umma")
     composed = torch.matmul(transition.double(), init.double()) + offset.double()
     assert oracle.rel_frobenius(composed.cpu(), want_state.double().cpu()) < 1e-5
+    assert torch.equal(segment.walk_outputs(init), want_out)
     out, state = segment.finish(init, True)
     assert torch.equal(out, want_out) and torch.equal(state, want_state)
     # decayed form: start again from the zero-state rows, rewrite the leading chunks only
-    segment.offset_and_transition(need_transition=False)
+    segment.walk_outputs(None)
     out = segment.finish_decayed(init)
     torch.cuda.synchronize()
     assert _status(native_library)[0] == 0
     assert oracle.max_abs(out.float().cpu(), want_out.float().cpu()) < 1e-6     # exp(-40) of the state is invisible in BF16
     changed = (out != zero_out).any(dim=(0, 2, 3)).nonzero().max().item()     # last token row that was rewritten
     assert changed < 64 * 8, changed                                           # ... lies in the first few chunks
+    # a gate that never decays that far, and one with a token that is no contraction: the offset pass walks the
+    # whole segment, bit-equal to the ordinary zero-state forward
+    long_key = k.clone()
+    long_key[:, -5] *= 3.0                                          # beta |k|^2 up to 9 in the last chunk
+    for change, k2, g2 in (("slow", k, g * 1e-3), ("long-key", long_key, g)):
+        segment = forward.prepare_segment(q, k2, v, g2, beta)
+        offset, _ = segment.early_pair(need_transition=False)
+        segment.join()
+        _, want_offset = forward(q, k2, v, g2, beta, None, True, configuration="umma")
+        assert torch.equal(offset, want_offset), change
     lib = native_library.lib
     assert lib.actlize_la_sm100_workspace_bytes(1, 64, 1, 1, 1 | 0x40) == -1    # modifiers need a walk-only call
     assert lib.actlize_la_sm100_workspace_bytes(1, 64, 1, 1, 0 | 0x20 | 0x40) == -1   # ... of the tcgen05 configuration
     assert lib.actlize_la_sm100_workspace_bytes(1, 64, 1, 1, 1 | 0x20 | 0xc0) > 0
+    assert lib.actlize_la_sm100_workspace_bytes(1, 64, 1, 1, 1 | 0x20 | 0x100000) > 0   # the offset pass
+    assert lib.actlize_la_sm100_workspace_bytes(1, 64, 1, 1, 1 | 0x100000) == -1        # ... is a walk-only call
+    assert lib.actlize_la_sm100_workspace_bytes(1, 64, 1, 1, 1 | 0x20 | 0x40 | 0x100000) == -1   # ... on its own

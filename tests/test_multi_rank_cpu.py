@@ -3,6 +3,7 @@
 The device forward is replaced by the CPU oracle (injected as ``forward_fn``); what is under
 test is the partitioning, the affine state hand-off and the send/recv choreography.
 """
+import contextlib
 import os
 import socket
 
@@ -29,20 +30,24 @@ class _OracleSegment:
         self.tensors = (q, k, v, g, beta)
         self.output = None
 
-    def prepare(self):
-        pass
-
-    def offset_pipelined(self):
-        return self.offset_and_transition(need_transition=False)[0]
-
-    def offset_and_transition(self, need_transition=True):
+    def early_pair(self, need_transition=True):
         q, k, v, g, beta = self.tensors
-        self.output, offset = _oracle_forward(q, k, v, g, beta, None)
+        _, offset = _oracle_forward(q, k, v, g, beta, None)
         transition = None
         if need_transition:
             eye = torch.eye(128).expand(q.shape[0], v.shape[2], 128, 128).contiguous()
             _, transition = _oracle_forward(q, k, torch.zeros_like(v), g, beta, eye)
         return offset, transition
+
+    def walk_outputs(self, initial=None):
+        self.output, _ = _oracle_forward(*self.tensors, initial)
+        return self.output
+
+    def side(self):
+        return contextlib.nullcontext()
+
+    def join(self, *tensors):
+        pass
 
     def finish(self, incoming, output_final_state=True):
         return _oracle_forward(*self.tensors, incoming, output_final_state)
@@ -131,9 +136,7 @@ def _worker(rank, world, port, mode, result_queue):
                 out, final = gdn_forward_sequence_parallel(
                     *part, init if rank == 0 else None, True, forward_fn=_oracle_forward, segment_lengths=lengths)
             else:
-                # the staged form: prepared segment walked several times; rank 0 still runs a complete forward
-                import actlizela_b200.gdn_interface as interface
-                interface.gdn_forward = _oracle_forward
+                # the staged form: one prepared segment per rank, walked several times
                 out, final = gdn_forward_sequence_parallel(
                     *part, init if rank == 0 else None, True, segment_fn=_OracleSegment,
                     until_decayed=(mode == "sp-decayed"), segment_lengths=lengths)
