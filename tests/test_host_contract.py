@@ -203,6 +203,14 @@ def test_native_argument_rejection_without_a_device(native_library):
     assert lib.actlize_la_sm100_launches_per_forward(1 | (4 << 8)) == 8
     assert lib.actlize_la_sm100_workspace_bytes(1, 64, 3, 4, 1) < 0
     assert lib.actlize_la_sm100_workspace_bytes(1, 64, 1, 1, 9) < 0
+    # the offset pass of the sequence-parallel scheme is a walk-only call of the tcgen05 configuration, on its own
+    offset_pass = 0x100000
+    assert lib.actlize_la_sm100_workspace_bytes(1, 64, 1, 1, 1 | 0x20 | offset_pass) > 0
+    for bad in (1 | offset_pass, 0 | 0x20 | offset_pass, 1 | 0x20 | 0x40 | offset_pass, 1 | 0x20 | (2 << 16) | offset_pass):
+        assert lib.actlize_la_sm100_workspace_bytes(1, 64, 1, 1, bad) < 0, hex(bad)
+    big = 1 << 40
+    walk_args = [ptr_ := 0x1000] * 5 + [None, ptr_ + 256, None, ptr_ + 512, big, 1, 64, 1, 1, 1, 1 | 0x20 | offset_pass, None]
+    assert lib.actlize_la_sm100_forward_prepared(*walk_args) == invalid     # the offset pass needs final_state
     args = [None] * 9 + [0, 1, 64, 1, 1, 1, 1, None]
     assert lib.actlize_la_sm100_forward_prepared(*args) == invalid
     ptr = 0x1000
