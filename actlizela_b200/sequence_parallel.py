@@ -145,20 +145,21 @@ def gdn_forward_sequence_parallel(q, k, v, g, beta, initial_state=None, output_f
 
     fold = native_fold_transitions if (q.is_cuda and apply_transition is native_apply_transition) else None
 
-    def exchange(offset, transition, want_outgoing=False):
-        """Post this rank's pair to every later rank and collect the pairs of every earlier rank, all at once.
-        Returns (incoming state of this rank, its outgoing state if asked for); (None, None) on rank 0."""
+    def exchange(offset, transition, want_outgoing=False, pair=None):
+        """Post this rank's pair to every later rank and collect the pairs of every earlier rank, all at once: one
+        message per (source, target), the pair travelling as one [2, B, Hv, 128, 128] block (``pair``, when the
+        caller already holds transition and offset back to back).  Returns (incoming state of this rank, its
+        outgoing state if asked for); (None, None) on rank 0."""
         ops = []
         pairs = torch.empty((rank, 2) + state_shape, dtype=torch.float32, device=q.device) if rank else None
-        for r in range(rank):
-            source = _neighbour(group, r)
-            if r > 0:                                      # rank 0 sends its outgoing state only
-                ops.append(dist.P2POp(dist.irecv, pairs[r, 0], source, group))
-            ops.append(dist.P2POp(dist.irecv, pairs[r, 1], source, group))
-        for target in later:
-            if transition is not None:
-                ops.append(dist.P2POp(dist.isend, transition, target, group))
-            ops.append(dist.P2POp(dist.isend, offset, target, group))
+        for r in range(rank):                              # rank 0 sends its outgoing state only
+            ops.append(dist.P2POp(dist.irecv, pairs[r] if r else pairs[0, 1], _neighbour(group, r), group))
+        if later:
+            if transition is None:
+                message = offset
+            else:
+                message = pair if pair is not None else torch.stack((transition, offset))
+            ops += [dist.P2POp(dist.isend, message, target, group) for target in later]
         for work in (dist.batch_isend_irecv(ops) if ops else []):
             work.wait()
         if pairs is None:
@@ -195,7 +196,8 @@ def gdn_forward_sequence_parallel(q, k, v, g, beta, initial_state=None, output_f
                 final = offset
             else:
                 incoming, final = exchange(offset, None if rank == 0 else transition,
-                                           want_outgoing=bool(rank and last and output_final_state))
+                                           want_outgoing=bool(rank and last and output_final_state),
+                                           pair=getattr(segment, "pair", None))
         segment.join(incoming, final)
         out = segment.finish_decayed(incoming) if rank else segment.output
         return out, (final if (last and output_final_state) else None)

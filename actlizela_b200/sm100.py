@@ -225,7 +225,7 @@ class PreparedSegment:
         self.nbytes = owner.workspace_bytes(b, t, hk, hv, self._CONFIG)
         self.workspace = torch.empty(self.nbytes, dtype=torch.uint8, device=q.device)
         self.output = torch.empty_like(v)
-        self._side = None
+        self._side = self.pair = None
 
     def _launch(self, config, initial, output, final):
         import torch
@@ -252,8 +252,11 @@ class PreparedSegment:
         ``join()`` orders the current stream behind the side stream."""
         import torch
         self._launch(self._CONFIG | self._PREPARE, None, self.output, None)
-        offset = self._state()
-        transition = self._state() if need_transition else None
+        # the pair in one block [2, B, Hv, 128, 128] = (M_r, b_r): it travels as one message
+        b, _, _, hv = self.dims
+        self.pair = torch.empty((2, b, hv, 128, 128), dtype=torch.float32, device=self.output.device) if need_transition else None
+        offset = self.pair[1] if need_transition else self._state()
+        transition = self.pair[0] if need_transition else None
         current = torch.cuda.current_stream()
         if self._side is None:
             self._side = self.owner._side_stream(self.output.device)
@@ -261,10 +264,9 @@ class PreparedSegment:
         eye, scratch = self.owner._transition_operands(self.output)
         with torch.cuda.stream(self._side):
             self._launch(self._CONFIG | self._WALK | self._OFFSET_TAIL, None, scratch, offset)
-            offset.record_stream(self._side)
             if need_transition:
                 self._launch(self._CONFIG | self._WALK | self._HOMOGENEOUS, eye, scratch, transition)
-                transition.record_stream(self._side)
+            (self.pair if need_transition else offset).record_stream(self._side)
         return offset, transition
 
     def walk_outputs(self, initial=None):
