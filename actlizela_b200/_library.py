@@ -141,6 +141,14 @@ class NativeLibrary:
             self._configured.add(key)
 
     @staticmethod
+    def current_stream_handle(device_index):
+        """The raw cudaStream_t of torch's current stream on a device, without building a Stream object (this sits
+        in front of every launch of the sequence-parallel path, whose host time shows at eight ranks)."""
+        import torch
+        raw = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+        return raw(device_index) if raw is not None else torch.cuda.current_stream(device_index).cuda_stream
+
+    @staticmethod
     def check(code):
         if code:
             raise RuntimeError(f"cuda_sm100 native call failed with CUDA error code {code}")

@@ -226,17 +226,23 @@ class PreparedSegment:
         self.workspace = torch.empty(self.nbytes, dtype=torch.uint8, device=q.device)
         self.output = torch.empty_like(v)
         self._side = self.pair = None
+        # what every launch passes, looked up once
+        self._entry = owner.library.lib.actlize_la_sm100_forward_prepared
+        self._pointers = tuple(x.data_ptr() for x in self.tensors)
+        self._workspace_pointer = self.workspace.data_ptr()
+        self._gate_fp32 = int(g.dtype == torch.float32)
+        self._device_index = q.device.index if q.device.index is not None else torch.cuda.current_device()
 
     def _launch(self, config, initial, output, final):
         import torch
-        q, k, v, g, beta = self.tensors
+        if torch.cuda.current_device() != self._device_index:
+            with torch.cuda.device(self._device_index):
+                return self._launch(config, initial, output, final)
         b, t, hk, hv = self.dims
-        with torch.cuda.device(q.device):
-            self.owner.library.check(self.owner.library.lib.actlize_la_sm100_forward_prepared(
-                q.data_ptr(), k.data_ptr(), v.data_ptr(), g.data_ptr(), beta.data_ptr(),
-                initial.data_ptr() if initial is not None else None, output.data_ptr(),
-                final.data_ptr() if final is not None else None, self.workspace.data_ptr(), self.nbytes,
-                b, t, hk, hv, int(g.dtype == torch.float32), config, torch.cuda.current_stream().cuda_stream))
+        self.owner.library.check(self._entry(
+            *self._pointers, initial.data_ptr() if initial is not None else None, output.data_ptr(),
+            final.data_ptr() if final is not None else None, self._workspace_pointer, self.nbytes,
+            b, t, hk, hv, self._gate_fp32, config, self.owner.library.current_stream_handle(self._device_index)))
 
     def _state(self):
         import torch

@@ -18,7 +18,7 @@ restatement of the reference's own FP32 path (oracle/) on the host cores instead
 The same line carries, at N = 1, `per_config` (every named shape timed through the policy's configuration, with
 its fraction of the per-shape roofline) and, at N > 1, the two multi-GPU forms the path has: `shard_cfg2` (B8 T4096
 split by batch over the ranks, no collective, strong scaling) and `sp_cfg4` (T131072 split over the ranks, states
-handed on with NCCL send/recv; the exact form and the one where the caller vouches for the decay), each with its efficiency against one GPU running the same
+handed on with NCCL send/recv; the exact form, the same with one all-gather, and the one where the caller vouches for the decay), each with its efficiency against one GPU running the same
 shape and a `parity` object (key-head group 0 of the timed tensors against the CPU restatement, computed outside
 the timed regions).
 """
@@ -464,9 +464,8 @@ def shard_cfg2_leg(device, rank, world, steps, peaks):
     plant_group(tensors, narrow)
     whole = lambda: gdn_forward(*tensors, output_final_state=True)
     mine = lambda: gdn_forward_sharded(*tensors, True, rank=rank, world_size=world)
-    for _ in range(3):
-        whole()
-        mine()
+    for fn in (whole, mine):          # warm-up in the shape of the measurement (allocator steady state)
+        timed_loop(fn, max(3, steps), device, world)
     ms_one, _ = timed_loop(whole, steps, device, world)
     ms_n, spread = timed_loop(mine, steps, device, world)
     worst = dict(out_max_abs=0.0, out_rel_f=0.0, state_rel_f=0.0)
@@ -485,7 +484,8 @@ def shard_cfg2_leg(device, rank, world, steps, peaks):
 
 def sp_cfg4_leg(device, rank, world, steps, peaks):
     """cfg4 (B1 T131072 Hk16 Hv32) split over the ranks as contiguous token segments, states handed on with NCCL
-    send/recv: strong scaling against one GPU running the whole sequence; the exact form and the vouched one."""
+    send/recv: strong scaling against one GPU running the whole sequence; the exact form (also with its pairs
+    moved by one all-gather) and the vouched one."""
     import torch
     from actlizela_b200 import gdn_forward
     from actlizela_b200.sequence_parallel import gdn_forward_sequence_parallel, segment_bounds
@@ -500,8 +500,7 @@ def sp_cfg4_leg(device, rank, world, steps, peaks):
     full = device_inputs(w, device, w.seed)
     plant_group(full, narrow)
     whole = lambda: gdn_forward(*full, output_final_state=True)
-    for _ in range(3):
-        whole()
+    timed_loop(whole, max(3, steps), device, world)
     ms_one, _ = timed_loop(whole, steps, device, world)
     part = [x[:, t0:t1].contiguous() for x in full[:5]]
     initial = full[5] if rank == 0 else None
@@ -512,11 +511,14 @@ def sp_cfg4_leg(device, rank, world, steps, peaks):
                   segments=f"{world} contiguous token segments, one per rank", one_gpu_ms=ms_one, scaling="strong")
     # "exact": decided on the device per (batch, value head), valid for any gate; "vouched": the caller states that
     # every segment forgets its incoming state, so no transition pass runs and only b travels to the next rank
-    for form, decayed in (("exact", False), ("vouched", True)):
+    # "exact_all_gather": the exact form with its pairs moved by one all-gather instead of world - 1 messages per rank
+    for form, decayed, collective in (("exact", False, "send_recv"), ("exact_all_gather", False, "all_gather"),
+                                      ("vouched", True, "send_recv")):
         call = lambda: gdn_forward_sequence_parallel(*part, initial, True, until_decayed=decayed,
-                                                     segment_lengths=lengths)
-        for _ in range(3):
-            call()
+                                                     segment_lengths=lengths, collective=collective)
+        # warm-up in the shape of the measurement: the host runs several calls ahead of the device, each holding a
+        # workspace of its own, so the caching allocator reaches its steady state only in such a loop
+        timed_loop(call, max(3, steps), device, world)
         ms, spread = timed_loop(call, steps, device, world)
         out, final = call()
         m = parity_metrics(out[:, :, :heads], want_out[:, t0:t1],

@@ -57,6 +57,11 @@ def main():
         else:
             rel_state = ((final - full_state).norm() / full_state.norm()).item()
             ok = ok and rel_state < 1e-5
+        # the same (a gate that never decays: every transition matrix is dense) through one all-gather
+        out_g, final_g = gdn_forward_sequence_parallel(*part, dev[5] if rank == 0 else None, True, collective="all_gather",
+                                                       segment_lengths=[b1 - b0 for b0, b1 in bounds])
+        torch.cuda.synchronize()
+        ok = ok and torch.equal(out_g, out) and (final is None or torch.equal(final_g, final))
         pieces = gdn_forward_sharded(*dev, True, rank=rank, world_size=world)
         ok = ok and all(torch.equal(o, full_out[b0:b1, :, v0:v1]) and torch.equal(s, full_state[b0:b1, v0:v1])
                         for (b0, b1, v0, v1), o, s in pieces)
@@ -70,9 +75,10 @@ def main():
         bounds2 = segment_bounds(w2.length, world)
         s0, s1 = bounds2[rank]
         part2 = [x[:, s0:s1].contiguous() for x in dev2[:5]]
-        for vouched in (False, True):        # the exact form (decides on the device) and the caller's statement
+        # the exact form (decides on the device) with either collective, and the caller's statement
+        for vouched, collective in ((False, "send_recv"), (False, "all_gather"), (True, "send_recv")):
             out2, final2 = gdn_forward_sequence_parallel(*part2, dev2[5] if rank == 0 else None, True,
-                                                         until_decayed=vouched,
+                                                         until_decayed=vouched, collective=collective,
                                                          segment_lengths=[b1 - b0 for b0, b1 in bounds2])
             torch.cuda.synchronize()
             want2 = full_out2[:, s0:s1].float()
