@@ -307,7 +307,7 @@ class PreparedSegment:
 
     def finish_decayed(self, incoming):
         """Rewrite only the leading chunks of ``self.output`` (those the incoming state still reaches, decay
-        above exp(-40) per batch and value head); valid after one of the offset passes."""
+        above exp(-40) per batch and value head); valid after ``walk_outputs(None)`` has written the zero-state rows."""
         self._launch(self._CONFIG | self._WALK | self._UNTIL_DECAYED, incoming, self.output, None)
         return self.output
 
