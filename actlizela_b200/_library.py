@@ -158,8 +158,12 @@ class NativeLibrary:
         Reads the host-visible record only: no synchronisation, so it reports launches that have already run."""
         import torch
         record = (C.c_int * 4)()
-        with torch.cuda.device(device):
+        index = torch.device(device).index
+        if index is None or index == torch.cuda.current_device():
             self.check(self.lib.actlize_la_sm100_last_failure(record))
+        else:
+            with torch.cuda.device(device):
+                self.check(self.lib.actlize_la_sm100_last_failure(record))
         return tuple(record) if record[0] else None
 
     def raise_on_failure(self, device, synchronize=False):

@@ -135,14 +135,19 @@ class Sm100Forward:
                  if output_final_state else None)
         nbytes = self.workspace_bytes(b, t, hk, hv, config)
         workspace = self._workspace(q.device, nbytes)
-        with torch.cuda.device(q.device):
-            stream = torch.cuda.current_stream().cuda_stream
-            self.library.check(self.library.lib.actlize_la_sm100_forward_prepared(
-                q.data_ptr(), k.data_ptr(), v.data_ptr(), g.data_ptr(), beta.data_ptr(),
-                initial_state.data_ptr() if initial_state is not None else None,
-                out.data_ptr(), final.data_ptr() if final is not None else None,
-                workspace.data_ptr(), nbytes, b, t, hk, hv,
-                int(g.dtype == torch.float32), config, stream))
+        if q.device.index != torch.cuda.current_device():
+            with torch.cuda.device(q.device):
+                return self._launch(q, k, v, g, beta, initial_state, out, final, workspace, nbytes, b, t, hk, hv, config)
+        return self._launch(q, k, v, g, beta, initial_state, out, final, workspace, nbytes, b, t, hk, hv, config)
+
+    def _launch(self, q, k, v, g, beta, initial_state, out, final, workspace, nbytes, b, t, hk, hv, config):
+        import torch
+        self.library.check(self.library.lib.actlize_la_sm100_forward_prepared(
+            q.data_ptr(), k.data_ptr(), v.data_ptr(), g.data_ptr(), beta.data_ptr(),
+            initial_state.data_ptr() if initial_state is not None else None,
+            out.data_ptr(), final.data_ptr() if final is not None else None,
+            workspace.data_ptr(), nbytes, b, t, hk, hv,
+            int(g.dtype == torch.float32), config, self.library.current_stream_handle(torch.cuda.current_device())))
         return out, final
 
     def prepare_segment(self, q, k, v, g, beta):

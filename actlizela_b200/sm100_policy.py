@@ -109,7 +109,16 @@ def select(shape, profile):
                      default_segments(shape[0], shape[1], shape[3]), default_parallel(shape[0], shape[1], shape[3]))
 
 
+_SELECTIONS = {}
+
+
 def selection_for(q, v, *, mode="device", sm_count=None):
+    """Selection for a pair of device tensors; remembered per (shapes, device, mode) after the first call, as the
+    reference remembers its route (actlize_la/sm90_auto.py:68-89): table and device profile are both static."""
+    key = (tuple(q.shape), tuple(v.shape), q.device, v.device, mode, sm_count)
+    held = _SELECTIONS.get(key)
+    if held is not None:
+        return held
     validate_profile_options(mode, "cuda_sm100", sm_count)
     if q.ndim != 4 or v.ndim != 4 or tuple(q.shape[:2]) != tuple(v.shape[:2]):
         raise ValueError("SM100 requires q/v [B,T,H,D] with matching batch and sequence")
@@ -118,4 +127,8 @@ def selection_for(q, v, *, mode="device", sm_count=None):
     shape = tuple(int(x) for x in (*q.shape[:3], v.shape[2], q.shape[3], v.shape[3]))
     profile = (get_device_profile(mode=mode, backend="cuda_sm100", sm_count=sm_count)
                if mode == "perfmodel" else device_profile(q.device.index))
-    return select(shape, profile)
+    held = select(shape, profile)
+    if len(_SELECTIONS) > 256:
+        _SELECTIONS.clear()
+    _SELECTIONS[key] = held
+    return held
