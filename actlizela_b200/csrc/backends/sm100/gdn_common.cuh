@@ -38,6 +38,18 @@ struct Geometry {
   }
 };
 
+// Parallel sub-segments of a walk over `chunks` chunks: sub-segment r covers [sub_segment_begin(r), sub_segment_begin(r + 1)).
+// Every CTA but the last walks on into its successor's leading chunks (about kNominalReach of them at typical gates),
+// so the last sub-segment is made that much longer than the others and all CTAs finish together; ranges too short
+// for that are cut evenly.
+constexpr int kNominalReach = 4;
+__host__ __device__ inline int sub_segment_begin(int chunks, int r, int parallel) {
+  if (r <= 0) return 0;
+  if (r >= parallel) return chunks;
+  const int body = chunks - kNominalReach;
+  return int((long long)(body >= parallel * kNominalReach ? body : chunks) * r / parallel);
+}
+
 // Packed mode: the sequence that owns global chunk `gchunk` (largest s with chunk_prefix[s] <= gchunk; empty
 // sequences share their successor's offset and are skipped by the search).
 __device__ __forceinline__ int varlen_sequence_of(const int* chunk_prefix, int count, int gchunk) {

@@ -231,6 +231,7 @@ prepare_umma_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
     // prepared LAST are the leading chunks of every sub-segment of every head, and the walk finds them in L2.
     // The grid covers heads x sub-segments x longest sub-segment; a slot behind a shorter sub-segment's end is empty.
     const int parallel = geo.parallel > 1 ? geo.parallel : 1;
+    // (The cut is an even one; the walk's own cut, sub_segment_begin, differs from it by a few chunks at most.)
     const int longest = (seg_chunks + parallel - 1) / parallel;
     const int units = geo.batch * geo.value_heads * parallel;
     const int offset = longest - 1 - int(blockIdx.x) / units, unit = int(blockIdx.x) % units;
@@ -903,9 +904,9 @@ walk_umma_kernel(const __grid_constant__ CUtensorMap tm_wh, const __grid_constan
   }
   int* reach_slot = limit_slot + 4;             // [8] per sub-segment: chunks an incoming state reaches, -1 = invalid
   if (parallel > 1 && warp >= 1 && warp < parallel) {
-    // plan (see the comment above the kernel): warp r scans sub-segment r, chunks [n r / P, n (r + 1) / P)
+    // plan (see the comment above the kernel): warp r scans sub-segment r (sub_segment_begin gives the cut)
     const int n = chunks;
-    const int r0 = int((long long)n * warp / parallel), r1 = int((long long)n * (warp + 1) / parallel);
+    const int r0 = sub_segment_begin(n, warp, parallel), r1 = sub_segment_begin(n, warp + 1, parallel);
     bool flagged = false;
     const int reach = decay_reach(ws.gates, block0 + r0, r1 - r0, lane, flagged);
     if (lane == 0) reach_slot[warp] = flagged ? -1 : reach;
@@ -937,7 +938,7 @@ walk_umma_kernel(const __grid_constant__ CUtensorMap tm_wh, const __grid_constan
       chunks = sub == 0 ? n : 0;             // the head's first CTA walks the whole range alone
       if (sub != 0) state_out = nullptr;
     } else {
-      const int c0 = int((long long)n * sub / parallel), c1 = int((long long)n * (sub + 1) / parallel);
+      const int c0 = sub_segment_begin(n, sub, parallel), c1 = sub_segment_begin(n, sub + 1, parallel);
       chunks = c1 - c0 + (sub + 1 < parallel ? reach_slot[sub + 1] : 0);
       t_first += c0 * kChunk;
       block0 += c0;
