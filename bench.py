@@ -696,7 +696,7 @@ def main():
     # DRAM traffic per launch from the committed ncu captures of a smaller case (profiles/; caches flushed before the
     # captured launch, so an upper bound), per (chunk, value head) block and scaled by the blocks of one launch
     blocks = shard.batch * shard.value_heads * ((shard.length + 63) // 64)
-    traffic = {"walk": 119.2e3, "prepare": 52.6e3}[top] * blocks if config_name == "umma" else None
+    traffic = {"walk": 108.3e3, "prepare": 52.3e3}[top] * blocks if config_name == "umma" else None
     whole_ms = max(alg_bytes / (hbm_peak * 1e9), alg_flops / (tensor_peak * 1e12)) * 1e3
     line = dict(
         metric=METRIC, value=workload.tokens * world / (ms_step * 1e-3), unit=UNIT, n_gpus=world,
