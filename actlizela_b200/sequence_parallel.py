@@ -76,13 +76,6 @@ def native_fold_transitions(pairs, transition, offset, want_outgoing):
     return incoming, outgoing
 
 
-def _torch_fold_transitions(pairs, transition, offset, want_outgoing):
-    state = pairs[0, 1]
-    for j in range(1, pairs.shape[0]):
-        state = _torch_apply_transition(pairs[j, 0], pairs[j, 1], state)
-    return state, (_torch_apply_transition(transition, offset, state) if want_outgoing else None)
-
-
 def _neighbour(group, rank):
     import torch.distributed as dist
     return dist.get_global_rank(group, rank) if group else rank
