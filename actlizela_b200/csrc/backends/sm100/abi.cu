@@ -35,18 +35,23 @@ bool geometry_ok(int b, int t, int hk, int hv) {
 // value head) only the shortest suffix of the sequence whose decay is below exp(-40) is walked, from a zero state,
 // no output row is written, and `final_state` receives the state the sequence ends in from a zero (or, to exp(-40),
 // any) incoming state; a head without such a suffix is walked whole.
+// Bit 21 (0x200000) is the PAIR pass: the offset pass and the transition pass (0x40 from an identity state the kernel
+// makes itself) in one launch, two CTAs per (batch, value head); `final_state` then points at the block
+// [2][B][Hv][128][128] = (transition matrices, offsets), `initial` is not read, and `output` is scratch the
+// transition CTAs may write.
 // Bits 16..19 hold the number of parallel sub-segments of the tcgen05 walk (0 or 1 = off, at most 8): every
 // (batch, value head) walk of a launch is cut into that many pieces walked by as many CTAs at the same time
 // (walk_umma_kernel); needs the tcgen05 prepare stage, which records the per-chunk contraction flag the split relies on.
 constexpr int kStageMask = 0x30, kPrepareOnly = 0x10, kWalkOnly = 0x20, kSegmentShift = 8, kMaxSegments = 16;
 constexpr int kWalkFlagMask = 0xc0, kHomogeneousBit = 0x40, kUntilDecayedBit = 0x80;
-constexpr int kParallelShift = 16, kMaxParallel = 8, kOffsetTailBit = 0x100000;
+constexpr int kParallelShift = 16, kMaxParallel = 8, kOffsetTailBit = 0x100000, kPairBit = 0x200000;
 bool config_ok(int config) {
   const int segments = (config >> kSegmentShift) & 0xff, parallel = (config >> kParallelShift) & 0xf;
   if (config < 0 || (config & 0xf) > 3 ||
-      (config & ~(kStageMask | kWalkFlagMask | 0xf | (0xff << kSegmentShift) | (0xf << kParallelShift) | kOffsetTailBit)) != 0)
+      (config & ~(kStageMask | kWalkFlagMask | 0xf | (0xff << kSegmentShift) | (0xf << kParallelShift) | kOffsetTailBit | kPairBit)) != 0)
     return false;
   if ((config & kOffsetTailBit) && (config & ~kOffsetTailBit) != (1 | kWalkOnly)) return false;
+  if ((config & kPairBit) && (config & ~kPairBit) != (1 | kWalkOnly)) return false;
   if ((config & kWalkFlagMask) && ((config & 0xf) != 1 || (config & kStageMask) != kWalkOnly)) return false;
   if (parallel > kMaxParallel || (parallel > 1 && ((config & 0xf) != 1 || (config & kWalkFlagMask)))) return false;
   return (config & kStageMask) != kStageMask && segments <= kMaxSegments;
@@ -178,6 +183,7 @@ __global__ void apply_transition_kernel(const float* __restrict__ m, const float
 // Exclusive scan of a rank's incoming state in one launch: `pairs` holds the (M_j, b_j) of the n earlier ranks as
 // [n][2][blocks][128][128] (M_0 is unused: rank 0 contributes its true outgoing state as b_0);
 // incoming = fold_j (M_j * incoming + b_j); optionally outgoing = my_m * incoming + my_b.  One CTA per block.
+// The result is the same as folding from pair 0 on: a zero M_j makes everything before it irrelevant.
 __global__ void fold_transitions_kernel(const float* __restrict__ pairs, int n, int blocks,
                                         float* __restrict__ incoming, float* __restrict__ outgoing,
                                         const float* __restrict__ my_m, const float* __restrict__ my_b) {
@@ -185,12 +191,26 @@ __global__ void fold_transitions_kernel(const float* __restrict__ pairs, int n, 
   __shared__ float tile_s[32][128];
   const long long block = kDim * kDim, base = (long long)blockIdx.x * block;
   float* state = incoming + base;
+  // the last pair whose transition is exactly zero forgets everything in front of it: the scan starts at its offset
+  int start = 0;
+  for (int j = n - 1; j >= 1; --j) {
+    const float4* m4 = reinterpret_cast<const float4*>(pairs + (2LL * j * blocks) * block + base);
+    bool nonzero = false;
+    for (int e = threadIdx.x; e < kDim * kDim / 4; e += blockDim.x) {
+      const float4 x = m4[e];
+      nonzero |= (x.x != 0.f) | (x.y != 0.f) | (x.z != 0.f) | (x.w != 0.f);
+    }
+    if (!__syncthreads_or(nonzero)) {
+      start = j;
+      break;
+    }
+  }
   {
-    const float4* b0 = reinterpret_cast<const float4*>(pairs + (1LL * blocks) * block + base);
+    const float4* b0 = reinterpret_cast<const float4*>(pairs + ((2LL * start + 1) * blocks) * block + base);
     float4* dst = reinterpret_cast<float4*>(state);
     for (int e = threadIdx.x; e < kDim * kDim / 4; e += blockDim.x) dst[e] = b0[e];
   }
-  for (int j = 1; j < n; ++j) {
+  for (int j = start + 1; j < n; ++j) {
     __syncthreads();                 // the state written by the previous step is visible to the whole CTA
     affine_step(pairs + (2LL * j * blocks) * block + base, pairs + ((2LL * j + 1) * blocks) * block + base, state, state,
                 tile_m, tile_s);
@@ -358,12 +378,12 @@ extern "C" int actlize_la_sm100_forward_prepared(
   if (output == workspace || (void*)final_state == workspace || (void*)final_state == output)
     return int(cudaErrorInvalidValue);
   if ((config & kUntilDecayedBit) && final_state) return int(cudaErrorInvalidValue);   // a cut-short walk has no final state
-  if ((config & kOffsetTailBit) && !final_state) return int(cudaErrorInvalidValue);    // the offset pass writes nothing else
+  if ((config & (kOffsetTailBit | kPairBit)) && !final_state) return int(cudaErrorInvalidValue);   // these passes write nothing else
   const Inputs in{static_cast<const __nv_bfloat16*>(q), static_cast<const __nv_bfloat16*>(k),
                   static_cast<const __nv_bfloat16*>(v), g, static_cast<const __nv_bfloat16*>(beta),
                   initial, static_cast<__nv_bfloat16*>(output), final_state, gate_fp32 ? 1 : 0,
                   ((config & kHomogeneousBit) ? kWalkHomogeneous : 0) | ((config & kUntilDecayedBit) ? kWalkUntilDecayed : 0) |
-                      ((config & kOffsetTailBit) ? kWalkTail : 0)};
+                      ((config & kOffsetTailBit) ? kWalkTail : 0) | ((config & kPairBit) ? kWalkPair : 0)};
   const Workspace ws = carve_workspace(workspace, geo);
   return run_forward(in, geo, ws, config, segments, static_cast<cudaStream_t>(opaque_stream));
 }

@@ -140,6 +140,8 @@ struct Inputs {
 };
 constexpr int kWalkHomogeneous = 1, kWalkUntilDecayed = 2;
 constexpr int kWalkTail = 8;              // offset pass: walk, from zero, only the suffix that decides the outgoing state
+constexpr int kWalkPair = 16;             // offset pass and transition pass in one launch, two CTAs per (batch, value head);
+                                          // final_state then is the block [2][B][Hv][128][128] = (transitions, offsets)
 constexpr int kWalkSelftestStall = 4;     // the TMA producer stops after the first chunk (failure-detection self-test)
 constexpr float kDecayedLog2 = -40.f * 1.4426950408889634f;
 

@@ -823,7 +823,13 @@ walk_umma_kernel(const __grid_constant__ CUtensorMap tm_wh, const __grid_constan
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int parallel = geo.parallel > 1 ? geo.parallel : 1;
-  const int bh = blockIdx.x / parallel, sub = blockIdx.x % parallel;
+  // Pair pass (kWalkPair): the grid holds two CTAs per (batch, value head); the first set runs the offset pass
+  // (kWalkTail), the second the transition pass (kWalkHomogeneous) from an identity state made here.
+  const bool pair_pass = (in.walk_flags & kWalkPair) != 0;
+  const int heads = geo.batch * geo.value_heads;
+  const int unit = blockIdx.x / parallel, sub = blockIdx.x % parallel;
+  const int bh = pair_pass ? unit % heads : unit;
+  const int flags = pair_pass ? (unit >= heads ? kWalkHomogeneous : kWalkTail) : in.walk_flags;
   int b = bh / geo.value_heads;
   const int hv = bh % geo.value_heads;
   const int hk = hv / geo.group();
@@ -843,6 +849,13 @@ walk_umma_kernel(const __grid_constant__ CUtensorMap tm_wh, const __grid_constan
   const float* state_in = geo.first_segment() ? in.initial : ws.carry;
   float* state_out = geo.last_segment() ? in.final_state : ws.carry;
   if (sub > 0) state_in = nullptr;
+  bool identity_in = false;
+  if (pair_pass) {
+    // final_state is the pair block [2][B][Hv][128][128]: transition matrices first, offsets behind them
+    state_in = nullptr;
+    identity_in = (flags & kWalkHomogeneous) != 0;
+    state_out = in.final_state + ((flags & kWalkTail) ? (long long)heads * kDim * kDim : 0);
+  }
 #ifdef GDN_SM100_PHASE_TIMING
   const long long t_begin = clock64();
 #endif
@@ -872,7 +885,7 @@ walk_umma_kernel(const __grid_constant__ CUtensorMap tm_wh, const __grid_constan
     tmem_alloc(tmem_slot, 512);
     tmem_relinquish();
   }
-  if ((in.walk_flags & kWalkUntilDecayed) && warp == kTmaWarp) {
+  if ((flags & kWalkUntilDecayed) && warp == kTmaWarp) {
     // first chunk boundary at which the accumulated decay is below exp(-40): 32 chunks per step, the per-chunk
     // decay exp(p_last) is word 64 of the chunk's gate vector
     float total = 0.f;
@@ -891,14 +904,14 @@ walk_umma_kernel(const __grid_constant__ CUtensorMap tm_wh, const __grid_constan
     }
     if (lane == 0) *limit_slot = stop;
   }
-  if ((in.walk_flags & kWalkHomogeneous) && warp == kTmaWarp) {
+  if ((flags & kWalkHomogeneous) && warp == kTmaWarp) {
     // transition pass: a range that decays below exp(-40) (all tokens contractions) has a transition matrix
     // below exp(-40) in norm; it is returned as exact zeros without walking
     bool flagged = false;
     const int reach = decay_reach(ws.gates, block0, chunks, lane, flagged);
     if (lane == 0) limit_slot[1] = (reach >= 0 && !flagged) ? 1 : 0;
   }
-  if ((in.walk_flags & kWalkTail) && warp == kTmaWarp) {
+  if ((flags & kWalkTail) && warp == kTmaWarp) {
     const int keep = decay_suffix(ws.gates, block0, chunks, lane);
     if (lane == 0) limit_slot[2] = keep > 0 ? keep : chunks;        // no such suffix: the whole range from zero
   }
@@ -915,13 +928,14 @@ walk_umma_kernel(const __grid_constant__ CUtensorMap tm_wh, const __grid_constan
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = *tmem_slot;
-  if (in.walk_flags & kWalkUntilDecayed) chunks = *limit_slot;
-  if ((in.walk_flags & kWalkHomogeneous) && limit_slot[1]) {
+  if (flags & kWalkUntilDecayed) chunks = *limit_slot;
+  if ((flags & kWalkHomogeneous) && limit_slot[1]) {
     chunks = 0;
     state_in = nullptr;           // zeros go into tensor memory and straight out as the transition matrix
+    identity_in = false;
   }
   int unstored = 0;                          // leading chunks whose output rows the previous sub-segment's CTA writes
-  if (in.walk_flags & kWalkTail) {
+  if (flags & kWalkTail) {
     // offset pass: only the suffix that determines the outgoing state, from zero, no output rows
     const int keep = limit_slot[2];
     t_first += (chunks - keep) * kChunk;
@@ -959,7 +973,8 @@ walk_umma_kernel(const __grid_constant__ CUtensorMap tm_wh, const __grid_constan
         uint32_t vals[32];
         const int k0 = half * 64 + part * 32;
 #pragma unroll
-        for (int j = 0; j < 32; ++j) vals[j] = init ? __float_as_uint(init[(k0 + j) * kDim]) : 0u;
+        for (int j = 0; j < 32; ++j)
+          vals[j] = init ? __float_as_uint(init[(k0 + j) * kDim]) : ((identity_in && k0 + j == v) ? __float_as_uint(1.f) : 0u);
         tmem_st32(taddr + kAccS + k0, vals);
       }
       tmem_wait_st();
@@ -1013,7 +1028,7 @@ walk_umma_kernel(const __grid_constant__ CUtensorMap tm_wh, const __grid_constan
 
       float u[32];
 #pragma unroll
-      for (int i = 0; i < 32; ++i) u[i] = (in.walk_flags & kWalkHomogeneous) ? 0.f : __ldg(urow + i * kDim);
+      for (int i = 0; i < 32; ++i) u[i] = (flags & kWalkHomogeneous) ? 0.f : __ldg(urow + i * kDim);
 
       ok = mbar_wait(bar_ws, c & 1, abort, 12, c);
       if (!ok) break;
@@ -1168,7 +1183,7 @@ walk_umma_kernel(const __grid_constant__ CUtensorMap tm_wh, const __grid_constan
       prefetch_tensormap(&tm_k);
       prefetch_tensormap(&tm_p);
       for (int c = 0; c < chunks; ++c) {
-        if ((in.walk_flags & kWalkSelftestStall) && c > 0) break;       // failure-detection self-test only
+        if ((flags & kWalkSelftestStall) && c > 0) break;       // failure-detection self-test only
         const int s = c % L::kStages;
         if (c >= L::kStages && !mbar_wait(empty + s, ((c / L::kStages) - 1) & 1, abort, 30, c)) break;
         uint8_t* st = sm + s * L::kStage;
@@ -1339,10 +1354,12 @@ int launch_walk_umma(const Inputs& in, const Geometry& geo, const Workspace& ws,
   const int parallel = geo.parallel > 1 ? geo.parallel : 1;
   if (parallel > 1 && (geo.varlen || in.walk_flags || parallel > geo.segment_chunks())) return int(cudaErrorInvalidValue);
   if ((in.walk_flags & kWalkSelftestStall) && (in.walk_flags != kWalkSelftestStall || geo.varlen)) return int(cudaErrorInvalidValue);
-  if ((in.walk_flags & kWalkTail) &&
-      (in.walk_flags != kWalkTail || geo.varlen || !geo.first_segment() || !geo.last_segment() || !in.final_state))
+  if ((in.walk_flags & (kWalkTail | kWalkPair)) &&
+      ((in.walk_flags != kWalkTail && in.walk_flags != kWalkPair) || parallel > 1 || geo.varlen || !geo.first_segment() ||
+       !geo.last_segment() || !in.final_state))
     return int(cudaErrorInvalidValue);
-  walk_umma_kernel<<<geo.batch * geo.value_heads * parallel, kWalkThreads, kWalkSmem, stream>>>(
+  const int per_head = (in.walk_flags & kWalkPair) ? 2 : parallel;
+  walk_umma_kernel<<<geo.batch * geo.value_heads * per_head, kWalkThreads, kWalkSmem, stream>>>(
       tm_wh, tm_wl, tm_q, tm_k, tm_p, tm_out, in, geo, ws);
   return int(cudaGetLastError());
 }

@@ -7,12 +7,12 @@ column independently, ``b`` is the final state of the segment run from a zero st
 ``M`` is the final state of the same recurrence run with ``v = 0`` from the identity.
 
 Scheme (exact for any decay, no host read anywhere):
-  1. every rank prepares its segment once.  Two short passes on a side stream give the pair early: ``b_r`` from a
-     zero-state walk of only the suffix of the segment that decides the outgoing state (the chunks since the decay
-     fell below exp(-40), counted from the segment's end; the whole segment when there is no such suffix), and
+  1. every rank prepares its segment once.  One short launch behind the prepare kernel gives the pair early: ``b_r``
+     from a zero-state walk of only the suffix of the segment that decides the outgoing state (the chunks since the
+     decay fell below exp(-40), counted from the segment's end; the whole segment when there is no such suffix), and
      ``M_r`` from the identity with ``v = 0`` (exact zeros at once for a segment that decays below exp(-40)); both
-     decisions are made on the device from the gate sums.  Meanwhile the main stream walks the segment's output
-     rows from a zero state (rank 0: from the caller's state);
+     decisions are made on the device from the gate sums.  Then the stream walks the segment's output rows from a
+     zero state (rank 0: from the caller's state);
   2. next to that walk, one grouped exchange of point-to-point messages: every rank sends its pair ``(M_r, b_r)``
      to every LATER rank (rank 0 sends its true outgoing state as ``b_0``) and receives the pairs of every EARLIER
      rank; the exclusive scan ``S_in(r) = M_{r-1} S_in(r-1) + b_{r-1}`` is then folded locally, in one kernel
@@ -186,7 +186,7 @@ def gdn_forward_sequence_parallel(q, k, v, g, beta, initial_state=None, output_f
             from .sm100 import load_sm100
             segment_fn = load_sm100().prepare_segment
         segment = segment_fn(q, k, v, g, beta)
-        # the pair leaves early (short passes on a side stream), so the exchange runs next to the long output walk
+        # the pair leaves early (one short launch), so the exchange runs on a side stream next to the long output walk
         offset, transition = segment.early_pair(need_transition=not until_decayed)
         segment.walk_outputs(initial_state if rank == 0 else None)
         incoming = final = None

@@ -85,8 +85,8 @@ class Sm100Forward:
         return torch.empty(nbytes, dtype=torch.uint8, device=device)
 
     def _side_stream(self, device):
-        """One extra, high-priority stream per device for the short passes (and the state exchange) that run next
-        to the long output walk: their CTAs get the next free SMs ahead of the walk's."""
+        """One extra, high-priority stream per device for the state exchange (and the fold behind it) that runs next
+        to the long output walk."""
         import torch
         streams = self.__dict__.setdefault("_side_streams", {})
         key = str(device)
@@ -94,17 +94,15 @@ class Sm100Forward:
             streams[key] = torch.cuda.Stream(device=device, priority=-1)
         return streams[key]
 
-    def _transition_operands(self, like):
-        """Identity states [B,Hv,128,128] and a throw-away output buffer for transition passes, kept per device and
-        shape (read-only, respectively garbage by definition, so sharing them between calls is harmless)."""
+    def _scratch_output(self, like):
+        """A throw-away output buffer for the passes that produce states only, kept per device and shape (garbage
+        by definition, so sharing it between calls is harmless)."""
         import torch
-        cache = self.__dict__.setdefault("_transition_cache", {})
-        b, _, hv, _ = like.shape
-        key = (str(like.device), tuple(like.shape))
+        cache = self.__dict__.setdefault("_scratch_cache", {})
+        key = (like.device, tuple(like.shape))
         held = cache.get(key)
         if held is None:
-            eye = torch.eye(128, dtype=torch.float32, device=like.device).expand(b, hv, 128, 128).contiguous()
-            held = cache[key] = (eye, torch.empty_like(like))
+            held = cache[key] = torch.empty_like(like)
             if len(cache) > 8:
                 cache.pop(next(iter(cache)))
         return held
@@ -216,7 +214,7 @@ class PreparedSegment:
     and the correction pass (true incoming state) share the prepare work.  Built on stage-restricted calls of ``actlize_la_sm100_forward_prepared`` (tcgen05
     configuration); nothing is launched before the first method call.
     """
-    _CONFIG, _PREPARE, _WALK, _HOMOGENEOUS, _UNTIL_DECAYED, _OFFSET_TAIL = 1, 0x10, 0x20, 0x40, 0x80, 0x100000
+    _CONFIG, _PREPARE, _WALK, _HOMOGENEOUS, _UNTIL_DECAYED, _OFFSET_TAIL, _PAIR = 1, 0x10, 0x20, 0x40, 0x80, 0x100000, 0x200000
 
     def __init__(self, owner, q, k, v, g, beta):
         import torch
@@ -255,29 +253,29 @@ class PreparedSegment:
         return torch.empty((b, hv, 128, 128), dtype=torch.float32, device=self.output.device)
 
     def early_pair(self, need_transition=True):
-        """(b_r, M_r) of ``S_out = M_r S_in + b_r``, produced EARLY: one prepare launch on the current stream, then,
-        on a high-priority side stream, the offset pass (per head only the suffix of the segment that decides the
-        outgoing state, from zero: a few chunks when the gate decays) and the transition pass (exact zeros at
-        once for a head whose segment decays below exp(-40)).  The caller launches the long output walk on the
-        current stream next (``walk_outputs``) and can exchange the pair inside ``side()`` while that walk runs;
-        ``join()`` orders the current stream behind the side stream."""
+        """(b_r, M_r) of ``S_out = M_r S_in + b_r``, produced EARLY: the prepare launch, then ONE short launch on the
+        same stream that holds, per (batch, value head), the offset pass (only the suffix of the segment that
+        decides the outgoing state, from zero: a few chunks when the gate decays) and, if asked for, the transition
+        pass (exact zeros at once for a head whose segment decays below exp(-40)).  The caller launches the long
+        output walk next (``walk_outputs``) and exchanges the pair inside ``side()``, a second stream that starts
+        behind the short launch, while that walk runs; ``join()`` orders the current stream behind the side stream."""
         import torch
         self._launch(self._CONFIG | self._PREPARE, None, self.output, None)
-        # the pair in one block [2, B, Hv, 128, 128] = (M_r, b_r): it travels as one message
-        b, _, _, hv = self.dims
-        self.pair = torch.empty((2, b, hv, 128, 128), dtype=torch.float32, device=self.output.device) if need_transition else None
-        offset = self.pair[1] if need_transition else self._state()
-        transition = self.pair[0] if need_transition else None
-        current = torch.cuda.current_stream()
+        scratch = self.owner._scratch_output(self.output)
+        if need_transition:
+            # the pair in one block [2, B, Hv, 128, 128] = (M_r, b_r): it travels as one message
+            b, _, _, hv = self.dims
+            self.pair = torch.empty((2, b, hv, 128, 128), dtype=torch.float32, device=self.output.device)
+            self._launch(self._CONFIG | self._WALK | self._PAIR, None, scratch, self.pair)
+            offset, transition = self.pair[1], self.pair[0]
+        else:
+            self.pair = None
+            offset, transition = self._state(), None
+            self._launch(self._CONFIG | self._WALK | self._OFFSET_TAIL, None, scratch, offset)
         if self._side is None:
             self._side = self.owner._side_stream(self.output.device)
-        self._side.wait_stream(current)
-        eye, scratch = self.owner._transition_operands(self.output)
-        with torch.cuda.stream(self._side):
-            self._launch(self._CONFIG | self._WALK | self._OFFSET_TAIL, None, scratch, offset)
-            if need_transition:
-                self._launch(self._CONFIG | self._WALK | self._HOMOGENEOUS, eye, scratch, transition)
-            (self.pair if need_transition else offset).record_stream(self._side)
+        self._side.wait_stream(torch.cuda.current_stream())
+        (self.pair if need_transition else offset).record_stream(self._side)
         return offset, transition
 
     def walk_outputs(self, initial=None):

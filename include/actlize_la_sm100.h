@@ -52,6 +52,12 @@ extern "C" {
  * exp(-40) is what it ends in from any.  A head without such a suffix is walked whole: then the result is bit-equal
  * to the ordinary zero-state walk.  It gives a sequence-parallel rank its outgoing state after a few chunks of work. */
 #define ACTLIZE_LA_SM100_WALK_OFFSET_SUFFIX 0x100000
+/* The offset pass and the transition pass (WALK_HOMOGENEOUS from an identity state, which the kernel makes itself) in
+ * ONE launch, two CTAs per (batch, value head); also a walk-only form of configuration 1 on its own.  `final_state`
+ * (required) then points at a block [2][B][Hv][128][128]: the transition matrices M, then the offsets b, of
+ * S_out = M S_in + b.  `initial` is not read; `output` must be a valid buffer the caller does not need (the transition
+ * CTAs of a segment that does not decay write their rows there). */
+#define ACTLIZE_LA_SM100_WALK_PAIR 0x200000
 
 /* ABI version of this library; the loader refuses a mismatch.
  * Counterpart: ala_abi_version in csrc/serving/abi.h:67-82. */

@@ -553,6 +553,10 @@ def test_prepared_segment_walks(forward, native_library):
     assert oracle.max_abs(out.float().cpu(), want_out.float().cpu()) < 1e-6     # exp(-40) of the state is invisible in BF16
     changed = (out != zero_out).any(dim=(0, 2, 3)).nonzero().max().item()     # last token row that was rewritten
     assert changed < 64 * 8, changed                                           # ... lies in the first few chunks
+    # the offset pass alone (what the vouched form launches) gives the same offset as the pair launch
+    alone, none = forward.prepare_segment(q, k, v, g, beta).early_pair(need_transition=False)
+    torch.cuda.synchronize()
+    assert none is None and torch.equal(alone, offset)
     # a gate that never decays that far, and one with a token that is no contraction: the offset pass walks the
     # whole segment, bit-equal to the ordinary zero-state forward
     long_key = k.clone()
@@ -563,6 +567,15 @@ def test_prepared_segment_walks(forward, native_library):
         segment.join()
         _, want_offset = forward(q, k2, v, g2, beta, None, True, configuration="umma")
         assert torch.equal(offset, want_offset), change
+        # ... and so does the pair launch, whose transition CTAs make their identity state themselves
+        segment = forward.prepare_segment(q, k2, v, g2, beta)
+        offset, transition = segment.early_pair()
+        segment.join()
+        torch.cuda.synchronize()
+        assert torch.equal(offset, want_offset), change
+        if change == "slow":
+            want_m = oracle.segment_transition(cpu[1], cpu[3] * 1e-3, cpu[4])
+            assert oracle.rel_frobenius(transition.cpu(), want_m) < 1e-3
     lib = native_library.lib
     assert lib.actlize_la_sm100_workspace_bytes(1, 64, 1, 1, 1 | 0x40) == -1    # modifiers need a walk-only call
     assert lib.actlize_la_sm100_workspace_bytes(1, 64, 1, 1, 0 | 0x20 | 0x40) == -1   # ... of the tcgen05 configuration

@@ -208,6 +208,10 @@ def test_native_argument_rejection_without_a_device(native_library):
     assert lib.actlize_la_sm100_workspace_bytes(1, 64, 1, 1, 1 | 0x20 | offset_pass) > 0
     for bad in (1 | offset_pass, 0 | 0x20 | offset_pass, 1 | 0x20 | 0x40 | offset_pass, 1 | 0x20 | (2 << 16) | offset_pass):
         assert lib.actlize_la_sm100_workspace_bytes(1, 64, 1, 1, bad) < 0, hex(bad)
+    pair_pass = 0x200000                          # offset and transition pass in one launch: likewise on its own
+    assert lib.actlize_la_sm100_workspace_bytes(1, 64, 1, 1, 1 | 0x20 | pair_pass) > 0
+    for bad in (1 | pair_pass, 1 | 0x20 | pair_pass | offset_pass, 1 | 0x20 | 0x80 | pair_pass, 3 | 0x20 | pair_pass):
+        assert lib.actlize_la_sm100_workspace_bytes(1, 64, 1, 1, bad) < 0, hex(bad)
     big = 1 << 40
     walk_args = [ptr_ := 0x1000] * 5 + [None, ptr_ + 256, None, ptr_ + 512, big, 1, 64, 1, 1, 1, 1 | 0x20 | offset_pass, None]
     assert lib.actlize_la_sm100_forward_prepared(*walk_args) == invalid     # the offset pass needs final_state
