@@ -102,8 +102,7 @@ def _check_segments(t, rank, world, group, segment_lengths, device):
 
 def gdn_forward_sequence_parallel(q, k, v, g, beta, initial_state=None, output_final_state=True, *,
                                   group=None, forward_fn=None, apply_transition=None, segment_fn=None,
-                                  until_decayed=False, segment_lengths=None, collective="send_recv",
-                                  **forward_options):
+                                  until_decayed=False, segment_lengths=None, **forward_options):
     """Forward over a sequence split across the ranks of ``group``.
 
     Every rank passes ITS OWN contiguous segment (q,k [B,Tr,Hk,128] ...), segments in rank
@@ -117,9 +116,6 @@ def gdn_forward_sequence_parallel(q, k, v, g, beta, initial_state=None, output_f
     contraction: L2-normalised keys, beta in [0, 1]); the transition pass is then skipped and only ``b_{r-1}``
     travels, from each rank to the next.  ``forward_fn`` (any complete forward) selects the generic three-pass
     form on complete forwards instead; ``segment_fn`` substitutes the prepared-segment factory.
-    ``collective="all_gather"`` (the same on every rank) moves the pairs of the exact form with ONE all-gather
-    instead of the world_size - 1 point-to-point messages of a rank: more bytes over NVLink (every rank receives
-    every pair), less host time per call, which is what limits many ranks with short segments.
     """
     import torch.distributed as dist
     rank, world = dist.get_rank(group), dist.get_world_size(group)
@@ -132,8 +128,6 @@ def gdn_forward_sequence_parallel(q, k, v, g, beta, initial_state=None, output_f
         apply_transition = native_apply_transition if q.is_cuda else _torch_apply_transition
     if world == 1:
         return forward_fn(q, k, v, g, beta, initial_state, output_final_state, **forward_options)
-    if collective not in ("send_recv", "all_gather"):
-        raise ValueError(f"collective must be 'send_recv' or 'all_gather', not {collective!r}")
     _check_segments(t, rank, world, group, segment_lengths, q.device)
     if staged and forward_options:
         raise ValueError("forward options apply to the generic form (forward_fn) only")
@@ -149,29 +143,18 @@ def gdn_forward_sequence_parallel(q, k, v, g, beta, initial_state=None, output_f
         message per (source, target), the pair travelling as one [2, B, Hv, 128, 128] block (``pair``, when the
         caller already holds transition and offset back to back).  Returns (incoming state of this rank, its
         outgoing state if asked for); (None, None) on rank 0."""
-        if collective == "all_gather":
-            mine = pair if (pair is not None and transition is not None) else None
-            if mine is None:
-                mine = torch.empty((2,) + state_shape, dtype=torch.float32, device=q.device)
-                mine[1].copy_(offset)
-                if transition is not None:                 # (the transition of rank 0 is never read)
-                    mine[0].copy_(transition)
-            gathered = torch.empty((world, 2) + state_shape, dtype=torch.float32, device=q.device)
-            dist.all_gather_into_tensor(gathered.view((world * 2,) + state_shape), mine, group=group)   # concatenation form
-            pairs = gathered[:rank] if rank else None
-        else:
-            ops = []
-            pairs = torch.empty((rank, 2) + state_shape, dtype=torch.float32, device=q.device) if rank else None
-            for r in range(rank):                          # rank 0 sends its outgoing state only
-                ops.append(dist.P2POp(dist.irecv, pairs[r] if r else pairs[0, 1], _neighbour(group, r), group))
-            if later:
-                if transition is None:
-                    message = offset
-                else:
-                    message = pair if pair is not None else torch.stack((transition, offset))
-                ops += [dist.P2POp(dist.isend, message, target, group) for target in later]
-            for work in (dist.batch_isend_irecv(ops) if ops else []):
-                work.wait()
+        ops = []
+        pairs = torch.empty((rank, 2) + state_shape, dtype=torch.float32, device=q.device) if rank else None
+        for r in range(rank):                              # rank 0 sends its outgoing state only
+            ops.append(dist.P2POp(dist.irecv, pairs[r] if r else pairs[0, 1], _neighbour(group, r), group))
+        if later:
+            if transition is None:
+                message = offset
+            else:
+                message = pair if pair is not None else torch.stack((transition, offset))
+            ops += [dist.P2POp(dist.isend, message, target, group) for target in later]
+        for work in (dist.batch_isend_irecv(ops) if ops else []):
+            work.wait()
         if pairs is None:
             return None, None
         if fold is not None:
@@ -225,3 +208,30 @@ def gdn_forward_sequence_parallel(q, k, v, g, beta, initial_state=None, output_f
     incoming, _ = exchange(offset, transition)
     out, final = forward_fn(q, k, v, g, beta, incoming, bool(output_final_state and last), **forward_options)
     return out, (final if (output_final_state and last) else None)
+
+
+def capture_sequence_parallel(q, k, v, g, beta, initial_state=None, output_final_state=True, **options):
+    """One ``gdn_forward_sequence_parallel`` call captured in a CUDA graph, on every rank of the group alike.
+
+    Returns ``(graph, output, final_state)``: ``graph.replay()`` runs the whole call again (prepare, the short
+    pair launch, the output walk, the NCCL exchange on its side stream, fold and correction) on the CURRENT
+    contents of the argument tensors and refills ``output`` / ``final_state`` in place.  A replay costs the host a
+    few microseconds instead of the few hundred an eager call needs to enqueue its launches and messages, which is
+    what limits many ranks with short segments.  Every rank must capture, and later replay, the same number of
+    times in the same order (the exchange inside is a collective).
+    """
+    if not q.is_cuda:
+        raise ValueError("capture needs CUDA tensors")
+    call = lambda: gdn_forward_sequence_parallel(q, k, v, g, beta, initial_state, output_final_state, **options)
+    current = torch.cuda.current_stream()
+    warm = torch.cuda.Stream(device=q.device)
+    warm.wait_stream(current)
+    with torch.cuda.stream(warm):                # lazy set-up (communicators, streams, caches) happens outside capture
+        for _ in range(2):
+            call()
+    current.wait_stream(warm)
+    torch.cuda.synchronize(q.device)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        output, final_state = call()
+    return graph, output, final_state

@@ -18,7 +18,7 @@ restatement of the reference's own FP32 path (oracle/) on the host cores instead
 The same line carries, at N = 1, `per_config` (every named shape timed through the policy's configuration, with
 its fraction of the per-shape roofline) and, at N > 1, the two multi-GPU forms the path has: `shard_cfg2` (B8 T4096
 split by batch over the ranks, no collective, strong scaling) and `sp_cfg4` (T131072 split over the ranks, states
-handed on with NCCL send/recv; the exact form, the same with one all-gather, and the one where the caller vouches for the decay), each with its efficiency against one GPU running the same
+handed on with NCCL send/recv; the exact form and the one where the caller vouches for the decay), each with its efficiency against one GPU running the same
 shape and a `parity` object (key-head group 0 of the timed tensors against the CPU restatement, computed outside
 the timed regions).
 """
@@ -484,11 +484,11 @@ def shard_cfg2_leg(device, rank, world, steps, peaks):
 
 def sp_cfg4_leg(device, rank, world, steps, peaks):
     """cfg4 (B1 T131072 Hk16 Hv32) split over the ranks as contiguous token segments, states handed on with NCCL
-    send/recv: strong scaling against one GPU running the whole sequence; the exact form (also with its pairs
-    moved by one all-gather) and the vouched one."""
+    send/recv: strong scaling against one GPU running the whole sequence; the exact form and the vouched one."""
     import torch
     from actlizela_b200 import gdn_forward
-    from actlizela_b200.sequence_parallel import gdn_forward_sequence_parallel, segment_bounds
+    from actlizela_b200.sequence_parallel import (capture_sequence_parallel, gdn_forward_sequence_parallel,
+                                                   segment_bounds)
     from actlizela_b200.workloads import WORKLOADS, make_inputs
     from oracle import gdn_oracle as oracle
     w = WORKLOADS["cfg4"]
@@ -511,21 +511,34 @@ def sp_cfg4_leg(device, rank, world, steps, peaks):
                   segments=f"{world} contiguous token segments, one per rank", one_gpu_ms=ms_one, scaling="strong")
     # "exact": decided on the device per (batch, value head), valid for any gate; "vouched": the caller states that
     # every segment forgets its incoming state, so no transition pass runs and only b travels to the next rank
-    # "exact_all_gather": the exact form with its pairs moved by one all-gather instead of world - 1 messages per rank
-    for form, decayed, collective in (("exact", False, "send_recv"), ("exact_all_gather", False, "all_gather"),
-                                      ("vouched", True, "send_recv")):
+    # "exact_graph": the exact form captured once in a CUDA graph and replayed (no host work per call beyond the replay)
+    for form, decayed, captured in (("exact", False, False), ("exact_graph", False, True), ("vouched", True, False)):
         call = lambda: gdn_forward_sequence_parallel(*part, initial, True, until_decayed=decayed,
-                                                     segment_lengths=lengths, collective=collective)
+                                                     segment_lengths=lengths)
+        if captured:
+            try:
+                graph, out, final = capture_sequence_parallel(*part, initial, True, until_decayed=decayed,
+                                                              segment_lengths=lengths)
+            except RuntimeError as err:              # reported, not fatal: the eager forms stand on their own
+                result[form] = dict(error=str(err).splitlines()[0][:200])
+                continue
+            call = graph.replay
         # warm-up in the shape of the measurement: the host runs several calls ahead of the device, each holding a
         # workspace of its own, so the caching allocator reaches its steady state only in such a loop
         timed_loop(call, max(3, steps), device, world)
         ms, spread = timed_loop(call, steps, device, world)
-        out, final = call()
+        if captured:
+            call()
+            torch.cuda.synchronize()
+        else:
+            out, final = call()
         m = parity_metrics(out[:, :, :heads], want_out[:, t0:t1],
                            final[:, :heads] if final is not None else None, want_state)
         result[form] = dict(ms=ms, median_ms=spread["median_ms"], tokens_per_s=w.tokens / (ms * 1e-3),
                             efficiency=ms_one / (world * ms), roofline_frac=roofline_ms(w, peaks) / (world * ms),
                             parity=reduce_parity(m, device, world))
+        if captured:
+            del graph
     return result
 
 

@@ -18,7 +18,8 @@ import torch
 import torch.distributed as dist
 
 from actlizela_b200 import gdn_forward
-from actlizela_b200.sequence_parallel import gdn_forward_sequence_parallel, segment_bounds
+from actlizela_b200.sequence_parallel import (capture_sequence_parallel, gdn_forward_sequence_parallel,
+                                               segment_bounds)
 from actlizela_b200.sharding import gdn_forward_sharded
 from actlizela_b200.workloads import WORKLOADS, make_inputs
 
@@ -57,11 +58,6 @@ def main():
         else:
             rel_state = ((final - full_state).norm() / full_state.norm()).item()
             ok = ok and rel_state < 1e-5
-        # the same (a gate that never decays: every transition matrix is dense) through one all-gather
-        out_g, final_g = gdn_forward_sequence_parallel(*part, dev[5] if rank == 0 else None, True, collective="all_gather",
-                                                       segment_lengths=[b1 - b0 for b0, b1 in bounds])
-        torch.cuda.synchronize()
-        ok = ok and torch.equal(out_g, out) and (final is None or torch.equal(final_g, final))
         pieces = gdn_forward_sharded(*dev, True, rank=rank, world_size=world)
         ok = ok and all(torch.equal(o, full_out[b0:b1, :, v0:v1]) and torch.equal(s, full_state[b0:b1, v0:v1])
                         for (b0, b1, v0, v1), o, s in pieces)
@@ -75,10 +71,9 @@ def main():
         bounds2 = segment_bounds(w2.length, world)
         s0, s1 = bounds2[rank]
         part2 = [x[:, s0:s1].contiguous() for x in dev2[:5]]
-        # the exact form (decides on the device) with either collective, and the caller's statement
-        for vouched, collective in ((False, "send_recv"), (False, "all_gather"), (True, "send_recv")):
+        for vouched in (False, True):        # the exact form (decides on the device) and the caller's statement
             out2, final2 = gdn_forward_sequence_parallel(*part2, dev2[5] if rank == 0 else None, True,
-                                                         until_decayed=vouched, collective=collective,
+                                                         until_decayed=vouched,
                                                          segment_lengths=[b1 - b0 for b0, b1 in bounds2])
             torch.cuda.synchronize()
             want2 = full_out2[:, s0:s1].float()
@@ -87,6 +82,17 @@ def main():
             ok = ok and against_oracle(out2, final2, oracle_out2, oracle_state2, (s0, s1))
             if rank == world - 1:
                 ok = ok and ((final2 - full_state2).norm() / full_state2.norm()).item() < 1e-4
+        # the exact form captured in a CUDA graph (every launch and the exchange inside it) and replayed twice
+        graph, out3, final3 = capture_sequence_parallel(*part2, dev2[5] if rank == 0 else None, True,
+                                                        segment_lengths=[b1 - b0 for b0, b1 in bounds2])
+        exact2, exact_final2 = gdn_forward_sequence_parallel(*part2, dev2[5] if rank == 0 else None, True,
+                                                             segment_lengths=[b1 - b0 for b0, b1 in bounds2])
+        for _ in range(2):
+            out3.zero_()
+            graph.replay()
+            torch.cuda.synchronize()
+            ok = ok and torch.equal(out3, exact2) and (final3 is None or torch.equal(final3, exact_final2))
+        del graph
         print(f"{'OK' if ok else 'FAIL'} rank {rank} of {world}: tokens [{t0},{t1}), "
               f"slabs {[p[0] for p in pieces]}", flush=True)
         dist.barrier()

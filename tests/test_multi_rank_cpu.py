@@ -130,18 +130,16 @@ def _worker(rank, world, port, mode, result_queue):
                 want_out, want_state = _oracle_forward(q, k, v, g, beta, init)
             bounds = segment_bounds(q.shape[1], world)
             lengths = [b1 - b0 for b0, b1 in bounds] if mode != "sp-staged" else None     # None: gathered first
-            collective = "all_gather" if mode.endswith("-gather") else "send_recv"
             t0, t1 = bounds[rank]
             part = [x[:, t0:t1].contiguous() for x in (q, k, v, g, beta)]
-            if mode in ("sp", "sp-gather"):
+            if mode == "sp":
                 out, final = gdn_forward_sequence_parallel(
-                    *part, init if rank == 0 else None, True, forward_fn=_oracle_forward, segment_lengths=lengths,
-                    collective=collective)
+                    *part, init if rank == 0 else None, True, forward_fn=_oracle_forward, segment_lengths=lengths)
             else:
                 # the staged form: one prepared segment per rank, walked several times
                 out, final = gdn_forward_sequence_parallel(
                     *part, init if rank == 0 else None, True, segment_fn=_OracleSegment,
-                    until_decayed=(mode == "sp-decayed"), segment_lengths=lengths, collective=collective)
+                    until_decayed=(mode == "sp-decayed"), segment_lengths=lengths)
             if mode == "sp" and world == 3:
                 # a segment that is not a multiple of 64 tokens is refused on every rank alike, before any message
                 try:
@@ -162,8 +160,7 @@ def _worker(rank, world, port, mode, result_queue):
 
 
 @pytest.mark.parametrize("mode,world", [("shard", 2), ("sp", 2), ("sp", 3), ("sp-staged", 2), ("sp-staged", 3),
-                                        ("sp-staged", 4), ("sp-decayed", 3), ("sp-decayed-partly", 3),
-                                        ("sp-gather", 3), ("sp-staged-gather", 3)])
+                                        ("sp-staged", 4), ("sp-decayed", 3), ("sp-decayed-partly", 3)])
 def test_two_rank_paths_match_the_unsplit_run(mode, world):
     ctx = mp.get_context("spawn")
     queue = ctx.Queue()
