@@ -20,6 +20,7 @@ _MODULES = {
     "gdn_forward_sharded": "sharding",
     "shard_plan": "sharding",
     "gdn_forward_sequence_parallel": "sequence_parallel",
+    "capture_sequence_parallel": "sequence_parallel",
     "gdn_forward_varlen": "varlen",
     "gdn_prepare_inputs": "aux_ops",
     "gdn_decode_step": "aux_ops",
