@@ -508,7 +508,10 @@ def sp_cfg4_leg(device, rank, world, steps, peaks):
     torch.cuda.empty_cache()
     want_out, want_state = oracle.chunk_forward_fp32(*narrow, output_final_state=True)
     result = dict(workload="cfg4 B1 T131072 Hk16 Hv32 fp32 gate, zero initial state",
-                  segments=f"{world} contiguous token segments, one per rank", one_gpu_ms=ms_one, scaling="strong")
+                  segments=f"{world} contiguous token segments, one per rank", one_gpu_ms=ms_one, scaling="strong",
+                  forms="exact: eager call; exact_graph: the same call captured once in a CUDA graph and replayed (no "
+                        "host work per call; the eager form is host-bound when the segments are short); vouched: the "
+                        "caller states that every segment forgets its incoming state")
     # "exact": decided on the device per (batch, value head), valid for any gate; "vouched": the caller states that
     # every segment forgets its incoming state, so no transition pass runs and only b travels to the next rank
     # "exact_graph": the exact form captured once in a CUDA graph and replayed (no host work per call beyond the replay)
