@@ -468,6 +468,18 @@ def shard_cfg2_leg(device, rank, world, steps, peaks):
         timed_loop(fn, max(3, steps), device, world)
     ms_one, _ = timed_loop(whole, steps, device, world)
     ms_n, spread = timed_loop(mine, steps, device, world)
+    # the same call replayed from a CUDA graph: at many ranks a call is short enough for the host's launch path and
+    # its jitter to show in the eager figure
+    ms_graph = None
+    try:
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            mine()
+        timed_loop(graph.replay, max(3, steps), device, world)
+        ms_graph, _ = timed_loop(graph.replay, steps, device, world)
+        del graph
+    except RuntimeError:                 # reported as missing, not fatal: the eager figure stands on its own
+        pass
     worst = dict(out_max_abs=0.0, out_rel_f=0.0, state_rel_f=0.0)
     heads = narrow[2].shape[2]
     for (b0, b1, v0, v1), out, final in mine():
@@ -479,6 +491,7 @@ def shard_cfg2_leg(device, rank, world, steps, peaks):
     return dict(workload="cfg2 B8 T4096 Hk16 Hv32 bf16 gate, zero initial state", sharding=f"batch rows over {world} ranks",
                 ms=ms_n, median_ms=spread["median_ms"], tokens_per_s=w.tokens / (ms_n * 1e-3), one_gpu_ms=ms_one,
                 efficiency=ms_one / (world * ms_n), roofline_frac=roofline_ms(w, peaks) / (world * ms_n),
+                graph_replay_ms=ms_graph, graph_replay_efficiency=(ms_one / (world * ms_graph)) if ms_graph else None,
                 scaling="strong", parity=reduce_parity(worst, device, world))
 
 
