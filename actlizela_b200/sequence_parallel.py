@@ -166,9 +166,11 @@ def gdn_forward_sequence_parallel(q, k, v, g, beta, initial_state=None, output_f
 
     if staged:
         if segment_fn is None:
+            # the segment is finished with when this call returns: its workspace can be the stream's standing one
             from .sm100 import load_sm100
-            segment_fn = load_sm100().prepare_segment
-        segment = segment_fn(q, k, v, g, beta)
+            segment = load_sm100().prepare_segment(q, k, v, g, beta, reuse_workspace=True)
+        else:
+            segment = segment_fn(q, k, v, g, beta)
         # the pair leaves early (one short launch), so the exchange runs on a side stream next to the long output walk
         offset, transition = segment.early_pair(need_transition=not until_decayed)
         segment.walk_outputs(initial_state if rank == 0 else None)

@@ -148,9 +148,27 @@ class Sm100Forward:
             int(g.dtype == torch.float32), config, self.library.current_stream_handle(torch.cuda.current_device())))
         return out, final
 
-    def prepare_segment(self, q, k, v, g, beta):
-        """Run the prepare stage once and return a handle on which several walks can follow."""
-        return PreparedSegment(self, q, k, v, g, beta)
+    def prepare_segment(self, q, k, v, g, beta, reuse_workspace=False):
+        """Run the prepare stage once and return a handle on which several walks can follow.  With
+        ``reuse_workspace`` the factors go into a workspace kept per (device, current stream) instead of one
+        allocated for this segment: for a caller that finishes with a segment before it prepares the next one on
+        the same stream (stream order then keeps the two apart), so that a loop of calls whose host side runs ahead
+        of the device does not hold, and allocate, one workspace of hundreds of megabytes per call in flight."""
+        return PreparedSegment(self, q, k, v, g, beta, reuse_workspace)
+
+    def _stream_workspace(self, device, nbytes):
+        import torch
+        if torch.cuda.is_current_stream_capturing():          # a graph keeps its own memory
+            return torch.empty(nbytes, dtype=torch.uint8, device=device)
+        cache = self.__dict__.setdefault("_stream_workspaces", {})
+        key = (device, torch.cuda.current_stream(device).cuda_stream)
+        held = cache.get(key)
+        if held is None or held.numel() < nbytes:
+            cache.pop(key, None)
+            while len(cache) >= 2:                            # these are large: keep the two most recent streams
+                cache.pop(next(iter(cache)))
+            held = cache[key] = torch.empty(nbytes, dtype=torch.uint8, device=device)
+        return held
 
     def varlen(self, q, k, v, g, beta, cu_seqlens, initial_states=None, output_final_state=True):
         """Packed sequences in one prepare and one walk launch (actlize_la_sm100_forward_varlen)."""
@@ -216,7 +234,7 @@ class PreparedSegment:
     """
     _CONFIG, _PREPARE, _WALK, _HOMOGENEOUS, _UNTIL_DECAYED, _OFFSET_TAIL, _PAIR = 1, 0x10, 0x20, 0x40, 0x80, 0x100000, 0x200000
 
-    def __init__(self, owner, q, k, v, g, beta):
+    def __init__(self, owner, q, k, v, g, beta, reuse_workspace=False):
         import torch
         self.dims = _validate(q, k, v, g, beta, None)
         self.owner, self.tensors = owner, (q, k, v, g, beta)
@@ -226,7 +244,8 @@ class PreparedSegment:
         # the walk alone, split into the policy's parallel sub-segments
         self.split_walk = self._CONFIG | self._WALK | ((selection.parallel << 16) if selection.parallel > 1 else 0)
         self.nbytes = owner.workspace_bytes(b, t, hk, hv, self._CONFIG)
-        self.workspace = torch.empty(self.nbytes, dtype=torch.uint8, device=q.device)
+        self.workspace = (owner._stream_workspace(q.device, self.nbytes) if reuse_workspace
+                          else torch.empty(self.nbytes, dtype=torch.uint8, device=q.device))
         self.output = torch.empty_like(v)
         self._side = self.pair = None
         # what every launch passes, looked up once
