@@ -77,12 +77,15 @@ class Sm100Forward:
         return n
 
     def _workspace(self, device, nbytes):
-        """Scratch of one call, from PyTorch's stream-ordered caching allocator (as the reference allocates its
-        workspace per call, actlize_la/_gdn_ppu10.py:48-55): calls on different streams never share it, and in
-        steady state no cudaMalloc is reached.  A configuration with several sequence segments additionally
-        uses the library's per-device streams and events: only one such call may be in flight per device."""
-        import torch
-        return torch.empty(nbytes, dtype=torch.uint8, device=device)
+        """Scratch of one call: a buffer kept per (device, current stream), grown on demand.  Calls on one stream
+        follow each other in stream order, so they can share it; calls on different streams never do.  (The
+        reference allocates its workspace per call from the caching allocator, actlize_la/_gdn_ppu10.py:48-55; with
+        the host running several calls ahead of the device that keeps one workspace of hundreds of megabytes alive
+        per call in flight, and the allocator's occasional cudaMalloc of one more stalls the host for milliseconds.)
+        Under stream capture the buffer comes from the graph's own pool.  A configuration with several sequence
+        segments additionally uses the library's per-device streams and events: only one such call may be in
+        flight per device."""
+        return self._stream_workspace(device, nbytes)
 
     def _side_stream(self, device):
         """One extra, high-priority stream per device for the state exchange (and the fold behind it) that runs next
@@ -161,7 +164,8 @@ class Sm100Forward:
         if torch.cuda.is_current_stream_capturing():          # a graph keeps its own memory
             return torch.empty(nbytes, dtype=torch.uint8, device=device)
         cache = self.__dict__.setdefault("_stream_workspaces", {})
-        key = (device, torch.cuda.current_stream(device).cuda_stream)
+        index = device.index if device.index is not None else torch.cuda.current_device()
+        key = (index, self.library.current_stream_handle(index))
         held = cache.get(key)
         if held is None or held.numel() < nbytes:
             cache.pop(key, None)

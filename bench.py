@@ -439,8 +439,7 @@ def per_config_legs(device, skip, peaks, steps=5):
         tensors = device_inputs(w, device, w.seed)
         sel = selection_for(tensors[0], tensors[2])
         call = lambda: gdn_forward(*tensors, output_final_state=True)
-        for _ in range(3):
-            call()
+        timed_loop(call, max(3, steps), device, 1)      # warm-up in the shape of the measurement (allocator steady state)
         ms, spread = timed_loop(call, steps, device, 1)
         legs[name] = dict(ms=ms, median_ms=spread["median_ms"], tokens_per_s=w.tokens / (ms * 1e-3),
                           roofline_ms=roofline_ms(w, peaks), frac=roofline_ms(w, peaks) / ms,
