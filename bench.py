@@ -425,7 +425,7 @@ def roofline_ms(w, peaks):
     return max(algorithmic_bytes(w) / (hbm_peak * 1e9), algorithmic_flops(w) / (tensor_peak * 1e12)) * 1e3
 
 
-def per_config_legs(device, skip, peaks, steps=5):
+def per_config_legs(device, skip, peaks, steps=11):
     """Every named shape on one GPU through the policy's configuration: ms, tokens/s and the fraction of the
     per-shape roofline (the slower of bytes / measured HBM bandwidth and FLOPs / measured BF16 peak)."""
     import torch
