@@ -263,6 +263,10 @@ def test_forward_validation_errors_are_value_errors():
     check(initial_state=torch.zeros(1, 2, 128, 128, dtype=torch.float64))
     with pytest.raises(ValueError):
         sm100.configuration_id("value64")
+    # the graph-capture form of the sequence-parallel call refuses host tensors before anything else happens
+    x = tensors()
+    with pytest.raises(ValueError, match="CUDA"):
+        actlizela_b200.capture_sequence_parallel(x["q"], x["k"], x["v"], x["g"], x["beta"])
 
 
 def test_build_entry_and_arch_guard_are_present():
