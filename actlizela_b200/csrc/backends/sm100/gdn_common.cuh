@@ -124,6 +124,10 @@ struct Inputs {
   //   kWalkHomogeneous  treat U as zero (the state-transition pass: V = 0)
   //   kWalkUntilDecayed stop a (batch, value head) walk at the first chunk boundary where the decay accumulated
   //                     since the walk's start is below exp(-40); later outputs are left as they are
+  //   kWalkTail         offset pass: from zero, only the suffix of the range that decides the outgoing state; no
+  //                     output rows; final_state receives that state
+  //   kWalkPair         kWalkTail and kWalkHomogeneous (from an identity state made in the kernel) in one launch,
+  //                     two CTAs per (batch, value head); final_state is then [2][B][Hv][128][128] = (M, b)
   int walk_flags = 0;
   // Fused input preparation (tcgen05 prepare kernel only): q, k, v are then read from the packed projection
   // rows `mixed` [B*T][mixed_stride] = [q heads | k heads | v heads] x 128, normalised in shared memory; the gate and
