@@ -17,8 +17,9 @@ restatement of the reference's own FP32 path (oracle/) on the host cores instead
 
 The same line carries, at N = 1, `per_config` (every named shape timed through the policy's configuration, with
 its fraction of the per-shape roofline) and, at N > 1, the two multi-GPU forms the path has: `shard_cfg2` (B8 T4096
-split by batch over the ranks, no collective, strong scaling) and `sp_cfg4` (T131072 split over the ranks, states
-handed on with NCCL send/recv; the exact form and the one where the caller vouches for the decay), each with its efficiency against one GPU running the same
+split by batch over the ranks, no collective, strong scaling; eager and replayed from a CUDA graph) and `sp_cfg4`
+(T131072 split over the ranks, states handed on with NCCL send/recv; the exact form, eager and replayed from a CUDA
+graph, and the one where the caller vouches for the decay), each with its efficiency against one GPU running the same
 shape and a `parity` object (key-head group 0 of the timed tensors against the CPU restatement, computed outside
 the timed regions).
 """
